@@ -1,0 +1,196 @@
+// Oracle (test infrastructure): f32 / half GEMM and GEMV by the reference's per-element order
+// contract.  Follows crates/wukong_runtime/src/gemm.rs (module docs :30-58, `select_kc` :253-256,
+// `Epilogue::apply` :751-780, the portable twin `sgemm_scalar` :3234-3282), gemv.rs (:28-88,
+// :141-180) and gemv_half.rs (`elem_scalar` :73-110, checked entries :440-529).
+#include "oracle_internal.h"
+#include <vector>
+#include <cmath>
+
+namespace wko {
+
+struct Epi {
+  const float* bias;
+  uint32_t act;
+  float alpha;
+};
+
+// gemm.rs:751-780.
+static inline float epi_apply(const Epi& e, float x, size_t j) {
+  float y = (e.alpha != 1.0f) ? e.alpha * x : x;
+  if (e.bias) y += e.bias[j];
+  switch (e.act) {
+    case 1: y = y > 0.0f ? y : 0.0f; break;
+    case 2: y = gelu1(y); break;
+    case 3: y = silu1(y); break;
+    default: break;
+  }
+  return y;
+}
+
+// gemm.rs:3234-3282: for each (i, j): K blocks of select_kc(k); every block is an ascending-p fma
+// chain from +0.0; the first block honours beta (a 0 / non-0 flag), later blocks add into C; the
+// epilogue runs once, on the last block, with the global column index.
+template <typename LoadA, typename LoadB>
+static void gemm_contract(LoadA la, LoadB lb, float* c, size_t m, size_t k, size_t n, float beta,
+                          const Epi* epi) {
+  const size_t kcap = (size_t)select_kc((i64)k);
+  par_for((i64)m * (i64)n, 4096, [&](i64 lo, i64 hi) {
+    for (i64 idx = lo; idx < hi; ++idx) {
+      size_t i = (size_t)idx / n, j = (size_t)idx % n;
+      float* cij = c + i * n + j;
+      size_t pc = 0;
+      while (pc < k) {
+        size_t kc = (k - pc) < kcap ? (k - pc) : kcap;
+        float acc = 0.0f;
+        for (size_t p = pc; p < pc + kc; ++p) acc = fmaf(la(i, p), lb(p, j), acc);
+        float beta_eff = (pc == 0) ? beta : 1.0f;
+        float val = (beta_eff == 0.0f) ? acc : *cij + acc;
+        *cij = (pc + kc == k && epi) ? epi_apply(*epi, val, j) : val;
+        pc += kc;
+      }
+    }
+  });
+}
+
+static void sgemm_f32(const float* a, const float* b, float* c, i64 m, i64 k, i64 n, i64 beta, bool at,
+                      bool bt, const Epi* epi) {
+  if (m <= 0 || k <= 0 || n <= 0) return;  // gemm.rs:1018-1020
+  size_t M = (size_t)m, K = (size_t)k, N = (size_t)n;
+  auto la = [=](size_t i, size_t p) { return at ? a[p * M + i] : a[i * K + p]; };
+  auto lb = [=](size_t p, size_t j) { return bt ? b[j * K + p] : b[p * N + j]; };
+  gemm_contract(la, lb, c, M, K, N, (float)beta, epi);
+}
+
+// gemm.rs:1436-1480: both half operands widen losslessly, then the f32 contract applies.
+static void sgemm_half_nt(const u16* a, const u16* b, float* c, i64 m, i64 k, i64 n, i64 beta, bool bf16,
+                          const Epi* epi) {
+  if (m <= 0 || k <= 0 || n <= 0) return;
+  size_t M = (size_t)m, K = (size_t)k, N = (size_t)n;
+  std::vector<float> af(M * K), bfv(N * K);
+  for (size_t i = 0; i < M * K; ++i) af[i] = bf16 ? bf16_bits_to_f32(a[i]) : f16_bits_to_f32(a[i]);
+  for (size_t i = 0; i < N * K; ++i) bfv[i] = bf16 ? bf16_bits_to_f32(b[i]) : f16_bits_to_f32(b[i]);
+  const float* ap = af.data();
+  const float* bp = bfv.data();
+  auto la = [=](size_t i, size_t p) { return ap[i * K + p]; };
+  auto lb = [=](size_t p, size_t j) { return bp[j * K + p]; };
+  gemm_contract(la, lb, c, M, K, N, (float)beta, epi);
+}
+
+// gemv.rs:60-88 with hsum256 (:28-38): four 8-lane fma accumulators over 32-element steps,
+// leftover 8-blocks into the first, tree (c0+c1)+(c2+c3), horizontal
+// ((v0+v4)+(v1+v5))+((v2+v6)+(v3+v7)), then an unfused scalar tail.
+static float gemv_row(const float* a, const float* x, size_t n) {
+  float c[4][8] = {};
+  size_t j = 0;
+  while (j + 32 <= n) {
+    for (int t = 0; t < 4; ++t)
+      for (int l = 0; l < 8; ++l) c[t][l] = fmaf(a[j + 8 * t + l], x[j + 8 * t + l], c[t][l]);
+    j += 32;
+  }
+  while (j + 8 <= n) {
+    for (int l = 0; l < 8; ++l) c[0][l] = fmaf(a[j + l], x[j + l], c[0][l]);
+    j += 8;
+  }
+  float v[8];
+  for (int l = 0; l < 8; ++l) v[l] = (c[0][l] + c[1][l]) + (c[2][l] + c[3][l]);
+  float s = ((v[0] + v[4]) + (v[1] + v[5])) + ((v[2] + v[6]) + (v[3] + v[7]));
+  while (j < n) {
+    s += a[j] * x[j];
+    ++j;
+  }
+  return s;
+}
+
+// gemv_half.rs:73-110 with beta = 0 and no epilogue (the checked GEMV entries).
+static i64 sgemv_half(const u16* w, i64 nw, const float* x, i64 nx, float* y, i64 ny, bool bf16) {
+  if (nw < 0 || nx < 0 || ny < 0) return -2;
+  // gemv_half_plan: w_len must be exactly N*K.
+  __int128 need = (__int128)ny * (__int128)nx;
+  if (need != (__int128)nw) return -2;
+  size_t N = (size_t)ny, K = (size_t)nx;
+  if (N == 0) return 0;
+  if (K == 0) {
+    for (size_t j = 0; j < N; ++j) y[j] = 0.0f;
+    return 0;
+  }
+  std::vector<float> xin(x, x + K);  // value semantics: inputs read as they were before the call
+  std::vector<float> out(N);
+  const size_t kcap = (size_t)select_kc((i64)K);
+  par_for((i64)N, 64, [&](i64 lo, i64 hi) {
+    for (i64 j = lo; j < hi; ++j) {
+      const u16* row = w + (size_t)j * K;
+      float cval = 0.0f;
+      size_t pc = 0;
+      while (pc < K) {
+        size_t pend = pc + ((K - pc) < kcap ? (K - pc) : kcap);
+        float acc = 0.0f;
+        for (size_t p = pc; p < pend; ++p) {
+          float wv = bf16 ? bf16_bits_to_f32(row[p]) : f16_bits_to_f32(row[p]);
+          acc = fmaf(xin[p], wv, acc);
+        }
+        cval = (pc == 0) ? acc : cval + acc;
+        pc = pend;
+      }
+      out[(size_t)j] = cval;
+    }
+  });
+  for (size_t j = 0; j < N; ++j) y[j] = out[j];
+  return 0;
+}
+
+}  // namespace wko
+
+using namespace wko;
+
+extern "C" {
+i64 wko_select_kc(i64 k) { return select_kc(k); }
+
+void wko_sgemm(const float* a, const float* b, float* c, i64 m, i64 k, i64 n, i64 beta) {
+  sgemm_f32(a, b, c, m, k, n, beta, false, false, nullptr);
+}
+void wko_sgemm_nt(const float* a, const float* b, float* c, i64 m, i64 k, i64 n, i64 beta) {
+  sgemm_f32(a, b, c, m, k, n, beta, false, true, nullptr);
+}
+void wko_sgemm_tn(const float* a, const float* b, float* c, i64 m, i64 k, i64 n, i64 beta) {
+  sgemm_f32(a, b, c, m, k, n, beta, true, false, nullptr);
+}
+void wko_sgemm_nt_epi(const float* a, const float* b, float* c, i64 m, i64 k, i64 n, i64 beta,
+                      const float* bias, i64 act) {
+  Epi e{bias, (uint32_t)act, 1.0f};
+  sgemm_f32(a, b, c, m, k, n, beta, false, true, &e);
+}
+void wko_sgemm_nt_alpha(const float* a, const float* b, float* c, i64 m, i64 k, i64 n, i64 beta, float alpha) {
+  Epi e{nullptr, 0u, alpha};
+  sgemm_f32(a, b, c, m, k, n, beta, false, true, &e);
+}
+void wko_sgemm_bf16_nt(const u16* a, const u16* b, float* c, i64 m, i64 k, i64 n, i64 beta) {
+  sgemm_half_nt(a, b, c, m, k, n, beta, true, nullptr);
+}
+void wko_sgemm_f16_nt(const u16* a, const u16* b, float* c, i64 m, i64 k, i64 n, i64 beta) {
+  sgemm_half_nt(a, b, c, m, k, n, beta, false, nullptr);
+}
+void wko_sgemm_bf16_nt_epi(const u16* a, const u16* b, float* c, i64 m, i64 k, i64 n, i64 beta,
+                           const float* bias, i64 act) {
+  Epi e{bias, (uint32_t)act, 1.0f};
+  sgemm_half_nt(a, b, c, m, k, n, beta, true, &e);
+}
+
+// gemv.rs:160-226.
+void wko_sgemv_alpha(const float* a, const float* x, float* y, i64 m, i64 n, float alpha) {
+  if (m <= 0 || n <= 0) return;
+  par_for(m, 16, [&](i64 lo, i64 hi) {
+    for (i64 i = lo; i < hi; ++i) {
+      float s = gemv_row(a + (size_t)i * (size_t)n, x, (size_t)n);
+      y[i] = (alpha != 1.0f) ? s * alpha : s;
+    }
+  });
+}
+void wko_sgemv(const float* a, const float* x, float* y, i64 m, i64 n) { wko_sgemv_alpha(a, x, y, m, n, 1.0f); }
+
+i64 wko_sgemv_bf16(const u16* w, i64 nw, const float* x, i64 nx, float* y, i64 ny) {
+  return sgemv_half(w, nw, x, nx, y, ny, true);
+}
+i64 wko_sgemv_f16(const u16* w, i64 nw, const float* x, i64 nx, float* y, i64 ny) {
+  return sgemv_half(w, nw, x, nx, y, ny, false);
+}
+}
