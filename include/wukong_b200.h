@@ -1,0 +1,192 @@
+/* wukong_b200 -- B200 (sm_100a) implementation of the tensor builtins of the Wukong runtime.
+ *
+ * PART 1 is the drop-in boundary: the `extern "C" wukong_*` symbols of the reference's kernel
+ * library (crates/wukong_runtime), same names, argument order, aliasing classes and status codes;
+ * the machine-readable signature table they were checked against is
+ * crates/wukong_codegen_llvm/src/runtime_abi.rs:7-232.  Pointers are HOST pointers; each call
+ * moves its operands to the GPU, runs the CUDA kernel and moves the result back.
+ *
+ * PART 2 is the device-resident API (`wkb_*`): the same kernels on DEVICE pointers with an explicit
+ * stream (a `cudaStream_t` passed as `void*`), plus the pieces a resident decode loop needs that the
+ * host ABI cannot express (bf16 storage, paged KV, dense tensor-core GEMM, block allocator,
+ * continuous-batching scheduler).  All `wkb_*` functions return 0 on success, a `cudaError_t` value
+ * (> 0) on a CUDA failure, or a negative status where documented.
+ *
+ * Every integer is `int64_t`, every float `float`, System V AMD64.  There is no CPU compute path in
+ * this library: without a usable CUDA device PART 1 aborts with a message.
+ */
+#ifndef WUKONG_B200_H
+#define WUKONG_B200_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ======================================= PART 1: runtime ABI ================================== */
+
+/* Status codes of the checked entries (quant.rs:61-65, gemv_half.rs:53-57, attention_kv.rs:97-102). */
+#define WUKONG_OK 0
+#define WUKONG_KV_BAD_GEOMETRY (-1)
+#define WUKONG_BAD_EXTENT (-2) /* QUANT_BAD_EXTENT, GEMV_BAD_EXTENT, KV_SHORT_OPERAND */
+
+/* Activation codes of the fused epilogue (gemm.rs:726-733): 0 identity, 1 relu, 2 gelu(tanh), 3 silu.
+ * vmath op codes (vmath.rs:81-116): 0 exp 1 log 2 tanh 3 sigmoid 4 relu 5 silu 6 gelu 15 sin 16 cos;
+ * vmath2 (vmath.rs:1506-1512): 9 silu_gate 10 gelu_gate 11 sigmoid_gate (out = act(x) * y).
+ * norm op codes (norm.rs:50-54): 0 softmax 1 layernorm 2 rmsnorm 3 log_softmax 4 l2norm.
+ * velem op (velem.rs:39-53): low byte 0 id / 1 relu / 2 relu6; |256 use y; |512 Hadamard; |1024 divide. */
+
+/* C[M,N] = A.B (gemm.rs:809), A.B^T (:839), A^T.B (:1245); beta is a 0 / non-0 accumulate flag.
+ * Non-positive extents write nothing.  Bit-identical to the reference (order contract gemm.rs:30-58). */
+void wukong_sgemm(const float* a, const float* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta);
+void wukong_sgemm_nt(const float* a, const float* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta);
+void wukong_sgemm_tn(const float* a, const float* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta);
+/* c = act(A.B^T + bias[j]) (gemm.rs:873); bias may be null. */
+void wukong_sgemm_nt_epi(const float* a, const float* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta,
+                         const float* bias, int64_t act);
+/* c = alpha * (A.B^T) (gemm.rs:924). */
+void wukong_sgemm_nt_alpha(const float* a, const float* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta,
+                           float alpha);
+void wukong_sgemm_parallel(const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t);
+void wukong_sgemm_nt_parallel(const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t);
+void wukong_sgemm_tn_parallel(const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t);
+void wukong_sgemm_nt_epi_parallel(const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t, const float*, int64_t);
+void wukong_sgemm_nt_alpha_parallel(const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t, float);
+
+/* Half-storage operands (bf16 / f16 bits), f32 accumulate and output (gemm.rs:1490,1549,1639,1705,1811,1870). */
+void wukong_sgemm_bf16_nt(const uint16_t* a, const uint16_t* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta);
+void wukong_sgemm_f16_nt(const uint16_t* a, const uint16_t* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta);
+void wukong_sgemm_bf16_nt_epi(const uint16_t* a, const uint16_t* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta, const float* bias, int64_t act);
+void wukong_sgemm_f16_nt_epi(const uint16_t* a, const uint16_t* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta, const float* bias, int64_t act);
+void wukong_sgemm_bf16_tn(const uint16_t* a, const uint16_t* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta);
+void wukong_sgemm_f16_tn(const uint16_t* a, const uint16_t* b, float* c, int64_t m, int64_t k, int64_t n, int64_t beta);
+void wukong_sgemm_bf16_nt_parallel(const uint16_t*, const uint16_t*, float*, int64_t, int64_t, int64_t, int64_t);
+void wukong_sgemm_f16_nt_parallel(const uint16_t*, const uint16_t*, float*, int64_t, int64_t, int64_t, int64_t);
+void wukong_sgemm_bf16_nt_epi_parallel(const uint16_t*, const uint16_t*, float*, int64_t, int64_t, int64_t, int64_t, const float*, int64_t);
+void wukong_sgemm_f16_nt_epi_parallel(const uint16_t*, const uint16_t*, float*, int64_t, int64_t, int64_t, int64_t, const float*, int64_t);
+void wukong_sgemm_bf16_tn_parallel(const uint16_t*, const uint16_t*, float*, int64_t, int64_t, int64_t, int64_t);
+void wukong_sgemm_f16_tn_parallel(const uint16_t*, const uint16_t*, float*, int64_t, int64_t, int64_t, int64_t);
+
+/* y[M] = (alpha *) A[M,N].x (gemv.rs:197,226): four 8-lane accumulators, fixed trees, unfused tail. */
+void wukong_sgemv(const float* a, const float* x, float* y, int64_t m, int64_t n);
+void wukong_sgemv_alpha(const float* a, const float* x, float* y, int64_t m, int64_t n, float alpha);
+void wukong_sgemv_parallel(const float*, const float*, float*, int64_t, int64_t);
+void wukong_sgemv_alpha_parallel(const float*, const float*, float*, int64_t, int64_t, float);
+/* y[N] = W[N,K].x with half-storage W (gemv_half.rs:465-529); N = ny, K = nx, nw must be N*K.
+ * Returns 0 or -2 (nothing touched).  K = 0 writes zeros. */
+int64_t wukong_sgemv_bf16(const uint16_t* w, int64_t nw, const float* x, int64_t nx, float* y, int64_t ny);
+int64_t wukong_sgemv_f16(const uint16_t* w, int64_t nw, const float* x, int64_t nx, float* y, int64_t ny);
+int64_t wukong_sgemv_bf16_parallel(const uint16_t*, int64_t, const float*, int64_t, float*, int64_t);
+int64_t wukong_sgemv_f16_parallel(const uint16_t*, int64_t, const float*, int64_t, float*, int64_t);
+
+/* GGML Q8_0 / Q4_0 packers and GEMV (quant.rs:488-605).  GEMV: x is quantised per call to Q8 with
+ * an exact f32 scale, block dots are exact i32, the row accumulates in block order.  Returns 0 / -2. */
+int64_t wukong_quantize_q8_0_f32(const float* x, int64_t nx, uint8_t* q, int64_t nq, int64_t k);
+int64_t wukong_quantize_q4_0_f32(const float* x, int64_t nx, uint8_t* q, int64_t nq, int64_t k);
+int64_t wukong_gemv_q8_0_f32(const uint8_t* w, int64_t nw, const float* x, int64_t nx, float* y, int64_t ny);
+int64_t wukong_gemv_q4_0_f32(const uint8_t* w, int64_t nw, const float* x, int64_t nx, float* y, int64_t ny);
+int64_t wukong_gemv_q8_0_f32_parallel(const uint8_t*, int64_t, const float*, int64_t, float*, int64_t);
+int64_t wukong_gemv_q4_0_f32_parallel(const uint8_t*, int64_t, const float*, int64_t, float*, int64_t);
+/* Group-wise int4 (quant.rs:742-800): element i = nibble i&1 of byte i>>1. */
+int64_t wukong_dequant_i4_f32(const uint8_t* q, int64_t nq, const float* scale, int64_t ns, int64_t group, float* out, int64_t nout);
+int64_t wukong_dequant_u4_f32(const uint8_t* q, int64_t nq, const float* scale, int64_t ns, const float* zero, int64_t nz, int64_t group, float* out, int64_t nout);
+
+/* Elementwise (vmath.rs:1063,1106,2022; velem.rs:212,537).  out may be exactly x. */
+void wukong_vmath_f32(const float* x, float* out, int64_t n, int64_t op);
+void wukong_vmath_f32_parallel(const float* x, float* out, int64_t n, int64_t op);
+void wukong_vmath2_f32(const float* x, const float* y, float* out, int64_t n, int64_t op);
+void wukong_velem_f32(const float* x, const float* y, float* out, int64_t n, float a, float b, float c, int64_t op);
+void wukong_velem_f32_parallel(const float* x, const float* y, float* out, int64_t n, float a, float b, float c, int64_t op);
+
+/* Row-wise norms (norm.rs:991,1041,1102,1157).  eps_bits = bits of the f32 eps, zero extended.
+ * The affine entries take only layernorm / rmsnorm; gamma / beta may be null (1 / 0). */
+void wukong_norm_f32(const float* x, float* out, int64_t rows, int64_t cols, int64_t eps_bits, int64_t op);
+void wukong_norm_affine_f32(const float* x, float* out, const float* gamma, const float* beta, int64_t rows, int64_t cols, int64_t eps_bits, int64_t op);
+void wukong_norm_f32_parallel(const float*, float*, int64_t, int64_t, int64_t, int64_t);
+void wukong_norm_affine_f32_parallel(const float*, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t);
+
+/* Decode attention over a padded KV cache (attention_kv.rs:1050,1099,1207,1255) and the cache
+ * append (:1331).  Returns 0, -1 (bad geometry) or -2 (short operand); nothing written on refusal. */
+int64_t wukong_attention_kv_f32(const float* q, int64_t nq, const float* k, int64_t nk, const float* v, int64_t nv,
+                                float* o, int64_t no, int64_t sq, int64_t skv, int64_t d, int64_t q_pos0,
+                                int64_t n_heads, int64_t n_kv_heads, int64_t q_stride, int64_t kv_stride, float scale,
+                                int64_t causal);
+int64_t wukong_attention_kv_f32_parallel(const float*, int64_t, const float*, int64_t, const float*, int64_t, float*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, float, int64_t);
+int64_t wukong_attention_kv_batch_f32(const float* q, int64_t nq, const float* k, int64_t nk, const float* v,
+                                      int64_t nv, float* o, int64_t no, const int32_t* kv_lens, int64_t nl,
+                                      const int32_t* q_pos, int64_t np, int64_t batch, int64_t sq, int64_t skv,
+                                      int64_t n_heads, int64_t n_kv_heads, int64_t d, float scale, int64_t causal);
+int64_t wukong_attention_kv_batch_f32_parallel(const float*, int64_t, const float*, int64_t, const float*, int64_t, float*, int64_t, const int32_t*, int64_t, const int32_t*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, float, int64_t);
+int64_t wukong_kv_append_f32(float* cache, int64_t ncache, const float* row, int64_t nrow, int64_t pos, int64_t stride);
+/* Square single-head attention (attention.rs:107). */
+void wukong_attention_f32(const float* q, const float* k, const float* v, float* o, int64_t s, int64_t d, float scale, int64_t causal);
+
+/* RoPE half-split, position = row index (rope.rs:143,190); embedding gather (embedding.rs:161,202);
+ * per-row arg-max, lowest index wins ties (rowarg.rs:210,227). */
+void wukong_rope_f32(const float* x, const float* inv_freq, float* out, int64_t rows, int64_t half);
+void wukong_rope_f32_parallel(const float* x, const float* inv_freq, float* out, int64_t rows, int64_t half);
+void wukong_embedding_f32(float* out, const float* weight, const int32_t* ids, int64_t t, int64_t h, int64_t v);
+void wukong_embedding_f32_parallel(float* out, const float* weight, const int32_t* ids, int64_t t, int64_t h, int64_t v);
+void wukong_rowargmax_i32(const float* x, int32_t* out, int64_t rows, int64_t cols);
+void wukong_rowargmax_i32_parallel(const float* x, int32_t* out, int64_t rows, int64_t cols);
+
+/* ===================================== PART 2: device-resident API ============================ */
+/* The reference's GPU path crosses host<->device on every call (crates/wukong_codegen_gpu/src/gpu.rs
+ * :1647-1663); these entries are what replaces it.  All pointers are DEVICE pointers. */
+
+int wkb_device_count(void);
+const char* wkb_build_arch(void);
+
+int wkb_vmath_f32(const float* x, float* out, int64_t n, int64_t op, void* stream);
+int wkb_vmath2_f32(const float* x, const float* y, float* out, int64_t n, int64_t op, void* stream);
+int wkb_velem_f32(const float* x, const float* y, float* out, int64_t n, float a, float b, float c, int64_t op, void* stream);
+/* bf16 activation, optionally gated: out = act(x) [* y]; op as vmath (4 relu, 5 silu, 6 gelu). */
+int wkb_act_bf16(const void* x, const void* y_gate_or_null, void* out, int64_t n, int64_t op, void* stream);
+
+/* fp32 norms, bit-identical to PART 1 (affine != 0 selects the affine entry's semantics). */
+int wkb_norm_f32(const float* x, float* out, const float* gamma, const float* beta, int64_t rows, int64_t cols,
+                 int64_t eps_bits, int64_t op, int affine, void* stream);
+/* Half-precision-path norms: dtype 0 = f32, 1 = bf16; op 0 softmax, 1 layernorm, 2 rmsnorm; f32 gamma /
+ * beta (nullable); cols % 8 == 0, cols <= 8192.  Widen, fp32 math, one rounding on the way out. */
+int wkb_norm_fast(const void* x, int in_dtype, void* out, int out_dtype, const float* gamma, const float* beta,
+                  int64_t rows, int64_t cols, float eps, int64_t op, void* stream);
+
+/* Order-contract GEMM on device operands; dtype 0 f32, 1 bf16 bits, 2 f16 bits (c is always f32). */
+int wkb_sgemm_contract(const void* a, int a_dtype, const void* b, int b_dtype, float* c, int64_t m, int64_t k,
+                       int64_t n, int64_t beta, int at, int bt, const float* bias, int64_t act, float alpha,
+                       int has_epi, void* stream);
+int wkb_sgemv_f32(const float* a, const float* x, float* y, int64_t m, int64_t n, float alpha, void* stream);
+
+/* Q4_0 / Q8_0.  wkb_q_split permutes raw 18 / 34-byte blocks into the resident layout: a quant
+ * plane (16 / 32 B per block) and an f16 scale plane.  wkb_quantize_act produces the per-call Q8
+ * activation (xq [nb*32] i8, dx [nb] f32, sx [nb] i32).  wkb_gemv_q_contract is bit-identical to the
+ * reference GEMV; wkb_gemv_q4_0_bf16x is the in-register-dequant form with bf16 activations. */
+int wkb_q_split(const uint8_t* raw, void* qs, void* d, int64_t nblocks, int q4, void* stream);
+int wkb_quantize_act(const float* x, int64_t k, void* xq, float* dx, int* sx, void* stream);
+int wkb_gemv_q_contract(const void* qs, const void* d, const void* xq, const float* dx, const int* sx, float* y,
+                        int64_t n, int64_t k, int q4, void* stream);
+int wkb_gemv_q4_0_bf16x(const void* qs, const void* d, const void* x_bf16, float* y, int64_t n, int64_t k, void* stream);
+int wkb_quantize_q(const float* x, uint8_t* q, int64_t rows, int64_t k, int q4, void* stream);
+int wkb_dequant_int4(const uint8_t* q, const float* scale, const float* zero_or_null, int64_t group, float* out, int64_t n, void* stream);
+
+/* fp32 decode attention on device operands (geometry already validated).  kv_lens / q_pos null
+ * selects the single-sequence form with (skv, q_pos0). */
+int wkb_attention_kv_f32(const float* q, const float* k, const float* v, float* o, const int* kv_lens,
+                         const int* q_pos, int64_t batch, int64_t sq, int64_t skv, int64_t d, int64_t q_pos0,
+                         int64_t n_heads, int64_t n_kv_heads, int64_t q_stride, int64_t kv_stride, int64_t q_bstride,
+                         int64_t kv_bstride, float scale, int64_t causal, void* stream);
+int wkb_attention_f32(const float* q, const float* k, const float* v, float* o, int64_t s, int64_t d, float scale, int64_t causal, void* stream);
+int wkb_kv_append_f32(float* cache, const float* row, int64_t nrow, int64_t pos, int64_t stride, void* stream);
+
+/* RoPE with an optional position vector (null: position = row); x is [rows, heads, 2*half]. */
+int wkb_rope_f32(const float* x, const float* inv_freq, const int* pos_or_null, float* out, int64_t rows, int64_t heads, int64_t half, void* stream);
+int wkb_rope_bf16(const void* x, const float* inv_freq, const int* pos, void* out, int64_t rows, int64_t heads, int64_t half, int64_t row_stride, void* stream);
+int wkb_embedding_f32(float* out, const float* weight, const int* ids, int64_t t, int64_t h, int64_t v, void* stream);
+/* out[r] = wte[ids[r]] + wpe[pos[r]] (bf16 tables, f32 out): the GPT-2 input embedding. */
+int wkb_embed_tok_pos_bf16(float* out, const void* wte, const void* wpe, const int* ids, const int* pos, int64_t t, int64_t h, int64_t v, int64_t npos, void* stream);
+int wkb_rowargmax_i32(const float* x, int* out, int64_t rows, int64_t cols, void* stream);
+int wkb_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WUKONG_B200_H */

@@ -1,0 +1,350 @@
+// Row-wise softmax / log-softmax / LayerNorm / RMSNorm / L2-norm over [rows, cols].
+//
+// Two families:
+//  * `norm_exact`: fp32, one warp per row, reproducing the reference's accumulator layout and
+//    combine trees lane for lane (norm.rs:56-178, :379-413, :466-490, :538-576, :757-796 of the
+//    reference runtime), so every output bit equals the CPU kernel's.  The reference's 8x8 = 64
+//    accumulator lanes map onto a warp as two per thread (lane L owns lanes L and L+32), which
+//    also makes each 64-element block two fully coalesced 128-byte loads.
+//  * `norm_fast`: f32 or bf16 storage for the half-precision decode path (no CPU kernel exists for
+//    bf16 rows in the reference; the contract is widen -> fp32 math -> round once).  One CTA per
+//    row, the row held in registers between the reduction and the writeback so HBM sees each
+//    element once in and once out, 128-bit loads and stores.
+#include "common.cuh"
+#include "wkb_device.h"
+
+namespace wkb {
+
+// ---------------------------------------------------------------------------------------------
+// exact family
+// ---------------------------------------------------------------------------------------------
+enum { RED_SSQ = 0, RED_SUM = 1, RED_DEV2 = 2 };
+
+template <int R>
+__device__ __forceinline__ float red_step(float acc, float v, float mean) {
+  if (R == RED_SSQ) return ffma(v, v, acc);
+  if (R == RED_SUM) return fadd(acc, v);
+  float d = fsub(v, mean);
+  return ffma(d, d, acc);
+}
+
+// hsum8 over the values held by lanes 0..7: ((a0+a1)+(a2+a3))+((a4+a5)+(a6+a7)), every lane.
+__device__ __forceinline__ float hsum8_lanes(float v) {
+  float a0 = __shfl_sync(0xffffffffu, v, 0), a1 = __shfl_sync(0xffffffffu, v, 1);
+  float a2 = __shfl_sync(0xffffffffu, v, 2), a3 = __shfl_sync(0xffffffffu, v, 3);
+  float a4 = __shfl_sync(0xffffffffu, v, 4), a5 = __shfl_sync(0xffffffffu, v, 5);
+  float a6 = __shfl_sync(0xffffffffu, v, 6), a7 = __shfl_sync(0xffffffffu, v, 7);
+  return fadd(fadd(fadd(a0, a1), fadd(a2, a3)), fadd(fadd(a4, a5), fadd(a6, a7)));
+}
+__device__ __forceinline__ float hmax8_lanes(float v) {
+  float a0 = __shfl_sync(0xffffffffu, v, 0), a1 = __shfl_sync(0xffffffffu, v, 1);
+  float a2 = __shfl_sync(0xffffffffu, v, 2), a3 = __shfl_sync(0xffffffffu, v, 3);
+  float a4 = __shfl_sync(0xffffffffu, v, 4), a5 = __shfl_sync(0xffffffffu, v, 5);
+  float a6 = __shfl_sync(0xffffffffu, v, 6), a7 = __shfl_sync(0xffffffffu, v, 7);
+  return maxnum(maxnum(maxnum(a0, a1), maxnum(a2, a3)), maxnum(maxnum(a4, a5), maxnum(a6, a7)));
+}
+
+// The 8-accumulator blocked reduction; returns hsum8 of the eight lane sums in every lane.
+template <int R>
+__device__ __forceinline__ float reduce8_warp(const float* x, i64 n, float mean, int lane) {
+  float a = 0.0f, b = 0.0f;  // accumulator lanes `lane` and `lane + 32` of the 64
+  i64 i = 0;
+  for (; i + 64 <= n; i += 64) {
+    a = red_step<R>(a, x[i + lane], mean);
+    b = red_step<R>(b, x[i + 32 + lane], mean);
+  }
+  for (; i + 8 <= n; i += 8)
+    if (lane < 8) a = red_step<R>(a, x[i + lane], mean);
+  a = fadd(a, b);                                                    // (t, t+4)
+  { float o = __shfl_down_sync(0xffffffffu, a, 16); if (lane < 16) a = fadd(a, o); }  // (0,2)(1,3)
+  { float o = __shfl_down_sync(0xffffffffu, a, 8);  if (lane < 8)  a = fadd(a, o); }  // (0,1)
+  if (lane < (int)(n - i)) a = red_step<R>(a, x[i + lane], mean);
+  return hsum8_lanes(a);
+}
+
+__device__ __forceinline__ float rowmax_warp(const float* x, i64 n, int lane) {
+  float a = -INFINITY, b = -INFINITY;
+  i64 i = 0;
+  for (; i + 64 <= n; i += 64) {
+    a = maxps(a, x[i + lane]);
+    b = maxps(b, x[i + 32 + lane]);
+  }
+  for (; i + 8 <= n; i += 8)
+    if (lane < 8) a = maxps(a, x[i + lane]);
+  a = maxps(b, a);  // higher chain first
+  { float o = __shfl_down_sync(0xffffffffu, a, 16); if (lane < 16) a = maxps(o, a); }
+  { float o = __shfl_down_sync(0xffffffffu, a, 8);  if (lane < 8)  a = maxps(o, a); }
+  if (lane < (int)(n - i)) a = maxnum(a, x[i + lane]);
+  return hmax8_lanes(a);
+}
+
+// Sum of exp1(x - m) with the reference's 8-lane, in-order chains (lane j folds elements = j mod 8
+// in ascending order, the tail into lanes 0..).  Optionally stores the exponentials.
+__device__ __forceinline__ float expsum_warp(const float* x, float* out, i64 n, float m,
+                                             int lane, bool store) {
+  float sm = 0.0f;  // every lane carries chain (lane & 7)
+  i64 nb8 = (n / 8) * 8;
+  int j = lane & 7;
+  for (i64 i = 0; i < nb8; i += 32) {
+    float e = 0.0f;
+    bool in = i + lane < nb8;
+    if (in) {
+      e = exp1(fsub(x[i + lane], m));
+      if (store) out[i + lane] = e;
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float eg = __shfl_sync(0xffffffffu, e, j + 8 * g);
+      if (i + 8 * g < nb8) sm = fadd(sm, eg);
+    }
+  }
+  int tail = (int)(n - nb8);
+  float e = 0.0f;
+  if (lane < tail) {
+    e = exp1(fsub(x[nb8 + lane], m));
+    if (store) out[nb8 + lane] = e;
+  }
+  float ej = __shfl_sync(0xffffffffu, e, j);
+  if (j < tail) sm = fadd(sm, ej);
+  return hsum8_lanes(sm);
+}
+
+__global__ void __launch_bounds__(256) norm_exact_kernel(const float* x, float* out,
+                                                         const float* __restrict__ gamma,
+                                                         const float* __restrict__ beta, i64 rows, i64 cols,
+                                                         float eps, int op, int affine) {
+  int lane = threadIdx.x & 31;
+  i64 warp = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
+  for (i64 r = warp; r < rows; r += nwarps) {
+    const float* xr = x + r * cols;
+    float* orow = out + r * cols;
+    if (op == 0) {
+      float m = rowmax_warp(xr, cols, lane);
+      float s = expsum_warp(xr, orow, cols, m, lane, true);
+      float inv = fdiv(1.0f, s);
+      __syncwarp();
+      for (i64 i = lane; i < cols; i += 32) orow[i] = fmul(orow[i], inv);
+    } else if (op == 3) {
+      float m = rowmax_warp(xr, cols, lane);
+      float s = expsum_warp(xr, orow, cols, m, lane, false);
+      float off = fadd(m, log1(s));
+      for (i64 i = lane; i < cols; i += 32) orow[i] = fsub(xr[i], off);
+    } else {
+      float invn = fdiv(1.0f, (float)cols);
+      float mean = 0.0f, inv;
+      if (op == 1) {
+        mean = fmul(reduce8_warp<RED_SUM>(xr, cols, 0.0f, lane), invn);
+        float var = reduce8_warp<RED_DEV2>(xr, cols, mean, lane);
+        inv = fdiv(1.0f, fsqrt(fadd(fmul(var, invn), eps)));
+      } else if (op == 2) {
+        inv = fdiv(1.0f, fsqrt(fadd(fmul(reduce8_warp<RED_SSQ>(xr, cols, 0.0f, lane), invn), eps)));
+      } else {
+        inv = fdiv(1.0f, fsqrt(fadd(reduce8_warp<RED_SSQ>(xr, cols, 0.0f, lane), eps)));
+      }
+      for (i64 i = lane; i < cols; i += 32) {
+        float nv = (op == 1) ? fmul(fsub(xr[i], mean), inv) : fmul(xr[i], inv);
+        if (affine) nv = ffma(nv, gamma ? gamma[i] : 1.0f, beta ? beta[i] : 0.0f);
+        orow[i] = nv;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// fast family
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct Vec8;  // 8 elements of T moved as 128-bit words
+template <> struct Vec8<__nv_bfloat16> {
+  uint4 w;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { w = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = w; }
+  __device__ __forceinline__ void unpack(float f[8]) const {
+    uint32_t s[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { f[2 * k] = u2f(s[k] << 16); f[2 * k + 1] = u2f(s[k] & 0xffff0000u); }
+  }
+  __device__ __forceinline__ void pack(const float f[8]) {
+    uint32_t s[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      s[k] = (uint32_t)f32_to_bf16_bits(f[2 * k]) | ((uint32_t)f32_to_bf16_bits(f[2 * k + 1]) << 16);
+    w = make_uint4(s[0], s[1], s[2], s[3]);
+  }
+};
+template <> struct Vec8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = reinterpret_cast<const float4*>(p)[0];
+    b = reinterpret_cast<const float4*>(p)[1];
+  }
+  __device__ __forceinline__ void store(float* p) const {
+    reinterpret_cast<float4*>(p)[0] = a;
+    reinterpret_cast<float4*>(p)[1] = b;
+  }
+  __device__ __forceinline__ void unpack(float f[8]) const {
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  __device__ __forceinline__ void pack(const float f[8]) {
+    a = make_float4(f[0], f[1], f[2], f[3]);
+    b = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+template <bool IS_MAX>
+__device__ __forceinline__ float block_reduce(float v, float* red) {
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : (IS_MAX ? -INFINITY : 0.0f);
+  return IS_MAX ? warp_max(r) : warp_sum(r);
+}
+
+// One CTA (NT threads) per row; each thread keeps up to VPT 8-element vectors of the row.
+// cols must be a multiple of 8 and <= NT * VPT * 8.
+template <typename TIn, typename TOut, int NT, int VPT>
+__global__ void __launch_bounds__(NT) norm_fast_kernel(const TIn* __restrict__ x, TOut* __restrict__ out,
+                                                       const float* __restrict__ gamma,
+                                                       const float* __restrict__ beta, i64 rows, int cols,
+                                                       float eps, int op) {
+  __shared__ float red[32];
+  const int nvec = cols >> 3;
+  for (i64 r = blockIdx.x; r < rows; r += gridDim.x) {
+    const TIn* xr = x + r * (i64)cols;
+    TOut* orow = out + r * (i64)cols;
+    float v[VPT][8];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      int vi = threadIdx.x + k * NT;
+      if (vi < nvec) {
+        Vec8<TIn> t;
+        t.load(xr + (i64)vi * 8);
+        t.unpack(v[k]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[k][e] = (op == 0) ? -INFINITY : 0.0f;
+      }
+    }
+    float scale = 1.0f, shift = 0.0f;
+    if (op == 0) {
+      float m = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m = fmaxf(m, v[k][e]);
+      m = block_reduce<true>(m, red);
+      float s = 0.0f;
+      const float l2e = 1.4426950408889634f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          v[k][e] = exp2f((v[k][e] - m) * l2e);
+          s += v[k][e];
+        }
+      s = block_reduce<false>(s, red);
+      scale = 1.0f / s;
+    } else if (op == 1) {
+      float s = 0.0f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += v[k][e];
+      float mean = block_reduce<false>(s, red) / (float)cols;
+      float q = 0.0f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        int vi = threadIdx.x + k * NT;
+        if (vi < nvec) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { float d = v[k][e] - mean; q = fmaf(d, d, q); }
+        }
+      }
+      q = block_reduce<false>(q, red);
+      scale = rsqrtf(q / (float)cols + eps);
+      shift = mean;
+    } else {
+      float q = 0.0f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q = fmaf(v[k][e], v[k][e], q);
+      q = block_reduce<false>(q, red);
+      scale = rsqrtf(q / (float)cols + eps);
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      int vi = threadIdx.x + k * NT;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float nv = (v[k][e] - shift) * scale;
+          if (op != 0) {
+            float g = gamma ? gamma[vi * 8 + e] : 1.0f;
+            float b = beta ? beta[vi * 8 + e] : 0.0f;
+            nv = fmaf(nv, g, b);
+          }
+          o[e] = nv;
+        }
+        Vec8<TOut> t;
+        t.pack(o);
+        t.store(orow + (i64)vi * 8);
+      }
+    }
+  }
+}
+
+template <typename TIn, typename TOut>
+static int launch_fast(const void* x, void* out, const float* g, const float* b, i64 rows, i64 cols, float eps,
+                       int op, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 8 != 0 || cols > 128 * 8 * 8) return (int)cudaErrorInvalidValue;
+  if (op < 0 || op > 2) return (int)cudaErrorInvalidValue;
+  if (((((uintptr_t)x) | ((uintptr_t)out)) & 15) != 0) return (int)cudaErrorMisalignedAddress;
+  int grid = (int)(rows < (i64)WKB_SM_COUNT * 16 ? rows : (i64)WKB_SM_COUNT * 16);
+  if (cols <= 128 * 8) {
+    norm_fast_kernel<TIn, TOut, 128, 1><<<grid, 128, 0, st>>>((const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
+  } else if (cols <= 128 * 8 * 2) {
+    norm_fast_kernel<TIn, TOut, 128, 2><<<grid, 128, 0, st>>>((const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
+  } else if (cols <= 128 * 8 * 4) {
+    norm_fast_kernel<TIn, TOut, 128, 4><<<grid, 128, 0, st>>>((const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
+  } else {
+    norm_fast_kernel<TIn, TOut, 128, 8><<<grid, 128, 0, st>>>((const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // namespace wkb
+
+using namespace wkb;
+
+extern "C" {
+
+int wkb_norm_f32(const float* x, float* out, const float* gamma, const float* beta, i64 rows, i64 cols,
+                 i64 eps_bits, i64 op, int affine, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (affine && op != 1 && op != 2) return 0;   // the affine entries ignore every other code
+  if (!affine && (op < 0 || op > 4)) return 0;  // unknown code: nothing written
+  float eps = __builtin_bit_cast(float, (uint32_t)eps_bits);
+  i64 warps_needed = rows;
+  i64 blocks = (warps_needed + 7) / 8;
+  i64 cap = (i64)WKB_SM_COUNT * 8;
+  if (blocks > cap) blocks = cap;
+  norm_exact_kernel<<<(int)blocks, 256, 0, as_stream(stream)>>>(x, out, gamma, beta, rows, cols, eps, (int)op, affine);
+  return (int)cudaGetLastError();
+}
+
+// in_dtype / out_dtype: 0 = f32, 1 = bf16.  op: 0 softmax, 1 layernorm, 2 rmsnorm.
+int wkb_norm_fast(const void* x, int in_dtype, void* out, int out_dtype, const float* gamma, const float* beta,
+                  i64 rows, i64 cols, float eps, i64 op, void* stream) {
+  cudaStream_t st = as_stream(stream);
+  if (in_dtype == 1 && out_dtype == 1) return launch_fast<__nv_bfloat16, __nv_bfloat16>(x, out, gamma, beta, rows, cols, eps, (int)op, st);
+  if (in_dtype == 0 && out_dtype == 1) return launch_fast<float, __nv_bfloat16>(x, out, gamma, beta, rows, cols, eps, (int)op, st);
+  if (in_dtype == 0 && out_dtype == 0) return launch_fast<float, float>(x, out, gamma, beta, rows, cols, eps, (int)op, st);
+  if (in_dtype == 1 && out_dtype == 0) return launch_fast<__nv_bfloat16, float>(x, out, gamma, beta, rows, cols, eps, (int)op, st);
+  return (int)cudaErrorInvalidValue;
+}
+}

@@ -1,0 +1,372 @@
+// GGML Q4_0 / Q8_0 block-quantised weights: packers, layout split, the weight-only quantised GEMV
+// and group-wise int4 dequantisation.
+//
+// Reference semantics (crates/wukong_runtime/src/quant.rs): a 32-value block is a little-endian f16
+// scale `d` followed by its quants; Q4_0 byte j holds element j (low nibble) and element j+16 (high
+// nibble), value d*(nibble-8) (:13-16).  The GEMV quantises the activation per call to Q8 blocks
+// with an exact f32 scale (:201-212), takes exact i32 block dots, and accumulates
+// `acc = acc + (dw*dx)*f32(isum)` in block order with every operation rounded once (:21-37,
+// :227-239).  `gemv_q_contract_kernel` reproduces exactly that, so y is bit-identical to the CPU
+// kernel: dp4a gives the exact integer dots, and the float recurrence runs in block order.
+//
+// Device layout.  The raw rows are 18 (34) bytes per block, so nothing in them is 16-byte aligned.
+// Resident weights are therefore held as two planes -- quants [N, nb] x 16 B (Q8: 32 B) and scales
+// [N, nb] x f16 -- produced by a pure byte permutation (`split_kernel`); the algorithmic bytes per
+// block are unchanged (18 / 34) and every nibble and scale bit survives, which the tests check.
+#include "common.cuh"
+#include "wkb_device.h"
+
+namespace wkb {
+
+// ---- layout split: raw [rows, nb*BB] bytes -> quant plane + scale plane -------------------------
+template <int BB>
+__global__ void __launch_bounds__(256) split_kernel(const u8* __restrict__ raw, u8* __restrict__ qs,
+                                                    u16* __restrict__ d, i64 nblocks) {
+  constexpr int QB = BB - 2;  // quant bytes per block
+  i64 stride = (i64)gridDim.x * blockDim.x;
+  // one thread per 2-byte unit of a block (BB/2 units: unit 0 is the scale)
+  i64 units = nblocks * (BB / 2);
+  for (i64 u = (i64)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += stride) {
+    i64 b = u / (BB / 2);
+    int w = (int)(u % (BB / 2));
+    u16 v = (u16)raw[b * BB + 2 * w] | ((u16)raw[b * BB + 2 * w + 1] << 8);
+    if (w == 0) d[b] = v;
+    else reinterpret_cast<u16*>(qs + b * QB)[w - 1] = v;
+  }
+}
+
+// ---- activation quantiser (quant.rs:132-146, :201-212) ------------------------------------------
+// One warp per block.  xq: [nb][32] int8 (zero padded), dx: [nb] f32, sx: [nb] i32 = sum of quants.
+__global__ void __launch_bounds__(128) quantize_act_kernel(const float* __restrict__ x, i64 k, int8_t* __restrict__ xq,
+                                                           float* __restrict__ dx, int* __restrict__ sx, i64 nb) {
+  int lane = threadIdx.x & 31;
+  i64 warp = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
+  for (i64 b = warp; b < nb; b += nwarps) {
+    i64 e = b * 32 + lane;
+    float v = e < k ? x[e] : 0.0f;
+    float a = fabsf(v);
+    if (a != a) a = 0.0f;  // `|x| > amax` is false for NaN
+    float amax = warp_max(a);
+    float dd = fdiv(amax, 127.0f);
+    float id = dd != 0.0f ? fdiv(1.0f, dd) : 0.0f;
+    float s = fmul(v, id);
+    int q;
+    if (s != s) q = 0;
+    else {
+      float r = roundf(s);  // half away from zero
+      r = r < -127.0f ? -127.0f : (r > 127.0f ? 127.0f : r);
+      q = (int)r;
+    }
+    if (e >= k) q = 0;
+    xq[b * 32 + lane] = (int8_t)q;
+    int tot = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    if (lane == 0) { dx[b] = dd; sx[b] = tot; }
+  }
+}
+
+// ---- the contract GEMV ---------------------------------------------------------------------------
+// A warp owns RB consecutive rows at a time; lane l owns blocks l, l+32, ...  Per block: the exact
+// integer dot by dp4a, the term (dw*dx)*f32(isum) with each product rounded once, parked in shared
+// memory; then lane r < RB adds row r's terms in block order.
+constexpr int GQ_RB = 4;
+
+template <bool Q4>
+__global__ void __launch_bounds__(128) gemv_q_contract_kernel(const uint4* __restrict__ qs, const u16* __restrict__ d,
+                                                              const int8_t* __restrict__ xq, const float* __restrict__ dx,
+                                                              const int* __restrict__ sx, float* __restrict__ y, i64 n,
+                                                              int nb) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  // x words transposed: xs[w][b], w = 0..7 (32-bit word of the block's 32 quants)
+  int* xs = reinterpret_cast<int*>(smem);
+  float* dxs = reinterpret_cast<float*>(xs + 8 * nb);
+  int* sxs = reinterpret_cast<int*>(dxs + nb);
+  float* terms = reinterpret_cast<float*>(sxs + nb);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < nb * 8; i += blockDim.x) {
+    int b = i >> 3, w = i & 7;
+    xs[w * nb + b] = reinterpret_cast<const int*>(xq)[i];
+  }
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) { dxs[i] = dx[i]; sxs[i] = sx[i]; }
+  __syncthreads();
+  float* myterms = terms + (size_t)warp * GQ_RB * nb;
+  constexpr int QW = Q4 ? 1 : 2;  // uint4 words per block
+  i64 nbatches = (n + GQ_RB - 1) / GQ_RB;
+  for (i64 batch = (i64)blockIdx.x * nwarps + warp; batch < nbatches; batch += (i64)gridDim.x * nwarps) {
+    i64 r0 = batch * GQ_RB;
+    for (int b = lane; b < nb; b += 32) {
+      int xw[8];
+#pragma unroll
+      for (int w = 0; w < 8; ++w) xw[w] = xs[w * nb + b];
+      float dxb = dxs[b];
+      int sxb = sxs[b];
+      uint4 wq[GQ_RB][QW];
+      u16 dw[GQ_RB];
+#pragma unroll
+      for (int r = 0; r < GQ_RB; ++r) {
+        i64 row = r0 + r < n ? r0 + r : n - 1;
+        const uint4* p = qs + (row * nb + b) * QW;
+#pragma unroll
+        for (int h = 0; h < QW; ++h) wq[r][h] = p[h];
+        dw[r] = d[row * nb + b];
+      }
+#pragma unroll
+      for (int r = 0; r < GQ_RB; ++r) {
+        int isum = 0;
+        if (Q4) {
+          uint32_t ws[4] = {wq[r][0].x, wq[r][0].y, wq[r][0].z, wq[r][0].w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            int lo = (int)(ws[w] & 0x0f0f0f0fu), hi = (int)((ws[w] >> 4) & 0x0f0f0f0fu);
+            isum = __dp4a(lo, xw[w], isum);       // elements 4w..4w+3
+            isum = __dp4a(hi, xw[w + 4], isum);   // elements 16+4w..16+4w+3
+          }
+          isum -= 8 * sxb;  // sum (nib-8)*x = sum nib*x - 8*sum x, all exact integers
+        } else {
+          uint32_t ws[8] = {wq[r][0].x, wq[r][0].y, wq[r][0].z, wq[r][0].w,
+                            wq[r][QW - 1].x, wq[r][QW - 1].y, wq[r][QW - 1].z, wq[r][QW - 1].w};
+#pragma unroll
+          for (int w = 0; w < 8; ++w) isum = __dp4a((int)ws[w], xw[w], isum);
+        }
+        float term = fmul(fmul(f16_bits_to_f32(dw[r]), dxb), (float)isum);
+        myterms[r * nb + b] = term;
+      }
+    }
+    __syncwarp();
+    if (lane < GQ_RB && r0 + lane < n) {
+      const float* t = myterms + lane * nb;
+      float acc = 0.0f;
+      for (int b = 0; b < nb; ++b) acc = fadd(acc, t[b]);
+      y[r0 + lane] = acc;
+    }
+    __syncwarp();
+  }
+}
+
+// ---- in-register-dequant GEMV with bf16 activations, fp32 accumulate ----------------------------
+// y[j] = sum_b f32(d_jb) * sum_e (nib_jbe - 8) * x[32b+e].  Each nibble becomes the f32 value
+// 16+nib by placing it in the top mantissa bits of 16.0f (exact), so the per-element work is one
+// shift, one logic op and one FMA; sum_e (16+nib)*x - 24*sum_e x removes the offset once per block.
+// Products are exact (5-bit x 8-bit significands); fp32 accumulation order is free here (no CPU
+// kernel defines one for bf16 activations), lane-per-block with a warp-shuffle tree at the end.
+__global__ void __launch_bounds__(128) gemv_q4_bf16x_kernel(const uint4* __restrict__ qs, const u16* __restrict__ d,
+                                                            const u16* __restrict__ xb, i64 k, float* __restrict__ y,
+                                                            i64 n, int nb) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  float* xt = reinterpret_cast<float*>(smem);  // xt[e][b]: element e of block b
+  float* sxs = xt + 32 * nb;                   // 24 * sum of the block's x
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < nb * 32; i += blockDim.x) {
+    int b = i >> 5, e = i & 31;
+    xt[e * nb + b] = (i64)i < k ? bf16_bits_to_f32(xb[i]) : 0.0f;
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+    float s = 0.0f;
+    for (int e = 0; e < 32; ++e) s += xt[e * nb + b];
+    sxs[b] = 24.0f * s;
+  }
+  __syncthreads();
+  i64 nbatches = (n + GQ_RB - 1) / GQ_RB;
+  for (i64 batch = (i64)blockIdx.x * nwarps + warp; batch < nbatches; batch += (i64)gridDim.x * nwarps) {
+    i64 r0 = batch * GQ_RB;
+    float acc[GQ_RB];
+#pragma unroll
+    for (int r = 0; r < GQ_RB; ++r) acc[r] = 0.0f;
+    for (int b = lane; b < nb; b += 32) {
+      uint4 wq[GQ_RB];
+      float dw[GQ_RB], part[GQ_RB];
+#pragma unroll
+      for (int r = 0; r < GQ_RB; ++r) {
+        i64 row = r0 + r < n ? r0 + r : n - 1;
+        wq[r] = qs[row * nb + b];
+        dw[r] = f16_bits_to_f32(d[row * nb + b]);
+        part[r] = 0.0f;
+      }
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          // nibble p of word w: byte p/2 of the word, low half if p is even
+          int e = 4 * w + (p >> 1) + ((p & 1) ? 16 : 0);
+          float xv = xt[e * nb + b];
+#pragma unroll
+          for (int r = 0; r < GQ_RB; ++r) {
+            uint32_t word = w == 0 ? wq[r].x : w == 1 ? wq[r].y : w == 2 ? wq[r].z : wq[r].w;
+            int sh = 19 - 4 * p;
+            uint32_t pos = sh >= 0 ? (word << sh) : (word >> (-sh));
+            float m = u2f((pos & 0x00780000u) | 0x41800000u);  // 16 + nib, exact
+            part[r] = fmaf(m, xv, part[r]);
+          }
+        }
+      }
+      float corr = sxs[b];
+#pragma unroll
+      for (int r = 0; r < GQ_RB; ++r) acc[r] = fmaf(dw[r], part[r] - corr, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < GQ_RB; ++r) {
+      float v = warp_sum(acc[r]);
+      if (lane == 0 && r0 + r < n) y[r0 + r] = v;
+    }
+  }
+}
+
+// ---- packers (quant.rs:154-197): one thread per block, the scalar scan order --------------------
+template <bool Q4>
+__global__ void __launch_bounds__(128) quantize_kernel(const float* __restrict__ x, u8* __restrict__ q, i64 rows,
+                                                       i64 k, i64 nb) {
+  constexpr int BB = Q4 ? 18 : 34;
+  i64 total = rows * nb;
+  i64 stride = (i64)gridDim.x * blockDim.x;
+  for (i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    i64 r = t / nb, b = t % nb;
+    const float* xr = x + r * k;
+    i64 lo = b * 32;
+    int bl = (int)((lo + 32 < k ? lo + 32 : k) - lo);
+    if (bl < 0) bl = 0;
+    u8* o = q + t * BB;
+    float amax = 0.0f, mx = 0.0f;
+    for (int e = 0; e < bl; ++e) {
+      float v = xr[lo + e];
+      if (Q4) { if (amax < fabsf(v)) { amax = fabsf(v); mx = v; } }
+      else    { if (fabsf(v) > amax) amax = fabsf(v); }
+    }
+    float dd = Q4 ? fdiv(mx, -8.0f) : fdiv(amax, 127.0f);
+    float id = dd != 0.0f ? fdiv(1.0f, dd) : 0.0f;
+    u16 h = __half_as_ushort(__float2half_rn(dd));
+    o[0] = (u8)(h & 0xff);
+    o[1] = (u8)(h >> 8);
+    if (Q4) {
+      for (int j = 0; j < 16; ++j) {
+        u8 nibs[2];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          int e = j + 16 * s;
+          float v = fmul(e < bl ? xr[lo + e] : 0.0f, id);
+          int iv;
+          if (v != v) iv = 8;
+          else {
+            float tt = fadd(v, 8.5f);
+            iv = tt >= 127.0f ? 127 : (tt <= -128.0f ? -128 : (int)tt);  // truncating, saturating cast
+            if (iv > 15) iv = 15;
+          }
+          nibs[s] = (u8)(int8_t)iv;
+        }
+        o[2 + j] = (u8)(nibs[0] | (nibs[1] << 4));
+      }
+    } else {
+      for (int e = 0; e < 32; ++e) {
+        int qv = 0;
+        if (e < bl) {
+          float s = fmul(xr[lo + e], id);
+          if (s == s) {
+            float rr = roundf(s);
+            rr = rr < -127.0f ? -127.0f : (rr > 127.0f ? 127.0f : rr);
+            qv = (int)rr;
+          }
+        }
+        o[2 + e] = (u8)(int8_t)qv;
+      }
+    }
+  }
+}
+
+// ---- group-wise int4 (quant.rs:607-688) -----------------------------------------------------------
+__global__ void __launch_bounds__(256) dequant_int4_kernel(const u8* __restrict__ q, const float* __restrict__ scale,
+                                                           const float* __restrict__ zero, i64 group,
+                                                           float* __restrict__ out, i64 n) {
+  i64 stride = (i64)gridDim.x * blockDim.x;
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    u8 b = q[i >> 1];
+    u8 nib = (i & 1) == 0 ? (b & 0x0f) : (b >> 4);
+    float s = scale[i / group];
+    float v;
+    if (!zero) {
+      int sv = (int)(int8_t)(nib << 4) >> 4;
+      v = fmul((float)sv, s);
+    } else {
+      v = fmul(fsub((float)nib, zero[i / group]), s);
+    }
+    out[i] = v;
+  }
+}
+
+static size_t contract_smem(int nb, int warps) { return (size_t)nb * (32 + 4 + 4) + (size_t)warps * GQ_RB * nb * 4; }
+
+}  // namespace wkb
+
+using namespace wkb;
+
+extern "C" {
+
+int wkb_q_split(const u8* raw, void* qs, void* d, i64 nblocks, int q4, void* stream) {
+  if (nblocks <= 0) return 0;
+  i64 units = nblocks * (q4 ? 9 : 17);
+  int grid = (int)((units + 255) / 256 < (i64)WKB_SM_COUNT * 16 ? (units + 255) / 256 : (i64)WKB_SM_COUNT * 16);
+  if (q4) split_kernel<18><<<grid, 256, 0, as_stream(stream)>>>(raw, (u8*)qs, (u16*)d, nblocks);
+  else split_kernel<34><<<grid, 256, 0, as_stream(stream)>>>(raw, (u8*)qs, (u16*)d, nblocks);
+  return (int)cudaGetLastError();
+}
+
+int wkb_quantize_act(const float* x, i64 k, void* xq, float* dx, int* sx, void* stream) {
+  i64 nb = (k + 31) / 32;
+  if (nb <= 0) return 0;
+  int grid = (int)((nb + 3) / 4 < (i64)WKB_SM_COUNT * 8 ? (nb + 3) / 4 : (i64)WKB_SM_COUNT * 8);
+  quantize_act_kernel<<<grid, 128, 0, as_stream(stream)>>>(x, k, (int8_t*)xq, dx, sx, nb);
+  return (int)cudaGetLastError();
+}
+
+// y = W x under the reference contract.  qs/d are the split planes; xq/dx/sx come from
+// wkb_quantize_act.  Bit-identical to the CPU kernel.
+int wkb_gemv_q_contract(const void* qs, const void* d, const void* xq, const float* dx, const int* sx, float* y,
+                        i64 n, i64 k, int q4, void* stream) {
+  if (n <= 0 || k <= 0) return 0;
+  int nb = (int)((k + 31) / 32);
+  int warps = 4;
+  while (warps > 1 && contract_smem(nb, warps) > 200 * 1024) warps >>= 1;
+  size_t sm = contract_smem(nb, warps);
+  if (sm > 200 * 1024) return (int)cudaErrorInvalidValue;
+  i64 nbatches = (n + GQ_RB - 1) / GQ_RB;
+  i64 blocks = (nbatches + warps - 1) / warps;
+  if (blocks > (i64)WKB_SM_COUNT * 8) blocks = (i64)WKB_SM_COUNT * 8;
+  auto kern = q4 ? gemv_q_contract_kernel<true> : gemv_q_contract_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<(int)blocks, warps * 32, sm, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const int8_t*)xq, dx, sx, y, n, nb);
+  return (int)cudaGetLastError();
+}
+
+int wkb_gemv_q4_0_bf16x(const void* qs, const void* d, const void* x_bf16, float* y, i64 n, i64 k, void* stream) {
+  if (n <= 0 || k <= 0) return 0;
+  int nb = (int)((k + 31) / 32);
+  size_t sm = (size_t)nb * 33 * 4;
+  if (sm > 200 * 1024) return (int)cudaErrorInvalidValue;
+  i64 nbatches = (n + GQ_RB - 1) / GQ_RB;
+  i64 blocks = (nbatches + 3) / 4;
+  if (blocks > (i64)WKB_SM_COUNT * 8) blocks = (i64)WKB_SM_COUNT * 8;
+  cudaError_t e = cudaFuncSetAttribute(gemv_q4_bf16x_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (e != cudaSuccess) return (int)e;
+  gemv_q4_bf16x_kernel<<<(int)blocks, 128, sm, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const u16*)x_bf16, k, y, n, nb);
+  return (int)cudaGetLastError();
+}
+
+int wkb_quantize_q(const float* x, u8* q, i64 rows, i64 k, int q4, void* stream) {
+  if (rows <= 0 || k <= 0) return 0;
+  i64 nb = (k + 31) / 32, total = rows * nb;
+  int grid = (int)((total + 127) / 128 < (i64)WKB_SM_COUNT * 16 ? (total + 127) / 128 : (i64)WKB_SM_COUNT * 16);
+  if (q4) quantize_kernel<true><<<grid, 128, 0, as_stream(stream)>>>(x, q, rows, k, nb);
+  else quantize_kernel<false><<<grid, 128, 0, as_stream(stream)>>>(x, q, rows, k, nb);
+  return (int)cudaGetLastError();
+}
+
+int wkb_dequant_int4(const u8* q, const float* scale, const float* zero_or_null, i64 group, float* out, i64 n,
+                     void* stream) {
+  if (n <= 0) return 0;
+  int grid = (int)((n + 255) / 256 < (i64)WKB_SM_COUNT * 16 ? (n + 255) / 256 : (i64)WKB_SM_COUNT * 16);
+  dequant_int4_kernel<<<grid, 256, 0, as_stream(stream)>>>(q, scale, zero_or_null, group, out, n);
+  return (int)cudaGetLastError();
+}
+}
