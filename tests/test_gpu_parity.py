@@ -23,9 +23,16 @@ def bits_equal(a, b):
 
 
 def assert_bits(a, b, what=""):
+    """Bit equality on every lane; a NaN lane must be a NaN lane (GPU arithmetic returns the
+    canonical NaN instead of propagating an operand's payload, so NaN payload bits are not compared)."""
     a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
     if a.tobytes() != b.tobytes():
-        bad = np.flatnonzero(a.view(np.uint32).ravel() != b.view(np.uint32).ravel())
+        diff = a.view(np.uint32).ravel() != b.view(np.uint32).ravel()
+        if a.dtype == np.float32:
+            diff &= ~(np.isnan(a.ravel()) & np.isnan(b.ravel()))
+        bad = np.flatnonzero(diff)
+        if bad.size == 0:
+            return
         raise AssertionError("%s: %d of %d lanes differ, first %d: %r vs %r" % (
             what, bad.size, a.size, bad[0], a.ravel()[bad[0]], b.ravel()[bad[0]]))
 

@@ -227,6 +227,29 @@ __device__ __host__ __forceinline__ u16 f32_to_bf16_bits(float x) {
 }
 __device__ __forceinline__ float bf16_bits_to_f32(u16 b) { return __uint_as_float(((uint32_t)b) << 16); }
 __device__ __forceinline__ float f16_bits_to_f32(u16 b) { return __half2float(__ushort_as_half(b)); }
+// f32 -> IEEE f16 bits, round to nearest even, in integer arithmetic (equals F16C / the `half`
+// crate).  Integer-only on purpose: a byte store fed directly by the hardware convert's 16-bit
+// result register came out with a wrong low byte on sm_100a builds.
+__device__ __forceinline__ u16 f32_to_f16_bits(float f) {
+  uint32_t x = __float_as_uint(f);
+  uint32_t sign = (x >> 16) & 0x8000u;
+  x &= 0x7fffffffu;
+  if (x > 0x7f800000u) return (u16)(sign | 0x7e00u | ((x >> 13) & 0x03ffu));
+  int e = (int)(x >> 23);
+  if (e >= 143) return (u16)(sign | 0x7c00u);
+  uint32_t m = (x & 0x007fffffu) | 0x00800000u;
+  if (e < 113) {
+    int sh = 126 - e;
+    if (sh >= 25) return (u16)sign;
+    uint32_t q = m >> sh, rem = m & ((1u << sh) - 1u), half = 1u << (sh - 1);
+    if (rem > half || (rem == half && (q & 1u))) ++q;
+    return (u16)(sign | q);
+  }
+  uint32_t q = ((uint32_t)(e - 112) << 10) | ((m & 0x007fffffu) >> 13);
+  uint32_t rem = m & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (q & 1u))) ++q;
+  return (u16)(sign | q);
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -236,9 +236,9 @@ __global__ void __launch_bounds__(128) quantize_kernel(const float* __restrict__
     }
     float dd = Q4 ? fdiv(mx, -8.0f) : fdiv(amax, 127.0f);
     float id = dd != 0.0f ? fdiv(1.0f, dd) : 0.0f;
-    u16 h = __half_as_ushort(__float2half_rn(dd));
-    o[0] = (u8)(h & 0xff);
-    o[1] = (u8)(h >> 8);
+    unsigned int h = (unsigned int)f32_to_f16_bits(dd);
+    o[0] = (u8)(h & 0xffu);
+    o[1] = (u8)((h >> 8) & 0xffu);
     if (Q4) {
       for (int j = 0; j < 16; ++j) {
         u8 nibs[2];
