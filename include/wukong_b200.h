@@ -186,6 +186,71 @@ int wkb_embed_tok_pos_bf16(float* out, const void* wte, const void* wpe, const i
 int wkb_rowargmax_i32(const float* x, int* out, int64_t rows, int64_t cols, void* stream);
 int wkb_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream);
 
+/* Paged KV cache (behaviour of crates/wukong_codegen_gpu/src/paged_kv.rs:84-151,428-628 and
+ * paged_attention.rs:395-534,1343-1410; kernels and HBM layout are this library's own).
+ * Per layer the K and V slabs are bf16 [num_pages][kv_heads][page_tokens][head_dim].
+ * block_table is [slots, max_blocks_per_seq] u32, padded; a "row" is one query token:
+ * row_slot[r] selects its table row, row_ctx[r] is how many leading keys it sees (0: zero output),
+ * row_pos[r] is where its own K/V land (< 0: inactive, nothing written).
+ * The decode call needs `scratch` of wkb_paged_attn_scratch_bytes(...) bytes; max_ctx bounds row_ctx.
+ * head_dim in {64, 128}; q_heads / kv_heads in {1, 2, 4} (and 8 at head_dim 128); out_dtype 0 f32, 1 bf16. */
+int64_t wkb_paged_attn_scratch_bytes(int64_t rows, int64_t q_heads, int64_t head_dim, int64_t max_ctx);
+int wkb_paged_attn_decode(const float* q, int64_t q_row_stride, const void* kcache, const void* vcache,
+                          const uint32_t* block_table, const int* row_slot, const int* row_ctx, void* out,
+                          int out_dtype, int64_t out_row_stride, int64_t rows, int64_t q_heads, int64_t kv_heads,
+                          int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq, int64_t max_ctx,
+                          float scale, float* scratch, void* stream);
+int wkb_paged_kv_append(const float* ksrc, const float* vsrc, int64_t src_row_stride, void* kcache, void* vcache,
+                        const uint32_t* block_table, const int* row_slot, const int* row_pos, int64_t rows,
+                        int64_t kv_heads, int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq,
+                        void* stream);
+
+/* Page allocator (host; behaviour of paged_kv.rs:428-628): LIFO free list handing out ascending
+ * pages on a fresh pool; append allocates only on a page boundary; -1 = out of pages, state unchanged. */
+void* wkb_blockmgr_new(int64_t num_blocks, int64_t block_size, int64_t num_slots, int64_t max_blocks_per_seq);
+void wkb_blockmgr_delete(void* h);
+int64_t wkb_blockmgr_append(void* h, int64_t slot, uint32_t* phys, int64_t* off);
+int64_t wkb_blockmgr_reserve(void* h, int64_t slot, int64_t tokens);
+void wkb_blockmgr_release(void* h, int64_t slot);
+int64_t wkb_blockmgr_can_grow(void* h, int64_t slot, int64_t tokens);
+int64_t wkb_blockmgr_free_blocks(void* h);
+int64_t wkb_blockmgr_used_blocks(void* h);
+int64_t wkb_blockmgr_context_len(void* h, int64_t slot);
+int64_t wkb_blockmgr_layout_epoch(void* h);
+int64_t wkb_blockmgr_locate(void* h, int64_t slot, int64_t pos, uint32_t* phys, int64_t* off);
+void wkb_blockmgr_flat_table(void* h, uint32_t* out);
+void wkb_blockmgr_ctx_lens(void* h, int32_t* out);
+
+/* Continuous-batching scheduler (host; behaviour of serving.rs:1346-1595): first-fit admission with
+ * a 64-request look-ahead, plan -> run -> commit per step.  plan_step returns the row count, 0 when
+ * idle, -1 when pages ran out (nothing changed), -3 when the previous step was not committed. */
+void* wkb_sched_new(int64_t bcap, int64_t num_blocks, int64_t block_size, int64_t max_blocks_per_seq,
+                    int64_t max_rows, int64_t prefill_chunk);
+void wkb_sched_delete(void* h);
+int64_t wkb_sched_enqueue(void* h, const int32_t* prompt, int64_t prompt_len, int64_t gen_len);
+int64_t wkb_sched_plan_step(void* h, int32_t* row_token, int32_t* row_pos, int32_t* row_slot, int32_t* row_ctx,
+                            int32_t* sample_row);
+int64_t wkb_sched_commit_step(void* h, const int32_t* sampled);
+void* wkb_sched_blockmgr(void* h);
+int64_t wkb_sched_num_active(void* h);
+int64_t wkb_sched_pending(void* h);
+int64_t wkb_sched_emitted(void* h);
+int64_t wkb_sched_admitted(void* h);
+int64_t wkb_sched_completed(void* h);
+int64_t wkb_sched_is_idle(void* h);
+int64_t wkb_sched_output_len(void* h, int64_t request);
+int64_t wkb_sched_output(void* h, int64_t request, int32_t* out, int64_t cap);
+
+/* Dense bf16 GEMM on tcgen05 tensor cores with TMEM accumulators and TMA-fed operands:
+ * C[M,N] = act(A[M,K].B[N,K]^T + bias[j]) (+ residual[i,j]); A, B bf16 with row pitches lda / ldb
+ * (elements, multiples of 8), C f32 or bf16 (c_bf16) with pitch ldc; fp32 accumulate; K % 8 == 0.
+ * Replaces the reference's wmma / wgmma NT families (ptx_wmma.rs, ptx_wgmma.rs) and their fused
+ * epilogues.  wkb_gemm_status returns 0 unless a bounded pipeline wait expired (then 1, 2 or 3). */
+int wkb_gemm_bf16_nt(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int c_bf16,
+                     int64_t m, int64_t n, int64_t k, const float* bias, int64_t act, const float* residual,
+                     int64_t ldr, void* stream);
+int wkb_gemm_status(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -232,7 +232,7 @@ void wko_attention_f32(const float* q, const float* k, const float* v, float* o,
 }
 
 // f64 full-softmax model of paged GQA decode attention.  Parity unpinned (property pinned).
-i64 wko_paged_attn_decode_f64(const float* q, const void* kcache, const void* vcache, int kv_dtype,
+i64 wko_paged_attn_decode_f64(const float* q, const void* kcache, const void* vcache, int kv_dtype, int layout,
                               const uint32_t* block_table, const int32_t* ctx_lens, float* o, i64 slots,
                               i64 q_heads, i64 kv_heads, i64 hd, i64 bs, i64 mbps, float scale) {
   if (slots < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || hd <= 0 || bs <= 0 || mbps < 0) return -1;
@@ -252,6 +252,8 @@ i64 wko_paged_attn_decode_f64(const float* q, const void* kcache, const void* vc
       double mx = -INFINITY;
       auto off = [&](size_t t) {
         size_t phys = block_table[b * (size_t)mbps + t / (size_t)bs];
+        if (layout == 1)  // [page][kv_head][token][dim]
+          return ((phys * (size_t)kv_heads + kvh) * (size_t)bs + t % (size_t)bs) * (size_t)hd;
         return ((phys * (size_t)bs + t % (size_t)bs) * (size_t)kv_heads + kvh) * (size_t)hd;
       };
       for (size_t t = 0; t < ctx; ++t) {

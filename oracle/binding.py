@@ -87,7 +87,7 @@ def _declare(L):
         "wko_attention_kv_batch_f32": (i64, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, vp, i64] + [i64] * 6 + [f32, i64]),
         "wko_kv_append_f32": (i64, [vp, i64, vp, i64, i64, i64]),
         "wko_attention_f32": (None, [vp, vp, vp, vp, i64, i64, f32, i64]),
-        "wko_paged_attn_decode_f64": (i64, [vp, vp, vp, C.c_int, vp, vp, vp] + [i64] * 6 + [f32]),
+        "wko_paged_attn_decode_f64": (i64, [vp, vp, vp, C.c_int, C.c_int, vp, vp, vp] + [i64] * 6 + [f32]),
         "wko_rope_f32": (None, [vp, vp, vp, i64, i64]),
         "wko_rope_pos_f32": (None, [vp, vp, vp, vp, i64, i64, i64]),
         "wko_embedding_f32": (None, [vp, vp, vp, i64, i64, i64]),
@@ -269,12 +269,13 @@ def attention(q, k, v, s, d, scale, causal):
     return o
 
 
-def paged_attn_decode(q, kcache, vcache, kv_dtype, block_table, ctx_lens, slots, q_heads, kv_heads, hd, bs, mbps, scale):
+def paged_attn_decode(q, kcache, vcache, kv_dtype, block_table, ctx_lens, slots, q_heads, kv_heads, hd, bs, mbps, scale,
+                      layout=0):
     q = f32a(q)
     bt = np.ascontiguousarray(block_table, np.uint32)
     cl = np.ascontiguousarray(ctx_lens, np.int32)
     o = np.empty(slots * q_heads * hd, np.float32)
-    st = lib().wko_paged_attn_decode_f64(p(q), p(kcache), p(vcache), kv_dtype, p(bt), p(cl), p(o), slots, q_heads,
+    st = lib().wko_paged_attn_decode_f64(p(q), p(kcache), p(vcache), kv_dtype, layout, p(bt), p(cl), p(o), slots, q_heads,
                                          kv_heads, hd, bs, mbps, scale)
     assert st == 0
     return o.reshape(slots, q_heads * hd)

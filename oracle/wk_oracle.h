@@ -97,8 +97,9 @@ void wko_attention_f32(const float* q, const float* k, const float* v, float* o,
 // Paged GQA decode attention, f64 accumulate, independent of the physical page layout.
 // Parity unpinned (property pinned): the reference gates this path only on a GPU, by tolerance
 // against an f64 model and by bit-identity across two physical layouts.
-// kv_dtype: 0 = f32, 1 = bf16 bits, 2 = f16 bits.  Cache layout [num_blocks, block_size, kv_heads, head_dim].
-i64 wko_paged_attn_decode_f64(const float* q, const void* kcache, const void* vcache, int kv_dtype,
+// kv_dtype: 0 = f32, 1 = bf16 bits, 2 = f16 bits.  layout 0: [num_blocks, block_size, kv_heads, head_dim]
+// (the reference's slab order, paged_kv.rs:139-151); layout 1: [num_blocks, kv_heads, block_size, head_dim].
+i64 wko_paged_attn_decode_f64(const float* q, const void* kcache, const void* vcache, int kv_dtype, int layout,
                               const uint32_t* block_table, const int32_t* ctx_lens, float* o, i64 slots,
                               i64 q_heads, i64 kv_heads, i64 head_dim, i64 block_size,
                               i64 max_blocks_per_seq, float scale);

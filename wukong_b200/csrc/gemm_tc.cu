@@ -1,0 +1,340 @@
+// Dense bf16 GEMM on the 5th-generation tensor cores: C[M,N] = epilogue(A[M,K] . B[N,K]^T).
+//
+// This is the B200 replacement for the reference's tensor-core GEMM families
+// (crates/wukong_codegen_gpu/src/ptx_wmma.rs `wmma_nt_bf16*` with fused bias / activation /
+// residual epilogues, and the sm_90a-only ptx_wgmma.rs which cannot load on sm_100): same operand
+// convention (both operands K-major, "NT"), fp32 accumulate, same epilogue menu
+// act(alpha-free A.B^T + bias[j]) (+ residual), act codes 0 identity / 1 relu / 2 gelu / 3 silu.
+//
+// Design (one 128 x 128 output tile per CTA, 192 threads):
+//   warp 0   one elected lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, no
+//            multicast) of a 128x64 A tile and a 128x64 B tile per stage into a 5-stage ring,
+//            completion counted on an mbarrier per stage;
+//   warp 1   allocates 128 TMEM columns, and one elected lane issues tcgen05.mma
+//            (cta_group::1, kind::f16, M=128 N=128 K=16) four times per stage straight from shared
+//            memory descriptors; tcgen05.commit releases the stage back to the producer and, after
+//            the last K step, signals the epilogue;
+//   warps 2-5 read the fp32 accumulator out of TMEM with tcgen05.ld (32 lanes x 32 columns per
+//            instruction; warp w owns lanes 32*(w%4)..), apply bias / activation / residual and
+//            store fp32 or bf16 rows.
+// Every mbarrier wait is bounded: on expiry the kernel records a code in `status`, stops issuing,
+// waits (bounded) for the copies it started, frees its TMEM and returns.
+// Ragged M / N / K are handled by TMA zero fill and masked stores; K % 8 == 0 is required (the
+// row pitch of a tensor map must be a multiple of 16 bytes).
+// Accumulation order is the tensor core's own, so results agree with the order-contract GEMM to
+// fp32 rounding (rtol 2e-2 is the stated bf16 bar; measured error is ~1e-6 relative to sum|a||b|).
+#include "common.cuh"
+#include "wkb_device.h"
+#include <cuda.h>
+#include <mutex>
+
+namespace wkb {
+
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 5, UMMA_K = 16;
+constexpr int TILE_A_BYTES = BM * BK * 2, TILE_B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 128;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded parity wait.  Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: start address (>>4) in bits
+// 0-13, leading byte offset (unused for swizzled K-major, encoded as 1) in 16-29, stride byte offset
+// = 1024 B (8 rows x 128 B) in 32-45, descriptor version 1 in 46-47, layout type 2 (SWIZZLE_128B)
+// in 61-63.
+__device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16: D = f32 (1 << 4), A = B = bf16 (1 << 7, 1 << 10), both K-major,
+// N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+struct GemmEpi {
+  const float* bias;       // [N] or null
+  const float* residual;   // [M, ldr] f32 or null (added after the activation)
+  i64 ldr;
+  int act;                 // 0 identity, 1 relu, 2 gelu, 3 silu
+  int out_bf16;            // 0: f32 C, 1: bf16 C
+};
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c,
+                    i64 ldc, int M, int N, int K, GemmEpi epi, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t bars = base + STAGES * STAGE_BYTES;  // full[STAGES], empty[STAGES], tmem_full, tmem slot
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t tmem_full_bar = bars + 8u * (2 * STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int kiters = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      bool ok = true;
+      for (int it = 0; it < kiters && ok; ++it) {
+        int s = it % STAGES;
+        uint32_t par = ((it / STAGES) & 1) ^ 1;
+        if (!mbar_wait(empty_bar(s), par)) { atomicExch(status, 1); ok = false; break; }
+        mbar_expect_tx(full_bar(s), STAGE_BYTES);
+        uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_A_BYTES;
+        tma_load_2d(sa, &map_a, full_bar(s), it * BK, m0);
+        tma_load_2d(sb, &map_b, full_bar(s), it * BK, n0);
+        issued = it + 1;
+      }
+      if (!ok) {
+        // wait (bounded) for the copies already started before the CTA may exit
+        for (int it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it)
+          mbar_wait(full_bar(it % STAGES), (it / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int it = 0; it < kiters; ++it) {
+        int s = it % STAGES;
+        if (!mbar_wait(full_bar(s), (it / STAGES) & 1)) { atomicExch(status, 2); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          uint64_t ad = make_sdesc(sa + k * UMMA_K * 2), bd = make_sdesc(sb + k * UMMA_K * 2);
+          umma_bf16(tmem_base, ad, bd, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+      }
+      if (ok) umma_commit(tmem_full_bar);
+    }
+  } else {
+    // epilogue warps 2..5: TMEM lane quarter (warp % 4)
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(tmem_full_bar, 0);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) {
+      if (lane == 0) atomicExch(status, 3);
+    } else {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < M) {
+          const int ncols = min(32, N - (n0 + c0));
+          if (ncols > 0) {
+            float v[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              float y = __uint_as_float(r[e]);
+              int col = n0 + c0 + e;
+              if (e < ncols) {
+                if (epi.bias) y += epi.bias[col];
+                y = act_apply(epi.act, y);
+                if (epi.residual) y += epi.residual[(i64)row * epi.ldr + col];
+              }
+              v[e] = y;
+            }
+            if (epi.out_bf16) {
+              u16* cp = reinterpret_cast<u16*>(c) + (i64)row * ldc + n0 + c0;
+              if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+                  uint4 pk;
+                  pk.x = (uint32_t)f32_to_bf16_bits(v[e]) | ((uint32_t)f32_to_bf16_bits(v[e + 1]) << 16);
+                  pk.y = (uint32_t)f32_to_bf16_bits(v[e + 2]) | ((uint32_t)f32_to_bf16_bits(v[e + 3]) << 16);
+                  pk.z = (uint32_t)f32_to_bf16_bits(v[e + 4]) | ((uint32_t)f32_to_bf16_bits(v[e + 5]) << 16);
+                  pk.w = (uint32_t)f32_to_bf16_bits(v[e + 6]) | ((uint32_t)f32_to_bf16_bits(v[e + 7]) << 16);
+                  *reinterpret_cast<uint4*>(cp + e) = pk;
+                }
+              } else {
+                for (int e = 0; e < ncols; ++e) cp[e] = f32_to_bf16_bits(v[e]);
+              }
+            } else {
+              float* cp = reinterpret_cast<float*>(c) + (i64)row * ldc + n0 + c0;
+              if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(cp + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+              } else {
+                for (int e = 0; e < ncols; ++e) cp[e] = v[e];
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side: tensor maps through the driver entry point (no link-time libcuda dependency) ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, k] with row pitch ld elements; box = [BK, box_rows]; 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, i64 rows, i64 k, i64 ld, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+static int* gemm_status_word() {
+  // one device word per device for the bounded-wait status; allocated at first use
+  static int* words[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!words[dev]) {
+    int* p = nullptr;
+    if (cudaMalloc((void**)&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+    words[dev] = p;
+  }
+  return words[dev];
+}
+
+}  // namespace wkb
+
+using namespace wkb;
+
+extern "C" {
+
+int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i64 ldc, int c_bf16, i64 m, i64 n, i64 k,
+                     const float* bias, i64 act, const float* residual, i64 ldr, void* stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if (k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)a) | ((uintptr_t)b)) & 15) return (int)cudaErrorMisalignedAddress;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, m, k, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, b, n, k, ldb, BN);
+  if (rc) return rc;
+  int* status = gemm_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63] = true;
+  }
+  GemmEpi epi{bias, residual, ldr, (int)act, c_bf16};
+  dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
+  gemm_bf16_tc_kernel<<<grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
+  return (int)cudaGetLastError();
+}
+
+// Reads (and clears) the bounded-wait status of the tensor-core GEMM on the current device:
+// 0 = every wait completed; 1 / 2 / 3 = the producer / MMA / epilogue wait ran out.  Synchronises.
+int wkb_gemm_status(void) {
+  int* status = gemm_status_word();
+  if (!status) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v) cudaMemset(status, 0, sizeof(int));
+  return v;
+}
+}

@@ -80,3 +80,56 @@ def rowargmax(x, out=None):
     out = torch.empty(rows, dtype=torch.int32, device=x.device) if out is None else out
     check(lib().wkb_rowargmax_i32(_p(x), _p(out), rows, cols, _s()), "wkb_rowargmax_i32")
     return out
+
+
+def gemm_bf16_nt(a, b, bias=None, act=0, residual=None, out_dtype=torch.float32, out=None):
+    """C = act(a @ b.T + bias) (+ residual) on the tcgen05 tensor cores; a [M,K], b [N,K] bf16."""
+    m, k = a.shape
+    n = b.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    ldr = residual.stride(0) if residual is not None else 0
+    check(lib().wkb_gemm_bf16_nt(_p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0),
+                                 int(out.dtype == torch.bfloat16), m, n, k, _p(bias), act, _p(residual), ldr, _s()),
+          "wkb_gemm_bf16_nt")
+    return out
+
+
+def gemm_status():
+    return lib().wkb_gemm_status()
+
+
+def sgemm_contract(a, b, c, m, k, n, beta=0, at=0, bt=1, bias=None, act=0, alpha=1.0, has_epi=0):
+    check(lib().wkb_sgemm_contract(_p(a), _DT[a.dtype], _p(b), _DT[b.dtype], _p(c), m, k, n, beta, at, bt, _p(bias), act,
+                                   alpha, has_epi, _s()), "wkb_sgemm_contract")
+    return c
+
+
+class PagedKV:
+    """Per-layer K/V slabs, bf16 [layers][pages][kv_heads][page_tokens][head_dim]."""
+
+    def __init__(self, layers, num_pages, kv_heads, head_dim, page_tokens=16, device="cuda"):
+        self.layers, self.num_pages, self.kv_heads, self.head_dim, self.page_tokens = layers, num_pages, kv_heads, head_dim, page_tokens
+        shape = (layers, num_pages, kv_heads, page_tokens, head_dim)
+        self.k = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        self.v = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+
+
+def paged_kv_append(kv, layer, ksrc, vsrc, src_row_stride, block_table, row_slot, row_pos, rows, mbps):
+    check(lib().wkb_paged_kv_append(_p(ksrc), _p(vsrc), src_row_stride, _p(kv.k[layer]), _p(kv.v[layer]), _p(block_table),
+                                    _p(row_slot), _p(row_pos), rows, kv.kv_heads, kv.head_dim, kv.page_tokens, mbps, _s()),
+          "wkb_paged_kv_append")
+
+
+def paged_attn_scratch(rows, q_heads, head_dim, max_ctx, device="cuda"):
+    n = lib().wkb_paged_attn_scratch_bytes(rows, q_heads, head_dim, max_ctx)
+    return torch.empty(n // 4, dtype=torch.float32, device=device)
+
+
+def paged_attn_decode(q, q_row_stride, kv, layer, block_table, row_slot, row_ctx, out, rows, q_heads, mbps, max_ctx, scale,
+                      scratch):
+    check(lib().wkb_paged_attn_decode(_p(q), q_row_stride, _p(kv.k[layer]), _p(kv.v[layer]), _p(block_table), _p(row_slot),
+                                      _p(row_ctx), _p(out), int(out.dtype == torch.bfloat16), out.stride(0), rows, q_heads,
+                                      kv.kv_heads, kv.head_dim, kv.page_tokens, mbps, max_ctx, scale, _p(scratch), _s()),
+          "wkb_paged_attn_decode")
+    return out
