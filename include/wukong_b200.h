@@ -184,6 +184,8 @@ int wkb_embedding_f32(float* out, const float* weight, const int* ids, int64_t t
 /* out[r] = wte[ids[r]] + wpe[pos[r]] (bf16 tables, f32 out): the GPT-2 input embedding. */
 int wkb_embed_tok_pos_bf16(float* out, const void* wte, const void* wpe, const int* ids, const int* pos, int64_t t, int64_t h, int64_t v, int64_t npos, void* stream);
 int wkb_rowargmax_i32(const float* x, int* out, int64_t rows, int64_t cols, void* stream);
+/* Same with a row pitch ld >= cols (padded logits). */
+int wkb_rowargmax_strided_i32(const float* x, int* out, int64_t rows, int64_t cols, int64_t ld, void* stream);
 int wkb_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream);
 
 /* Paged KV cache (behaviour of crates/wukong_codegen_gpu/src/paged_kv.rs:84-151,428-628 and

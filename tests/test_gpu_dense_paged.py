@@ -1,0 +1,159 @@
+"""GPU parity of the half-precision decode kernels: the tcgen05 GEMM, the fast norms, the paged KV
+append / decode attention, against the CPU oracle in the same precision recipe."""
+import math
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import torch
+    from wukong_b200 import _lib, device
+    _lib.require_gpu()
+    return device
+
+
+def bf16_t(x_np, orc):
+    import torch
+    return torch.from_numpy(orc.to_bf16_bits(x_np).view(np.int16).reshape(x_np.shape)).cuda().view(torch.bfloat16)
+
+
+def test_gemm_tc_matches_order_contract_gemm(dev, orc):
+    """rtol 2e-2 on logits is the stated bf16 bar; the tensor-core GEMM differs from the
+    order-contract GEMM only by fp32 summation order, so the test holds it to 1e-5 * sum|a||b|."""
+    import torch
+    rng = np.random.default_rng(0)
+    for (m, n, k) in [(1, 1, 8), (128, 128, 64), (130, 70, 200), (64, 768, 768), (512, 2304, 768), (33, 1000, 3072),
+                      (257, 129, 72)]:
+        a = rng.standard_normal((m, k)).astype(np.float32)
+        b = rng.standard_normal((n, k)).astype(np.float32)
+        bias = rng.standard_normal(n).astype(np.float32)
+        res = rng.standard_normal((m, n)).astype(np.float32)
+        ab, bb = orc.to_bf16_bits(a), orc.to_bf16_bits(b)
+        ref = orc.sgemm_half_nt(ab, bb, m, k, n)
+        at, bt = bf16_t(a, orc), bf16_t(b, orc)
+        c = dev.gemm_bf16_nt(at, bt).cpu().numpy()
+        bound = 1e-5 * (np.abs(orc.from_bf16_bits(ab)).reshape(m, k) @ np.abs(orc.from_bf16_bits(bb)).reshape(n, k).T) + 1e-6
+        assert (np.abs(c - ref) <= bound).all(), (m, n, k, np.abs(c - ref).max())
+        assert np.allclose(c, ref, rtol=2e-2, atol=1e-3)
+        for act in (0, 1, 2, 3):
+            refe = orc.sgemm_half_nt(ab, bb, m, k, n, bias=bias, act=act) + res
+            ce = dev.gemm_bf16_nt(at, bt, bias=torch.from_numpy(bias).cuda(), act=act, residual=torch.from_numpy(res).cuda())
+            # the activations are at most 1.13-Lipschitz, so the pre-activation bound carries over
+            assert (np.abs(ce.cpu().numpy() - refe) <= 1.2 * bound + 1e-5).all(), (m, n, k, act)
+        cb = dev.gemm_bf16_nt(at, bt, bias=torch.from_numpy(bias).cuda(), act=2, out_dtype=torch.bfloat16)
+        refb = orc.sgemm_half_nt(ab, bb, m, k, n, bias=bias, act=2)
+        got = cb.float().cpu().numpy()
+        assert np.allclose(got, refb, rtol=2e-2, atol=2e-2)
+    assert dev.gemm_status() == 0
+    # linearity at a size the oracle does not run: C(a1 + a2) == C(a1) + C(a2) for exactly representable inputs
+    a1 = torch.randint(-4, 5, (1024, 4096), device="cuda").to(torch.bfloat16)
+    a2 = torch.randint(-4, 5, (1024, 4096), device="cuda").to(torch.bfloat16)
+    b = torch.randint(-4, 5, (2048, 4096), device="cuda").to(torch.bfloat16)
+    c12 = dev.gemm_bf16_nt((a1 + a2), b)
+    assert torch.equal(c12, dev.gemm_bf16_nt(a1, b) + dev.gemm_bf16_nt(a2, b))  # integers: exact in fp32
+    assert torch.equal(c12, (a1 + a2).float() @ b.float().T)
+    assert dev.gemm_status() == 0
+
+
+def test_norm_fast_matches_oracle_recipe(dev, orc):
+    """bf16 rows: widen -> the oracle's fp32 norm -> round once.  The fast kernel reduces in a
+    different order, so outputs may differ by one bf16 ulp on a few lanes: rtol 2e-2 (the bf16 bar)."""
+    import torch
+    rng = np.random.default_rng(1)
+    for rows, cols in [(7, 768), (33, 4096), (5, 8), (3, 8192), (64, 1024)]:
+        x = rng.standard_normal((rows, cols)).astype(np.float32) * 2
+        g = rng.standard_normal(cols).astype(np.float32)
+        b = rng.standard_normal(cols).astype(np.float32)
+        xb = orc.from_bf16_bits(orc.to_bf16_bits(x)).reshape(rows, cols)
+        xt = bf16_t(x, orc)
+        gt, btt = torch.from_numpy(g).cuda(), torch.from_numpy(b).cuda()
+        for op, ref in ((0, orc.norm(xb, 0)), (1, orc.norm_affine(xb, g, b, 1, 1e-5)), (2, orc.norm_affine(xb, g, None, 2, 1e-5))):
+            got = dev.norm_fast(xt, op, 1e-5, gt if op else None, btt if op == 1 else None).float().cpu().numpy()
+            want = orc.from_bf16_bits(orc.to_bf16_bits(ref)).reshape(rows, cols)
+            assert np.allclose(got, want, rtol=2e-2, atol=1e-3), (rows, cols, op, np.abs(got - want).max())
+        # f32 in, f32 out agrees with the exact kernel to fp32 rounding
+        xf = torch.from_numpy(x).cuda()
+        got = dev.norm_fast(xf, 1, 1e-5, gt, btt).cpu().numpy()
+        assert np.allclose(got, orc.norm_affine(x, g, b, 1, 1e-5), rtol=1e-4, atol=1e-5)
+
+
+def _build_paged(rng, dev, orc, ctx, q_heads, kv_heads, hd, page, nblk, mbps, perm_seed):
+    import torch
+    slots = len(ctx)
+    kflat = [rng.standard_normal((c, kv_heads, hd)).astype(np.float32) for c in ctx]
+    vflat = [rng.standard_normal((c, kv_heads, hd)).astype(np.float32) for c in ctx]
+    return kflat, vflat
+
+
+def test_paged_append_and_decode(dev, orc):
+    import torch
+    from wukong_b200.paged import BlockManager
+    for (q_heads, kv_heads, hd, ctx) in [(12, 12, 64, [5, 300, 0, 17, 640, 256, 257]), (32, 8, 128, [128, 1000, 33, 0]),
+                                         (8, 4, 64, [31, 32, 33, 511]), (8, 2, 128, [600, 1])]:
+        rng = np.random.default_rng(2)
+        slots, page, mbps = len(ctx), 16, 64
+        nblk = sum((c + page - 1) // page for c in ctx) + 7
+        kflat = [rng.standard_normal((c, kv_heads * hd)).astype(np.float32) for c in ctx]
+        vflat = [rng.standard_normal((c, kv_heads * hd)).astype(np.float32) for c in ctx]
+        q = rng.standard_normal((slots, q_heads * hd)).astype(np.float32)
+        scale = 1.0 / math.sqrt(hd)
+        outs = []
+        for perm_seed in (0, 1):
+            # two physical layouts of the same logical history: pages handed out in different orders
+            order = np.random.default_rng(perm_seed).permutation(slots)
+            mgr = BlockManager(nblk, page, slots, mbps)
+            if perm_seed:
+                mgr.reserve(slots - 1, 16 * 3); mgr.free(slots - 1)   # scramble the free list
+            for s in order:
+                if ctx[s]:
+                    mgr.reserve(int(s), int(ctx[s]))
+            bt = torch.from_numpy(mgr.flat_block_table().astype(np.int64)).to(torch.int32).cuda()
+            kv = dev.PagedKV(1, nblk, kv_heads, hd, page)
+            kv.k.fill_(float("nan")); kv.v.fill_(float("nan"))
+            # append every token through the kernel, one launch per sequence (rows = its tokens)
+            for s in range(slots):
+                if not ctx[s]:
+                    continue
+                src = torch.from_numpy(np.concatenate([kflat[s], vflat[s]], 1)).cuda()
+                row_slot = torch.full((ctx[s],), s, dtype=torch.int32, device="cuda")
+                row_pos = torch.arange(ctx[s], dtype=torch.int32, device="cuda")
+                dev.paged_kv_append(kv, 0, src, src[:, kv_heads * hd:], src.stride(0), bt, row_slot, row_pos, ctx[s], mbps)
+            # an inactive row writes nothing
+            junk = torch.full((1, 2 * kv_heads * hd), 1e9, device="cuda")
+            dev.paged_kv_append(kv, 0, junk, junk[:, kv_heads * hd:], junk.stride(0), bt, torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                torch.full((1,), -1, dtype=torch.int32, device="cuda"), 1, mbps)
+            row_slot = torch.arange(slots, dtype=torch.int32, device="cuda")
+            row_ctx = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+            scratch = dev.paged_attn_scratch(slots, q_heads, hd, max(ctx))
+            out = torch.empty((slots, q_heads * hd), dtype=torch.float32, device="cuda")
+            dev.paged_attn_decode(torch.from_numpy(q).cuda(), q_heads * hd, kv, 0, bt, row_slot, row_ctx, out, slots, q_heads, mbps,
+                                  max(ctx), scale, scratch)
+            outs.append(out.cpu().numpy())
+            # block-table gather is bit-exact: every cached element is the bf16 rounding of its source
+            kc = kv.k[0].view(torch.int16).cpu().numpy().view(np.uint16)
+            table = mgr.flat_block_table()
+            for s in range(slots):
+                for t in (0, ctx[s] // 2, ctx[s] - 1):
+                    if ctx[s] == 0:
+                        continue
+                    page_id = table[s, t // page]
+                    got = kc[page_id, :, t % page, :].reshape(-1)
+                    assert np.array_equal(got, orc.to_bf16_bits(kflat[s][t]))
+            ref = orc.paged_attn_decode(q, kv.k[0].view(torch.int16).cpu().numpy().view(np.uint16),
+                                        kv.v[0].view(torch.int16).cpu().numpy().view(np.uint16), 1, table, ctx, slots, q_heads,
+                                        kv_heads, hd, page, mbps, scale, layout=1)
+            assert np.allclose(outs[-1], ref, rtol=1e-4, atol=1e-5), (q_heads, kv_heads, hd, np.abs(outs[-1] - ref).max())
+        assert outs[0].tobytes() == outs[1].tobytes(), "decode output depends on the physical page layout"
+        for s in range(slots):
+            if ctx[s] == 0:
+                assert (outs[0][s] == 0).all()
+        assert not np.isnan(outs[0]).any()
+        # bf16 output path
+        outb = torch.empty((slots, q_heads * hd), dtype=torch.bfloat16, device="cuda")
+        dev.paged_attn_decode(torch.from_numpy(q).cuda(), q_heads * hd, kv, 0, bt, row_slot, row_ctx, outb, slots, q_heads, mbps,
+                              max(ctx), scale, scratch)
+        assert np.array_equal(outb.view(torch.int16).cpu().numpy().view(np.uint16), orc.to_bf16_bits(outs[1]).reshape(slots, -1))

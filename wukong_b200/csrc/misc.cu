@@ -77,11 +77,11 @@ __global__ void __launch_bounds__(256) embed_tok_pos_kernel(float* __restrict__ 
 // One CTA per row.  Candidates fold with (strictly greater) or (equal and lower index); NaNs past
 // column 0 never enter; a NaN at column 0 wins outright.
 __global__ void __launch_bounds__(256) rowargmax_kernel(const float* __restrict__ x, int* __restrict__ out, i64 rows,
-                                                        i64 cols) {
+                                                        i64 cols, i64 ld) {
   __shared__ float sv[8];
   __shared__ long long si[8];
   for (i64 r = blockIdx.x; r < rows; r += gridDim.x) {
-    const float* row = x + r * cols;
+    const float* row = x + r * ld;
     float bv = -INFINITY;
     i64 bi = cols;  // "no candidate yet"
     for (i64 j = threadIdx.x; j < cols; j += blockDim.x) {
@@ -167,7 +167,14 @@ int wkb_embed_tok_pos_bf16(float* out, const void* wte, const void* wpe, const i
 int wkb_rowargmax_i32(const float* x, int* out, i64 rows, i64 cols, void* stream) {
   if (rows <= 0 || cols <= 0) return 0;
   int grid = (int)(rows < (i64)WKB_SM_COUNT * 8 ? rows : (i64)WKB_SM_COUNT * 8);
-  rowargmax_kernel<<<grid, 256, 0, as_stream(stream)>>>(x, out, rows, cols);
+  rowargmax_kernel<<<grid, 256, 0, as_stream(stream)>>>(x, out, rows, cols, cols);
+  return (int)cudaGetLastError();
+}
+
+int wkb_rowargmax_strided_i32(const float* x, int* out, i64 rows, i64 cols, i64 ld, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  int grid = (int)(rows < (i64)WKB_SM_COUNT * 8 ? rows : (i64)WKB_SM_COUNT * 8);
+  rowargmax_kernel<<<grid, 256, 0, as_stream(stream)>>>(x, out, rows, cols, ld);
   return (int)cudaGetLastError();
 }
 

@@ -40,7 +40,7 @@ struct PagedGeo {
   i64 q_row_stride;
 };
 
-// scratch layout: [row][q_head][chunk] x (HD + 2) floats: acc[HD], m, l
+// scratch layout: [row][q_head][chunk] x (HD + 4) floats: acc[HD], m, l, 2 pad (keeps records 16-byte aligned)
 template <int HD, int G>
 __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
     const float* __restrict__ q, const uint4* __restrict__ kcache, const uint4* __restrict__ vcache,
@@ -61,8 +61,8 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   const int row = (int)(unit / ((i64)g.max_chunks * g.kv_heads));
   const int ctx = row_ctx[row];
   const int t0 = chunk * PA_CHUNK;
-  float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 2);
-  const i64 head_stride = (i64)g.max_chunks * (HD + 2);
+  float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
+  const i64 head_stride = (i64)g.max_chunks * (HD + 4);
   if (t0 >= ctx) {  // nothing visible in this chunk: mark it empty
     if (lane < G) { float* s = sbase + lane * head_stride; s[HD] = -INFINITY; s[HD + 1] = 0.0f; }
     return;
@@ -192,13 +192,13 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const float* __re
   int ctx = row_ctx[row];
   int nch = ctx <= 0 ? 0 : (ctx + PA_CHUNK - 1) / PA_CHUNK;
   if (nch > max_chunks) nch = max_chunks;
-  const float* s = scratch + rh * (i64)max_chunks * (HD + 2);
+  const float* s = scratch + rh * (i64)max_chunks * (HD + 4);
   float mm = -INFINITY;
-  for (int c = 0; c < nch; ++c) mm = fmaxf(mm, s[(i64)c * (HD + 2) + HD]);
+  for (int c = 0; c < nch; ++c) mm = fmaxf(mm, s[(i64)c * (HD + 4) + HD]);
   float lsum = 0.0f;
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int c = 0; c < nch; ++c) {
-    const float* sc = s + (i64)c * (HD + 2);
+    const float* sc = s + (i64)c * (HD + 4);
     float w = exp2f(sc[HD] - mm);
     lsum = fmaf(sc[HD + 1], w, lsum);
     float4 a = *reinterpret_cast<const float4*>(sc + dq * 4);
@@ -273,7 +273,7 @@ extern "C" {
 i64 wkb_paged_attn_scratch_bytes(i64 rows, i64 q_heads, i64 head_dim, i64 max_ctx) {
   i64 chunks = (max_ctx + PA_CHUNK - 1) / PA_CHUNK;
   if (chunks < 1) chunks = 1;
-  return rows * q_heads * chunks * (head_dim + 2) * 4;
+  return rows * q_heads * chunks * (head_dim + 4) * 4;
 }
 
 int wkb_paged_attn_decode(const float* q, i64 q_row_stride, const void* kcache, const void* vcache,
@@ -283,7 +283,9 @@ int wkb_paged_attn_decode(const float* q, i64 q_row_stride, const void* kcache, 
                           void* stream) {
   if (rows <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || page_tokens <= 0) return (int)cudaErrorInvalidValue;
-  if ((q_row_stride % 4) != 0 || (((uintptr_t)q) & 15) != 0) return (int)cudaErrorMisalignedAddress;
+  if ((q_row_stride % 4) != 0 || ((((uintptr_t)q) | ((uintptr_t)scratch) | ((uintptr_t)kcache) | ((uintptr_t)vcache)) & 15) != 0)
+    return (int)cudaErrorMisalignedAddress;
+  if (out_row_stride % 4 != 0 || (((uintptr_t)out) & 15) != 0) return (int)cudaErrorMisalignedAddress;
   i64 chunks = (max_ctx + PA_CHUNK - 1) / PA_CHUNK;
   if (chunks < 1) chunks = 1;
   PagedGeo g{(int)rows, (int)q_heads, (int)kv_heads, (int)page_tokens, (int)max_blocks_per_seq, (int)chunks, q_row_stride};

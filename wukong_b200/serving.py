@@ -1,0 +1,223 @@
+"""GPT-2-shape decode serving on device-resident tensors: weights, paged KV, the per-step forward
+over a flat batch of rows, and the engine that ties the scheduler to it.
+
+The structure follows the reference's Rust-launched serving stack (crates/wukong_codegen_gpu/src/
+serving.rs: `DecodeLayer::forward_step_on` :684-937, `DecodeModel` :942, `Scheduler::step_graphed`
+:1536-1575) -- norm -> QKV GEMM -> KV append through the block table -> paged decode attention ->
+output projection with fused residual -> norm -> MLP GEMMs with fused activation / residual, the
+whole step replayed as one CUDA graph -- widened to a real model: token + position embedding in
+front, final norm, tied LM head and greedy arg-max behind (the .wk program this mirrors is
+examples/gpt2_generate.wk:137-255 of the reference).
+
+Precision recipe (what "bf16" means here, and what the CPU oracle model in the tests restates):
+weights and KV cache bf16; residual stream fp32; every GEMM bf16 x bf16 with fp32 accumulation;
+norm outputs, attention outputs and the MLP hidden rounded once to bf16; logits fp32.
+torch is used for device memory, streams and graph capture only; every kernel is this library's.
+"""
+import math
+
+import numpy as np
+import torch
+
+from . import device as dev
+from ._lib import lib, check
+from .paged import Scheduler
+
+
+class GPT2Config:
+    def __init__(self, n_layer=12, d_model=768, n_head=12, d_ff=3072, vocab=50257, n_pos=1024, eps=1e-5):
+        self.n_layer, self.d_model, self.n_head, self.d_ff, self.vocab, self.n_pos, self.eps = n_layer, d_model, n_head, d_ff, vocab, n_pos, eps
+        self.head_dim = d_model // n_head
+        assert self.head_dim in (64, 128) and d_model % 8 == 0 and d_ff % 8 == 0
+
+    def n_params(self):
+        d, f = self.d_model, self.d_ff
+        return self.vocab * d + self.n_pos * d + self.n_layer * (4 * d * d + 2 * d * f + 9 * d + f) + 2 * d
+
+
+def _bf16_bits(x):
+    """f32 -> bf16 bits, round to nearest even (values here are finite)."""
+    b = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((b + np.uint32(0x7FFF) + ((b >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
+def synth_weights(cfg, seed=0):
+    """Seeded stand-in for a checkpoint: every matrix, bias and embedding ~N(0, 0.02), LayerNorm
+    gamma = 1, beta = 0.  Returns host arrays: matrices as bf16 bits (uint16), vectors as f32."""
+    rng = np.random.default_rng(seed)
+    n = lambda *shape: (rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02))
+    d, f = cfg.d_model, cfg.d_ff
+    w = {"wte": _bf16_bits(n(cfg.vocab, d)), "wpe": _bf16_bits(n(cfg.n_pos, d)), "layers": [],
+         "lnf_g": np.ones(d, np.float32), "lnf_b": np.zeros(d, np.float32)}
+    for _ in range(cfg.n_layer):
+        w["layers"].append({
+            "ln1_g": np.ones(d, np.float32), "ln1_b": np.zeros(d, np.float32),
+            "w_qkv": _bf16_bits(n(3 * d, d)), "b_qkv": n(3 * d),
+            "w_o": _bf16_bits(n(d, d)), "b_o": n(d),
+            "ln2_g": np.ones(d, np.float32), "ln2_b": np.zeros(d, np.float32),
+            "w_fc": _bf16_bits(n(f, d)), "b_fc": n(f),
+            "w_proj": _bf16_bits(n(d, f)), "b_proj": n(d),
+        })
+    return w
+
+
+def _to_dev(a, device):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if a.dtype == np.uint16:
+        t = torch.from_numpy(np.ascontiguousarray(a).view(np.int16))
+        return t.to(device).view(torch.bfloat16)
+    return t.to(device)
+
+
+class DecodeModel:
+    """Device-resident GPT-2-shape model over a paged KV cache; `forward(n)` runs the first n rows of
+    the row buffers (token, position, slot, visible keys) and leaves arg-max tokens in `next_tok`."""
+
+    def __init__(self, cfg, weights, bcap, num_pages, max_blocks_per_seq, max_rows=None, page_tokens=16, device="cuda"):
+        self.cfg, self.bcap, self.device = cfg, bcap, device
+        self.max_rows = max_rows or bcap
+        self.page_tokens, self.mbps = page_tokens, max_blocks_per_seq
+        self.max_ctx = max_blocks_per_seq * page_tokens
+        d, f, R = cfg.d_model, cfg.d_ff, self.max_rows
+        self.w = {k: _to_dev(v, device) for k, v in weights.items() if k != "layers"}
+        self.layers = [{k: _to_dev(v, device) for k, v in lw.items()} for lw in weights["layers"]]
+        self.kv = dev.PagedKV(cfg.n_layer, num_pages, cfg.n_head, cfg.head_dim, page_tokens, device)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.row_token, self.row_pos = torch.zeros(R, **i32), torch.full((R,), -1, **i32)
+        self.row_slot, self.row_ctx = torch.zeros(R, **i32), torch.zeros(R, **i32)
+        self.sample_rows = torch.zeros(R, **i32)
+        self.block_table = torch.zeros((bcap, max_blocks_per_seq), **i32)
+        self.x = torch.zeros((R, d), dtype=torch.float32, device=device)
+        self.h = torch.zeros((R, d), dtype=torch.bfloat16, device=device)
+        self.qkv = torch.zeros((R, 3 * d), dtype=torch.float32, device=device)
+        self.att = torch.zeros((R, d), dtype=torch.bfloat16, device=device)
+        self.ff = torch.zeros((R, f), dtype=torch.bfloat16, device=device)
+        self.xs = torch.zeros((bcap, d), dtype=torch.float32, device=device)
+        self.hs = torch.zeros((bcap, d), dtype=torch.bfloat16, device=device)
+        self.ldl = (cfg.vocab + 7) // 8 * 8                      # logits pitch, 16-byte aligned rows
+        self.logits = torch.zeros((bcap, self.ldl), dtype=torch.float32, device=device)
+        self.next_tok = torch.zeros(bcap, **i32)
+        self.scratch = dev.paged_attn_scratch(R, cfg.n_head, cfg.head_dim, self.max_ctx, device)
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.launches_per_forward = 0
+
+    # -- one forward over the first n rows; n_sample rows (indices in sample_rows) reach the LM head
+    def forward(self, n, n_sample):
+        cfg, L, s = self.cfg, lib(), torch.cuda.current_stream().cuda_stream
+        d, f, p = cfg.d_model, cfg.d_ff, (lambda t: t.data_ptr())
+        launches = 0
+        check(L.wkb_embed_tok_pos_bf16(p(self.x), p(self.w["wte"]), p(self.w["wpe"]), p(self.row_token), p(self.row_pos), n, d,
+                                       cfg.vocab, cfg.n_pos, s), "embed")
+        launches += 1
+        for li, lw in enumerate(self.layers):
+            check(L.wkb_norm_fast(p(self.x), 0, p(self.h), 1, p(lw["ln1_g"]), p(lw["ln1_b"]), n, d, cfg.eps, 1, s), "ln1")
+            check(L.wkb_gemm_bf16_nt(p(self.h), d, p(lw["w_qkv"]), d, p(self.qkv), 3 * d, 0, n, 3 * d, d, p(lw["b_qkv"]), 0, None, 0, s), "qkv")
+            check(L.wkb_paged_kv_append(p(self.qkv) + 4 * d, p(self.qkv) + 8 * d, 3 * d, p(self.kv.k[li]), p(self.kv.v[li]),
+                                        p(self.block_table), p(self.row_slot), p(self.row_pos), n, cfg.n_head, cfg.head_dim,
+                                        self.page_tokens, self.mbps, s), "kv_append")
+            check(L.wkb_paged_attn_decode(p(self.qkv), 3 * d, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
+                                          p(self.row_ctx), p(self.att), 1, d, n, cfg.n_head, cfg.n_head, cfg.head_dim, self.page_tokens,
+                                          self.mbps, self.max_ctx, self.scale, p(self.scratch), s), "attn")
+            check(L.wkb_gemm_bf16_nt(p(self.att), d, p(lw["w_o"]), d, p(self.x), d, 0, n, d, d, p(lw["b_o"]), 0, p(self.x), d, s), "o_proj")
+            check(L.wkb_norm_fast(p(self.x), 0, p(self.h), 1, p(lw["ln2_g"]), p(lw["ln2_b"]), n, d, cfg.eps, 1, s), "ln2")
+            check(L.wkb_gemm_bf16_nt(p(self.h), d, p(lw["w_fc"]), d, p(self.ff), f, 1, n, f, d, p(lw["b_fc"]), 2, None, 0, s), "fc")
+            check(L.wkb_gemm_bf16_nt(p(self.ff), f, p(lw["w_proj"]), f, p(self.x), d, 0, n, d, f, p(lw["b_proj"]), 0, p(self.x), d, s), "proj")
+            launches += 9
+        # LM head on the sampled rows only: gather -> final norm -> tied head -> arg-max
+        check(L.wkb_embedding_f32(p(self.xs), p(self.x), p(self.sample_rows), n_sample, d, n, s), "gather")
+        check(L.wkb_norm_fast(p(self.xs), 0, p(self.hs), 1, p(self.w["lnf_g"]), p(self.w["lnf_b"]), n_sample, d, cfg.eps, 1, s), "lnf")
+        check(L.wkb_gemm_bf16_nt(p(self.hs), d, p(self.w["wte"]), d, p(self.logits), self.ldl, 0, n_sample, cfg.vocab, d, None, 0, None, 0, s), "lm_head")
+        check(L.wkb_rowargmax_strided_i32(p(self.logits), p(self.next_tok), n_sample, cfg.vocab, self.ldl, s), "argmax")
+        self.launches_per_forward = launches + 4
+        return self.next_tok
+
+
+class Engine:
+    """Scheduler + model: `step()` = plan rows -> upload them (and the block table when it moved) ->
+    forward (one CUDA-graph replay for a decode-only step) -> read the sampled tokens -> commit."""
+
+    def __init__(self, cfg, weights, bcap, num_pages, max_blocks_per_seq, max_rows=None, prefill_chunk=256, page_tokens=16,
+                 device="cuda", use_graph=True):
+        self.cfg, self.bcap = cfg, bcap
+        self.model = DecodeModel(cfg, weights, bcap, num_pages, max_blocks_per_seq, max_rows, page_tokens, device)
+        self.sched = Scheduler(bcap, num_pages, page_tokens, max_blocks_per_seq, self.model.max_rows, prefill_chunk)
+        R = self.model.max_rows
+        pin = lambda n, dt=torch.int32: torch.zeros(n, dtype=dt).pin_memory()
+        # one pinned staging block: token | pos | slot | ctx | sample_rows
+        self.h_rows = pin(5 * R)
+        self.d_rows = torch.zeros(5 * R, dtype=torch.int32, device=device)
+        m = self.model
+        m.row_token, m.row_pos, m.row_slot, m.row_ctx, m.sample_rows = (self.d_rows[i * R:(i + 1) * R] for i in range(5))
+        self.h_table = pin(bcap * max_blocks_per_seq)
+        self.h_next = pin(bcap)
+        self.uploaded_epoch = -1
+        self.use_graph = use_graph
+        self.graph = None
+        self.stream = torch.cuda.Stream(device=device)
+        self.h2d_bytes = self.d2h_bytes = self.kernel_launches = 0
+
+    def enqueue(self, prompt, gen_len):
+        return self.sched.enqueue(prompt, gen_len)
+
+    def step(self):
+        s, m, R = self.sched, self.model, self.model.max_rows
+        n = s.plan_step()
+        if n == 0:
+            return 0
+        hr = self.h_rows.numpy()
+        # decode-only step: every row is the one sampled row of its slot (one token per sequence)
+        decode_only = n <= self.bcap and np.array_equal(s.sample_row[s.row_slot[:n]], np.arange(n, dtype=np.int32))
+        # rows past n are inactive: they write no KV (pos < 0), see no key (ctx 0) and are never sampled
+        hr[0 * R:0 * R + n] = s.row_token[:n]; hr[0 * R + n:1 * R] = 0
+        hr[1 * R:1 * R + n] = s.row_pos[:n]; hr[1 * R + n:2 * R] = -1
+        hr[2 * R:2 * R + n] = s.row_slot[:n]; hr[2 * R + n:3 * R] = 0
+        hr[3 * R:3 * R + n] = s.row_ctx[:n]; hr[3 * R + n:4 * R] = 0
+        sampled_slots = np.flatnonzero(s.sample_row >= 0)
+        if decode_only:
+            hr[4 * R:4 * R + self.bcap] = np.arange(self.bcap)   # graph path: the head runs on every decode row
+        else:
+            hr[4 * R:4 * R + sampled_slots.size] = s.sample_row[sampled_slots]
+        with torch.cuda.stream(self.stream):
+            self.d_rows.copy_(self.h_rows, non_blocking=True)
+            self.h2d_bytes += self.h_rows.numel() * 4
+            ep = s.manager.layout_epoch()
+            if ep != self.uploaded_epoch:
+                s.manager.flat_block_table(self.h_table.numpy().view(np.uint32).reshape(self.bcap, -1))
+                m.block_table.view(-1).copy_(self.h_table, non_blocking=True)
+                self.uploaded_epoch = ep
+                self.h2d_bytes += self.h_table.numel() * 4
+            if decode_only and self.use_graph:
+                if self.graph is None:
+                    m.forward(self.bcap, self.bcap)          # eager once (also warms every kernel)
+                    self.stream.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=self.stream):
+                        m.forward(self.bcap, self.bcap)
+                    self.graph = g
+                    # the eager run already appended this step's K/V rows; replaying rewrites the same values
+                self.graph.replay()
+                nrows_head = self.bcap
+            elif decode_only:
+                m.forward(self.bcap, self.bcap)
+                nrows_head = self.bcap
+            else:
+                m.forward(n, max(1, sampled_slots.size))
+                nrows_head = sampled_slots.size
+            self.kernel_launches += m.launches_per_forward
+            self.h_next.copy_(m.next_tok, non_blocking=True)
+            self.d2h_bytes += self.bcap * 4
+        self.stream.synchronize()
+        nxt = self.h_next.numpy()
+        sampled = np.zeros(self.bcap, np.int32)
+        if decode_only:
+            sampled[sampled_slots] = nxt[s.sample_row[sampled_slots]]
+        else:
+            sampled[sampled_slots] = nxt[:sampled_slots.size]
+        return s.commit_step(sampled)
+
+    def run_until_idle(self, max_steps=1 << 30):
+        steps = 0
+        while not self.sched.is_idle() and steps < max_steps:
+            self.step()
+            steps += 1
+        return steps
