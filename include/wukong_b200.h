@@ -187,6 +187,8 @@ int wkb_rowargmax_i32(const float* x, int* out, int64_t rows, int64_t cols, void
 /* Same with a row pitch ld >= cols (padded logits). */
 int wkb_rowargmax_strided_i32(const float* x, int* out, int64_t rows, int64_t cols, int64_t ld, void* stream);
 int wkb_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream);
+/* Decode feedback on the device: row_token = next_tok, row_pos += 1, row_ctx += 1 for active rows. */
+int wkb_decode_advance(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, int64_t n, void* stream);
 
 /* Paged KV cache (behaviour of crates/wukong_codegen_gpu/src/paged_kv.rs:84-151,428-628 and
  * paged_attention.rs:395-534,1343-1410; kernels and HBM layout are this library's own).

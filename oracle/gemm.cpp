@@ -52,10 +52,55 @@ static void gemm_contract(LoadA la, LoadB lb, float* c, size_t m, size_t k, size
   });
 }
 
+// The NT form with B read in its storage type, eight output columns in flight.  Each (i, j) still runs
+// exactly the chain of `gemm_contract` (ascending p per K block, blocks folded in order), so the
+// bits are the same; the eight independent chains only hide the FMA latency, which is what makes
+// the timed CPU baseline a fair port rather than a latency-bound loop.
+template <typename TB>
+static inline float widen_b(TB v);
+template <> inline float widen_b<float>(float v) { return v; }
+struct Bf16B { u16 b; };
+struct F16B { u16 b; };
+template <> inline float widen_b<Bf16B>(Bf16B v) { return bf16_bits_to_f32(v.b); }
+template <> inline float widen_b<F16B>(F16B v) { return f16_bits_to_f32(v.b); }
+
+template <typename TB>
+static void gemm_nt_fast(const float* a, const TB* b, float* c, size_t M, size_t K, size_t N, float beta,
+                         const Epi* epi) {
+  const size_t kcap = (size_t)select_kc((i64)K);
+  const size_t ngroups = (N + 7) / 8;
+  par_for((i64)(M * ngroups), 8, [&](i64 lo, i64 hi) {
+    for (i64 u = lo; u < hi; ++u) {
+      size_t i = (size_t)u / ngroups, j0 = ((size_t)u % ngroups) * 8;
+      size_t nj = N - j0 < 8 ? N - j0 : 8;
+      const float* ar = a + i * K;
+      const TB* br[8];
+      for (size_t jj = 0; jj < 8; ++jj) br[jj] = b + (j0 + (jj < nj ? jj : 0)) * K;
+      float cv[8];
+      for (size_t jj = 0; jj < 8; ++jj) cv[jj] = jj < nj ? c[i * N + j0 + jj] : 0.0f;
+      for (size_t pc = 0; pc < K; pc += kcap) {
+        size_t kc = K - pc < kcap ? K - pc : kcap;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (size_t p = pc; p < pc + kc; ++p) {
+          float av = ar[p];
+          for (size_t jj = 0; jj < 8; ++jj) acc[jj] = fmaf(av, widen_b<TB>(br[jj][p]), acc[jj]);
+        }
+        float beta_eff = pc == 0 ? beta : 1.0f;
+        for (size_t jj = 0; jj < 8; ++jj) {
+          float val = beta_eff == 0.0f ? acc[jj] : cv[jj] + acc[jj];
+          cv[jj] = (pc + kc == K && epi) ? epi_apply(*epi, val, j0 + jj < N ? j0 + jj : 0) : val;
+        }
+      }
+      for (size_t jj = 0; jj < nj; ++jj) c[i * N + j0 + jj] = cv[jj];
+    }
+  });
+}
+
 static void sgemm_f32(const float* a, const float* b, float* c, i64 m, i64 k, i64 n, i64 beta, bool at,
                       bool bt, const Epi* epi) {
   if (m <= 0 || k <= 0 || n <= 0) return;  // gemm.rs:1018-1020
   size_t M = (size_t)m, K = (size_t)k, N = (size_t)n;
+  if (!at && bt) { gemm_nt_fast<float>(a, b, c, M, K, N, (float)beta, epi); return; }
   auto la = [=](size_t i, size_t p) { return at ? a[p * M + i] : a[i * K + p]; };
   auto lb = [=](size_t p, size_t j) { return bt ? b[j * K + p] : b[p * N + j]; };
   gemm_contract(la, lb, c, M, K, N, (float)beta, epi);
@@ -66,14 +111,10 @@ static void sgemm_half_nt(const u16* a, const u16* b, float* c, i64 m, i64 k, i6
                           const Epi* epi) {
   if (m <= 0 || k <= 0 || n <= 0) return;
   size_t M = (size_t)m, K = (size_t)k, N = (size_t)n;
-  std::vector<float> af(M * K), bfv(N * K);
+  std::vector<float> af(M * K);
   for (size_t i = 0; i < M * K; ++i) af[i] = bf16 ? bf16_bits_to_f32(a[i]) : f16_bits_to_f32(a[i]);
-  for (size_t i = 0; i < N * K; ++i) bfv[i] = bf16 ? bf16_bits_to_f32(b[i]) : f16_bits_to_f32(b[i]);
-  const float* ap = af.data();
-  const float* bp = bfv.data();
-  auto la = [=](size_t i, size_t p) { return ap[i * K + p]; };
-  auto lb = [=](size_t p, size_t j) { return bp[j * K + p]; };
-  gemm_contract(la, lb, c, M, K, N, (float)beta, epi);
+  if (bf16) gemm_nt_fast<Bf16B>(af.data(), reinterpret_cast<const Bf16B*>(b), c, M, K, N, (float)beta, epi);
+  else gemm_nt_fast<F16B>(af.data(), reinterpret_cast<const F16B*>(b), c, M, K, N, (float)beta, epi);
 }
 
 // gemv.rs:60-88 with hsum256 (:28-38): four 8-lane fma accumulators over 32-element steps,

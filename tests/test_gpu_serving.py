@@ -20,7 +20,7 @@ def _run(cfg_kw, reqs, bcap, seed=0, **eng_kw):
 
 
 def test_tokens_match_oracle_small_model(orc):
-    from oracle_gpt2 import OracleGPT2
+    from oracle.gpt2_model import OracleGPT2
     from wukong_b200 import device as dev
     rng = np.random.default_rng(0)
     cfg_kw = dict(n_layer=2, d_model=256, n_head=4, d_ff=512, vocab=1000, n_pos=128)

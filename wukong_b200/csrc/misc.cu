@@ -122,6 +122,18 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* a, const floa
   for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = a[i] + b[i];
 }
 
+// Device-side feedback of a decode step: the sampled token becomes the next input and the row moves
+// one position on (inactive rows, pos < 0, stay inactive).  Lets a run of decode steps replay with
+// no host round trip (the block table must already cover the positions ahead).
+__global__ void decode_advance_kernel(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, int n) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && row_pos[i] >= 0) {
+    row_token[i] = next_tok[i];
+    row_pos[i] += 1;
+    row_ctx[i] += 1;
+  }
+}
+
 static inline int grid_for(i64 items, int per_block) {
   i64 b = (items + per_block - 1) / per_block;
   i64 cap = (i64)WKB_SM_COUNT * 16;
@@ -175,6 +187,12 @@ int wkb_rowargmax_strided_i32(const float* x, int* out, i64 rows, i64 cols, i64 
   if (rows <= 0 || cols <= 0) return 0;
   int grid = (int)(rows < (i64)WKB_SM_COUNT * 8 ? rows : (i64)WKB_SM_COUNT * 8);
   rowargmax_kernel<<<grid, 256, 0, as_stream(stream)>>>(x, out, rows, cols, ld);
+  return (int)cudaGetLastError();
+}
+
+int wkb_decode_advance(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, i64 n, void* stream) {
+  if (n <= 0) return 0;
+  decode_advance_kernel<<<(int)((n + 255) / 256), 256, 0, as_stream(stream)>>>(row_token, row_pos, row_ctx, next_tok, (int)n);
   return (int)cudaGetLastError();
 }
 

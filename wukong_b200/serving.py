@@ -128,7 +128,7 @@ class DecodeModel:
         check(L.wkb_norm_fast(p(self.xs), 0, p(self.hs), 1, p(self.w["lnf_g"]), p(self.w["lnf_b"]), n_sample, d, cfg.eps, 1, s), "lnf")
         check(L.wkb_gemm_bf16_nt(p(self.hs), d, p(self.w["wte"]), d, p(self.logits), self.ldl, 0, n_sample, cfg.vocab, d, None, 0, None, 0, s), "lm_head")
         check(L.wkb_rowargmax_strided_i32(p(self.logits), p(self.next_tok), n_sample, cfg.vocab, self.ldl, s), "argmax")
-        self.launches_per_forward = launches + 4
+        self.launches_per_forward = launches + len(self.layers) + 4   # the attention call is two kernels
         return self.next_tok
 
 
@@ -155,13 +155,15 @@ class Engine:
         self.graph = None
         self.stream = torch.cuda.Stream(device=device)
         self.h2d_bytes = self.d2h_bytes = self.kernel_launches = 0
+        self._planned = None
 
     def enqueue(self, prompt, gen_len):
         return self.sched.enqueue(prompt, gen_len)
 
     def step(self):
         s, m, R = self.sched, self.model, self.model.max_rows
-        n = s.plan_step()
+        n = self._planned if self._planned is not None else s.plan_step()   # a caller may have planned already
+        self._planned = None
         if n == 0:
             return 0
         hr = self.h_rows.numpy()
@@ -214,6 +216,21 @@ class Engine:
         else:
             sampled[sampled_slots] = nxt[:sampled_slots.size]
         return s.commit_step(sampled)
+
+    def capture_resident_loop(self):
+        """A CUDA graph of one decode step that feeds itself: forward over all slots, then the
+        sampled tokens become the next inputs on the device.  The caller must have extended every
+        slot's block table far enough ahead (BlockManager.reserve) and uploaded it."""
+        m = self.model
+        def body():
+            m.forward(self.bcap, self.bcap)
+            check(lib().wkb_decode_advance(m.row_token.data_ptr(), m.row_pos.data_ptr(), m.row_ctx.data_ptr(),
+                                           m.next_tok.data_ptr(), self.bcap, torch.cuda.current_stream().cuda_stream), "advance")
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(self.stream):
+            with torch.cuda.graph(g, stream=self.stream):
+                body()
+        return g
 
     def run_until_idle(self, max_steps=1 << 30):
         steps = 0
