@@ -254,6 +254,11 @@ int wkb_gemm_bf16_nt(const void* a, int64_t lda, const void* b, int64_t ldb, voi
                      int64_t m, int64_t n, int64_t k, const float* bias, int64_t act, const float* residual,
                      int64_t ldr, void* stream);
 int wkb_gemm_status(void);
+/* Greedy sampling fused into the LM-head GEMM: out[i] = argmax_j (A.B^T + bias)[i,j]; the logits are
+ * never written.  part_val / part_idx are scratch of m * wkb_gemm_argmax_tiles(n) elements each. */
+int64_t wkb_gemm_argmax_tiles(int64_t n);
+int wkb_gemm_bf16_nt_argmax(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k,
+                            const float* bias, float* part_val, int* part_idx, int* out, void* stream);
 
 #ifdef __cplusplus
 }

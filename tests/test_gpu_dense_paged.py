@@ -59,6 +59,26 @@ def test_gemm_tc_matches_order_contract_gemm(dev, orc):
     assert dev.gemm_status() == 0
 
 
+def test_gemm_fused_argmax_equals_argmax_of_logits(dev, orc):
+    import torch
+    from wukong_b200 import lib
+    rng = np.random.default_rng(3)
+    for (m, n, k) in [(5, 1000, 64), (130, 50257, 768), (512, 300, 128)]:
+        a = bf16_t(rng.standard_normal((m, k)).astype(np.float32), orc)
+        b = bf16_t(rng.standard_normal((n, k)).astype(np.float32), orc)
+        b[7] = b[3]                      # an exact tie between two columns: the lower one must win
+        logits = dev.gemm_bf16_nt(a, b)
+        want = dev.rowargmax(logits.contiguous())
+        tiles = lib().wkb_gemm_argmax_tiles(n)
+        pv = torch.empty(m * tiles, device="cuda"); pi = torch.empty(m * tiles, dtype=torch.int32, device="cuda")
+        out = torch.empty(m, dtype=torch.int32, device="cuda")
+        rc = lib().wkb_gemm_bf16_nt_argmax(a.data_ptr(), k, b.data_ptr(), k, m, n, k, None, pv.data_ptr(), pi.data_ptr(),
+                                           out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0 and torch.equal(out, want)
+        assert list(dev.rowargmax(logits.contiguous()).cpu().numpy()) == list(orc.rowargmax(logits.cpu().numpy()))
+    assert dev.gemm_status() == 0
+
+
 def test_norm_fast_matches_oracle_recipe(dev, orc):
     """bf16 rows: widen -> the oracle's fp32 norm -> round once.  The fast kernel reduces in a
     different order, so outputs may differ by one bf16 ulp on a few lanes: rtol 2e-2 (the bf16 bar)."""

@@ -94,14 +94,31 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+#ifdef WKB_GEMM_TRACE
+// Diagnostic build only: CTA (0,0) records globaltimer stamps (ns) after the status word.
+__device__ __forceinline__ void trace_stamp(int* status, int slot) {
+  if (blockIdx.x == 0 && blockIdx.y == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    reinterpret_cast<unsigned long long*>(status)[1 + slot] = t;
+  }
+}
+#define WKB_TRACE(slot) trace_stamp(status, slot)
+#else
+#define WKB_TRACE(slot)
+#endif
+
 struct GemmEpi {
   const float* bias;       // [N] or null
   const float* residual;   // [M, ldr] f32 or null (added after the activation)
   i64 ldr;
   int act;                 // 0 identity, 1 relu, 2 gelu, 3 silu
   int out_bf16;            // 0: f32 C, 1: bf16 C
+  int* arg_idx;            // arg-max mode: per-(row, column tile) winning column (values go to C)
 };
 
+// ACT and OUT_BF16 are compile-time so that an identity epilogue carries no transcendental code.
+template <int ACT, bool OUT_BF16, bool ARGMAX>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c,
                     i64 ldc, int M, int N, int K, GemmEpi epi, int* status) {
@@ -118,6 +135,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int kiters = (K + BK - 1) / BK;
+  if (threadIdx.x == 0) WKB_TRACE(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -134,6 +152,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) WKB_TRACE(1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -171,6 +190,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
       }
       if (ok) umma_commit(tmem_full_bar);
+      WKB_TRACE(2);
     }
   } else {
     // epilogue warps 2..5: TMEM lane quarter (warp % 4)
@@ -183,6 +203,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (lane == 0) atomicExch(status, 3);
     } else {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (threadIdx.x == 64) WKB_TRACE(3);
+      float* stage = reinterpret_cast<float*>(gen_base) + (warp - 2) * (32 * 33);
+      float best_v = -INFINITY;
+      int best_i = -1;
+      bool pinned = false;
+      (void)stage; (void)best_v; (void)best_i; (void)pinned;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -198,52 +224,55 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < M) {
-          const int ncols = min(32, N - (n0 + c0));
-          if (ncols > 0) {
-            float v[32];
+        if (ARGMAX) {
+          // thread = row: ascending scan of its 32 columns keeps the lowest index on a tie; NaNs never
+          // win, except that a NaN in global column 0 pins the row to 0 (the arg-max rule of the ABI)
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              float y = __uint_as_float(r[e]);
-              int col = n0 + c0 + e;
-              if (e < ncols) {
-                if (epi.bias) y += epi.bias[col];
-                y = act_apply(epi.act, y);
-                if (epi.residual) y += epi.residual[(i64)row * epi.ldr + col];
-              }
-              v[e] = y;
-            }
-            if (epi.out_bf16) {
-              u16* cp = reinterpret_cast<u16*>(c) + (i64)row * ldc + n0 + c0;
-              if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
-#pragma unroll
-                for (int e = 0; e < 32; e += 8) {
-                  uint4 pk;
-                  pk.x = (uint32_t)f32_to_bf16_bits(v[e]) | ((uint32_t)f32_to_bf16_bits(v[e + 1]) << 16);
-                  pk.y = (uint32_t)f32_to_bf16_bits(v[e + 2]) | ((uint32_t)f32_to_bf16_bits(v[e + 3]) << 16);
-                  pk.z = (uint32_t)f32_to_bf16_bits(v[e + 4]) | ((uint32_t)f32_to_bf16_bits(v[e + 5]) << 16);
-                  pk.w = (uint32_t)f32_to_bf16_bits(v[e + 6]) | ((uint32_t)f32_to_bf16_bits(v[e + 7]) << 16);
-                  *reinterpret_cast<uint4*>(cp + e) = pk;
-                }
-              } else {
-                for (int e = 0; e < ncols; ++e) cp[e] = f32_to_bf16_bits(v[e]);
-              }
-            } else {
-              float* cp = reinterpret_cast<float*>(c) + (i64)row * ldc + n0 + c0;
-              if (ncols == 32 && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0)) {
-#pragma unroll
-                for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(cp + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-              } else {
-                for (int e = 0; e < ncols; ++e) cp[e] = v[e];
-              }
+          for (int e = 0; e < 32; ++e) {
+            int col = n0 + c0 + e;
+            float y = __uint_as_float(r[e]);
+            if (col < N) {
+              if (epi.bias) y += epi.bias[col];
+              if (col == 0 && y != y) { best_v = INFINITY; best_i = 0; pinned = true; }
+              if (!pinned && y == y && (best_i < 0 || y > best_v)) { best_v = y; best_i = col; }
             }
           }
+        } else {
+          // transpose through shared memory (the pipeline stages are idle now) so that a lane owns a
+          // column and every global access is one coalesced row segment
+#pragma unroll
+          for (int e = 0; e < 32; ++e) stage[lane * 33 + e] = __uint_as_float(r[e]);
+          __syncwarp();
+          const int col = n0 + c0 + lane;
+          const bool col_ok = col < N;
+          const float bias_v = (col_ok && epi.bias) ? epi.bias[col] : 0.0f;
+          const int row0 = m0 + quarter * 32;
+#pragma unroll 4
+          for (int rr = 0; rr < 32; ++rr) {
+            const int grow = row0 + rr;
+            if (grow < M && col_ok) {
+              float y = stage[rr * 33 + lane] + bias_v;
+              y = act_apply(ACT, y);
+              if (epi.residual) y += epi.residual[(i64)grow * epi.ldr + col];
+              if (OUT_BF16) reinterpret_cast<u16*>(c)[(i64)grow * ldc + col] = f32_to_bf16_bits(y);
+              else reinterpret_cast<float*>(c)[(i64)grow * ldc + col] = y;
+            }
+          }
+          __syncwarp();
         }
+      }
+      if (ARGMAX && row < M) {
+        // partial result of this column tile: [row][tile] (value, index); index -1 = no candidate
+        const i64 slot = (i64)row * gridDim.x + blockIdx.x;
+        reinterpret_cast<float*>(c)[slot] = best_v;
+        epi.arg_idx[slot] = best_i;
       }
     }
   }
+  if (threadIdx.x == 64) WKB_TRACE(4);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (threadIdx.x == 0) WKB_TRACE(5);
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -281,6 +310,30 @@ static int make_map(CUtensorMap* map, const void* ptr, i64 rows, i64 k, i64 ld, 
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// One warp per row folds the per-tile candidates: greater value wins, equal values keep the lower
+// column, a pinned row (value +inf from a NaN at column 0, index 0) wins outright by its index rule.
+__global__ void __launch_bounds__(128) argmax_tiles_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int tiles,
+                                                           int* __restrict__ out, int rows) {
+  int lane = threadIdx.x & 31;
+  int row = (int)(((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+  if (row >= rows) return;
+  float bv = -INFINITY;
+  int bi = -1;
+  for (int t = lane; t < tiles; t += 32) {
+    float v = pv[(i64)row * tiles + t];
+    int i = pi[(i64)row * tiles + t];
+    if (i >= 0 && (bi < 0 || v > bv)) { bv = v; bi = i; }
+  }
+#pragma unroll
+  for (int ofs = 16; ofs > 0; ofs >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, bv, ofs);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, ofs);
+    bool take = oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi));
+    if (take) { bv = ov; bi = oi; }
+  }
+  if (lane == 0) out[row] = bi < 0 ? 0 : bi;
+}
+
 static int* gemm_status_word() {
   // one device word per device for the bounded-wait status; allocated at first use
   static int* words[64] = {nullptr};
@@ -288,8 +341,8 @@ static int* gemm_status_word() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   if (!words[dev]) {
     int* p = nullptr;
-    if (cudaMalloc((void**)&p, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, sizeof(int));
+    if (cudaMalloc((void**)&p, 256) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 256);
     words[dev] = p;
   }
   return words[dev];
@@ -313,17 +366,61 @@ int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i6
   if (rc) return rc;
   int* status = gemm_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
+  if (act < 0 || act > 3) return (int)cudaErrorInvalidValue;
+  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, void*, i64, int, int, int, GemmEpi, int*);
+  static const KernelFn table[4][2] = {
+      {gemm_bf16_tc_kernel<0, false, false>, gemm_bf16_tc_kernel<0, true, false>},
+      {gemm_bf16_tc_kernel<1, false, false>, gemm_bf16_tc_kernel<1, true, false>},
+      {gemm_bf16_tc_kernel<2, false, false>, gemm_bf16_tc_kernel<2, true, false>},
+      {gemm_bf16_tc_kernel<3, false, false>, gemm_bf16_tc_kernel<3, true, false>}};
+  KernelFn kern = table[act][c_bf16 ? 1 : 0];
+  static bool attr_set[64][8] = {{false}};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int slot = (int)act * 2 + (c_bf16 ? 1 : 0);
+  if (!attr_set[dev & 63][slot]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63][slot] = true;
+  }
+  GemmEpi epi{bias, residual, ldr, (int)act, c_bf16, nullptr};
+  dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
+  kern<<<grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
+  return (int)cudaGetLastError();
+}
+
+i64 wkb_gemm_argmax_tiles(i64 n) { return (n + BN - 1) / BN; }
+
+// out[i] = argmax_j (A.B^T + bias)[i, j] without materialising the product: every column tile leaves
+// one (value, column) candidate per row in part_val / part_idx ([m, wkb_gemm_argmax_tiles(n)] each),
+// then a small kernel folds them.  Ties and NaNs follow wkb_rowargmax_i32.
+int wkb_gemm_bf16_nt_argmax(const void* a, i64 lda, const void* b, i64 ldb, i64 m, i64 n, i64 k, const float* bias,
+                            float* part_val, int* part_idx, int* out, void* stream) {
+  if (m <= 0 || n <= 0) return 0;
+  if (k <= 0 || k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)a) | ((uintptr_t)b)) & 15) return (int)cudaErrorMisalignedAddress;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, m, k, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, b, n, k, ldb, BN);
+  if (rc) return rc;
+  int* status = gemm_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  auto kern = gemm_bf16_tc_kernel<0, false, true>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev & 63] = true;
   }
-  GemmEpi epi{bias, residual, ldr, (int)act, c_bf16};
+  GemmEpi epi{bias, nullptr, 0, 0, 0, part_idx};
   dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
-  gemm_bf16_tc_kernel<<<grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
+  kern<<<grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(ma, mb, part_val, 0, (int)m, (int)n, (int)k, epi, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  argmax_tiles_kernel<<<(unsigned)((m * 32 + 127) / 128), 128, 0, as_stream(stream)>>>(part_val, part_idx, (int)grid.x, out, (int)m);
   return (int)cudaGetLastError();
 }
 
@@ -337,4 +434,11 @@ int wkb_gemm_status(void) {
   if (v) cudaMemset(status, 0, sizeof(int));
   return v;
 }
+
+#ifdef WKB_GEMM_TRACE
+int wkb_gemm_trace(void* host256) {
+  int* status = gemm_status_word();
+  return status ? (int)cudaMemcpy(host256, status, 256, cudaMemcpyDeviceToHost) : -1;
+}
+#endif
 }

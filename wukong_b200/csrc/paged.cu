@@ -11,7 +11,7 @@
 // so one (page, head) is a single contiguous page_tokens*head_dim*2-byte run (2 KiB at d=64, 4 KiB at
 // d=128) and a warp step reads 512 contiguous bytes.
 //
-// Decode kernel.  The unit of work is (row, kv head, 256-token chunk of the logical sequence), one
+// Decode kernel.  The unit of work is (row, kv head, 128-token chunk of the logical sequence), one
 // warp each.  A lane owns 8 head dims (one 128-bit load) of one token; 32/(d/8) tokens per step.
 // Partial dots are reduce-scattered so each lane ends up owning one token's score; softmax runs in
 // base 2 on those; each lane then accumulates its 8 output dims over its tokens.  All query heads
@@ -25,7 +25,7 @@
 
 namespace wkb {
 
-constexpr int PA_CHUNK = 256;   // logical tokens per work unit
+constexpr int PA_CHUNK = 128;   // logical tokens per work unit
 constexpr int PA_WARPS = 4;
 
 __device__ __forceinline__ void unpack8(const uint4& w, float f[8]) {
@@ -36,7 +36,7 @@ __device__ __forceinline__ void unpack8(const uint4& w, float f[8]) {
 }
 
 struct PagedGeo {
-  int rows, q_heads, kv_heads, page_tokens, mbps, max_chunks;
+  int rows, q_heads, kv_heads, page_tokens, page_shift, mbps, max_chunks;
   i64 q_row_stride;
 };
 
@@ -50,15 +50,18 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   constexpr int TPW = 32 / LPT;     // tokens per warp step
   constexpr int STEPS = LPT;        // steps per tile (so the reduce-scatter is square)
   constexpr int TILE = STEPS * TPW; // 32 tokens
+  constexpr bool PREFETCH_V = (HD == 64) || (G <= 2);
   static_assert(TILE == 32, "tile is one token per lane");
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int grp = lane / LPT, j = lane % LPT;
   const i64 unit = (i64)blockIdx.x * PA_WARPS + warp;
   const i64 units = (i64)g.rows * g.kv_heads * g.max_chunks;
   if (unit >= units) return;
-  const int chunk = (int)(unit % g.max_chunks);
-  const int kvh = (int)((unit / g.max_chunks) % g.kv_heads);
-  const int row = (int)(unit / ((i64)g.max_chunks * g.kv_heads));
+  // chunk is the slowest-varying index: CTAs of a late chunk are (almost) all empty and retire at
+  // once instead of pinning idle warps beside busy ones
+  const int chunk = (int)(unit / ((i64)g.rows * g.kv_heads));
+  const int kvh = (int)(unit % g.kv_heads);
+  const int row = (int)((unit / g.kv_heads) % g.rows);
   const int ctx = row_ctx[row];
   const int t0 = chunk * PA_CHUNK;
   float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
@@ -88,19 +91,27 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   const i64 page_units = (i64)g.kv_heads * g.page_tokens * LPT;  // uint4 per page
   const i64 head_off = (i64)kvh * g.page_tokens * LPT;
   for (int tile0 = t0; tile0 < t1; tile0 += TILE) {
+    // ---- issue every K (and, when registers allow, V) load of the tile before any math, so one
+    //      warp keeps up to 2 * STEPS * 512 B in flight
+    uint4 kw[STEPS], vw[PREFETCH_V ? STEPS : 1];
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s) {
+      int tok = tile0 + s * TPW + grp;
+      kw[s] = make_uint4(0, 0, 0, 0);
+      if (PREFETCH_V) vw[PREFETCH_V ? s : 0] = make_uint4(0, 0, 0, 0);
+      if (tok < t1) {
+        uint32_t page = bt[tok >> g.page_shift];
+        i64 idx = (i64)page * page_units + head_off + (i64)(tok & (g.page_tokens - 1)) * LPT + j;
+        kw[s] = kcache[idx];
+        if (PREFETCH_V) vw[PREFETCH_V ? s : 0] = vcache[idx];
+      }
+    }
     // ---- scores: partial dots of this lane's 8 dims, for token (s*TPW + grp) at each step s
     float part[G][STEPS];
 #pragma unroll
     for (int s = 0; s < STEPS; ++s) {
-      int tok = tile0 + s * TPW + grp;
-      bool ok = tok < t1;
-      uint4 kw = make_uint4(0, 0, 0, 0);
-      if (ok) {
-        uint32_t page = bt[tok / g.page_tokens];
-        kw = kcache[(i64)page * page_units + head_off + (i64)(tok % g.page_tokens) * LPT + j];
-      }
       float kf[8];
-      unpack8(kw, kf);
+      unpack8(kw[s], kf);
 #pragma unroll
       for (int h = 0; h < G; ++h) {
         float d = 0.0f;
@@ -144,13 +155,15 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
     for (int s = 0; s < STEPS; ++s) {
       int tok = tile0 + s * TPW + grp;
       bool ok = tok < t1;
-      uint4 vw = make_uint4(0, 0, 0, 0);
-      if (ok) {
-        uint32_t page = bt[tok / g.page_tokens];
-        vw = vcache[(i64)page * page_units + head_off + (i64)(tok % g.page_tokens) * LPT + j];
+      uint4 vcur = make_uint4(0, 0, 0, 0);
+      if (PREFETCH_V) {
+        vcur = vw[PREFETCH_V ? s : 0];
+      } else if (ok) {
+        uint32_t page = bt[tok >> g.page_shift];
+        vcur = vcache[(i64)page * page_units + head_off + (i64)(tok & (g.page_tokens - 1)) * LPT + j];
       }
       float vf[8];
-      unpack8(vw, vf);
+      unpack8(vcur, vf);
 #pragma unroll
       for (int h = 0; h < G; ++h) {
         float pt = __shfl_sync(0xffffffffu, p[h], grp * LPT + s);
@@ -282,13 +295,16 @@ int wkb_paged_attn_decode(const float* q, i64 q_row_stride, const void* kcache, 
                           i64 page_tokens, i64 max_blocks_per_seq, i64 max_ctx, float scale, float* scratch,
                           void* stream) {
   if (rows <= 0) return 0;
-  if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || page_tokens <= 0) return (int)cudaErrorInvalidValue;
+  if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
+  if (page_tokens < 4 || (page_tokens & (page_tokens - 1)) != 0) return (int)cudaErrorInvalidValue;  // power of two, >= 4
+  int page_shift = 0;
+  while ((1 << page_shift) < page_tokens) ++page_shift;
   if ((q_row_stride % 4) != 0 || ((((uintptr_t)q) | ((uintptr_t)scratch) | ((uintptr_t)kcache) | ((uintptr_t)vcache)) & 15) != 0)
     return (int)cudaErrorMisalignedAddress;
   if (out_row_stride % 4 != 0 || (((uintptr_t)out) & 15) != 0) return (int)cudaErrorMisalignedAddress;
   i64 chunks = (max_ctx + PA_CHUNK - 1) / PA_CHUNK;
   if (chunks < 1) chunks = 1;
-  PagedGeo g{(int)rows, (int)q_heads, (int)kv_heads, (int)page_tokens, (int)max_blocks_per_seq, (int)chunks, q_row_stride};
+  PagedGeo g{(int)rows, (int)q_heads, (int)kv_heads, (int)page_tokens, page_shift, (int)max_blocks_per_seq, (int)chunks, q_row_stride};
   int G = (int)(q_heads / kv_heads);
   cudaStream_t st = as_stream(stream);
 #define WKB_PA_CASE(HD_, G_) \

@@ -369,4 +369,5 @@ int wkb_dequant_int4(const u8* q, const float* scale, const float* zero_or_null,
   dequant_int4_kernel<<<grid, 256, 0, as_stream(stream)>>>(q, scale, zero_or_null, group, out, n);
   return (int)cudaGetLastError();
 }
+
 }

@@ -97,6 +97,10 @@ class DecodeModel:
         self.ldl = (cfg.vocab + 7) // 8 * 8                      # logits pitch, 16-byte aligned rows
         self.logits = torch.zeros((bcap, self.ldl), dtype=torch.float32, device=device)
         self.next_tok = torch.zeros(bcap, **i32)
+        tiles = lib().wkb_gemm_argmax_tiles(cfg.vocab)
+        self.part_val = torch.zeros(bcap * tiles, dtype=torch.float32, device=device)
+        self.part_idx = torch.zeros(bcap * tiles, **i32)
+        self.keep_logits = False      # True: materialise fp32 logits (tests); False: arg-max fused into the LM head
         self.scratch = dev.paged_attn_scratch(R, cfg.n_head, cfg.head_dim, self.max_ctx, device)
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.launches_per_forward = 0
@@ -126,8 +130,12 @@ class DecodeModel:
         # LM head on the sampled rows only: gather -> final norm -> tied head -> arg-max
         check(L.wkb_embedding_f32(p(self.xs), p(self.x), p(self.sample_rows), n_sample, d, n, s), "gather")
         check(L.wkb_norm_fast(p(self.xs), 0, p(self.hs), 1, p(self.w["lnf_g"]), p(self.w["lnf_b"]), n_sample, d, cfg.eps, 1, s), "lnf")
-        check(L.wkb_gemm_bf16_nt(p(self.hs), d, p(self.w["wte"]), d, p(self.logits), self.ldl, 0, n_sample, cfg.vocab, d, None, 0, None, 0, s), "lm_head")
-        check(L.wkb_rowargmax_strided_i32(p(self.logits), p(self.next_tok), n_sample, cfg.vocab, self.ldl, s), "argmax")
+        if self.keep_logits:
+            check(L.wkb_gemm_bf16_nt(p(self.hs), d, p(self.w["wte"]), d, p(self.logits), self.ldl, 0, n_sample, cfg.vocab, d, None, 0, None, 0, s), "lm_head")
+            check(L.wkb_rowargmax_strided_i32(p(self.logits), p(self.next_tok), n_sample, cfg.vocab, self.ldl, s), "argmax")
+        else:
+            check(L.wkb_gemm_bf16_nt_argmax(p(self.hs), d, p(self.w["wte"]), d, n_sample, cfg.vocab, d, None, p(self.part_val),
+                                            p(self.part_idx), p(self.next_tok), s), "lm_head_argmax")
         self.launches_per_forward = launches + len(self.layers) + 4   # the attention call is two kernels
         return self.next_tok
 
