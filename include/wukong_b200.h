@@ -165,6 +165,11 @@ int wkb_quantize_act(const float* x, int64_t k, void* xq, float* dx, int* sx, vo
 int wkb_gemv_q_contract(const void* qs, const void* d, const void* xq, const float* dx, const int* sx, float* y,
                         int64_t n, int64_t k, int q4, void* stream);
 int wkb_gemv_q4_0_bf16x(const void* qs, const void* d, const void* x_bf16, float* y, int64_t n, int64_t k, void* stream);
+/* No counterpart in the reference.  The Q4_0 contract GEMV for callers that must not allocate device
+ * memory: the Q8 activation scratch is a fixed device array inside the library, so K <= 32768 (larger K
+ * is refused with cudaErrorInvalidValue and a message).  The first call on a device resolves the array's
+ * address and should precede any stream capture.  Calls share the array: overlapping calls race. */
+int wkb_gemv_q4_0_f32_noalloc(const void* qs, const void* d, const float* x, float* y, int64_t n, int64_t k, void* stream);
 int wkb_quantize_q(const float* x, uint8_t* q, int64_t rows, int64_t k, int q4, void* stream);
 int wkb_dequant_int4(const uint8_t* q, const float* scale, const float* zero_or_null, int64_t group, float* out, int64_t n, void* stream);
 

@@ -294,6 +294,16 @@ __global__ void __launch_bounds__(256) dequant_int4_kernel(const u8* __restrict_
   }
 }
 
+// ---- scratch of the allocation-free GEMV entry ----------------------------------------------------
+// The per-call Q8 activation (quants, block scales, block sums) lives in this fixed array instead of
+// caller- or runtime-allocated memory.  Every GPU that loads the library holds it until exit.
+constexpr i64 NOALLOC_MAX_K = 32768;
+constexpr i64 NOALLOC_MAX_NB = NOALLOC_MAX_K / 32;
+constexpr i64 NOALLOC_XQ_BYTES = NOALLOC_MAX_K;                // i8 quants
+constexpr i64 NOALLOC_DX_OFF = NOALLOC_XQ_BYTES;               // f32 scales
+constexpr i64 NOALLOC_SX_OFF = NOALLOC_DX_OFF + NOALLOC_MAX_NB * 4;  // i32 sums
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SX_OFF + NOALLOC_MAX_NB * 4];
+
 static size_t contract_smem(int nb, int warps) { return (size_t)nb * (32 + 4 + 4) + (size_t)warps * GQ_RB * nb * 4; }
 
 }  // namespace wkb
@@ -370,4 +380,37 @@ int wkb_dequant_int4(const u8* q, const float* scale, const float* zero_or_null,
   return (int)cudaGetLastError();
 }
 
+// y = W x for resident Q4_0 weights, bit-identical to wkb_gemv_q_contract, for callers that cannot
+// allocate device memory (a runtime that owns every byte of its arena up front, a plug-in called
+// inside someone else's memory-managed region, code running where a cudaMalloc would synchronise the
+// device at the wrong moment).  The Q8 activation scratch is the library's fixed device array, so
+// K is limited to 32768.  The first call on each device looks the array's device address up (make it
+// before any stream capture starts); no call allocates or frees anything.  All calls share the one
+// array: it is fully rewritten by each call (nothing needs to start at zero), and two calls whose
+// kernels overlap on the GPU -- different streams, or different host threads -- race on it.
+int wkb_gemv_q4_0_f32_noalloc(const void* qs, const void* d, const float* x, float* y, i64 n, i64 k, void* stream) {
+  if (n <= 0 || k <= 0) return 0;
+  if (k > NOALLOC_MAX_K) {
+    fprintf(stderr, "wkb_gemv_q4_0_f32_noalloc: K = %lld exceeds the fixed scratch (max %lld); use wkb_gemv_q_contract\n",
+            (long long)k, (long long)NOALLOC_MAX_K);
+    return (int)cudaErrorInvalidValue;
+  }
+  static unsigned char* base[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  if (!base[dev]) {
+    // the array's name is a host-side stand-in here; this is its address on the current device
+    unsigned char* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    base[dev] = p;
+  }
+  unsigned char* s = base[dev];
+  int rc = wkb_quantize_act(x, k, s, reinterpret_cast<float*>(s + NOALLOC_DX_OFF), reinterpret_cast<int*>(s + NOALLOC_SX_OFF), stream);
+  if (rc) return rc;
+  return wkb_gemv_q_contract(qs, d, s, reinterpret_cast<const float*>(s + NOALLOC_DX_OFF),
+                             reinterpret_cast<const int*>(s + NOALLOC_SX_OFF), y, n, k, 1, stream);
+}
 }
