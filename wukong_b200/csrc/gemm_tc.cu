@@ -6,17 +6,19 @@
 // convention (both operands K-major, "NT"), fp32 accumulate, same epilogue menu
 // act(alpha-free A.B^T + bias[j]) (+ residual), act codes 0 identity / 1 relu / 2 gelu / 3 silu.
 //
-// Design (one 128 x 128 output tile per CTA, 192 threads):
+// Design (persistent CTAs, one per SM, looping over 128 x 128 output tiles; 192 threads):
 //   warp 0   one elected lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, no
 //            multicast) of a 128x64 A tile and a 128x64 B tile per stage into a 5-stage ring,
 //            completion counted on an mbarrier per stage;
-//   warp 1   allocates 128 TMEM columns, and one elected lane issues tcgen05.mma
-//            (cta_group::1, kind::f16, M=128 N=128 K=16) four times per stage straight from shared
-//            memory descriptors; tcgen05.commit releases the stage back to the producer and, after
-//            the last K step, signals the epilogue;
+//   warp 1   allocates 256 TMEM columns (two accumulator buffers), and one elected lane issues
+//            tcgen05.mma (cta_group::1, kind::f16, M=128 N=128 K=16) four times per stage straight
+//            from shared memory descriptors; tcgen05.commit releases the stage back to the producer
+//            and, after a tile's last K step, hands the accumulator buffer to the epilogue;
 //   warps 2-5 read the fp32 accumulator out of TMEM with tcgen05.ld (32 lanes x 32 columns per
-//            instruction; warp w owns lanes 32*(w%4)..), apply bias / activation / residual and
-//            store fp32 or bf16 rows.
+//            instruction; warp w owns lanes 32*(w%4)..), release the buffer as soon as it is in
+//            registers (so the next tile's MMAs overlap this tile's epilogue), transpose through
+//            shared memory and store coalesced rows with bias / activation / residual applied, or
+//            keep a per-row arg-max candidate instead of storing (greedy LM head).
 // Every mbarrier wait is bounded: on expiry the kernel records a code in `status`, stops issuing,
 // waits (bounded) for the copies it started, frees its TMEM and returns.
 // Ragged M / N / K are handled by TMA zero fill and masked stores; K % 8 == 0 is required (the
@@ -34,8 +36,10 @@ constexpr int BM = 128, BN = 128, BK = 64, STAGES = 5, UMMA_K = 16;
 constexpr int TILE_A_BYTES = BM * BK * 2, TILE_B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
 constexpr int GEMM_THREADS = 192;
-constexpr uint32_t TMEM_COLS = 128;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t TMEM_COLS = 256;             // two 128-column accumulator buffers
+constexpr int EPI_STAGE_BYTES = 4 * 32 * 33 * 4;  // one 32 x 33 fp32 transpose pad per epilogue warp
+constexpr int NUM_BARS = 2 * STAGES + 4;          // full / empty per stage, tmem full / empty per buffer
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -117,7 +121,28 @@ struct GemmEpi {
   int* arg_idx;            // arg-max mode: per-(row, column tile) winning column (values go to C)
 };
 
-// ACT and OUT_BF16 are compile-time so that an identity epilogue carries no transcendental code.
+// GELU for bf16 output: x * sigmoid(2u), u = sqrt(2/pi)(x + 0.044715 x^3), with the hardware exp2 and
+// reciprocal.  Relative error ~1e-6, three orders below the bf16 rounding that follows; the exact
+// sequence (gelu1) stays in use wherever fp32 values are returned.
+__device__ __forceinline__ float gelu_fast(float x) {
+  float u = 0.7978846f * fmaf(0.044715f * x * x, x, x);
+  float e = exp2f(-2.8853900817779268f * u);  // exp(-2u)
+  return __fdividef(x, 1.0f + e);
+}
+
+template <int ACT, bool OUT_BF16>
+__device__ __forceinline__ float epi_act(float y) {
+  if (ACT == 2 && OUT_BF16) return gelu_fast(y);
+  return act_apply(ACT, y);
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Persistent kernel: CTA b works on tiles b, b + gridDim.x, ...; tile t is (m_tile = t % tiles_m,
+// n_tile = t / tiles_m), so CTAs running side by side share one B (weight) tile through L2.
+// ACT / OUT_BF16 / ARGMAX are compile-time so an identity epilogue carries no transcendental code.
 template <int ACT, bool OUT_BF16, bool ARGMAX>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c,
@@ -126,20 +151,24 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - raw);
-  const uint32_t bars = base + STAGES * STAGE_BYTES;  // full[STAGES], empty[STAGES], tmem_full, tmem slot
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+  // layout: STAGES x (A tile, B tile) | epilogue staging 4 x 32 x 33 floats | barriers | tmem slot
+  float* stage_all = reinterpret_cast<float*>(gen_base + STAGES * STAGE_BYTES);
+  const uint32_t bars = base + STAGES * STAGE_BYTES + EPI_STAGE_BYTES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 8 * NUM_BARS);
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  const uint32_t tmem_full_bar = bars + 8u * (2 * STAGES);
+  auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
   const int kiters = (K + BK - 1) / BK;
   if (threadIdx.x == 0) WKB_TRACE(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    mbar_init(tmem_full_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -155,64 +184,77 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0) WKB_TRACE(1);
 
   if (warp == 0) {
+    // ---------------- TMA producer ----------------
     if (lane == 0) {
-      int issued = 0;
+      int it = 0, issued_from = 0;
       bool ok = true;
-      for (int it = 0; it < kiters && ok; ++it) {
-        int s = it % STAGES;
-        uint32_t par = ((it / STAGES) & 1) ^ 1;
-        if (!mbar_wait(empty_bar(s), par)) { atomicExch(status, 1); ok = false; break; }
-        mbar_expect_tx(full_bar(s), STAGE_BYTES);
-        uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_A_BYTES;
-        tma_load_2d(sa, &map_a, full_bar(s), it * BK, m0);
-        tma_load_2d(sb, &map_b, full_bar(s), it * BK, n0);
-        issued = it + 1;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+        for (int kk = 0; kk < kiters; ++kk, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1)) { atomicExch(status, 1); ok = false; break; }
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_A_BYTES;
+          tma_load_2d(sa, &map_a, full_bar(s), kk * BK, m0);
+          tma_load_2d(sb, &map_b, full_bar(s), kk * BK, n0);
+        }
       }
       if (!ok) {
         // wait (bounded) for the copies already started before the CTA may exit
-        for (int it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it)
-          mbar_wait(full_bar(it % STAGES), (it / STAGES) & 1);
+        issued_from = it > STAGES ? it - STAGES : 0;
+        for (int j = issued_from; j < it; ++j) mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1);
       }
     }
   } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
     if (lane == 0) {
+      int it = 0, local = 0;
       bool ok = true;
-      for (int it = 0; it < kiters; ++it) {
-        int s = it % STAGES;
-        if (!mbar_wait(full_bar(s), (it / STAGES) & 1)) { atomicExch(status, 2); ok = false; break; }
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+        const int buf = local & 1;
+        // the epilogue must have drained this accumulator buffer (two tiles ago)
+        if (!mbar_wait(tempty_bar(buf), ((local >> 1) & 1) ^ 1)) { atomicExch(status, 4); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_A_BYTES;
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        for (int kk = 0; kk < kiters; ++kk, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full_bar(s), (it / STAGES) & 1)) { atomicExch(status, 2); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          uint64_t ad = make_sdesc(sa + k * UMMA_K * 2), bd = make_sdesc(sb + k * UMMA_K * 2);
-          umma_bf16(tmem_base, ad, bd, (it > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_d, make_sdesc(sa + k * UMMA_K * 2), make_sdesc(sb + k * UMMA_K * 2), (kk > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
         }
-        umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+        if (ok) umma_commit(tfull_bar(buf));
       }
-      if (ok) umma_commit(tmem_full_bar);
       WKB_TRACE(2);
     }
   } else {
-    // epilogue warps 2..5: TMEM lane quarter (warp % 4)
+    // ---------------- epilogue warps 2..5: TMEM lane quarter (warp % 4) ----------------
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
+    float* stage = stage_all + (warp - 2) * (32 * 33);
+    (void)stage;
+    int local = 0;
     bool ok = true;
-    if (lane == 0) ok = mbar_wait(tmem_full_bar, 0);
-    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    if (!ok) {
-      if (lane == 0) atomicExch(status, 3);
-    } else {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+      const int row = m0 + quarter * 32 + lane;
+      int good = 1;
+      if (lane == 0) good = mbar_wait(tfull_bar(buf), (local >> 1) & 1) ? 1 : 0;
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { if (lane == 0) atomicExch(status, 3); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (threadIdx.x == 64) WKB_TRACE(3);
-      float* stage = reinterpret_cast<float*>(gen_base) + (warp - 2) * (32 * 33);
+      if (threadIdx.x == 64 && local == 0) WKB_TRACE(3);
       float best_v = -INFINITY;
       int best_i = -1;
       bool pinned = false;
-      (void)stage; (void)best_v; (void)best_i; (void)pinned;
+      (void)best_v; (void)best_i; (void)pinned;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
-        uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -224,12 +266,18 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 == BN) {
+          // the accumulator buffer is fully in registers: hand it back to the MMA warp
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(buf));
+        }
         if (ARGMAX) {
           // thread = row: ascending scan of its 32 columns keeps the lowest index on a tie; NaNs never
           // win, except that a NaN in global column 0 pins the row to 0 (the arg-max rule of the ABI)
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            int col = n0 + c0 + e;
+            const int col = n0 + c0 + e;
             float y = __uint_as_float(r[e]);
             if (col < N) {
               if (epi.bias) y += epi.bias[col];
@@ -238,22 +286,27 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
           }
         } else {
-          // transpose through shared memory (the pipeline stages are idle now) so that a lane owns a
-          // column and every global access is one coalesced row segment
+          // transpose through shared memory so that a lane owns a column and every global access is
+          // one coalesced row segment; the residual rows are fetched first so their latency overlaps
+          const int col = n0 + c0 + lane;
+          const bool col_ok = col < N;
+          const int row0 = m0 + quarter * 32;
+          float res[32];
+          if (epi.residual) {
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr)
+              res[rr] = (col_ok && row0 + rr < M) ? epi.residual[(i64)(row0 + rr) * epi.ldr + col] : 0.0f;
+          }
 #pragma unroll
           for (int e = 0; e < 32; ++e) stage[lane * 33 + e] = __uint_as_float(r[e]);
           __syncwarp();
-          const int col = n0 + c0 + lane;
-          const bool col_ok = col < N;
           const float bias_v = (col_ok && epi.bias) ? epi.bias[col] : 0.0f;
-          const int row0 = m0 + quarter * 32;
-#pragma unroll 4
+#pragma unroll
           for (int rr = 0; rr < 32; ++rr) {
             const int grow = row0 + rr;
             if (grow < M && col_ok) {
-              float y = stage[rr * 33 + lane] + bias_v;
-              y = act_apply(ACT, y);
-              if (epi.residual) y += epi.residual[(i64)grow * epi.ldr + col];
+              float y = epi_act<ACT, OUT_BF16>(stage[rr * 33 + lane] + bias_v);
+              if (epi.residual) y += res[rr];
               if (OUT_BF16) reinterpret_cast<u16*>(c)[(i64)grow * ldc + col] = f32_to_bf16_bits(y);
               else reinterpret_cast<float*>(c)[(i64)grow * ldc + col] = y;
             }
@@ -263,7 +316,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       if (ARGMAX && row < M) {
         // partial result of this column tile: [row][tile] (value, index); index -1 = no candidate
-        const i64 slot = (i64)row * gridDim.x + blockIdx.x;
+        const i64 slot = (i64)row * tiles_n + (t / tiles_m);
         reinterpret_cast<float*>(c)[slot] = best_v;
         epi.arg_idx[slot] = best_i;
       }
@@ -334,6 +387,18 @@ __global__ void __launch_bounds__(128) argmax_tiles_kernel(const float* __restri
   if (lane == 0) out[row] = bi < 0 ? 0 : bi;
 }
 
+static i64 sm_count() {
+  static int counts[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return WKB_SM_COUNT;
+  if (!counts[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = WKB_SM_COUNT;
+    counts[dev] = n;
+  }
+  return counts[dev];
+}
+
 static int* gemm_status_word() {
   // one device word per device for the bounded-wait status; allocated at first use
   static int* words[64] = {nullptr};
@@ -384,7 +449,8 @@ int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i6
     attr_set[dev & 63][slot] = true;
   }
   GemmEpi epi{bias, residual, ldr, (int)act, c_bf16, nullptr};
-  dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
+  i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
   kern<<<grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
   return (int)cudaGetLastError();
 }
@@ -416,16 +482,18 @@ int wkb_gemm_bf16_nt_argmax(const void* a, i64 lda, const void* b, i64 ldb, i64 
     attr_set[dev & 63] = true;
   }
   GemmEpi epi{bias, nullptr, 0, 0, 0, part_idx};
-  dim3 grid((unsigned)((n + BN - 1) / BN), (unsigned)((m + BM - 1) / BM));
+  i64 tiles_n = (n + BN - 1) / BN, tiles = tiles_n * ((m + BM - 1) / BM);
+  unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
   kern<<<grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(ma, mb, part_val, 0, (int)m, (int)n, (int)k, epi, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  argmax_tiles_kernel<<<(unsigned)((m * 32 + 127) / 128), 128, 0, as_stream(stream)>>>(part_val, part_idx, (int)grid.x, out, (int)m);
+  argmax_tiles_kernel<<<(unsigned)((m * 32 + 127) / 128), 128, 0, as_stream(stream)>>>(part_val, part_idx, (int)tiles_n, out, (int)m);
   return (int)cudaGetLastError();
 }
 
 // Reads (and clears) the bounded-wait status of the tensor-core GEMM on the current device:
-// 0 = every wait completed; 1 / 2 / 3 = the producer / MMA / epilogue wait ran out.  Synchronises.
+// 0 = every wait completed; 1 / 2 / 3 / 4 = the producer / MMA-operand / epilogue / MMA-accumulator
+// wait ran out.  Synchronises.
 int wkb_gemm_status(void) {
   int* status = gemm_status_word();
   if (!status) return -1;

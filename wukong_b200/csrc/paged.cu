@@ -94,17 +94,21 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
     // ---- issue every K (and, when registers allow, V) load of the tile before any math, so one
     //      warp keeps up to 2 * STEPS * 512 B in flight
     uint4 kw[STEPS], vw[PREFETCH_V ? STEPS : 1];
+    // The tile's page ids (at most 8 for 4-token pages) are fetched by the first lanes in one go and
+    // handed out by shuffle, so no K/V load waits on its own table lookup.  Tokens past the visible
+    // end are clamped onto the last visible token: their loads are real (finite) data and their
+    // weight is forced to zero below, which keeps the whole block free of branches.
+    const int last_tok = t1 - 1;
+    const int first_page = tile0 >> g.page_shift;
+    const int last_page = last_tok >> g.page_shift;
+    uint32_t my_page = bt[min(first_page + (lane & 7), last_page)];
 #pragma unroll
     for (int s = 0; s < STEPS; ++s) {
-      int tok = tile0 + s * TPW + grp;
-      kw[s] = make_uint4(0, 0, 0, 0);
-      if (PREFETCH_V) vw[PREFETCH_V ? s : 0] = make_uint4(0, 0, 0, 0);
-      if (tok < t1) {
-        uint32_t page = bt[tok >> g.page_shift];
-        i64 idx = (i64)page * page_units + head_off + (i64)(tok & (g.page_tokens - 1)) * LPT + j;
-        kw[s] = kcache[idx];
-        if (PREFETCH_V) vw[PREFETCH_V ? s : 0] = vcache[idx];
-      }
+      int tok = min(tile0 + s * TPW + grp, last_tok);
+      uint32_t page = __shfl_sync(0xffffffffu, my_page, (tok >> g.page_shift) - first_page);
+      i64 idx = (i64)page * page_units + head_off + (i64)(tok & (g.page_tokens - 1)) * LPT + j;
+      kw[s] = kcache[idx];
+      if (PREFETCH_V) vw[PREFETCH_V ? s : 0] = vcache[idx];
     }
     // ---- scores: partial dots of this lane's 8 dims, for token (s*TPW + grp) at each step s
     float part[G][STEPS];
@@ -153,13 +157,12 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
     // ---- values: acc[dims of this lane] += p(token) * v(token)
 #pragma unroll
     for (int s = 0; s < STEPS; ++s) {
-      int tok = tile0 + s * TPW + grp;
-      bool ok = tok < t1;
-      uint4 vcur = make_uint4(0, 0, 0, 0);
+      uint4 vcur;
       if (PREFETCH_V) {
         vcur = vw[PREFETCH_V ? s : 0];
-      } else if (ok) {
-        uint32_t page = bt[tok >> g.page_shift];
+      } else {
+        int tok = min(tile0 + s * TPW + grp, last_tok);
+        uint32_t page = __shfl_sync(0xffffffffu, my_page, (tok >> g.page_shift) - first_page);
         vcur = vcache[(i64)page * page_units + head_off + (i64)(tok & (g.page_tokens - 1)) * LPT + j];
       }
       float vf[8];

@@ -1,0 +1,174 @@
+"""Kernel micro-suite: per-kernel throughput against the measured roofline.
+
+    python -m wukong_b200.microbench            # prints one JSON line per case
+
+Cases (seeded synthetic inputs of the named shapes):
+  gemm_bf16      C = A.B^T, M = N = K in {1024, 4096, 8192}, inputs ~N(0,1), fp32 accumulate
+  gemv_q4_0      y = W.x, W 4096x4096 and 11008x4096 Q4_0 (f16 scale ~|N(0,0.02)|, nibbles uniform),
+                 reference contract (Q8 activation, exact block dots) and bf16-activation variant
+  rmsnorm/softmax  8192 rows x 4096, bf16
+  paged_attn     batch 64, ctx uniform [128, 4096], 32 q heads / 8 kv heads, d = 128, bf16, 16-token pages
+Memory-bound kernels rotate through enough distinct operand sets to exceed the 126 MB L2; every case
+is timed with CUDA events over one CUDA graph of `reps` launches after warm-up.
+"""
+import json
+import math
+import os
+import sys
+
+import numpy as np
+import torch
+
+from . import device as dev
+from ._lib import lib, check, require_gpu
+
+L2_BYTES = 126 << 20
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as fh:
+            p = json.load(fh)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def time_graph(fn, reps, warm=3):
+    """Average microseconds per call of `fn(i)`, i = 0..reps-1, replayed as one CUDA graph."""
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for i in range(min(warm, reps)):
+            fn(i)
+        st.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(reps):
+                fn(i)
+        g.replay()
+        st.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        g.replay()
+        e1.record(st)
+        st.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def _s():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def case_gemm(size, hbm, tf, src):
+    a = torch.randn(size, size, device="cuda").to(torch.bfloat16)
+    b = torch.randn(size, size, device="cuda").to(torch.bfloat16)
+    c = torch.empty(size, size, device="cuda")
+    us = time_graph(lambda i: dev.gemm_bf16_nt(a, b, out=c), 10)
+    t = 2 * size ** 3 / us / 1e6
+    return {"case": "gemm_bf16", "shape": [size] * 3, "us": us, "achieved": t, "unit": "TFLOP/s", "bound": "tensor", "peak": tf,
+            "frac": t / tf, "peak_source": "of " + src}
+
+
+def q4_weights(n, k, rng):
+    nb = k // 32
+    raw = rng.integers(0, 256, (n * nb, 18), dtype=np.uint8)
+    sc = np.abs(rng.standard_normal(n * nb) * 0.02).astype(np.float16).view(np.uint16)
+    raw[:, 0] = sc & 0xFF
+    raw[:, 1] = sc >> 8
+    return raw.reshape(-1)
+
+
+def case_gemv_q4(n, k, variant, hbm, tf, src):
+    rng = np.random.default_rng(0)
+    nb = k // 32
+    bytes_w = n * nb * 18
+    copies = max(2, L2_BYTES * 3 // bytes_w + 1)
+    planes = []
+    raw = torch.from_numpy(q4_weights(n, k, rng)).cuda()
+    for _ in range(copies):
+        planes.append(dev.q_split(raw, n * nb, q4=True))
+    x = torch.randn(k, device="cuda")
+    xb = x.to(torch.bfloat16)
+    y = torch.empty(n, device="cuda")
+    xq, dx, sx = dev.quantize_act(x)
+    if variant == "contract":
+        def fn(i):
+            qs, d = planes[i % copies]
+            check(lib().wkb_quantize_act(x.data_ptr(), k, xq.data_ptr(), dx.data_ptr(), sx.data_ptr(), _s()), "qact")
+            dev.gemv_q_contract(qs, d, xq, dx, sx, n, k, out=y)
+    else:
+        def fn(i):
+            qs, d = planes[i % copies]
+            dev.gemv_q4_0_bf16x(qs, d, xb, n, k, out=y)
+    us = time_graph(fn, copies * 2)
+    alg = bytes_w + 2 * k + 4 * n
+    gbs = alg / us / 1e3
+    return {"case": "gemv_q4_0_" + variant, "shape": [n, k], "us": us, "achieved": gbs, "unit": "GB/s", "bound": "hbm", "peak": hbm,
+            "frac": gbs / hbm, "algorithmic_bytes": alg, "rotating_copies": copies, "peak_source": "of " + src}
+
+
+def case_norm(op, hbm, tf, src):
+    rows, cols = 8192, 4096
+    copies = 4                                   # 4 x 64 MB inputs
+    xs = [torch.randn(rows, cols, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+    out = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
+    g = torch.ones(cols, device="cuda")
+    us = time_graph(lambda i: dev.norm_fast(xs[i % copies], op, 1e-5, g if op else None, None, out=out), 12)
+    alg = 2 * rows * cols * 2 + (cols * 4 if op else 0)
+    gbs = alg / us / 1e3
+    return {"case": {0: "softmax_bf16", 2: "rmsnorm_bf16", 1: "layernorm_bf16"}[op], "shape": [rows, cols], "us": us, "achieved": gbs,
+            "unit": "GB/s", "bound": "hbm", "peak": hbm, "frac": gbs / hbm, "algorithmic_bytes": alg, "peak_source": "of " + src}
+
+
+def case_paged_attn(hbm, tf, src):
+    rng = np.random.default_rng(0)
+    B, H, HKV, D, page, pool = 64, 32, 8, 128, 16, 65536
+    ctx = rng.integers(128, 4097, B).astype(np.int32)
+    mbps = 256
+    perm = rng.permutation(pool).astype(np.uint32)
+    table = np.zeros((B, mbps), np.uint32)
+    nxt = 0
+    for b in range(B):
+        n = (int(ctx[b]) + page - 1) // page
+        table[b, :n] = perm[nxt:nxt + n]
+        nxt += n
+    kv = dev.PagedKV(1, pool, HKV, D, page)
+    kv.k.normal_()
+    kv.v.normal_()
+    q = torch.randn(B, H * D, device="cuda")
+    bt = torch.from_numpy(table.view(np.int32)).cuda()
+    row_slot = torch.arange(B, dtype=torch.int32, device="cuda")
+    row_ctx = torch.from_numpy(ctx).cuda()
+    out = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
+    scratch = dev.paged_attn_scratch(B, H, D, 4096)
+    fn = lambda i: dev.paged_attn_decode(q, H * D, kv, 0, bt, row_slot, row_ctx, out, B, H, mbps, 4096, 1.0 / math.sqrt(D), scratch)
+    us = time_graph(fn, 10)
+    alg = float(ctx.sum()) * 2 * HKV * D * 2 + B * H * D * (4 + 2) + B * mbps * 4
+    gbs = alg / us / 1e3
+    return {"case": "paged_attn_decode", "shape": {"batch": B, "q_heads": H, "kv_heads": HKV, "d": D, "ctx": "U[128,4096]"}, "us": us,
+            "achieved": gbs, "unit": "GB/s", "bound": "hbm", "peak": hbm, "frac": gbs / hbm, "algorithmic_bytes": alg,
+            "note": "555 MB of KV per launch exceeds L2", "peak_source": "of " + src}
+
+
+def run(out=sys.stdout):
+    require_gpu()
+    hbm, tf, src = peaks()
+    results = []
+    for size in (1024, 4096, 8192):
+        results.append(case_gemm(size, hbm, tf, src))
+    for (n, k) in ((4096, 4096), (11008, 4096)):
+        for variant in ("contract", "bf16x"):
+            results.append(case_gemv_q4(n, k, variant, hbm, tf, src))
+    for op in (2, 0):
+        results.append(case_norm(op, hbm, tf, src))
+    results.append(case_paged_attn(hbm, tf, src))
+    if dev.gemm_status() != 0:
+        raise RuntimeError("tensor-core GEMM reported an expired pipeline wait")
+    for r in results:
+        print(json.dumps(r), file=out, flush=True)
+    return results
+
+
+if __name__ == "__main__":
+    run()
