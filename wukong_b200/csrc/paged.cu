@@ -25,7 +25,7 @@
 
 namespace wkb {
 
-constexpr int PA_CHUNK = 128;   // logical tokens per work unit
+constexpr int PA_CHUNK_MIN = 128;   // smallest split of the logical sequence (sizes the scratch)
 constexpr int PA_WARPS = 4;
 
 __device__ __forceinline__ void unpack8(const uint4& w, float f[8]) {
@@ -36,7 +36,7 @@ __device__ __forceinline__ void unpack8(const uint4& w, float f[8]) {
 }
 
 struct PagedGeo {
-  int rows, q_heads, kv_heads, page_tokens, page_shift, mbps, max_chunks;
+  int rows, q_heads, kv_heads, page_tokens, page_shift, mbps, max_chunks, chunk_tokens;
   i64 q_row_stride;
 };
 
@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   constexpr int STEPS = LPT;        // steps per tile (so the reduce-scatter is square)
   constexpr int TILE = STEPS * TPW; // 32 tokens
   constexpr bool PREFETCH_V = (HD == 64) || (G <= 2);
+  constexpr bool DOUBLE_BUFFER = (HD == 64 && G <= 2) || (HD == 128 && G == 1);
   static_assert(TILE == 32, "tile is one token per lane");
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int grp = lane / LPT, j = lane % LPT;
@@ -63,14 +64,14 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   const int kvh = (int)(unit % g.kv_heads);
   const int row = (int)((unit / g.kv_heads) % g.rows);
   const int ctx = row_ctx[row];
-  const int t0 = chunk * PA_CHUNK;
+  const int t0 = chunk * g.chunk_tokens;
   float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
   const i64 head_stride = (i64)g.max_chunks * (HD + 4);
   if (t0 >= ctx) {  // nothing visible in this chunk: mark it empty
     if (lane < G) { float* s = sbase + lane * head_stride; s[HD] = -INFINITY; s[HD + 1] = 0.0f; }
     return;
   }
-  const int t1 = min(ctx, t0 + PA_CHUNK);
+  const int t1 = min(ctx, t0 + g.chunk_tokens);
   const uint32_t* bt = block_table + (i64)row_slot[row] * g.mbps;
   // this lane's 8 query dims for each head of the group, pre-scaled by scale*log2(e)
   float qv[G][8];
@@ -90,18 +91,16 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   }
   const i64 page_units = (i64)g.kv_heads * g.page_tokens * LPT;  // uint4 per page
   const i64 head_off = (i64)kvh * g.page_tokens * LPT;
-  for (int tile0 = t0; tile0 < t1; tile0 += TILE) {
-    // ---- issue every K (and, when registers allow, V) load of the tile before any math, so one
-    //      warp keeps up to 2 * STEPS * 512 B in flight
-    uint4 kw[STEPS], vw[PREFETCH_V ? STEPS : 1];
-    // The tile's page ids (at most 8 for 4-token pages) are fetched by the first lanes in one go and
-    // handed out by shuffle, so no K/V load waits on its own table lookup.  Tokens past the visible
-    // end are clamped onto the last visible token: their loads are real (finite) data and their
-    // weight is forced to zero below, which keeps the whole block free of branches.
-    const int last_tok = t1 - 1;
+  // Tokens past the visible end are clamped onto the last visible token: their loads are real
+  // (finite) data and their weight is forced to zero, which keeps the loops free of branches.
+  const int last_tok = t1 - 1;
+  const int last_page = last_tok >> g.page_shift;
+  // Issue every K (and, when registers allow, V) load of one 32-token tile.  The tile's page ids (at
+  // most 8 for 4-token pages) are fetched by the first lanes in one go and handed out by shuffle, so
+  // no K/V load waits on its own table lookup.
+  auto load_tile = [&](int tile0, uint4 (&kw)[STEPS], uint4 (&vw)[PREFETCH_V ? STEPS : 1], uint32_t& my_page) {
     const int first_page = tile0 >> g.page_shift;
-    const int last_page = last_tok >> g.page_shift;
-    uint32_t my_page = bt[min(first_page + (lane & 7), last_page)];
+    my_page = bt[min(first_page + (lane & 7), last_page)];
 #pragma unroll
     for (int s = 0; s < STEPS; ++s) {
       int tok = min(tile0 + s * TPW + grp, last_tok);
@@ -110,6 +109,10 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
       kw[s] = kcache[idx];
       if (PREFETCH_V) vw[PREFETCH_V ? s : 0] = vcache[idx];
     }
+  };
+  auto compute_tile = [&](int tile0, uint4 (&kw)[STEPS], uint4 (&vw)[PREFETCH_V ? STEPS : 1], uint32_t my_page) {
+    const int first_page = tile0 >> g.page_shift;
+    (void)first_page; (void)my_page;
     // ---- scores: partial dots of this lane's 8 dims, for token (s*TPW + grp) at each step s
     float part[G][STEPS];
 #pragma unroll
@@ -174,6 +177,27 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
         for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(pt, vf[e], acc[h][e]);
       }
     }
+  };
+  if constexpr (DOUBLE_BUFFER) {
+    // Two register buffers: the next tile's loads are in flight while the current tile is reduced.
+    uint4 kwA[STEPS], vwA[PREFETCH_V ? STEPS : 1], kwB[STEPS], vwB[PREFETCH_V ? STEPS : 1];
+    uint32_t pgA = 0, pgB = 0;
+    load_tile(t0, kwA, vwA, pgA);
+    for (int tile0 = t0; tile0 < t1; tile0 += 2 * TILE) {
+      if (tile0 + TILE < t1) load_tile(tile0 + TILE, kwB, vwB, pgB);
+      compute_tile(tile0, kwA, vwA, pgA);
+      if (tile0 + TILE < t1) {
+        if (tile0 + 2 * TILE < t1) load_tile(tile0 + 2 * TILE, kwA, vwA, pgA);
+        compute_tile(tile0 + TILE, kwB, vwB, pgB);
+      }
+    }
+  } else {
+    uint4 kw[STEPS], vw[PREFETCH_V ? STEPS : 1];
+    uint32_t pg = 0;
+    for (int tile0 = t0; tile0 < t1; tile0 += TILE) {
+      load_tile(tile0, kw, vw, pg);
+      compute_tile(tile0, kw, vw, pg);
+    }
   }
   // ---- combine the token groups (fixed xor tree over the group bits), then the lane sums of l
 #pragma unroll
@@ -198,7 +222,7 @@ template <int HD>
 __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const float* __restrict__ scratch, void* __restrict__ out,
                                                                int out_dtype, i64 out_row_stride,
                                                                const int* __restrict__ row_ctx, int rows, int q_heads,
-                                                               int max_chunks) {
+                                                               int max_chunks, int chunk_tokens) {
   i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x;
   i64 total = (i64)rows * q_heads * (HD / 4);
   if (idx >= total) return;
@@ -206,7 +230,7 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const float* __re
   i64 rh = idx / (HD / 4);
   int row = (int)(rh / q_heads), h = (int)(rh % q_heads);
   int ctx = row_ctx[row];
-  int nch = ctx <= 0 ? 0 : (ctx + PA_CHUNK - 1) / PA_CHUNK;
+  int nch = ctx <= 0 ? 0 : (ctx + chunk_tokens - 1) / chunk_tokens;
   if (nch > max_chunks) nch = max_chunks;
   const float* s = scratch + rh * (i64)max_chunks * (HD + 4);
   float mm = -INFINITY;
@@ -276,7 +300,7 @@ static int launch_decode(const float* q, const void* kc, const void* vc, const u
   if (e != cudaSuccess) return (int)e;
   i64 total = (i64)g.rows * g.q_heads * (HD / 4);
   paged_attn_merge_kernel<HD><<<(unsigned)((total + 127) / 128), 128, 0, st>>>(scratch, out, out_dtype, out_row_stride,
-                                                                                row_ctx, g.rows, g.q_heads, g.max_chunks);
+                                                                                row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens);
   return (int)cudaGetLastError();
 }
 
@@ -287,7 +311,7 @@ using namespace wkb;
 extern "C" {
 
 i64 wkb_paged_attn_scratch_bytes(i64 rows, i64 q_heads, i64 head_dim, i64 max_ctx) {
-  i64 chunks = (max_ctx + PA_CHUNK - 1) / PA_CHUNK;
+  i64 chunks = (max_ctx + PA_CHUNK_MIN - 1) / PA_CHUNK_MIN;   // worst case: the smallest split
   if (chunks < 1) chunks = 1;
   return rows * q_heads * chunks * (head_dim + 4) * 4;
 }
@@ -305,9 +329,16 @@ int wkb_paged_attn_decode(const float* q, i64 q_row_stride, const void* kcache, 
   if ((q_row_stride % 4) != 0 || ((((uintptr_t)q) | ((uintptr_t)scratch) | ((uintptr_t)kcache) | ((uintptr_t)vcache)) & 15) != 0)
     return (int)cudaErrorMisalignedAddress;
   if (out_row_stride % 4 != 0 || (((uintptr_t)out) & 15) != 0) return (int)cudaErrorMisalignedAddress;
-  i64 chunks = (max_ctx + PA_CHUNK - 1) / PA_CHUNK;
+  // How finely a sequence is split depends on the launch shape only (never on the data): few
+  // (row, kv head) pairs need the split for parallelism, many pairs are better off amortising the
+  // per-unit set-up over longer runs.
+  // Aim for about 4096 units at full context, between 128 and 512 tokens each.
+  i64 want = rows * kv_heads * (max_ctx > 0 ? max_ctx : 1) / 4096;
+  int chunk_tokens = PA_CHUNK_MIN;
+  while (chunk_tokens < 512 && chunk_tokens * 2 <= want) chunk_tokens *= 2;
+  i64 chunks = (max_ctx + chunk_tokens - 1) / chunk_tokens;
   if (chunks < 1) chunks = 1;
-  PagedGeo g{(int)rows, (int)q_heads, (int)kv_heads, (int)page_tokens, page_shift, (int)max_blocks_per_seq, (int)chunks, q_row_stride};
+  PagedGeo g{(int)rows, (int)q_heads, (int)kv_heads, (int)page_tokens, page_shift, (int)max_blocks_per_seq, (int)chunks, chunk_tokens, q_row_stride};
   int G = (int)(q_heads / kv_heads);
   cudaStream_t st = as_stream(stream);
 #define WKB_PA_CASE(HD_, G_) \
