@@ -299,17 +299,22 @@ def run_ours(args):
     a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     p = lambda t: t.data_ptr()
     with torch.cuda.stream(eng.stream):
-        s = eng.stream.cuda_stream
         def attn(li):
+            s = torch.cuda.current_stream().cuda_stream
             check(lib().wkb_paged_attn_decode(p(m.qkv), 3 * d, p(m.kv.k[li]), p(m.kv.v[li]), p(m.block_table), p(m.row_slot), p(m.row_ctx),
                                               p(m.att), 1, d, S, cfg.n_head, cfg.n_head, cfg.head_dim, PAGE, MBPS, m.max_ctx, m.scale,
                                               p(m.scratch), s), "attn")
         for li in range(cfg.n_layer):
             attn(li)
-        a0.record(eng.stream)
-        for _ in range(reps):
+        eng.stream.synchronize()
+        ag = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(ag, stream=eng.stream):
             for li in range(cfg.n_layer):
                 attn(li)
+        ag.replay()
+        a0.record(eng.stream)
+        for _ in range(reps):
+            ag.replay()
         a1.record(eng.stream)
     eng.stream.synchronize()
     attn_ms = a0.elapsed_time(a1) / (reps * cfg.n_layer)
@@ -317,8 +322,11 @@ def run_ours(args):
     attn_bytes = float(ctx_end.sum()) * 2 * d * 2 + S * d * (4 + 2) + S * 4 * 2
     peak, peak_kind = hbm_peak()
     achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+    # DRAM traffic per launch: 1.04 x the algorithmic bytes, from the ncu capture summarised in
+    # profiles/paged_attn_decode_ncu.md (taken at 128 sequences; traffic grows with the visible tokens)
     roofline = {"kernel": "paged_attn_decode_kernel<64,1> (+ chunk merge)", "bound": "hbm", "achieved": achieved, "peak": peak,
-                "peak_source": "of " + peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "peak_source": "of " + peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": 1.04 * attn_bytes,
+                "traffic_source": "ncu at 128 sequences, scaled by visible tokens",
                 "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
                 "share_of_step": attn_ms * cfg.n_layer / (dev_ms / K)}
 
