@@ -167,6 +167,27 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------
 # this library, one replica per GPU
 # ------------------------------------------------------------------------------------------------
+def shard_prompts(rank, seqs, vocab):
+    """This rank's shard of the workload: `seqs` prompts drawn from a rank-specific seeded stream, so
+    the global job is world x seqs distinct sequences and no two ranks share one (replicas exchange
+    nothing on the data path)."""
+    import numpy as np
+    rng = np.random.default_rng(100 + rank)
+    lens = rng.integers(PROMPT_LO, PROMPT_HI + 1, seqs)
+    return [rng.integers(0, vocab, int(L)) for L in lens]
+
+
+def max_over_ranks_ms(ms, world, device):
+    """Whole-job time of a region = the slowest rank's device time."""
+    if world == 1:
+        return ms
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def hbm_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -199,15 +220,15 @@ def run_ours(args):
     eng = Engine(cfg, weights, bcap=S, num_pages=num_pages, max_blocks_per_seq=MBPS, max_rows=max(8192, S),
                  prefill_chunk=512, page_tokens=PAGE, device="cuda:%d" % local)
     m, sched = eng.model, eng.sched
-    rng = np.random.default_rng(100 + rank)
-    lens = rng.integers(PROMPT_LO, PROMPT_HI + 1, S)
+    prompts = shard_prompts(rank, S, cfg.vocab)
+    lens = np.array([p.size for p in prompts])
     budget = MBPS * PAGE - PROMPT_HI - 8          # decode positions available to every sequence
     need = 2 * (K + W) + 40
     if need > budget:
         raise SystemExit("steps + warmup too large for the block-table width: need %d decode positions, have %d" % (need, budget))
     gen_len = max(GEN_NOMINAL, need + 64)         # nobody retires inside the measurement
-    for L in lens:
-        eng.enqueue(rng.integers(0, cfg.vocab, int(L)), gen_len)
+    for pr in prompts:
+        eng.enqueue(pr, gen_len)
 
     # ---- prefill (untimed): run engine steps until every sequence is decoding
     t_pre = time.perf_counter()
@@ -232,11 +253,7 @@ def run_ours(args):
             torch.cuda.synchronize()
 
     def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return max_over_ranks_ms(ms, world, "cuda")
 
     clocks = ClockSampler(local)
 
