@@ -259,6 +259,12 @@ int wkb_gemm_bf16_nt(const void* a, int64_t lda, const void* b, int64_t ldb, voi
                      int64_t m, int64_t n, int64_t k, const float* bias, int64_t act, const float* residual,
                      int64_t ldr, void* stream);
 int wkb_gemm_status(void);
+/* The same GEMM over OCP E4M3FN codes (one byte per element, the codec of crates/wukong_runtime/src/fp8.rs
+ * :66-164; the reference's GPU counterpart is ptx_fp8.rs `fp8_gemm_nt*`): tcgen05 kind::f8f6f4, fp32
+ * accumulate, K % 16 == 0, pitches multiples of 16. */
+int wkb_gemm_e4m3_nt(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int c_bf16,
+                     int64_t m, int64_t n, int64_t k, const float* bias, int64_t act, const float* residual,
+                     int64_t ldr, void* stream);
 /* Greedy sampling fused into the LM-head GEMM: out[i] = argmax_j (A.B^T + bias)[i,j]; the logits are
  * never written.  part_val / part_idx are scratch of m * wkb_gemm_argmax_tiles(n) elements each. */
 int64_t wkb_gemm_argmax_tiles(int64_t n);

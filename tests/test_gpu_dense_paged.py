@@ -79,6 +79,33 @@ def test_gemm_fused_argmax_equals_argmax_of_logits(dev, orc):
     assert dev.gemm_status() == 0
 
 
+def test_gemm_e4m3_matches_decode_then_gemm(dev, orc):
+    """f8 GEMM: the reference has no CPU f8 GEMM, so the oracle is "decode every E4M3 code with the
+    pinned codec, then the fp32 order-contract GEMM" (parity unpinned on the reference side).  Products
+    of two E4M3 values are exact in fp32; only the fp32 summation order differs."""
+    import torch
+    L = orc.lib()
+    table = np.array([L.wko_f8e4m3_to_f32(c) for c in range(256)], np.float32)
+    rng = np.random.default_rng(4)
+    for (m, n, k) in [(128, 128, 128), (70, 200, 48), (512, 768, 1024), (33, 129, 16)]:
+        a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.float8_e4m3fn).view(torch.uint8)
+        b = torch.from_numpy(rng.standard_normal((n, k)).astype(np.float32)).cuda().to(torch.float8_e4m3fn).view(torch.uint8)
+        ac, bc = a.cpu().numpy(), b.cpu().numpy()
+        # torch's encoder agrees with the pinned codec on these values
+        sample = torch.from_numpy(ac[:2].copy()).view(torch.float8_e4m3fn).float().numpy()
+        assert np.array_equal(sample, table[ac[:2]])
+        af, bf = table[ac], table[bc]
+        ref = orc.sgemm(af, bf, m, k, n, "nt")
+        got = dev.gemm_e4m3_nt(a, b).cpu().numpy()
+        bound = 1e-5 * (np.abs(af) @ np.abs(bf).T) + 1e-6
+        assert (np.abs(got - ref) <= bound).all(), (m, n, k, np.abs(got - ref).max())
+        bias = rng.standard_normal(n).astype(np.float32)
+        gote = dev.gemm_e4m3_nt(a, b, bias=torch.from_numpy(bias).cuda(), act=3).cpu().numpy()
+        refe = orc.sgemm(af, bf, m, k, n, bias=bias, act=3)
+        assert (np.abs(gote - refe) <= 1.2 * bound + 1e-5).all()
+    assert dev.gemm_status() == 0
+
+
 def test_norm_fast_matches_oracle_recipe(dev, orc):
     """bf16 rows: widen -> the oracle's fp32 norm -> round once.  The fast kernel reduces in a
     different order, so outputs may differ by one bf16 ulp on a few lanes: rtol 2e-2 (the bf16 bar)."""

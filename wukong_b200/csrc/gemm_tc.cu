@@ -32,8 +32,10 @@
 
 namespace wkb {
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 5, UMMA_K = 16;
-constexpr int TILE_A_BYTES = BM * BK * 2, TILE_B_BYTES = BN * BK * 2;
+constexpr int BM = 128, BN = 128, STAGES = 5;
+constexpr int BK_BYTES = 128;   // one 128-byte swizzle row of K per stage: 64 bf16 or 128 e4m3 elements
+constexpr int UMMA_K_BYTES = 32;  // K extent of one tcgen05.mma: 16 bf16 or 32 e4m3 elements
+constexpr int TILE_A_BYTES = BM * BK_BYTES, TILE_B_BYTES = BN * BK_BYTES;
 constexpr int STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 256;             // two 128-column accumulator buffers
@@ -86,12 +88,21 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr) {
 // Instruction descriptor, kind::f16: D = f32 (1 << 4), A = B = bf16 (1 << 7, 1 << 10), both K-major,
 // N >> 3 in bits 17-22, M >> 4 in bits 24-28.
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// kind::f8f6f4 with A = B = E4M3 (format code 0), D = f32.
+constexpr uint32_t IDESC_F8 = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
       " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_e4m3(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC_F8), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -143,7 +154,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // Persistent kernel: CTA b works on tiles b, b + gridDim.x, ...; tile t is (m_tile = t % tiles_m,
 // n_tile = t / tiles_m), so CTAs running side by side share one B (weight) tile through L2.
 // ACT / OUT_BF16 / ARGMAX are compile-time so an identity epilogue carries no transcendental code.
-template <int ACT, bool OUT_BF16, bool ARGMAX>
+template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c,
                     i64 ldc, int M, int N, int K, GemmEpi epi, int* status) {
@@ -163,6 +174,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
+  constexpr int BK = F8 ? BK_BYTES : BK_BYTES / 2;  // elements of K per stage
   const int kiters = (K + BK - 1) / BK;
   if (threadIdx.x == 0) WKB_TRACE(0);
 
@@ -222,8 +234,11 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_A_BYTES;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(tmem_d, make_sdesc(sa + k * UMMA_K * 2), make_sdesc(sb + k * UMMA_K * 2), (kk > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK_BYTES / UMMA_K_BYTES; ++k) {
+            const uint64_t ad = make_sdesc(sa + k * UMMA_K_BYTES), bd = make_sdesc(sb + k * UMMA_K_BYTES);
+            if (F8) umma_e4m3(tmem_d, ad, bd, (kk > 0 || k > 0) ? 1u : 0u);
+            else umma_bf16(tmem_d, ad, bd, (kk > 0 || k > 0) ? 1u : 0u);
+          }
           umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
         }
         if (ok) umma_commit(tfull_bar(buf));
@@ -349,15 +364,16 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 
-// 2-D bf16 tensor [rows, k] with row pitch ld elements; box = [BK, box_rows]; 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* ptr, i64 rows, i64 k, i64 ld, int box_rows) {
+// 2-D tensor [rows, k] of bf16 (or 1-byte e4m3) with row pitch ld elements; box = [128 bytes of K,
+// box_rows]; 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, i64 rows, i64 k, i64 ld, int box_rows, bool f8 = false) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return (int)cudaErrorNotSupported;
   cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (f8 ? 1 : 2)};
+  cuuint32_t box[2] = {(cuuint32_t)(f8 ? BK_BYTES : BK_BYTES / 2), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  CUresult r = enc(map, f8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
@@ -434,10 +450,47 @@ int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i6
   if (act < 0 || act > 3) return (int)cudaErrorInvalidValue;
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, void*, i64, int, int, int, GemmEpi, int*);
   static const KernelFn table[4][2] = {
-      {gemm_bf16_tc_kernel<0, false, false>, gemm_bf16_tc_kernel<0, true, false>},
-      {gemm_bf16_tc_kernel<1, false, false>, gemm_bf16_tc_kernel<1, true, false>},
-      {gemm_bf16_tc_kernel<2, false, false>, gemm_bf16_tc_kernel<2, true, false>},
-      {gemm_bf16_tc_kernel<3, false, false>, gemm_bf16_tc_kernel<3, true, false>}};
+      {gemm_bf16_tc_kernel<0, false, false, false>, gemm_bf16_tc_kernel<0, true, false, false>},
+      {gemm_bf16_tc_kernel<1, false, false, false>, gemm_bf16_tc_kernel<1, true, false, false>},
+      {gemm_bf16_tc_kernel<2, false, false, false>, gemm_bf16_tc_kernel<2, true, false, false>},
+      {gemm_bf16_tc_kernel<3, false, false, false>, gemm_bf16_tc_kernel<3, true, false, false>}};
+  KernelFn kern = table[act][c_bf16 ? 1 : 0];
+  static bool attr_set[64][8] = {{false}};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int slot = (int)act * 2 + (c_bf16 ? 1 : 0);
+  if (!attr_set[dev & 63][slot]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63][slot] = true;
+  }
+  GemmEpi epi{bias, residual, ldr, (int)act, c_bf16, nullptr};
+  i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
+  kern<<<grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
+  return (int)cudaGetLastError();
+}
+
+// E4M3 x E4M3 -> fp32 accumulate: same kernel with kind::f8f6f4 MMAs and 128 elements of K per stage.
+int wkb_gemm_e4m3_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i64 ldc, int c_bf16, i64 m, i64 n, i64 k,
+                     const float* bias, i64 act, const float* residual, i64 ldr, void* stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if (k % 16 != 0 || lda % 16 != 0 || ldb % 16 != 0) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)a) | ((uintptr_t)b)) & 15) return (int)cudaErrorMisalignedAddress;
+  if (act < 0 || act > 3) return (int)cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, m, k, lda, BM, true);
+  if (rc) return rc;
+  rc = make_map(&mb, b, n, k, ldb, BN, true);
+  if (rc) return rc;
+  int* status = gemm_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, void*, i64, int, int, int, GemmEpi, int*);
+  static const KernelFn table[4][2] = {
+      {gemm_bf16_tc_kernel<0, false, false, true>, gemm_bf16_tc_kernel<0, true, false, true>},
+      {gemm_bf16_tc_kernel<1, false, false, true>, gemm_bf16_tc_kernel<1, true, false, true>},
+      {gemm_bf16_tc_kernel<2, false, false, true>, gemm_bf16_tc_kernel<2, true, false, true>},
+      {gemm_bf16_tc_kernel<3, false, false, true>, gemm_bf16_tc_kernel<3, true, false, true>}};
   KernelFn kern = table[act][c_bf16 ? 1 : 0];
   static bool attr_set[64][8] = {{false}};
   int dev = 0;
@@ -472,7 +525,7 @@ int wkb_gemm_bf16_nt_argmax(const void* a, i64 lda, const void* b, i64 ldb, i64 
   if (rc) return rc;
   int* status = gemm_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
-  auto kern = gemm_bf16_tc_kernel<0, false, true>;
+  auto kern = gemm_bf16_tc_kernel<0, false, true, false>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);

@@ -95,6 +95,18 @@ def gemm_bf16_nt(a, b, bias=None, act=0, residual=None, out_dtype=torch.float32,
     return out
 
 
+def gemm_e4m3_nt(a_codes, b_codes, bias=None, act=0, residual=None, out_dtype=torch.float32):
+    """C = act(a @ b.T + bias) (+ residual) for E4M3FN codes held in uint8 tensors a [M,K], b [N,K]."""
+    m, k = a_codes.shape
+    n = b_codes.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=a_codes.device)
+    ldr = residual.stride(0) if residual is not None else 0
+    check(lib().wkb_gemm_e4m3_nt(_p(a_codes), a_codes.stride(0), _p(b_codes), b_codes.stride(0), _p(out), out.stride(0),
+                                 int(out.dtype == torch.bfloat16), m, n, k, _p(bias), act, _p(residual), ldr, _s()),
+          "wkb_gemm_e4m3_nt")
+    return out
+
+
 def gemm_status():
     return lib().wkb_gemm_status()
 
