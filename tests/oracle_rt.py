@@ -32,3 +32,9 @@ class OracleRT:
 
     def exp(self, x, out):
         out[:] = self.o.vmath(x, 0).reshape(out.shape)
+
+    def silu(self, x, out):
+        out[:] = self.o.vmath(x, 5).reshape(out.shape)
+
+    def hadamard(self, x, y, out):
+        out[:] = self.o.velem(x, y, 1.0, 1.0, 0.0, 512).reshape(out.shape)

@@ -43,3 +43,17 @@ def test_gpt2_124m_shape_fp32(orc):
     for t in range(7):
         assert got[2][t][0].tobytes() == want[2][t][0].tobytes(), t
     orc.set_threads(1)
+
+
+def test_llama_block_example(orc):
+    """examples/llama_block.wk through the C ABI: the reference's golden values, and every output lane
+    equal to the oracle's run of the same trace."""
+    from wukong_b200 import _lib, runtime, wk_programs
+    from oracle_rt import OracleRT
+    import fixtures_wk as fx
+    _lib.require_gpu()
+    ins = wk_programs.llama_block_inputs()
+    got = wk_programs.llama_block(runtime, **ins)
+    want = wk_programs.llama_block(OracleRT(orc), **ins)
+    assert [int(t) for t in fx.rust_round(got[[0, 64, 256, 511]] * np.float32(10000.0))] == [-1227, 1204, 593, -404]
+    assert got.tobytes() == want.tobytes()

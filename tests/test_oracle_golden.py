@@ -430,3 +430,12 @@ def test_paged_model_layout_invariance(orc):
     st, o = orc.attention_kv_batch(q, kp, vp_, ctx, ctx - 1, slots, 1, skv, qh, kvh, hd, 0.25, True)
     assert st == 0
     np.testing.assert_allclose(o.reshape(slots, -1), outs[0], rtol=1e-4, atol=1e-4)
+
+
+def test_llama_block_example_golden(orc):
+    """examples/llama_block.wk of the reference: `EXPECT-OUT-VALUES: -1227 1204 593 -404`
+    (round(out[k] * 10000) for k = 0, 64, 256, 511), derived there from an independent f64 evaluation."""
+    from oracle_rt import OracleRT
+    from wukong_b200 import wk_programs
+    out = wk_programs.llama_block(OracleRT(orc), **wk_programs.llama_block_inputs())
+    assert [int(t) for t in fx.rust_round(out[[0, 64, 256, 511]] * np.float32(10000.0))] == [-1227, 1204, 593, -404]

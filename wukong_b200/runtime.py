@@ -120,6 +120,16 @@ def silu_gate(a, b, out):
     lib().wukong_vmath2_f32(_p(_f32(a)), _p(_f32(b)), _p(_f32(out)), a.size, 9)
 
 
+def hadamard(x, y, out):
+    """out = x * y, the `VE_HADAMARD` form of wukong_velem_f32 (velem.rs:46)."""
+    lib().wukong_velem_f32(_p(_f32(x)), _p(_f32(y)), _p(_f32(out)), x.size, 1.0, 1.0, 0.0, 512)
+
+
+def residual_add(x, y, out):
+    """out = x + y, the `VE_USE_Y` affine form with a = b = 1, c = 0 (velem.rs:44)."""
+    lib().wukong_velem_f32(_p(_f32(x)), _p(_f32(y)), _p(_f32(out)), x.size, 1.0, 1.0, 0.0, 256)
+
+
 def softmax(x, out, rows, cols):
     lib().wukong_norm_f32(_p(_f32(x)), _p(_f32(out)), rows, cols, 0, NORM_SOFTMAX)
 

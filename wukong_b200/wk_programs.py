@@ -112,3 +112,65 @@ def _strict_argmax(row):
         return 0
     m = np.nanmax(row)
     return int(np.flatnonzero(row == m)[0]) if m > best else bi
+
+
+def llama_block_inputs():
+    """The deterministic operands of examples/llama_block.wk:183-204."""
+    i512, i4096, i16384, i64_ = (np.arange(n) for n in (512, 4096, 16384, 64))
+    f = lambda v: v.astype(F)
+    x = f(i512 % 13) * F(0.02) - F(0.12)
+    wq = f(i4096 % 7) * F(0.01) - F(0.03)
+    wk = f(i4096 % 11) * F(0.008) - F(0.04)
+    wv = f(i4096 % 5) * F(0.012) - F(0.024)
+    wo = f(i4096 % 9) * F(0.009) - F(0.036)
+    wg = f(i16384 % 17) * F(0.004) - F(0.032)
+    wu = f(i16384 % 19) * F(0.003) - F(0.027)
+    wd = f(i16384 % 23) * F(0.0025) - F(0.0275)
+    rg1 = F(1.0) + f(i64_ % 3) * F(0.1)
+    rg2 = F(1.0) - f(i64_ % 4) * F(0.05)
+    return dict(x=x.astype(F), rg1=rg1.astype(F), wq=wq.astype(F), wk=wk.astype(F), wv=wv.astype(F), wo=wo.astype(F),
+                rg2=rg2.astype(F), wg=wg.astype(F), wu=wu.astype(F), wd=wd.astype(F))
+
+
+def llama_block(rt, x, rg1, wq, wk, wv, wo, rg2, wg, wu, wd):
+    """The trace of examples/llama_block.wk:35-181 (S = 8, D = 64, 4 heads of 16, Dff = 256): two affine
+    RMSNorms, seven `sgemm_nt`, one `vmath(silu)` and one Hadamard `velem` are dispatched; the
+    interleaved-pair RoPE and the per-head causal softmax attention are plain loops in the source and run
+    here as float32 numpy in the same operator order."""
+    S, D, H, hd, Dff = 8, 64, 4, 16, 256
+    nrm = np.zeros((S, D), F)
+    rt.rmsnorm(x.reshape(S, D).copy(), rg1, nrm, S, D, 1e-5)
+    q, k, v = (np.zeros((S, D), F) for _ in range(3))
+    rt.matmul_nt(nrm, wq, q, S, D, D)
+    rt.matmul_nt(nrm, wk, k, S, D, D)
+    rt.matmul_nt(nrm, wv, v, S, D, D)
+    # RoPE, interleaved pairs (2p, 2p+1): freq = 10000^(-2p/hd), theta = pos * freq
+    p = np.arange(hd // 2)
+    freq = np.power(F(10000.0), -(2 * p).astype(F) / F(16.0)).astype(F)
+    theta = (np.arange(S, dtype=F)[:, None] * freq[None, :]).astype(F)
+    c, sn = np.cos(theta).astype(F), np.sin(theta).astype(F)
+    for t in (q, k):
+        tv = t.reshape(S, H, hd // 2, 2)
+        t0, t1 = tv[..., 0].copy(), tv[..., 1].copy()
+        tv[..., 0] = t0 * c[:, None, :] - t1 * sn[:, None, :]
+        tv[..., 1] = t0 * sn[:, None, :] + t1 * c[:, None, :]
+    attn = np.zeros((S, D), F)
+    for hh in range(H):
+        sl = slice(hh * hd, (hh + 1) * hd)
+        sc = ((q[:, sl] @ k[:, sl].T) * F(0.25)).astype(F)
+        sc[np.triu_indices(S, 1)] = F(-1.0e30)
+        e = np.exp(sc - sc.max(1, keepdims=True)).astype(F)
+        attn[:, sl] = ((e * (F(1.0) / e.sum(1, keepdims=True))) @ v[:, sl]).astype(F)
+    a = np.zeros((S, D), F)
+    rt.matmul_nt(attn, wo, a, S, D, D)
+    a[:] = x.reshape(S, D) + a
+    rt.rmsnorm(a.copy(), rg2, nrm, S, D, 1e-5)
+    gate, up, h = (np.zeros((S, Dff), F) for _ in range(3))
+    rt.matmul_nt(nrm, wg, gate, S, D, Dff)
+    rt.matmul_nt(nrm, wu, up, S, D, Dff)
+    rt.silu(gate, gate)
+    rt.hadamard(gate, up, h)
+    out = np.zeros((S, D), F)
+    rt.matmul_nt(h, wd, out, S, Dff, D)
+    out[:] = a + out
+    return out.reshape(-1)
