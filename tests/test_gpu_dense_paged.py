@@ -57,6 +57,15 @@ def test_gemm_tc_matches_order_contract_gemm(dev, orc):
     assert torch.equal(c12, dev.gemm_bf16_nt(a1, b) + dev.gemm_bf16_nt(a2, b))  # integers: exact in fp32
     assert torch.equal(c12, (a1 + a2).float() @ b.float().T)
     assert dev.gemm_status() == 0
+    # a shape large enough for the 128 x 256 tile variant (ragged in M and N), exact on small integers
+    a = torch.randint(-3, 4, (2100, 512), device="cuda").to(torch.bfloat16)
+    b = torch.randint(-3, 4, (8200, 512), device="cuda").to(torch.bfloat16)
+    bias = torch.randint(-5, 6, (8200,), device="cuda").float()
+    res = torch.randint(-5, 6, (2100, 8200), device="cuda").float()
+    want = torch.relu(a.float() @ b.float().T + bias) + res
+    assert torch.equal(dev.gemm_bf16_nt(a, b, bias=bias, act=1, residual=res), want)
+    assert torch.equal(dev.gemm_bf16_nt(a, b, bias=bias, act=1, residual=res, out_dtype=torch.bfloat16).float(), want.to(torch.bfloat16).float())
+    assert dev.gemm_status() == 0
 
 
 def test_gemm_fused_argmax_equals_argmax_of_logits(dev, orc):

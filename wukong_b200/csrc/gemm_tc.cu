@@ -38,10 +38,10 @@ constexpr int UMMA_K_BYTES = 32;  // K extent of one tcgen05.mma: 16 bf16 or 32 
 constexpr int TILE_A_BYTES = BM * BK_BYTES, TILE_B_BYTES = BN * BK_BYTES;
 constexpr int STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
 constexpr int GEMM_THREADS = 192;
-constexpr uint32_t TMEM_COLS = 256;             // two 128-column accumulator buffers
 constexpr int EPI_STAGE_BYTES = 4 * 32 * 33 * 4;  // one 32 x 33 fp32 transpose pad per epilogue warp
-constexpr int NUM_BARS = 2 * STAGES + 4;          // full / empty per stage, tmem full / empty per buffer
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int BN_WIDE = 256;
+constexpr int SMEM_BYTES_WIDE = 4 * (TILE_A_BYTES + BN_WIDE * BK_BYTES) + EPI_STAGE_BYTES + 1024 + 256;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -87,22 +87,23 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr) {
 }
 // Instruction descriptor, kind::f16: D = f32 (1 << 4), A = B = bf16 (1 << 7, 1 << 10), both K-major,
 // N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-// kind::f8f6f4 with A = B = E4M3 (format code 0), D = f32.
-constexpr uint32_t IDESC_F8 = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// (kind::f8f6f4 with A = B = E4M3 uses format code 0 for both operands.)
+__host__ __device__ constexpr uint32_t make_idesc(int bn, bool f8) {
+  return (1u << 4) | (f8 ? 0u : ((1u << 7) | (1u << 10))) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
       " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void umma_e4m3(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_e4m3(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
       " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC_F8), "r"(accumulate)
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -154,10 +155,17 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // Persistent kernel: CTA b works on tiles b, b + gridDim.x, ...; tile t is (m_tile = t % tiles_m,
 // n_tile = t / tiles_m), so CTAs running side by side share one B (weight) tile through L2.
 // ACT / OUT_BF16 / ARGMAX are compile-time so an identity epilogue carries no transcendental code.
-template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8>
+template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8, bool WIDE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c,
                     i64 ldc, int M, int N, int K, GemmEpi epi, int* status) {
+  // tile shape of this instantiation: 128 x 128 with a 5-stage ring, or 128 x 256 with 4 stages
+  constexpr int BN = WIDE ? 256 : 128;
+  constexpr int STAGES = WIDE ? 4 : 5;
+  constexpr int TILE_B_BYTES = BN * BK_BYTES, STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
+  constexpr int NUM_BARS = 2 * STAGES + 4;
+  constexpr uint32_t TMEM_COLS = 2 * BN;       // two accumulator buffers
+  constexpr uint32_t IDESC_ = make_idesc(BN, F8);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -236,8 +244,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int k = 0; k < BK_BYTES / UMMA_K_BYTES; ++k) {
             const uint64_t ad = make_sdesc(sa + k * UMMA_K_BYTES), bd = make_sdesc(sb + k * UMMA_K_BYTES);
-            if (F8) umma_e4m3(tmem_d, ad, bd, (kk > 0 || k > 0) ? 1u : 0u);
-            else umma_bf16(tmem_d, ad, bd, (kk > 0 || k > 0) ? 1u : 0u);
+            if (F8) umma_e4m3(tmem_d, ad, bd, IDESC_, (kk > 0 || k > 0) ? 1u : 0u);
+            else umma_bf16(tmem_d, ad, bd, IDESC_, (kk > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
         }
@@ -450,24 +458,37 @@ int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i6
   if (act < 0 || act > 3) return (int)cudaErrorInvalidValue;
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, void*, i64, int, int, int, GemmEpi, int*);
   static const KernelFn table[4][2] = {
-      {gemm_bf16_tc_kernel<0, false, false, false>, gemm_bf16_tc_kernel<0, true, false, false>},
-      {gemm_bf16_tc_kernel<1, false, false, false>, gemm_bf16_tc_kernel<1, true, false, false>},
-      {gemm_bf16_tc_kernel<2, false, false, false>, gemm_bf16_tc_kernel<2, true, false, false>},
-      {gemm_bf16_tc_kernel<3, false, false, false>, gemm_bf16_tc_kernel<3, true, false, false>}};
-  KernelFn kern = table[act][c_bf16 ? 1 : 0];
-  static bool attr_set[64][8] = {{false}};
+      {gemm_bf16_tc_kernel<0, false, false, false, false>, gemm_bf16_tc_kernel<0, true, false, false, false>},
+      {gemm_bf16_tc_kernel<1, false, false, false, false>, gemm_bf16_tc_kernel<1, true, false, false, false>},
+      {gemm_bf16_tc_kernel<2, false, false, false, false>, gemm_bf16_tc_kernel<2, true, false, false, false>},
+      {gemm_bf16_tc_kernel<3, false, false, false, false>, gemm_bf16_tc_kernel<3, true, false, false, false>}};
+  static const KernelFn table_wide[4][2] = {
+      {gemm_bf16_tc_kernel<0, false, false, false, true>, gemm_bf16_tc_kernel<0, true, false, false, true>},
+      {gemm_bf16_tc_kernel<1, false, false, false, true>, gemm_bf16_tc_kernel<1, true, false, false, true>},
+      {gemm_bf16_tc_kernel<2, false, false, false, true>, gemm_bf16_tc_kernel<2, true, false, false, true>},
+      {gemm_bf16_tc_kernel<3, false, false, false, true>, gemm_bf16_tc_kernel<3, true, false, false, true>}};
+  // 128 x 256 tiles halve the operand bytes per flop; they pay off once there are at least two waves of them
+  const i64 tiles_wide = ((n + BN_WIDE - 1) / BN_WIDE) * ((m + BM - 1) / BM);
+  const bool wide = tiles_wide >= 2 * sm_count();
+  if (wide) {
+    rc = make_map(&mb, b, n, k, ldb, BN_WIDE);
+    if (rc) return rc;
+  }
+  KernelFn kern = wide ? table_wide[act][c_bf16 ? 1 : 0] : table[act][c_bf16 ? 1 : 0];
+  const int smem = wide ? SMEM_BYTES_WIDE : SMEM_BYTES;
+  static bool attr_set[64][16] = {{false}};
   int dev = 0;
   cudaGetDevice(&dev);
-  int slot = (int)act * 2 + (c_bf16 ? 1 : 0);
+  int slot = (int)act * 2 + (c_bf16 ? 1 : 0) + (wide ? 8 : 0);
   if (!attr_set[dev & 63][slot]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev & 63][slot] = true;
   }
   GemmEpi epi{bias, residual, ldr, (int)act, c_bf16, nullptr};
-  i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  i64 tiles = wide ? tiles_wide : ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
   unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
+  kern<<<grid, GEMM_THREADS, smem, as_stream(stream)>>>(ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
   return (int)cudaGetLastError();
 }
 
@@ -487,10 +508,10 @@ int wkb_gemm_e4m3_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i6
   if (!status) return (int)cudaErrorMemoryAllocation;
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, void*, i64, int, int, int, GemmEpi, int*);
   static const KernelFn table[4][2] = {
-      {gemm_bf16_tc_kernel<0, false, false, true>, gemm_bf16_tc_kernel<0, true, false, true>},
-      {gemm_bf16_tc_kernel<1, false, false, true>, gemm_bf16_tc_kernel<1, true, false, true>},
-      {gemm_bf16_tc_kernel<2, false, false, true>, gemm_bf16_tc_kernel<2, true, false, true>},
-      {gemm_bf16_tc_kernel<3, false, false, true>, gemm_bf16_tc_kernel<3, true, false, true>}};
+      {gemm_bf16_tc_kernel<0, false, false, true, false>, gemm_bf16_tc_kernel<0, true, false, true, false>},
+      {gemm_bf16_tc_kernel<1, false, false, true, false>, gemm_bf16_tc_kernel<1, true, false, true, false>},
+      {gemm_bf16_tc_kernel<2, false, false, true, false>, gemm_bf16_tc_kernel<2, true, false, true, false>},
+      {gemm_bf16_tc_kernel<3, false, false, true, false>, gemm_bf16_tc_kernel<3, true, false, true, false>}};
   KernelFn kern = table[act][c_bf16 ? 1 : 0];
   static bool attr_set[64][8] = {{false}};
   int dev = 0;
@@ -525,7 +546,7 @@ int wkb_gemm_bf16_nt_argmax(const void* a, i64 lda, const void* b, i64 ldb, i64 
   if (rc) return rc;
   int* status = gemm_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
-  auto kern = gemm_bf16_tc_kernel<0, false, true, false>;
+  auto kern = gemm_bf16_tc_kernel<0, false, true, false, false>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
