@@ -298,14 +298,25 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (ARGMAX) {
           // thread = row: ascending scan of its 32 columns keeps the lowest index on a tie; NaNs never
           // win, except that a NaN in global column 0 pins the row to 0 (the arg-max rule of the ABI)
+          if (n0 + c0 + 32 <= N && n0 + c0 > 0 && !epi.bias) {
+            // interior chunk: branch-free scan (a NaN fails `y > best_v`; column 0 is not in this chunk)
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = n0 + c0 + e;
-            float y = __uint_as_float(r[e]);
-            if (col < N) {
-              if (epi.bias) y += epi.bias[col];
-              if (col == 0 && y != y) { best_v = INFINITY; best_i = 0; pinned = true; }
-              if (!pinned && y == y && (best_i < 0 || y > best_v)) { best_v = y; best_i = col; }
+            for (int e = 0; e < 32; ++e) {
+              const float y = __uint_as_float(r[e]);
+              const bool take = !pinned && (y > best_v || (best_i < 0 && y == y));
+              best_v = take ? y : best_v;
+              best_i = take ? n0 + c0 + e : best_i;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int col = n0 + c0 + e;
+              float y = __uint_as_float(r[e]);
+              if (col < N) {
+                if (epi.bias) y += epi.bias[col];
+                if (col == 0 && y != y) { best_v = INFINITY; best_i = 0; pinned = true; }
+                if (!pinned && y == y && (best_i < 0 || y > best_v)) { best_v = y; best_i = col; }
+              }
             }
           }
         } else {
@@ -314,24 +325,45 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const int col = n0 + c0 + lane;
           const bool col_ok = col < N;
           const int row0 = m0 + quarter * 32;
+          const int nrows = min(32, M - row0);  // rows of this warp inside the matrix (may be <= 0)
+          const bool full = nrows == 32;        // warp-uniform: the straight-line path has no per-row branch
           float res[32];
-          if (epi.residual) {
+          if (epi.residual && full && col_ok) {
+            const float* rp = epi.residual + (i64)row0 * epi.ldr + col;
 #pragma unroll
-            for (int rr = 0; rr < 32; ++rr)
-              res[rr] = (col_ok && row0 + rr < M) ? epi.residual[(i64)(row0 + rr) * epi.ldr + col] : 0.0f;
+            for (int rr = 0; rr < 32; ++rr) res[rr] = rp[(i64)rr * epi.ldr];
           }
 #pragma unroll
           for (int e = 0; e < 32; ++e) stage[lane * 33 + e] = __uint_as_float(r[e]);
           __syncwarp();
           const float bias_v = (col_ok && epi.bias) ? epi.bias[col] : 0.0f;
+          if (col_ok) {
+            if (full) {
+              float vals[32];
 #pragma unroll
-          for (int rr = 0; rr < 32; ++rr) {
-            const int grow = row0 + rr;
-            if (grow < M && col_ok) {
-              float y = epi_act<ACT, OUT_BF16>(stage[rr * 33 + lane] + bias_v);
-              if (epi.residual) y += res[rr];
-              if (OUT_BF16) reinterpret_cast<u16*>(c)[(i64)grow * ldc + col] = f32_to_bf16_bits(y);
-              else reinterpret_cast<float*>(c)[(i64)grow * ldc + col] = y;
+              for (int rr = 0; rr < 32; ++rr) vals[rr] = epi_act<ACT, OUT_BF16>(stage[rr * 33 + lane] + bias_v);
+              if (epi.residual) {
+#pragma unroll
+                for (int rr = 0; rr < 32; ++rr) vals[rr] += res[rr];
+              }
+              if (OUT_BF16) {
+                u16* cp = reinterpret_cast<u16*>(c) + (i64)row0 * ldc + col;
+#pragma unroll
+                for (int rr = 0; rr < 32; ++rr) cp[(i64)rr * ldc] = f32_to_bf16_bits(vals[rr]);
+              } else {
+                float* cp = reinterpret_cast<float*>(c) + (i64)row0 * ldc + col;
+#pragma unroll
+                for (int rr = 0; rr < 32; ++rr) cp[(i64)rr * ldc] = vals[rr];
+              }
+            } else {
+#pragma unroll 1
+              for (int rr = 0; rr < nrows; ++rr) {
+                const i64 grow = row0 + rr;
+                float y = epi_act<ACT, OUT_BF16>(stage[rr * 33 + lane] + bias_v);
+                if (epi.residual) y += epi.residual[grow * epi.ldr + col];
+                if (OUT_BF16) reinterpret_cast<u16*>(c)[grow * ldc + col] = f32_to_bf16_bits(y);
+                else reinterpret_cast<float*>(c)[grow * ldc + col] = y;
+              }
             }
           }
           __syncwarp();
