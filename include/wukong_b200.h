@@ -185,6 +185,20 @@ int wkb_kv_append_f32(float* cache, const float* row, int64_t nrow, int64_t pos,
 /* RoPE with an optional position vector (null: position = row); x is [rows, heads, 2*half]. */
 int wkb_rope_f32(const float* x, const float* inv_freq, const int* pos_or_null, float* out, int64_t rows, int64_t heads, int64_t half, void* stream);
 int wkb_rope_bf16(const void* x, const float* inv_freq, const int* pos, void* out, int64_t rows, int64_t heads, int64_t half, int64_t row_stride, void* stream);
+/* RoPE in place on the leading `heads` heads (query heads then key heads) of each fused-QKV row of pitch
+ * row_stride floats; same pairing and sin / cos sequence as wkb_rope_f32, position from pos[row]. */
+int wkb_rope_qk_f32(float* x, int64_t row_stride, const float* inv_freq, const int* pos, int64_t rows, int64_t heads,
+                    int64_t half, void* stream);
+/* Residual add fused with RMSNorm: x += delta (delta may be null), out = bf16(x / sqrt(mean(x^2) + eps) * gamma);
+ * cols % 4 == 0.  The norm is the RMSNORM op of crates/wukong_runtime/src/norm.rs:50-54 in the
+ * half-precision recipe (fp32 statistics, one rounding on the way out). */
+int wkb_add_rmsnorm_bf16(float* x, const float* delta_or_null, const float* gamma_or_null, void* out_bf16, int64_t rows,
+                         int64_t cols, float eps, void* stream);
+/* Greedy sampling with the vocabulary split over ranks: pack (value bits, idx_local + col_offset) of each
+ * row's local arg-max into pairs[rows][2]; after gathering the ranks' pairs into [world][rows][2], pick the
+ * row's token by the arg-max rule of wukong_rowargmax_i32 applied across ranks. */
+int wkb_argmax_pack(const float* logits, int64_t ld, const int* idx_local, int64_t col_offset, int64_t rows, int* pairs, void* stream);
+int wkb_argmax_pick(const int* pairs, int64_t world, int64_t rows, int* out, void* stream);
 int wkb_embedding_f32(float* out, const float* weight, const int* ids, int64_t t, int64_t h, int64_t v, void* stream);
 /* out[r] = wte[ids[r]] + wpe[pos[r]] (bf16 tables, f32 out): the GPT-2 input embedding. */
 int wkb_embed_tok_pos_bf16(float* out, const void* wte, const void* wpe, const int* ids, const int* pos, int64_t t, int64_t h, int64_t v, int64_t npos, void* stream);
@@ -259,6 +273,20 @@ int wkb_gemm_bf16_nt(const void* a, int64_t lda, const void* b, int64_t ldb, voi
                      int64_t m, int64_t n, int64_t k, const float* bias, int64_t act, const float* residual,
                      int64_t ldr, void* stream);
 int wkb_gemm_status(void);
+
+/* W4A16 GEMM on the tensor cores for batched decode: out[m, n] = x[m, k] . W[n, k]^T with W resident as the
+ * two Q4_0 planes of wkb_q_split whose rows are padded to k_pitch (a multiple of 256; the padding blocks
+ * hold zero scales), x bf16 with row pitch ldx.  The weight the tensor core multiplies is exactly
+ * bf16(bf16(d) * (nib - 8)); accumulation is fp32.  out_mode 0: f32 out[m, n]; 1: bf16 out[m, n];
+ * 2: SwiGLU -- W rows interleaved (gate_0, up_0, gate_1, up_1, ...), bf16 out[m, n / 2] =
+ * silu(gate) * up.  Rows are processed 64 at a time.  `workspace` (at least
+ * wkb_gemm_q4_0_workspace_bytes(n, k_pitch), zero-filled once when allocated, one per stream) holds the
+ * K-slice partial sums and their arrival counters; the result does not depend on arrival order.
+ * Counterpart in the reference: the W4A16 tile kernels of crates/wukong_codegen_gpu/src/ptx_int4.rs. */
+int64_t wkb_gemm_q4_0_workspace_bytes(int64_t n, int64_t k_pitch);
+int wkb_gemm_q4_0_bf16_nt(const void* qs, const void* d, int64_t k_pitch, const void* x_bf16, int64_t ldx, void* out,
+                          int64_t ldo, int out_mode, int64_t m, int64_t n, int64_t k, void* workspace,
+                          int64_t workspace_bytes, void* stream);
 /* The same GEMM over OCP E4M3FN codes (one byte per element, the codec of crates/wukong_runtime/src/fp8.rs
  * :66-164; the reference's GPU counterpart is ptx_fp8.rs `fp8_gemm_nt*`): tcgen05 kind::f8f6f4, fp32
  * accumulate, K % 16 == 0, pitches multiples of 16. */

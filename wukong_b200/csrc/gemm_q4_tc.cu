@@ -1,0 +1,464 @@
+// W4A16 GEMM on the tensor cores: out[M, N] = x[M, K] . W[N, K]^T for resident Q4_0 weights and bf16
+// activations, M <= 64 rows per pass (batched decode).  Replaces the reference's int4 GEMM family
+// (crates/wukong_codegen_gpu/src/ptx_int4.rs: dequantise-in-register W4A16 tiles over mma.sync) for
+// sm_100a; block format and nibble order are the Q4_0 ones of crates/wukong_runtime/src/quant.rs:13-16.
+//
+// The kernel is bound by the weight stream (0.5625 B per weight), so it is built around keeping that
+// stream busy on every SM:
+//   * the activation slice x[:, k-slice] (<= 1024 columns, 128 KB) is loaded once per CTA and stays
+//     in shared memory; a CTA owns one K slice and walks over weight-row tiles of 128 rows;
+//   * warp 0 streams raw tiles (128 rows x 256 K: 16 KB of nibbles + 2 KB of f16 scales) through a
+//     3-stage TMA ring (128-byte swizzle, no multicast);
+//   * warps 2-9 dequantise: thread = (row, one 32-value block); nibble -> bf16 with one byte permute
+//     (0x4300 | nib = 128 + nib exactly), subtract 136, multiply by the block scale rounded to bf16,
+//     all in bf16x2 (the reference's kernel does the same two operations per pair in f16x2, its
+//     activations being f16); the 64 B result goes to the MMA operand buffer in the 128-byte-swizzle K-major
+//     layout; fence.proxy.async + mbarrier hand the 128 x 64 sub-tile to the MMA warp;
+//   * warp 1 issues tcgen05.mma (M = 128 weight rows, N = 64 activation rows, K = 16) x 4 per
+//     sub-tile into one of two TMEM accumulators; tcgen05.commit recycles the operand buffer;
+//   * warps 10-13 read the accumulator (thread = weight row, 64 activation rows in registers).
+//     With one K slice they finish the tile directly.  With several, they write the partial tile to
+//     the workspace and count arrivals per (tile, lane quarter); the last arriving warp adds the
+//     slices in slice order (so the result does not depend on arrival order) and finishes.
+//   Finishing = optional SwiGLU (rows interleaved gate, up, gate, up ...: silu(gate) * up), rounding to
+//   bf16 if asked, and a store that is coalesced across lanes (consecutive n for one m).
+// The weight value the tensor core sees is exactly bf16_rn(bf16_rn(d) * (nib - 8)); accumulation is
+// fp32 in the tensor core's own order.
+// Every mbarrier wait is bounded; on expiry a code is recorded in the status word, the role stops
+// issuing, and the CTA drains and frees its TMEM.
+#include "common.cuh"
+#include "wkb_device.h"
+#include "tc_common.cuh"
+
+namespace wkb {
+int* gemm_status_word();
+i64 gemm_sm_count();
+
+namespace q4tc {
+
+constexpr int TN = 128;        // weight rows per tile (MMA M)
+constexpr int TM = 64;         // activation rows per pass (MMA N)
+constexpr int STAGE_K = 256;   // K per raw stage: 128 B of nibbles per row
+constexpr int KS_MAX = 1024;   // K per resident activation slice
+constexpr int RAW_STAGES = 3;
+constexpr int RAW_BYTES = TN * 128, SCALE_BYTES = TN * 16, RAW_STAGE_BYTES = RAW_BYTES + SCALE_BYTES;
+constexpr int A_BYTES = TN * 128, A_BUFS = 2;
+constexpr int X_SUB_BYTES = TM * 128;
+constexpr int X_BYTES = (KS_MAX / 64) * X_SUB_BYTES;
+constexpr int NUM_BARS = 1 + 2 * RAW_STAGES + 2 * A_BUFS + 4;
+constexpr int SMEM = X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + A_BUFS * A_BYTES + 1024 + 256;
+// The arrival counters sit in a fixed-size head of the workspace so that GEMMs of different shapes can share
+// one workspace: no partial sum ever lands where another shape keeps a counter.
+constexpr int COUNTER_BYTES = 65536;
+constexpr int DEQ_WARPS = 8, THREADS = 32 * (2 + DEQ_WARPS + 4);
+// instruction descriptor, kind::f16: D = f32, A = B = bf16 (the two operand formats must agree: an f16 A with a
+// bf16 B is rejected by the hardware as an illegal instruction)
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
+
+struct Plan {
+  int n_tiles, kstages, ksplit, stages_per_slice, groups;
+};
+
+// Choose the K split: a slice holds at most KS_MAX / STAGE_K stages; among the feasible splits take
+// the one with the fewest (rounds x (stages + 1)) -- the +1 stands for the per-tile fixed cost.
+inline Plan make_plan(i64 n, i64 k, i64 sms) {
+  Plan p;
+  p.n_tiles = (int)((n + TN - 1) / TN);
+  p.kstages = (int)((k + STAGE_K - 1) / STAGE_K);
+  int best_cost = 1 << 30;
+  p.ksplit = 1; p.stages_per_slice = p.kstages; p.groups = 1;
+  for (int sps = KS_MAX / STAGE_K; sps >= 1; --sps) {
+    int ks = (p.kstages + sps - 1) / sps;
+    if (ks > sms) continue;
+    int groups = (int)(sms / ks);
+    if (groups > p.n_tiles) groups = p.n_tiles;
+    int rounds = (p.n_tiles + groups - 1) / groups;
+    int cost = rounds * (sps + 1);
+    if (cost < best_cost) { best_cost = cost; p.ksplit = ks; p.stages_per_slice = sps; p.groups = groups; }
+  }
+  return p;
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+// two nibbles (already isolated in bytes, widened to 0x4300 | nib = 128 + nib in bf16) -> bf16x2 of
+// d * (nib - 8): the subtraction is exact, the product is rounded once
+__device__ __forceinline__ uint32_t deq2(uint32_t pair_bits, uint32_t d2) {
+  uint32_t r;
+  asm("{\n .reg .b32 t;\n sub.rn.bf16x2 t, %1, %2;\n mul.rn.bf16x2 %0, t, %3;\n}"
+      : "=r"(r) : "r"(pair_bits), "r"(0x43084308u), "r"(d2));
+  return r;
+}
+// eight nibble-bytes (two words) -> one 16-byte chunk of bf16
+__device__ __forceinline__ uint4 deq8(uint32_t wa, uint32_t wb, uint32_t d2) {
+  uint4 o;
+  o.x = deq2(prmt(wa, 0x43434343u, 0x4140u), d2);
+  o.y = deq2(prmt(wa, 0x43434343u, 0x4342u), d2);
+  o.z = deq2(prmt(wb, 0x43434343u, 0x4140u), d2);
+  o.w = deq2(prmt(wb, 0x43434343u, 0x4342u), d2);
+  return o;
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Finish 32 activation rows (m0 .. m0+31) of weight row n held one per register.
+// MODE 0: f32 out[m, n]; 1: bf16 out[m, n]; 2: SwiGLU, bf16 out[m, n / 2] from (gate = even n, up = odd n).
+template <int MODE>
+__device__ __forceinline__ void finish32(const float (&v)[32], int m0, int M, int n, int N, void* out, i64 ldo) {
+  const int mcount = min(32, M - m0);
+  if (MODE == 2) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const float up = __shfl_xor_sync(0xffffffffu, v[e], 1);
+      if (e < mcount && n < N && !(n & 1)) {
+        const float y = fmul(silu1(v[e]), up);
+        reinterpret_cast<u16*>(out)[(i64)(m0 + e) * ldo + (n >> 1)] = f32_to_bf16_bits(y);
+      }
+    }
+  } else if (n < N) {
+    if (mcount == 32) {
+      if (MODE == 1) {
+        u16* p = reinterpret_cast<u16*>(out) + (i64)m0 * ldo + n;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) p[(i64)e * ldo] = f32_to_bf16_bits(v[e]);
+      } else {
+        float* p = reinterpret_cast<float*>(out) + (i64)m0 * ldo + n;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) p[(i64)e * ldo] = v[e];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        if (e < mcount) {
+          if (MODE == 1) reinterpret_cast<u16*>(out)[(i64)(m0 + e) * ldo + n] = f32_to_bf16_bits(v[e]);
+          else reinterpret_cast<float*>(out)[(i64)(m0 + e) * ldo + n] = v[e];
+        }
+      }
+    }
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_q,
+                  const __grid_constant__ CUtensorMap map_d, void* out, i64 ldo, int M, int N, Plan plan,
+                  float* ws, int* counters, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - raw);
+  const uint32_t x_base = base, raw_base = base + X_BYTES, a_base = raw_base + RAW_STAGES * RAW_STAGE_BYTES;
+  const uint32_t bars = a_base + A_BUFS * A_BYTES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + A_BUFS * A_BYTES + 8 * NUM_BARS);
+  const uint32_t x_full = bars;
+  auto raw_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto raw_empty = [&](int s) { return bars + 8u * (1 + RAW_STAGES + s); };
+  auto a_full = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + b); };
+  auto a_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + A_BUFS + b); };
+  auto t_full = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_BUFS + b); };
+  auto t_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_BUFS + 2 + b); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ks = blockIdx.x % plan.ksplit, group = blockIdx.x / plan.ksplit;
+  const int stage0 = ks * plan.stages_per_slice;
+  const int nstages = min(plan.stages_per_slice, plan.kstages - stage0);  // >= 1 by construction
+  const int nsub = nstages * (STAGE_K / 64);
+
+  if (threadIdx.x == 0) {
+    mbar_init(x_full, 1);
+    for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DEQ_WARPS); }
+    for (int b = 0; b < A_BUFS; ++b) { mbar_init(a_full(b), DEQ_WARPS); mbar_init(a_empty(b), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(t_full(b), 1); mbar_init(t_empty(b), 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2u * TM) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      mbar_expect_tx(x_full, (uint32_t)nsub * X_SUB_BYTES);
+      for (int j = 0; j < nsub; ++j) tma_load_2d(x_base + j * X_SUB_BYTES, &map_x, x_full, stage0 * STAGE_K + j * 64, 0);
+      int it = 0;
+      bool ok = true;
+      for (int t = group; t < plan.n_tiles && ok; t += plan.groups) {
+        for (int s = 0; s < nstages; ++s, ++it) {
+          const int slot = it % RAW_STAGES;
+          if (!mbar_wait(raw_empty(slot), ((it / RAW_STAGES) & 1) ^ 1)) { atomicExch(status, 11); ok = false; break; }
+          mbar_expect_tx(raw_full(slot), RAW_STAGE_BYTES);
+          const uint32_t dst = raw_base + slot * RAW_STAGE_BYTES;
+          tma_load_2d(dst, &map_q, raw_full(slot), (stage0 + s) * (STAGE_K / 2), t * TN);
+          tma_load_2d(dst + RAW_BYTES, &map_d, raw_full(slot), (stage0 + s) * (STAGE_K / 32), t * TN);
+        }
+      }
+      if (!ok) {
+        // wait (bounded) for the copies already started before the CTA may exit
+        mbar_wait(x_full, 0);
+        for (int j = it > RAW_STAGES ? it - RAW_STAGES : 0; j < it; ++j) mbar_wait(raw_full(j % RAW_STAGES), (j / RAW_STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      bool ok = mbar_wait(x_full, 0);
+      if (!ok) atomicExch(status, 12);
+      int ab = 0, local = 0;
+      for (int t = group; t < plan.n_tiles && ok; t += plan.groups, ++local) {
+        const int acc = local & 1;
+        if (!mbar_wait(t_empty(acc), ((local >> 1) & 1) ^ 1)) { atomicExch(status, 13); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TM);
+        for (int sub = 0; sub < nsub; ++sub, ++ab) {
+          const int buf = ab % A_BUFS;
+          if (!mbar_wait(a_full(buf), (ab / A_BUFS) & 1)) { atomicExch(status, 14); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = a_base + buf * A_BYTES, sb = x_base + sub * X_SUB_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_d, make_sdesc(sa + k * 32), make_sdesc(sb + k * 32), IDESC, (sub > 0 || k > 0) ? 1u : 0u);
+          umma_commit(a_empty(buf));
+        }
+        if (ok) umma_commit(t_full(acc));
+      }
+    }
+  } else if (warp < 2 + DEQ_WARPS) {
+    // ---------------- dequantisers: thread = (weight row r, block half hb of each 64-K sub-tile) ----------------
+    const int td = threadIdx.x - 64;
+    const int r = td & 127, hb = td >> 7;
+    const uint32_t swz = (uint32_t)(r & 7);
+    int it = 0, ab = 0;
+    bool ok = true;
+    for (int t = group; t < plan.n_tiles && ok; t += plan.groups) {
+      for (int s = 0; s < nstages && ok; ++s, ++it) {
+        const int slot = it % RAW_STAGES;
+        int good = 1;
+        if (lane == 0) good = mbar_wait(raw_full(slot), (it / RAW_STAGES) & 1) ? 1 : 0;
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) { if (lane == 0) atomicExch(status, 15); ok = false; break; }
+        const uint8_t* rawp = gen + X_BYTES + slot * RAW_STAGE_BYTES;
+        const uint4 sc = *reinterpret_cast<const uint4*>(rawp + RAW_BYTES + r * 16);
+        uint4 q[4];
+#pragma unroll
+        for (int sub = 0; sub < 4; ++sub)
+          q[sub] = *reinterpret_cast<const uint4*>(rawp + r * 128 + (((uint32_t)(sub * 2 + hb) ^ swz) << 4));
+#pragma unroll
+        for (int sub = 0; sub < 4; ++sub, ++ab) {
+          // scale of block (sub * 2 + hb): f16 bits -> f32 -> bf16, duplicated into both halves
+          const uint32_t sw = sub == 0 ? sc.x : sub == 1 ? sc.y : sub == 2 ? sc.z : sc.w;
+          const uint32_t db = f32_to_bf16_bits(f16_bits_to_f32((u16)(hb ? (sw >> 16) : (sw & 0xFFFFu))));
+          const uint32_t d2 = db | (db << 16);
+          const uint4 w = q[sub];
+          const uint4 c0 = deq8(w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, d2);                // elements 0-7
+          const uint4 c1 = deq8(w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu, d2);                // 8-15
+          const uint4 c2 = deq8((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, d2);  // 16-23
+          const uint4 c3 = deq8((w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu, d2);  // 24-31
+          const int buf = ab % A_BUFS;
+          if (lane == 0) good = mbar_wait(a_empty(buf), ((ab / A_BUFS) & 1) ^ 1) ? 1 : 0;
+          good = __shfl_sync(0xffffffffu, good, 0);
+          if (!good) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
+          uint8_t* arow = gen + X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + buf * A_BYTES + r * 128;
+          *reinterpret_cast<uint4*>(arow + (((uint32_t)(hb * 4 + 0) ^ swz) << 4)) = c0;
+          *reinterpret_cast<uint4*>(arow + (((uint32_t)(hb * 4 + 1) ^ swz) << 4)) = c1;
+          *reinterpret_cast<uint4*>(arow + (((uint32_t)(hb * 4 + 2) ^ swz) << 4)) = c2;
+          *reinterpret_cast<uint4*>(arow + (((uint32_t)(hb * 4 + 3) ^ swz) << 4)) = c3;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(a_full(buf));
+        }
+        __syncwarp();
+        if (ok && lane == 0) mbar_arrive(raw_empty(slot));
+      }
+    }
+  } else {
+    // ---------------- epilogue warps: TMEM lane quarter (warp % 4), thread = weight row ----------------
+    const int quarter = warp & 3;
+    const i64 n_pad = (i64)plan.n_tiles * TN;
+    int local = 0;
+    bool ok = true;
+    for (int t = group; t < plan.n_tiles && ok; t += plan.groups, ++local) {
+      const int acc = local & 1;
+      const int n = t * TN + quarter * 32 + lane;
+      int good = 1;
+      if (lane == 0) good = mbar_wait(t_full(acc), (local >> 1) & 1) ? 1 : 0;
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TM);
+      if (plan.ksplit == 1) {
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          uint32_t rr[32];
+          tmem_ld32(taddr + h * 32, rr);
+          if (h == 1) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(t_empty(acc));
+          }
+          float v[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(rr[e]);
+          finish32<MODE>(v, h * 32, M, n, N, out, ldo);
+        }
+      } else {
+        float* mine = ws + ((i64)ks * n_pad + n) * TM;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          uint32_t rr[32];
+          tmem_ld32(taddr + h * 32, rr);
+          if (h == 1) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(t_empty(acc));
+          }
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            *reinterpret_cast<uint4*>(mine + h * 32 + e) = make_uint4(rr[e], rr[e + 1], rr[e + 2], rr[e + 3]);
+        }
+        // publish, count this warp in, and let the last warp of this (tile, quarter) add the slices up
+        __threadfence();
+        __syncwarp();
+        int prev = 0;
+        if (lane == 0) prev = atomicAdd(&counters[t * 4 + quarter], 1);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == plan.ksplit - 1) {
+          __threadfence();
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            float v[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0.0f;
+            for (int s = 0; s < plan.ksplit; ++s) {
+              const float4* src = reinterpret_cast<const float4*>(ws + ((i64)s * n_pad + n) * TM + h * 32);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float4 p = __ldcg(src + e);
+                v[4 * e] = s ? fadd(v[4 * e], p.x) : p.x;
+                v[4 * e + 1] = s ? fadd(v[4 * e + 1], p.y) : p.y;
+                v[4 * e + 2] = s ? fadd(v[4 * e + 2], p.z) : p.z;
+                v[4 * e + 3] = s ? fadd(v[4 * e + 3], p.w) : p.w;
+              }
+            }
+            finish32<MODE>(v, h * 32, M, n, N, out, ldo);
+          }
+          __syncwarp();
+          if (lane == 0) counters[t * 4 + quarter] = 0;  // ready for the next launch
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * TM) : "memory");
+  }
+}
+
+static int encode(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* ptr, i64 inner, i64 rows, i64 pitch_bytes,
+                  int box_inner, int box_rows, bool swizzle) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  (void)esize;
+  CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace q4tc
+}  // namespace wkb
+
+using namespace wkb;
+
+extern "C" {
+
+int64_t wkb_gemm_q4_0_workspace_bytes(int64_t n, int64_t k_pitch) {
+  if (n <= 0 || k_pitch <= 0) return 256;
+  q4tc::Plan p = q4tc::make_plan(n, k_pitch, gemm_sm_count());
+  i64 counters = q4tc::COUNTER_BYTES;
+  i64 partial = p.ksplit > 1 ? (i64)p.ksplit * p.n_tiles * q4tc::TN * q4tc::TM * 4 : 0;
+  return counters + partial;
+}
+
+int wkb_gemm_q4_0_bf16_nt(const void* qs, const void* d, int64_t k_pitch, const void* x_bf16, int64_t ldx, void* out,
+                          int64_t ldo, int out_mode, int64_t m, int64_t n, int64_t k, void* workspace,
+                          int64_t workspace_bytes, void* stream) {
+  if (m <= 0 || n <= 0) return 0;
+  if (k <= 0 || k > k_pitch || k_pitch % q4tc::STAGE_K != 0 || k % 8 != 0 || ldx % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (out_mode < 0 || out_mode > 2 || (out_mode == 2 && (n & 1))) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)qs) | ((uintptr_t)d) | ((uintptr_t)x_bf16) | ((uintptr_t)workspace)) & 15) return (int)cudaErrorMisalignedAddress;
+  if (!workspace || workspace_bytes < wkb_gemm_q4_0_workspace_bytes(n, k_pitch)) return (int)cudaErrorInvalidValue;
+  int* status = gemm_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  q4tc::Plan plan = q4tc::make_plan(n, k_pitch, gemm_sm_count());
+  // stages past the logical K hold only padding: do not visit them
+  plan.kstages = (int)((k + q4tc::STAGE_K - 1) / q4tc::STAGE_K);
+  {
+    q4tc::Plan full = plan;
+    plan.ksplit = (plan.kstages + full.stages_per_slice - 1) / full.stages_per_slice;
+    if (plan.ksplit < 1) plan.ksplit = 1;
+  }
+  CUtensorMap mq, md;
+  int rc = q4tc::encode(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, qs, k_pitch / 2, n, k_pitch / 2, 128, q4tc::TN, true);
+  if (rc) return rc;
+  rc = q4tc::encode(&md, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d, k_pitch / 32, n, k_pitch / 32 * 2, 8, q4tc::TN, false);
+  if (rc) return rc;
+  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, void*, i64, int, int, q4tc::Plan, float*, int*, int*);
+  static const KernelFn table[3] = {q4tc::gemm_q4_tc_kernel<0>, q4tc::gemm_q4_tc_kernel<1>, q4tc::gemm_q4_tc_kernel<2>};
+  static bool attr_set[64][3] = {{false}};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev][out_mode]) {
+    cudaError_t e = cudaFuncSetAttribute(table[out_mode], cudaFuncAttributeMaxDynamicSharedMemorySize, q4tc::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev][out_mode] = true;
+  }
+  int* counters = reinterpret_cast<int*>(workspace);
+  if ((i64)plan.n_tiles * 16 > q4tc::COUNTER_BYTES) return (int)cudaErrorInvalidValue;
+  float* ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + q4tc::COUNTER_BYTES);
+  const i64 out_cols = out_mode == 2 ? n / 2 : n;
+  (void)out_cols;
+  const int esz = out_mode == 0 ? 4 : 2;
+  for (i64 m0 = 0; m0 < m; m0 += q4tc::TM) {
+    const i64 mc = m - m0 < q4tc::TM ? m - m0 : q4tc::TM;
+    CUtensorMap mx;
+    rc = q4tc::encode(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (const u16*)x_bf16 + m0 * ldx, k, mc, ldx * 2, 64, q4tc::TM, true);
+    if (rc) return rc;
+    void* o = reinterpret_cast<uint8_t*>(out) + m0 * ldo * esz;
+    table[out_mode]<<<plan.ksplit * plan.groups, q4tc::THREADS, q4tc::SMEM, as_stream(stream)>>>(
+        mx, mq, md, o, ldo, (int)mc, (int)n, plan, ws, counters, status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+}  // extern "C"

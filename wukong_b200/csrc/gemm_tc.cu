@@ -27,8 +27,7 @@
 // fp32 rounding (rtol 2e-2 is the stated bf16 bar; measured error is ~1e-6 relative to sum|a||b|).
 #include "common.cuh"
 #include "wkb_device.h"
-#include <cuda.h>
-#include <mutex>
+#include "tc_common.cuh"
 
 namespace wkb {
 
@@ -42,72 +41,11 @@ constexpr int EPI_STAGE_BYTES = 4 * 32 * 33 * 4;  // one 32 x 33 fp32 transpose 
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int BN_WIDE = 256;
 constexpr int SMEM_BYTES_WIDE = 4 * (TILE_A_BYTES + BN_WIDE * BK_BYTES) + EPI_STAGE_BYTES + 1024 + 256;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded parity wait.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
-    uint32_t done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: start address (>>4) in bits
-// 0-13, leading byte offset (unused for swizzled K-major, encoded as 1) in 16-29, stride byte offset
-// = 1024 B (8 rows x 128 B) in 32-45, descriptor version 1 in 46-47, layout type 2 (SWIZZLE_128B)
-// in 61-63.
-__device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
 // Instruction descriptor, kind::f16: D = f32 (1 << 4), A = B = bf16 (1 << 7, 1 << 10), both K-major,
 // N >> 3 in bits 17-22, M >> 4 in bits 24-28.
 // (kind::f8f6f4 with A = B = E4M3 uses format code 0 for both operands.)
 __host__ __device__ constexpr uint32_t make_idesc(int bn, bool f8) {
   return (1u << 4) | (f8 ? 0u : ((1u << 7) | (1u << 10))) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_e4m3(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 #ifdef WKB_GEMM_TRACE
@@ -146,10 +84,6 @@ template <int ACT, bool OUT_BF16>
 __device__ __forceinline__ float epi_act(float y) {
   if (ACT == 2 && OUT_BF16) return gelu_fast(y);
   return act_apply(ACT, y);
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // Persistent kernel: CTA b works on tiles b, b + gridDim.x, ...; tile t is (m_tile = t % tiles_m,
@@ -387,23 +321,6 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
-// ---- host side: tensor maps through the driver entry point (no link-time libcuda dependency) ----
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
-        qr == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  });
-  return fn;
-}
-
 // 2-D tensor [rows, k] of bf16 (or 1-byte e4m3) with row pitch ld elements; box = [128 bytes of K,
 // box_rows]; 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* ptr, i64 rows, i64 k, i64 ld, int box_rows, bool f8 = false) {
@@ -455,7 +372,7 @@ static i64 sm_count() {
   return counts[dev];
 }
 
-static int* gemm_status_word() {
+int* gemm_status_word() {
   // one device word per device for the bounded-wait status; allocated at first use
   static int* words[64] = {nullptr};
   int dev = 0;
@@ -468,6 +385,8 @@ static int* gemm_status_word() {
   }
   return words[dev];
 }
+
+i64 gemm_sm_count() { return sm_count(); }
 
 }  // namespace wkb
 

@@ -75,6 +75,50 @@ def gemv_q4_0_bf16x(qs, d, x_bf16, n, k, out=None):
     return y
 
 
+class Q4Weight:
+    """Resident Q4_0 matrix [n, k] for the tensor-core GEMM: nibble plane [n, k_pitch/32, 16] u8 and scale
+    plane [n, k_pitch/32] f16, rows padded with zero blocks to k_pitch (a multiple of 256)."""
+
+    def __init__(self, qs, d, n, k, k_pitch):
+        self.qs, self.d, self.n, self.k, self.k_pitch = qs, d, n, k, k_pitch
+
+    @staticmethod
+    def from_raw(raw_u8, n, k):
+        """`raw_u8`: device tensor of the n * (k/32) 18-byte blocks as the reference stores them."""
+        if k % 32:
+            raise ValueError("k must be a multiple of 32")
+        nb = k // 32
+        qs, d = q_split(raw_u8, n * nb, q4=True)
+        kp = (k + 255) // 256 * 256
+        if kp != k:
+            nbp = kp // 32
+            qs_p = torch.zeros(n, nbp, 16, dtype=torch.uint8, device=qs.device)
+            d_p = torch.zeros(n, nbp, dtype=torch.float16, device=qs.device)
+            qs_p[:, :nb] = qs.view(n, nb, 16)
+            d_p[:, :nb] = d.view(n, nb)
+            qs, d = qs_p, d_p
+        return Q4Weight(qs.view(n, kp // 32, 16), d.view(n, kp // 32), n, k, kp)
+
+
+def gemm_q4_workspace(n, k_pitch, device="cuda"):
+    return torch.zeros(int(lib().wkb_gemm_q4_0_workspace_bytes(n, k_pitch)), dtype=torch.uint8, device=device)
+
+
+def gemm_q4_0_bf16_nt(w, x_bf16, mode=0, out=None, workspace=None):
+    """out[m, n] = x . W^T (mode 0 f32, 1 bf16) or the SwiGLU of interleaved gate / up rows (mode 2, bf16 [m, n/2])."""
+    m, k = x_bf16.shape
+    if k != w.k or x_bf16.dtype != torch.bfloat16:
+        raise ValueError("activation must be bf16 [m, k]")
+    cols = w.n // 2 if mode == 2 else w.n
+    if out is None:
+        out = torch.empty(m, cols, dtype=torch.float32 if mode == 0 else torch.bfloat16, device=x_bf16.device)
+    if workspace is None:
+        workspace = gemm_q4_workspace(w.n, w.k_pitch, x_bf16.device)
+    check(lib().wkb_gemm_q4_0_bf16_nt(_p(w.qs), _p(w.d), w.k_pitch, _p(x_bf16), x_bf16.stride(0), _p(out), out.stride(0), mode,
+                                      m, w.n, k, _p(workspace), workspace.numel(), _s()), "wkb_gemm_q4_0_bf16_nt")
+    return out
+
+
 def rowargmax(x, out=None):
     rows, cols = x.shape
     out = torch.empty(rows, dtype=torch.int32, device=x.device) if out is None else out

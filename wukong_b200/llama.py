@@ -1,0 +1,336 @@
+"""Llama-shape decode block stack with Q4_0 weights, tensor-parallel over the GPUs of one node.
+
+What runs per decode step and layer on each rank (all kernels are this library's; torch supplies device
+memory, streams, graph capture and the process group):
+
+    RMSNorm (fused with the previous residual add)            wkb_add_rmsnorm_bf16
+    fused QKV projection, W4A16 on the tensor cores            wkb_gemm_q4_0_bf16_nt
+    RoPE in place on the q / k heads at the rows' positions    wkb_rope_qk_f32
+    K / V append through the block table                       wkb_paged_kv_append
+    paged GQA decode attention                                 wkb_paged_attn_decode
+    output projection (this rank's K slice)                    wkb_gemm_q4_0_bf16_nt
+    -- sum over ranks --
+    residual add + RMSNorm                                     wkb_add_rmsnorm_bf16
+    gate / up projection with the SwiGLU epilogue              wkb_gemm_q4_0_bf16_nt (mode 2)
+    down projection (this rank's K slice)                      wkb_gemm_q4_0_bf16_nt
+    -- sum over ranks --
+
+The split is the one the reference validates on one GPU (crates/wukong_codegen_gpu/src/serving.rs:
+4161-4240): QKV, gate / up and the LM head are split by output rows (whole heads, FFN columns,
+vocabulary rows), O and down by input columns on Q4_0 block boundaries; the KV cache holds only this
+rank's KV heads; norms and the residual stream are replicated.  Greedy sampling over a split
+vocabulary gathers each rank's (value, index) candidate and applies the arg-max rule across ranks.
+"""
+import math
+
+import numpy as np
+import torch
+
+from . import device as dev
+from ._lib import lib, check
+
+
+class LlamaConfig:
+    def __init__(self, n_layer=32, d_model=4096, n_head=32, n_kv_head=8, d_ff=11008, vocab=32000, rope_base=10000.0, eps=1e-5):
+        self.n_layer, self.d_model, self.n_head, self.n_kv_head = n_layer, d_model, n_head, n_kv_head
+        self.d_ff, self.vocab, self.rope_base, self.eps = d_ff, vocab, rope_base, eps
+        self.head_dim = d_model // n_head
+        if self.head_dim not in (64, 128) or d_model % 32 or d_ff % 32:
+            raise ValueError("head_dim must be 64 or 128; d_model and d_ff multiples of 32")
+
+    def check_world(self, world):
+        if self.n_kv_head % world or self.n_head % world or self.vocab % world or (self.d_ff // 32) % world:
+            raise ValueError("heads, vocabulary and FFN blocks must divide by the tensor-parallel degree")
+
+    def linear_params(self):
+        d, hd = self.d_model, self.head_dim
+        return self.n_layer * (2 * d * self.n_head * hd + 2 * d * self.n_kv_head * hd + 3 * d * self.d_ff)
+
+
+def synth_q4_raw(rng, n, k, sigma=0.02):
+    """Raw Q4_0 rows [n, k/32, 18]: uniform nibbles, f16 scale |N(0, sigma)|."""
+    nb = k // 32
+    raw = rng.integers(0, 256, (n, nb, 18), dtype=np.uint8)
+    sc = np.abs(rng.standard_normal((n, nb)) * sigma).astype(np.float16).view(np.uint16)
+    raw[:, :, 0] = (sc & 0xFF).astype(np.uint8)
+    raw[:, :, 1] = (sc >> 8).astype(np.uint8)
+    return raw
+
+
+def synth_llama_raw(cfg, seed=0, sigma=0.02):
+    """Host-side seeded weights for small configurations (the oracle consumes the same arrays).  `sigma` is the
+    spread of the block scales: 0.02 is the benchmark's; a small model wants less, or its random attention and
+    SwiGLU saturate and amplify any rounding difference between two implementations."""
+    rng = np.random.default_rng(seed)
+    d, hd, F = cfg.d_model, cfg.head_dim, cfg.d_ff
+    q4 = lambda n, k: synth_q4_raw(rng, n, k, sigma)
+    w = {"embed": rng.standard_normal((cfg.vocab, d)).astype(np.float32), "norm_f": np.ones(d, np.float32),
+         "lm_head": q4(cfg.vocab, d), "layers": []}
+    for _ in range(cfg.n_layer):
+        w["layers"].append(dict(norm1=np.ones(d, np.float32), norm2=np.ones(d, np.float32), wq=q4(cfg.n_head * hd, d),
+                                wk=q4(cfg.n_kv_head * hd, d), wv=q4(cfg.n_kv_head * hd, d), wo=q4(d, cfg.n_head * hd),
+                                wgate=q4(F, d), wup=q4(F, d), wdown=q4(d, F)))
+    return w
+
+
+def shard_rows(raw, rank, world):
+    n = raw.shape[0] // world
+    return raw[rank * n:(rank + 1) * n]
+
+
+def shard_cols(raw, rank, world):
+    nb = raw.shape[1] // world
+    return raw[:, rank * nb:(rank + 1) * nb]
+
+
+def interleave_rows(a, b):
+    out = np.empty((2 * a.shape[0],) + a.shape[1:], a.dtype)
+    out[0::2], out[1::2] = a, b
+    return out
+
+
+class LlamaRankWeights:
+    """One rank's resident weights: Q4Weight planes per linear, f32 norm gains and embedding."""
+
+    def __init__(self):
+        self.layers, self.embed, self.norm_f, self.lm_head = [], None, None, None
+
+    @staticmethod
+    def _q4(raw, device):
+        n, nb, _ = raw.shape
+        return dev.Q4Weight.from_raw(torch.from_numpy(np.ascontiguousarray(raw).reshape(-1)).to(device), n, nb * 32)
+
+    @staticmethod
+    def from_raw(cfg, w, rank=0, world=1, device="cuda"):
+        cfg.check_world(world)
+        out = LlamaRankWeights()
+        f32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(device)
+        out.embed, out.norm_f = f32(w["embed"]), f32(w["norm_f"])
+        out.lm_head = LlamaRankWeights._q4(shard_rows(w["lm_head"], rank, world), device)
+        for lw in w["layers"]:
+            qkv = np.concatenate([shard_rows(lw["wq"], rank, world), shard_rows(lw["wk"], rank, world), shard_rows(lw["wv"], rank, world)])
+            gu = interleave_rows(shard_rows(lw["wgate"], rank, world), shard_rows(lw["wup"], rank, world))
+            out.layers.append(dict(norm1=f32(lw["norm1"]), norm2=f32(lw["norm2"]), wqkv=LlamaRankWeights._q4(qkv, device),
+                                   wo=LlamaRankWeights._q4(shard_cols(lw["wo"], rank, world), device),
+                                   wgu=LlamaRankWeights._q4(gu, device),
+                                   wdown=LlamaRankWeights._q4(shard_cols(lw["wdown"], rank, world), device)))
+        return out
+
+    @staticmethod
+    def synth_device(cfg, rank=0, world=1, seed=0, device="cuda"):
+        """Full-size seeded weights generated on the device: every rank draws the same full matrices (same
+        generator state) and keeps its own slice, so all tensor-parallel degrees compute one function."""
+        cfg.check_world(world)
+        g = torch.Generator(device=device)
+        g.manual_seed(seed)
+        d, hd, F = cfg.d_model, cfg.head_dim, cfg.d_ff
+
+        def full(n, k):
+            qs = torch.randint(0, 256, (n, k // 32, 16), dtype=torch.uint8, device=device, generator=g)
+            sc = (torch.randn((n, k // 32), device=device, generator=g) * 0.02).abs().to(torch.float16)
+            return qs, sc
+
+        def make(qs, sc):
+            n, nb = sc.shape
+            k = nb * 32
+            kp = (k + 255) // 256 * 256
+            if kp != k:
+                qp = torch.zeros(n, kp // 32, 16, dtype=torch.uint8, device=device)
+                sp = torch.zeros(n, kp // 32, dtype=torch.float16, device=device)
+                qp[:, :nb], sp[:, :nb] = qs, sc
+                qs, sc = qp, sp
+            return dev.Q4Weight(qs.contiguous(), sc.contiguous(), n, k, kp)
+
+        rows = lambda t, n: t[rank * (n // world):(rank + 1) * (n // world)]
+        cols = lambda t, nb: t[:, rank * (nb // world):(rank + 1) * (nb // world)]
+        out = LlamaRankWeights()
+        out.embed = torch.randn((cfg.vocab, d), device=device, generator=g)
+        out.norm_f = torch.ones(d, device=device)
+        qs, sc = full(cfg.vocab, d)
+        out.lm_head = make(rows(qs, cfg.vocab), rows(sc, cfg.vocab))
+        for _ in range(cfg.n_layer):
+            (q_q, q_s), (k_q, k_s), (v_q, v_s) = full(cfg.n_head * hd, d), full(cfg.n_kv_head * hd, d), full(cfg.n_kv_head * hd, d)
+            o_q, o_s = full(d, cfg.n_head * hd)
+            (g_q, g_s), (u_q, u_s) = full(F, d), full(F, d)
+            d_q, d_s = full(d, F)
+            nq, nkv = cfg.n_head * hd, cfg.n_kv_head * hd
+            qkv_q = torch.cat([rows(q_q, nq), rows(k_q, nkv), rows(v_q, nkv)])
+            qkv_s = torch.cat([rows(q_s, nq), rows(k_s, nkv), rows(v_s, nkv)])
+            gu_q = torch.stack([rows(g_q, F), rows(u_q, F)], dim=1).reshape(-1, d // 32, 16)
+            gu_s = torch.stack([rows(g_s, F), rows(u_s, F)], dim=1).reshape(-1, d // 32)
+            out.layers.append(dict(norm1=torch.ones(d, device=device), norm2=torch.ones(d, device=device),
+                                   wqkv=make(qkv_q, qkv_s), wo=make(cols(o_q, nq // 32), cols(o_s, nq // 32)),
+                                   wgu=make(gu_q, gu_s), wdown=make(cols(d_q, F // 32), cols(d_s, F // 32))))
+        return out
+
+    def q4_bytes(self):
+        """Algorithmic weight bytes one decode step streams on this rank (18 B per 32 weights)."""
+        tot = self.lm_head.n * (self.lm_head.k // 32) * 18
+        for lw in self.layers:
+            for key in ("wqkv", "wo", "wgu", "wdown"):
+                tot += lw[key].n * (lw[key].k // 32) * 18
+        return tot
+
+
+class LlamaDecodeModel:
+    """One rank of the tensor-parallel decode model.  `forward(n)` runs rows 0..n-1 of the row buffers
+    (token, position, slot, visible keys); `reduce(t)` must sum `t` over the ranks in place (None: one rank);
+    `gather(pairs, all_pairs)` must gather the ranks' arg-max candidates (None: one rank)."""
+
+    def __init__(self, cfg, weights, rank, world, bcap, num_pages, max_blocks_per_seq, page_tokens=16, device="cuda",
+                 reduce=None, gather=None):
+        cfg.check_world(world)
+        self.cfg, self.w, self.rank, self.world, self.bcap, self.device = cfg, weights, rank, world, bcap, device
+        self.reduce, self.gather = reduce, gather
+        self.page_tokens, self.mbps, self.max_ctx = page_tokens, max_blocks_per_seq, max_blocks_per_seq * page_tokens
+        d, hd, R = cfg.d_model, cfg.head_dim, bcap
+        self.hq, self.hkv, self.f = cfg.n_head // world, cfg.n_kv_head // world, cfg.d_ff // world
+        self.vloc = cfg.vocab // world
+        self.qkv_w = (self.hq + 2 * self.hkv) * hd
+        self.kv = dev.PagedKV(cfg.n_layer, num_pages, self.hkv, hd, page_tokens, device)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.row_token, self.row_pos = torch.zeros(R, **i32), torch.full((R,), -1, **i32)
+        self.row_slot, self.row_ctx = torch.arange(R, **i32), torch.zeros(R, **i32)
+        self.block_table = torch.zeros((bcap, max_blocks_per_seq), **i32)
+        f32 = dict(dtype=torch.float32, device=device)
+        bf = dict(dtype=torch.bfloat16, device=device)
+        self.x, self.part = torch.zeros((R, d), **f32), torch.zeros((R, d), **f32)
+        self.xn = torch.zeros((R, d), **bf)
+        self.qkv = torch.zeros((R, self.qkv_w), **f32)
+        self.att = torch.zeros((R, self.hq * hd), **bf)
+        self.h = torch.zeros((R, self.f), **bf)
+        self.logits = torch.zeros((R, self.vloc), **f32)
+        self.idx_local, self.next_tok = torch.zeros(R, **i32), torch.zeros(R, **i32)
+        self.pairs, self.all_pairs = torch.zeros((R, 2), **i32), torch.zeros((world, R, 2), **i32)
+        half = hd // 2
+        inv = 1.0 / (np.float32(cfg.rope_base) ** (np.arange(half, dtype=np.float32) * np.float32(2.0 / hd)))
+        self.inv_freq = torch.from_numpy(inv.astype(np.float32)).to(device)
+        ws_bytes = max(int(lib().wkb_gemm_q4_0_workspace_bytes(w.n, w.k_pitch))
+                       for w in [weights.lm_head] + [lw[k] for lw in weights.layers for k in ("wqkv", "wo", "wgu", "wdown")])
+        self.workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=device)
+        self.scratch = dev.paged_attn_scratch(R, self.hq, hd, self.max_ctx, device)
+        self.scale = 1.0 / math.sqrt(hd)
+        self.launches_per_forward = 0
+
+    def _gemm(self, w, x, ldx, out, ldo, mode, n, what):
+        p = lambda t: t.data_ptr()
+        check(lib().wkb_gemm_q4_0_bf16_nt(p(w.qs), p(w.d), w.k_pitch, p(x), ldx, p(out), ldo, mode, n, w.n, w.k, p(self.workspace),
+                                          self.workspace.numel(), torch.cuda.current_stream().cuda_stream), what)
+
+    # ---- phases (a caller that emulates several ranks on one device runs them in lockstep) ----
+    def begin(self, n):
+        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
+        cfg = self.cfg
+        check(L.wkb_embedding_f32(p(self.x), p(self.w.embed), p(self.row_token), n, cfg.d_model, cfg.vocab, s), "embedding")
+        check(L.wkb_add_rmsnorm_bf16(p(self.x), None, p(self.w.layers[0]["norm1"]), p(self.xn), n, cfg.d_model, cfg.eps, s), "norm1")
+
+    def attn_part(self, li, n):
+        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
+        cfg, lw, hd = self.cfg, self.w.layers[li], self.cfg.head_dim
+        self._gemm(lw["wqkv"], self.xn, cfg.d_model, self.qkv, self.qkv_w, 0, n, "qkv")
+        check(L.wkb_rope_qk_f32(p(self.qkv), self.qkv_w, p(self.inv_freq), p(self.row_pos), n, self.hq + self.hkv, hd // 2, s), "rope")
+        k_ptr, v_ptr = p(self.qkv) + 4 * self.hq * hd, p(self.qkv) + 4 * (self.hq + self.hkv) * hd
+        check(L.wkb_paged_kv_append(k_ptr, v_ptr, self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
+                                    p(self.row_pos), n, self.hkv, hd, self.page_tokens, self.mbps, s), "kv_append")
+        check(L.wkb_paged_attn_decode(p(self.qkv), self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
+                                      p(self.row_ctx), p(self.att), 1, self.hq * hd, n, self.hq, self.hkv, hd, self.page_tokens, self.mbps,
+                                      self.max_ctx, self.scale, p(self.scratch), s), "attention")
+        self._gemm(lw["wo"], self.att, self.hq * hd, self.part, cfg.d_model, 0, n, "o_proj")
+
+    def after_attn(self, li, n):
+        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
+        check(L.wkb_add_rmsnorm_bf16(p(self.x), p(self.part), p(self.w.layers[li]["norm2"]), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), "norm2")
+
+    def mlp_part(self, li, n):
+        lw = self.w.layers[li]
+        self._gemm(lw["wgu"], self.xn, self.cfg.d_model, self.h, self.f, 2, n, "gate_up")
+        self._gemm(lw["wdown"], self.h, self.f, self.part, self.cfg.d_model, 0, n, "down")
+
+    def after_mlp(self, li, n):
+        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
+        gain = self.w.layers[li + 1]["norm1"] if li + 1 < self.cfg.n_layer else self.w.norm_f
+        check(L.wkb_add_rmsnorm_bf16(p(self.x), p(self.part), p(gain), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), "norm_next")
+
+    def head_local(self, n):
+        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
+        self._gemm(self.w.lm_head, self.xn, self.cfg.d_model, self.logits, self.vloc, 0, n, "lm_head")
+        check(L.wkb_rowargmax_strided_i32(p(self.logits), p(self.idx_local), n, self.vloc, self.vloc, s), "argmax")
+        check(L.wkb_argmax_pack(p(self.logits), self.vloc, p(self.idx_local), self.rank * self.vloc, n, p(self.pairs), s), "argmax_pack")
+
+    def head_pick(self, n):
+        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
+        check(L.wkb_argmax_pick(p(self.all_pairs), self.world, self.bcap, p(self.next_tok), s), "argmax_pick")
+
+    def forward(self, n):
+        self.begin(n)
+        for li in range(self.cfg.n_layer):
+            self.attn_part(li, n)
+            if self.reduce is not None:
+                self.reduce(self.part)
+            self.after_attn(li, n)
+            self.mlp_part(li, n)
+            if self.reduce is not None:
+                self.reduce(self.part)
+            self.after_mlp(li, n)
+        self.head_local(n)
+        if self.gather is not None:
+            self.gather(self.pairs, self.all_pairs)
+        else:
+            self.all_pairs[0].copy_(self.pairs)
+        self.head_pick(n)
+        # per layer: 2 norms, 4 GEMMs, rope, append, attention (2 kernels); embedding + first norm; head: GEMM, arg-max, pack, pick
+        self.launches_per_forward = self.cfg.n_layer * 10 + 2 + 4
+        return self.next_tok
+
+    def advance(self, n):
+        """Device-side feedback between decode steps: the sampled token becomes the next input, positions and
+        visible-key counts move on by one."""
+        p = lambda t: t.data_ptr()
+        check(lib().wkb_decode_advance(p(self.row_token), p(self.row_pos), p(self.row_ctx), p(self.next_tok), n,
+                                       torch.cuda.current_stream().cuda_stream), "advance")
+
+
+class LocalTensorParallel:
+    """All ranks of a tensor-parallel group on ONE device, run in lockstep with the sums done in rank order.
+    It exists to check the sharded model against the unsharded one where only one GPU is at hand; the
+    multi-process path uses LlamaDecodeModel with a process-group reduce."""
+
+    def __init__(self, cfg, host_weights, world, bcap, num_pages, max_blocks_per_seq, page_tokens=16, device="cuda"):
+        self.world = world
+        self.models = [LlamaDecodeModel(cfg, LlamaRankWeights.from_raw(cfg, host_weights, r, world, device), r, world, bcap, num_pages,
+                                        max_blocks_per_seq, page_tokens, device) for r in range(world)]
+
+    def _sum_parts(self, n):
+        m0 = self.models[0]
+        s = torch.cuda.current_stream().cuda_stream
+        cnt = n * m0.cfg.d_model
+        for m in self.models[1:]:
+            check(lib().wkb_add_f32(m0.part.data_ptr(), m.part.data_ptr(), m0.part.data_ptr(), cnt, s), "sum")
+        for m in self.models[1:]:
+            m.part.copy_(m0.part)
+
+    def set_rows(self, token, pos, slot, ctx, block_table):
+        for m in self.models:
+            m.row_token.copy_(token); m.row_pos.copy_(pos); m.row_slot.copy_(slot); m.row_ctx.copy_(ctx)
+            m.block_table.copy_(block_table)
+
+    def forward(self, n):
+        ms = self.models
+        for m in ms:
+            m.begin(n)
+        for li in range(ms[0].cfg.n_layer):
+            for m in ms:
+                m.attn_part(li, n)
+            self._sum_parts(n)
+            for m in ms:
+                m.after_attn(li, n)
+                m.mlp_part(li, n)
+            self._sum_parts(n)
+            for m in ms:
+                m.after_mlp(li, n)
+        for m in ms:
+            m.head_local(n)
+        for r, m in enumerate(ms):
+            ms[0].all_pairs[r].copy_(m.pairs)
+        ms[0].head_pick(n)
+        return ms[0].next_tok

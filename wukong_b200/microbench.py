@@ -7,6 +7,8 @@ Cases (seeded synthetic inputs of the named shapes):
   gemv_q4_0      y = W.x, W 4096x4096 and 11008x4096 Q4_0 (f16 scale ~|N(0,0.02)|, nibbles uniform),
                  reference contract (Q8 activation, exact block dots) and bf16-activation variant
   rmsnorm/softmax  8192 rows x 4096, bf16
+  gemm_q4_0_bf16 batch 64 against the three linear shapes of a 7B-shape block (fused QKV 6144x4096, gate/up
+                 22016x4096 with the SwiGLU epilogue, down projection 4096x11008), tensor-core W4A16
   paged_attn     batch 64, ctx uniform [128, 4096], 32 q heads / 8 kv heads, d = 128, bf16, 16-token pages
 Memory-bound kernels rotate through enough distinct operand sets to exceed the 126 MB L2; every case
 is timed with CUDA events over one CUDA graph of `reps` launches after warm-up.
@@ -108,6 +110,27 @@ def case_gemv_q4(n, k, variant, hbm, tf, src):
             "frac": gbs / hbm, "algorithmic_bytes": alg, "rotating_copies": copies, "peak_source": "of " + src}
 
 
+def case_gemm_q4(m, n, k, mode, hbm, tf, src):
+    """W4A16 tensor-core GEMM at decode batch m: bound by the weight stream (18 B per 32 weights)."""
+    rng = np.random.default_rng(0)
+    nb = k // 32
+    bytes_w = n * nb * 18
+    copies = max(2, L2_BYTES * 3 // bytes_w + 1)
+    raw = torch.from_numpy(q4_weights(n, k, rng)).cuda()
+    ws_ = [dev.Q4Weight.from_raw(raw, n, k) for _ in range(copies)]
+    for w in ws_[1:]:
+        w.qs, w.d = w.qs.clone(), w.d.clone()
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    out = torch.empty(m, n // 2 if mode == 2 else n, dtype=torch.float32 if mode == 0 else torch.bfloat16, device="cuda")
+    work = dev.gemm_q4_workspace(n, ws_[0].k_pitch)
+    us = time_graph(lambda i: dev.gemm_q4_0_bf16_nt(ws_[i % copies], x, mode=mode, out=out, workspace=work), copies * 2)
+    alg = bytes_w + 2 * m * k + out.numel() * out.element_size()
+    gbs = alg / us / 1e3
+    return {"case": "gemm_q4_0_bf16" + ("_swiglu" if mode == 2 else ""), "shape": [m, n, k], "us": us, "achieved": gbs, "unit": "GB/s",
+            "bound": "hbm", "peak": hbm, "frac": gbs / hbm, "algorithmic_bytes": alg, "tflops": 2 * m * n * k / us / 1e6,
+            "rotating_copies": copies, "peak_source": "of " + src}
+
+
 def case_norm(op, hbm, tf, src):
     rows, cols = 8192, 4096
     copies = 4                                   # 4 x 64 MB inputs
@@ -160,6 +183,8 @@ def run(out=sys.stdout):
     for (n, k) in ((4096, 4096), (11008, 4096)):
         for variant in ("contract", "bf16x"):
             results.append(case_gemv_q4(n, k, variant, hbm, tf, src))
+    for (n, k, mode) in ((6144, 4096, 0), (22016, 4096, 2), (4096, 11008, 0)):
+        results.append(case_gemm_q4(64, n, k, mode, hbm, tf, src))
     for op in (2, 0):
         results.append(case_norm(op, hbm, tf, src))
     results.append(case_paged_attn(hbm, tf, src))
