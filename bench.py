@@ -3,6 +3,7 @@ paged KV with 16-token pages, 512 concurrent sequences per GPU (prompts uniform 
 
     python bench.py --gpus N --steps K --warmup W            # this library (one replica per GPU)
     python bench.py --impl reference --steps K --warmup W    # the CPU port of the reference kernels
+    python bench.py --workload llama_int4 --gpus N ...        # second workload: tensor-parallel Q4_0 Llama-shape stack
 
 A step is one decode step of every resident sequence (one token each).  `value` is measured with
 all inputs resident in HBM (a self-feeding CUDA graph per step); `e2e` is measured through the public
@@ -37,6 +38,9 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqs", type=int, default=SEQS_PER_GPU, help="sequences per GPU (default: the named workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="gpt2_serving", choices=["gpt2_serving", "llama_int4"],
+                    help="gpt2_serving: the headline workload (sequence-sharded replicas); llama_int4: the tensor-parallel Q4_0 stack")
+    ap.add_argument("--layers", type=int, default=0, help="llama_int4 only: run a shorter stack (0: the named 32 layers)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     a.steps = max(a.steps, 1)
@@ -377,7 +381,10 @@ def sched_commit_via_engine(eng, n_planned):
 
 if __name__ == "__main__":
     a = parse()
-    if a.impl == "reference":
+    if a.workload == "llama_int4":
+        import bench_llama
+        (bench_llama.run_reference if a.impl == "reference" else bench_llama.run_ours)(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

@@ -1,0 +1,274 @@
+"""Second benchmark workload: the Llama-7B-shape Q4_0 block stack, batch 64 decode at context 2048,
+tensor-parallel over the GPUs of one node (python bench.py --workload llama_int4 --gpus N ...).
+
+A step is one decode step of the 64 sequences (64 tokens for the whole job, whatever the GPU count:
+tensor parallelism splits one model, so scaling is strong).  Weights are seeded synthetic Q4_0 blocks of
+the named shapes; the KV cache is filled with seeded normal values standing for the 2048-token prefill
+(the timed region is decode; a real prefill of the same cache changes none of its work).
+`value` replays a captured CUDA graph of whole steps with the token feedback on the device; `e2e` goes
+through host buffers every step (rows up, tokens down)."""
+import json
+import os
+import time
+
+import bench as B
+
+BATCH, CTX0, PAGE = 64, 2048, 16
+
+
+def llama_config_dict(cfg, world, batch, ctx0):
+    return {"workload": "Llama-7B-shape Q4_0 block stack, batch %d decode at context %d (BASELINE configs[4])" % (batch, ctx0),
+            "layers": cfg.n_layer, "d_model": cfg.d_model, "heads": cfg.n_head, "kv_heads": cfg.n_kv_head, "d_ff": cfg.d_ff,
+            "vocab": cfg.vocab, "batch": batch, "context": ctx0, "weights": "Q4_0 (18 B per 32 weights), activations bf16",
+            "kv": "paged bf16, %d-token pages, synthetic fill standing for the prefill" % PAGE,
+            "parallelism": "tp%d (heads / FFN columns / vocabulary split, 2 all-reduces per layer)" % world,
+            "l2": "per-step inputs (weights + KV, several GB per GPU) exceed the 126 MB L2; no flush needed"}
+
+
+def cpu_llama_tok_s(cfg, batch, ctx, threads):
+    """CPU port on a bounded sample: ONE layer of the stack at the benchmark's batch and context -- the seven
+    Q4_0 linears through the reference-contract GEMV (one call per row, rows in parallel inside the kernel),
+    RoPE, GQA attention over `ctx` bf16 keys, SwiGLU -- timed once after a warm-up on a quarter of the rows;
+    the step time is that x n_layer (the LM head and norms are left out, which flatters the CPU)."""
+    import numpy as np
+    from oracle import binding as orc
+    from wukong_b200.llama import synth_q4_raw
+    orc.set_threads(threads)
+    rng = np.random.default_rng(0)
+    d, hd, F = cfg.d_model, cfg.head_dim, cfg.d_ff
+    shapes = {"q": (cfg.n_head * hd, d), "k": (cfg.n_kv_head * hd, d), "v": (cfg.n_kv_head * hd, d), "o": (d, cfg.n_head * hd),
+              "gate": (F, d), "up": (F, d), "down": (d, F)}
+    w = {k: synth_q4_raw(rng, n, kk).reshape(-1) for k, (n, kk) in shapes.items()}
+    kc = rng.standard_normal((batch, ctx, cfg.n_kv_head, hd)).astype(np.float32)
+    vc = rng.standard_normal((batch, ctx, cfg.n_kv_head, hd)).astype(np.float32)
+    x = rng.standard_normal((batch, d)).astype(np.float32)
+    inv = (1.0 / (10000.0 ** (np.arange(hd // 2, dtype=np.float32) * 2.0 / hd))).astype(np.float32)
+
+    def lin(name, a):
+        n = shapes[name][0]
+        return np.stack([orc.gemv_q(w[name], a[r], n)[1] for r in range(a.shape[0])])
+
+    def layer(rows):
+        xs = x[:rows]
+        xn = orc.norm_affine(xs, np.ones(d, np.float32), np.zeros(d, np.float32), 2, 1e-5)
+        q, k, v = lin("q", xn), lin("k", xn), lin("v", xn)
+        pos = np.full(rows, ctx, np.int32)
+        q, k = orc.rope_pos(q, inv, pos, cfg.n_head), orc.rope_pos(k, inv, pos, cfg.n_kv_head)
+        g = cfg.n_head // cfg.n_kv_head
+        qh = q.reshape(rows, cfg.n_kv_head, g, hd)
+        sc = np.einsum("bkgd,btkd->bkgt", qh, kc[:rows]) * (1.0 / np.sqrt(hd))
+        e = np.exp(sc - sc.max(-1, keepdims=True))
+        att = np.einsum("bkgt,btkd->bkgd", e / e.sum(-1, keepdims=True), vc[:rows]).reshape(rows, -1).astype(np.float32)
+        xs = xs + lin("o", att)
+        xn = orc.norm_affine(xs, np.ones(d, np.float32), np.zeros(d, np.float32), 2, 1e-5)
+        gt, up = lin("gate", xn), lin("up", xn)
+        return xs + lin("down", (gt / (1.0 + np.exp(-gt)) * up).astype(np.float32))
+
+    layer(max(1, batch // 4))
+    t0 = time.perf_counter()
+    layer(batch)
+    dt = time.perf_counter() - t0
+    return batch / (dt * cfg.n_layer), "1 of %d layers at batch %d, context %d, timed once (%.1f s); step = layer x %d" % (
+        cfg.n_layer, batch, ctx, dt, cfg.n_layer)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from wukong_b200.llama import LlamaConfig
+    cfg = LlamaConfig()
+    threads = os.cpu_count() or 1
+    tok_s, sample = cpu_llama_tok_s(cfg, BATCH, CTX0, threads)
+    line = {"impl": "reference", "metric": B.METRIC, "value": tok_s, "unit": B.UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * BATCH / tok_s, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int4 weights x int8 activations (reference GEMV contract), f32 accumulate", "data": "synthetic",
+            "config": llama_config_dict(cfg, 1, BATCH, CTX0),
+            "cpu_baseline": {"value": tok_s, "unit": B.UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tok_s, "unit": B.UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from wukong_b200 import _lib, device as dev
+    from wukong_b200._lib import lib, check
+    from wukong_b200.llama import LlamaConfig, LlamaRankWeights, LlamaDecodeModel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    _lib.require_gpu()
+    torch.cuda.set_device(local)
+    device = "cuda:%d" % local
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    K, W = args.steps, args.warmup
+    cfg = LlamaConfig(n_layer=args.layers) if args.layers else LlamaConfig()
+    weights = LlamaRankWeights.synth_device(cfg, rank, world, 0, device)
+    positions = CTX0 + 2 * (K + W) + 8          # the e2e region and the resident loop both move every sequence on
+    mbps = (positions + PAGE - 1) // PAGE
+    num_pages = BATCH * mbps
+    reduce = (lambda t: dist.all_reduce(t)) if world > 1 else None
+    gather = (lambda pairs, allp: dist.all_gather_into_tensor(allp, pairs)) if world > 1 else None
+    m = LlamaDecodeModel(cfg, weights, rank, world, BATCH, num_pages, mbps, PAGE, device, reduce, gather)
+    g = torch.Generator(device=device)
+    g.manual_seed(1 + rank)
+    m.kv.k.normal_(generator=g)
+    m.kv.v.normal_(generator=g)
+    rng = np.random.default_rng(0)                 # same rows and block table on every rank
+    table = rng.permutation(num_pages).astype(np.int32).reshape(BATCH, mbps)
+    m.block_table.copy_(torch.from_numpy(table))
+    h_rows = torch.zeros(3 * BATCH, dtype=torch.int32).pin_memory()
+    h_next = torch.zeros(BATCH, dtype=torch.int32).pin_memory()
+    d_rows = torch.zeros(3 * BATCH, dtype=torch.int32, device=device)
+    m.row_token, m.row_pos, m.row_ctx = (d_rows[i * BATCH:(i + 1) * BATCH] for i in range(3))
+    hr = h_rows.numpy()
+    hr[:BATCH] = rng.integers(0, cfg.vocab, BATCH)
+    hr[BATCH:2 * BATCH] = CTX0
+    hr[2 * BATCH:] = CTX0 + 1
+    stream = torch.cuda.Stream(device=device)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def capture(fn):
+        """CUDA graph of fn on `stream` (the all-reduces are captured with it); None if capture is refused."""
+        try:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                fn()
+            return gr
+        except Exception as exc:       # fall back to eager launches, and say so in the output line
+            if rank == 0:
+                print("graph capture failed, running eagerly: %r" % (exc,), flush=True)
+            torch.cuda.synchronize()
+            return None
+
+    with torch.cuda.stream(stream):
+        d_rows.copy_(h_rows, non_blocking=True)
+        for _ in range(2):
+            m.forward(BATCH)           # eager warm-up: first-use attribute calls, NCCL channel setup
+    stream.synchronize()
+    g_fwd = capture(lambda: m.forward(BATCH))
+    run_fwd = g_fwd.replay if g_fwd is not None else (lambda: m.forward(BATCH))
+
+    def e2e_step():
+        with torch.cuda.stream(stream):
+            d_rows.copy_(h_rows, non_blocking=True)
+            run_fwd()
+            h_next.copy_(m.next_tok, non_blocking=True)
+        stream.synchronize()
+        hr[:BATCH] = h_next.numpy()
+        hr[BATCH:] += 1
+
+    clocks = B.ClockSampler(local)
+    for _ in range(W):
+        e2e_step()
+    barrier()
+    clocks.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(K):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = B.max_over_ranks_ms(e0.elapsed_time(e1), world, "cuda")
+
+    # ---- device-resident loop: forward + on-device feedback per step, one graph
+    def step_resident():
+        m.forward(BATCH)
+        m.advance(BATCH)
+
+    with torch.cuda.stream(stream):
+        d_rows.copy_(h_rows, non_blocking=True)
+    stream.synchronize()
+    g_step = capture(step_resident)
+    run_step = g_step.replay if g_step is not None else step_resident
+    with torch.cuda.stream(stream):
+        for _ in range(W):
+            run_step()
+    barrier()
+    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        d0.record(stream)
+        for _ in range(K):
+            run_step()
+        d1.record(stream)
+    barrier()
+    clocks.stop()
+    dev_ms = B.max_over_ranks_ms(d0.elapsed_time(d1), world, "cuda")
+    if dev.gemm_status() != 0:
+        raise SystemExit("tensor-core GEMM reported an expired pipeline wait")
+
+    # ---- the two HBM streams timed alone on the same state: paged attention (KV) and the four linears (weights)
+    p = lambda t: t.data_ptr()
+    hd = cfg.head_dim
+
+    def timed(fn, reps=3):
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            gr = capture(fn)
+            run = gr.replay if gr is not None else fn
+            run()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            for _ in range(reps):
+                run()
+            a1.record(stream)
+        stream.synchronize()
+        return a0.elapsed_time(a1) / reps
+
+    def all_attn():
+        s = torch.cuda.current_stream().cuda_stream
+        for li in range(cfg.n_layer):
+            check(lib().wkb_paged_attn_decode(p(m.qkv), m.qkv_w, p(m.kv.k[li]), p(m.kv.v[li]), p(m.block_table), p(m.row_slot),
+                                              p(m.row_ctx), p(m.att), 1, m.hq * hd, BATCH, m.hq, m.hkv, hd, PAGE, mbps, m.max_ctx,
+                                              m.scale, p(m.scratch), s), "attention")
+
+    def all_gemm():
+        for lw in weights.layers:
+            m._gemm(lw["wqkv"], m.xn, cfg.d_model, m.qkv, m.qkv_w, 0, BATCH, "qkv")
+            m._gemm(lw["wo"], m.att, m.hq * hd, m.part, cfg.d_model, 0, BATCH, "o_proj")
+            m._gemm(lw["wgu"], m.xn, cfg.d_model, m.h, m.f, 2, BATCH, "gate_up")
+            m._gemm(lw["wdown"], m.h, m.f, m.part, cfg.d_model, 0, BATCH, "down")
+
+    attn_ms = timed(all_attn) / cfg.n_layer
+    gemm_ms = timed(all_gemm) / cfg.n_layer
+    ctx_now = float(m.row_ctx.float().mean().item())
+    attn_bytes = BATCH * ctx_now * 2 * m.hkv * hd * 2 + BATCH * m.hq * hd * (4 + 2) + BATCH * mbps * 4
+    layer_w_bytes = sum(lw[k].n * (lw[k].k // 32) * 18 for lw in weights.layers[:1] for k in ("wqkv", "wo", "wgu", "wdown"))
+    gemm_bytes = layer_w_bytes + BATCH * (2 * cfg.d_model + m.hq * hd + m.f) * 2 + BATCH * (m.qkv_w + 2 * cfg.d_model) * 4 + BATCH * m.f * 2
+    peak, peak_kind = B.hbm_peak()
+    step_ms = dev_ms / K
+    a_gbs, g_gbs = attn_bytes / (attn_ms * 1e-3) / 1e9, gemm_bytes / (gemm_ms * 1e-3) / 1e9
+    roofline = {"kernel": "paged_attn_decode_kernel<128,%d> (+ chunk merge)" % (m.hq // m.hkv), "bound": "hbm", "achieved": a_gbs,
+                "peak": peak, "peak_source": "of " + peak_kind, "unit": "GB/s", "frac": a_gbs / peak, "traffic": None,
+                "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms, "share_of_step": attn_ms * cfg.n_layer / step_ms,
+                "second_stream": {"kernel": "gemm_q4_tc_kernel (4 linears of a layer)", "bound": "hbm", "achieved": g_gbs, "unit": "GB/s",
+                                  "frac": g_gbs / peak, "algorithmic_bytes_per_layer": gemm_bytes, "ms_per_layer": gemm_ms,
+                                  "share_of_step": gemm_ms * cfg.n_layer / step_ms}}
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            tok_s, sample = cpu_llama_tok_s(cfg, BATCH, CTX0, threads)
+            cpu = {"value": tok_s, "unit": B.UNIT, "cores": threads, "kind": "port", "sample": sample}
+        line = {"metric": B.METRIC, "value": BATCH * K / (dev_ms * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "bf16 (Q4_0 weights dequantised in-register, fp32 accumulate)", "data": "synthetic",
+                "config": llama_config_dict(cfg, world, BATCH, CTX0),
+                "e2e": {"value": BATCH * K / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": int(h_rows.numel() * 4),
+                        "d2h_bytes_per_step": int(h_next.numel() * 4), "ms_per_step": e2e_ms / K},
+                "gpu_launches": int((m.launches_per_forward + 1) * K), "graph": g_step is not None, "roofline": roofline,
+                "cpu_baseline": cpu, "clocks": clocks.summary(),
+                "weights_bytes_per_gpu": int(weights.q4_bytes()), "kv_bytes_read_per_step_per_gpu": attn_bytes * cfg.n_layer}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
