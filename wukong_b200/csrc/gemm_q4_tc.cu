@@ -3,20 +3,23 @@
 // (crates/wukong_codegen_gpu/src/ptx_int4.rs: dequantise-in-register W4A16 tiles over mma.sync) for
 // sm_100a; block format and nibble order are the Q4_0 ones of crates/wukong_runtime/src/quant.rs:13-16.
 //
-// The kernel is bound by the weight stream (0.5625 B per weight), so it is built around keeping that
-// stream busy on every SM:
+// The kernel is bound by the weight stream (0.5625 B per weight) and, on this part, by the instructions it
+// takes to turn nibbles into tensor-core operands, so it is built to keep both busy on every SM:
 //   * the activation slice x[:, k-slice] (<= 1024 columns, 128 KB) is loaded once per CTA and stays
 //     in shared memory; a CTA owns one K slice and walks over weight-row tiles of 128 rows;
 //   * warp 0 streams raw tiles (128 rows x 256 K: 16 KB of nibbles + 2 KB of f16 scales) through a
-//     3-stage TMA ring (128-byte swizzle, no multicast);
-//   * warps 2-9 dequantise: thread = (row, one 32-value block); nibble -> bf16 with one byte permute
-//     (0x4300 | nib = 128 + nib exactly), subtract 136, multiply by the block scale rounded to bf16,
-//     all in bf16x2 (the reference's kernel does the same two operations per pair in f16x2, its
-//     activations being f16); the 64 B result goes to the MMA operand buffer in the 128-byte-swizzle K-major
-//     layout; fence.proxy.async + mbarrier hand the 128 x 64 sub-tile to the MMA warp;
-//   * warp 1 issues tcgen05.mma (M = 128 weight rows, N = 64 activation rows, K = 16) x 4 per
-//     sub-tile into one of two TMEM accumulators; tcgen05.commit recycles the operand buffer;
-//   * warps 10-13 read the accumulator (thread = weight row, 64 activation rows in registers).
+//     5-stage TMA ring (128-byte swizzle, no multicast);
+//   * warps 2-17 dequantise: thread = weight row, two 32-value blocks of each stage; nibble -> bf16 with
+//     one byte permute (0x4300 | nib = 128 + nib exactly), subtract 136, multiply by the block scale rounded
+//     to bf16, all in bf16x2 (the reference's kernel does the same two operations per pair in f16x2, its
+//     activations being f16).  The result is written with tcgen05.st straight into TENSOR MEMORY, where
+//     lane = weight row and a column holds two consecutive K values: the MMA's A operand never touches
+//     shared memory, so there is no swizzled store, no proxy fence, and the 256 KB of TMEM give three
+//     whole 256-K stages of operand buffering on top of the two accumulators;
+//   * warp 1 issues tcgen05.mma with A in tensor memory and B (activations) from shared memory
+//     (M = 128 weight rows, N = 64 activation rows, K = 16) x 16 per stage into one of two TMEM
+//     accumulators; tcgen05.commit recycles the operand stage;
+//   * warps 18-21 read the accumulator (thread = weight row, 64 activation rows in registers).
 //     With one K slice they finish the tile directly.  With several, they write the partial tile to
 //     the workspace and count arrivals per (tile, lane quarter); the last arriving warp adds the
 //     slices in slice order (so the result does not depend on arrival order) and finishes.
@@ -40,17 +43,20 @@ constexpr int TN = 128;        // weight rows per tile (MMA M)
 constexpr int TM = 64;         // activation rows per pass (MMA N)
 constexpr int STAGE_K = 256;   // K per raw stage: 128 B of nibbles per row
 constexpr int KS_MAX = 1024;   // K per resident activation slice
-constexpr int RAW_STAGES = 3;
+constexpr int RAW_STAGES = 5;
 constexpr int RAW_BYTES = TN * 128, SCALE_BYTES = TN * 16, RAW_STAGE_BYTES = RAW_BYTES + SCALE_BYTES;
-constexpr int A_BYTES = TN * 128, A_BUFS = 2;
 constexpr int X_SUB_BYTES = TM * 128;
 constexpr int X_BYTES = (KS_MAX / 64) * X_SUB_BYTES;
-constexpr int NUM_BARS = 1 + 2 * RAW_STAGES + 2 * A_BUFS + 4;
-constexpr int SMEM = X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + A_BUFS * A_BYTES + 1024 + 256;
+// tensor memory: columns 0-127 two fp32 accumulators (64 activation rows each), 128-511 three stage buffers of
+// dequantised weights (256 K as 128 columns of bf16 pairs; lane = weight row)
+constexpr int A_STAGES = 3, A_STAGE_COLS = STAGE_K / 2, A_COL0 = 2 * TM;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int NUM_BARS = 1 + 2 * RAW_STAGES + 2 * A_STAGES + 4;
+constexpr int SMEM = X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + 1024 + 256;
 // The arrival counters sit in a fixed-size head of the workspace so that GEMMs of different shapes can share
 // one workspace: no partial sum ever lands where another shape keeps a counter.
 constexpr int COUNTER_BYTES = 65536;
-constexpr int DEQ_WARPS = 8, THREADS = 32 * (2 + DEQ_WARPS + 4);
+constexpr int DEQ_WARPS = 16, THREADS = 32 * (2 + DEQ_WARPS + 4);
 // instruction descriptor, kind::f16: D = f32, A = B = bf16 (the two operand formats must agree: an f16 A with a
 // bf16 B is rejected by the hardware as an illegal instruction)
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
@@ -60,7 +66,8 @@ struct Plan {
 };
 
 // Choose the K split: a slice holds at most KS_MAX / STAGE_K stages; among the feasible splits take
-// the one with the fewest (rounds x (stages + 1)) -- the +1 stands for the per-tile fixed cost.
+// the one with the fewest (rounds x (stages + 1)) -- the +1 stands for the per-tile fixed cost -- and,
+// between equals, the one with fewer slices to add up.
 inline Plan make_plan(i64 n, i64 k, i64 sms) {
   Plan p;
   p.n_tiles = (int)((n + TN - 1) / TN);
@@ -73,7 +80,7 @@ inline Plan make_plan(i64 n, i64 k, i64 sms) {
     int groups = (int)(sms / ks);
     if (groups > p.n_tiles) groups = p.n_tiles;
     int rounds = (p.n_tiles + groups - 1) / groups;
-    int cost = rounds * (sps + 1);
+    int cost = rounds * (sps + 1) * 8 + ks;
     if (cost < best_cost) { best_cost = cost; p.ksplit = ks; p.stages_per_slice = sps; p.groups = groups; }
   }
   return p;
@@ -92,14 +99,55 @@ __device__ __forceinline__ uint32_t deq2(uint32_t pair_bits, uint32_t d2) {
       : "=r"(r) : "r"(pair_bits), "r"(0x43084308u), "r"(d2));
   return r;
 }
-// eight nibble-bytes (two words) -> one 16-byte chunk of bf16
-__device__ __forceinline__ uint4 deq8(uint32_t wa, uint32_t wb, uint32_t d2) {
-  uint4 o;
-  o.x = deq2(prmt(wa, 0x43434343u, 0x4140u), d2);
-  o.y = deq2(prmt(wa, 0x43434343u, 0x4342u), d2);
-  o.z = deq2(prmt(wb, 0x43434343u, 0x4140u), d2);
-  o.w = deq2(prmt(wb, 0x43434343u, 0x4342u), d2);
-  return o;
+// one 32-value block (16 raw bytes: byte j = element j | element j + 16 << 4) -> 16 registers of bf16 pairs in
+// element order
+__device__ __forceinline__ void deq_block(const uint4 w, uint32_t d2, uint32_t* o) {
+  const uint32_t lo[4] = {w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu};
+  const uint32_t hi[4] = {(w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o[2 * i] = deq2(prmt(lo[i], 0x43434343u, 0x4140u), d2);          // elements 4i, 4i+1
+    o[2 * i + 1] = deq2(prmt(lo[i], 0x43434343u, 0x4342u), d2);      // 4i+2, 4i+3
+    o[8 + 2 * i] = deq2(prmt(hi[i], 0x43434343u, 0x4140u), d2);      // 16+4i, 16+4i+1
+    o[8 + 2 * i + 1] = deq2(prmt(hi[i], 0x43434343u, 0x4342u), d2);  // 16+4i+2, 16+4i+3
+  }
+}
+// f16 scale bits -> the scale rounded to bf16 (nearest even), in both halves of a register
+__device__ __forceinline__ uint32_t bf16x2_of_f16(uint32_t h) {
+  uint32_t r;
+  asm("{\n .reg .b16 t;\n .reg .f32 f;\n cvt.u16.u32 t, %1;\n cvt.f32.f16 f, t;\n cvt.rn.bf16x2.f32 %0, f, f;\n}" : "=r"(r) : "r"(h));
+  return r;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+// MMA with the A operand in tensor memory (lane = row, a column holds two consecutive K elements)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 registers -> 32 consecutive columns of this thread's TMEM lane; returns once the store has landed
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -162,16 +210,16 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
-  const uint32_t x_base = base, raw_base = base + X_BYTES, a_base = raw_base + RAW_STAGES * RAW_STAGE_BYTES;
-  const uint32_t bars = a_base + A_BUFS * A_BYTES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + A_BUFS * A_BYTES + 8 * NUM_BARS);
+  const uint32_t x_base = base, raw_base = base + X_BYTES;
+  const uint32_t bars = raw_base + RAW_STAGES * RAW_STAGE_BYTES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + 8 * NUM_BARS);
   const uint32_t x_full = bars;
   auto raw_full = [&](int s) { return bars + 8u * (1 + s); };
   auto raw_empty = [&](int s) { return bars + 8u * (1 + RAW_STAGES + s); };
   auto a_full = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + b); };
-  auto a_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + A_BUFS + b); };
-  auto t_full = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_BUFS + b); };
-  auto t_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_BUFS + 2 + b); };
+  auto a_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + A_STAGES + b); };
+  auto t_full = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_STAGES + b); };
+  auto t_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_STAGES + 2 + b); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ks = blockIdx.x % plan.ksplit, group = blockIdx.x / plan.ksplit;
@@ -182,7 +230,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(x_full, 1);
     for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DEQ_WARPS); }
-    for (int b = 0; b < A_BUFS; ++b) { mbar_init(a_full(b), DEQ_WARPS); mbar_init(a_empty(b), 1); }
+    for (int b = 0; b < A_STAGES; ++b) { mbar_init(a_full(b), DEQ_WARPS); mbar_init(a_empty(b), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(t_full(b), 1); mbar_init(t_empty(b), 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
@@ -190,7 +238,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2u * TM) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -208,7 +256,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       for (int t = group; t < plan.n_tiles && ok; t += plan.groups) {
         for (int s = 0; s < nstages; ++s, ++it) {
           const int slot = it % RAW_STAGES;
-          if (!mbar_wait(raw_empty(slot), ((it / RAW_STAGES) & 1) ^ 1)) { atomicExch(status, 11); ok = false; break; }
+          if (!mbar_wait_relaxed(raw_empty(slot), ((it / RAW_STAGES) & 1) ^ 1, 64)) { atomicExch(status, 11); ok = false; break; }
           mbar_expect_tx(raw_full(slot), RAW_STAGE_BYTES);
           const uint32_t dst = raw_base + slot * RAW_STAGE_BYTES;
           tma_load_2d(dst, &map_q, raw_full(slot), (stage0 + s) * (STAGE_K / 2), t * TN);
@@ -222,35 +270,39 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
+    // ---------------- MMA issuer: A (dequantised weights) from tensor memory, B (activations) from shared memory ----------------
     if (lane == 0) {
       bool ok = mbar_wait(x_full, 0);
       if (!ok) atomicExch(status, 12);
-      int ab = 0, local = 0;
+      int as = 0, local = 0;
       for (int t = group; t < plan.n_tiles && ok; t += plan.groups, ++local) {
         const int acc = local & 1;
-        if (!mbar_wait(t_empty(acc), ((local >> 1) & 1) ^ 1)) { atomicExch(status, 13); ok = false; break; }
+        if (!mbar_wait_relaxed(t_empty(acc), ((local >> 1) & 1) ^ 1, 32)) { atomicExch(status, 13); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TM);
-        for (int sub = 0; sub < nsub; ++sub, ++ab) {
-          const int buf = ab % A_BUFS;
-          if (!mbar_wait(a_full(buf), (ab / A_BUFS) & 1)) { atomicExch(status, 14); ok = false; break; }
+        for (int s = 0; s < nstages; ++s, ++as) {
+          const int buf = as % A_STAGES;
+          if (!mbar_wait(a_full(buf), (as / A_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t sa = a_base + buf * A_BYTES, sb = x_base + sub * X_SUB_BYTES;
+          const uint32_t ta = tmem_base + (uint32_t)(A_COL0 + buf * A_STAGE_COLS);
+          const uint32_t sb = x_base + (uint32_t)(s * 4) * X_SUB_BYTES;
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_d, make_sdesc(sa + k * 32), make_sdesc(sb + k * 32), IDESC, (sub > 0 || k > 0) ? 1u : 0u);
+          for (int sub = 0; sub < 4; ++sub)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_bf16_ts(tmem_d, ta + (uint32_t)(sub * 32 + k * 8), make_sdesc(sb + sub * X_SUB_BYTES + k * 32), IDESC,
+                           (s > 0 || sub > 0 || k > 0) ? 1u : 0u);
           umma_commit(a_empty(buf));
         }
         if (ok) umma_commit(t_full(acc));
       }
     }
   } else if (warp < 2 + DEQ_WARPS) {
-    // ---------------- dequantisers: thread = (weight row r, block half hb of each 64-K sub-tile) ----------------
-    const int td = threadIdx.x - 64;
-    const int r = td & 127, hb = td >> 7;
+    // ---------------- dequantisers: thread = weight row (its TMEM lane), two 32-value blocks of every 256-K stage ----------------
+    const int quarter = warp & 3, part = (warp - 2) >> 2;   // a warp reaches only the TMEM lanes of its quarter
+    const int r = quarter * 32 + lane;
     const uint32_t swz = (uint32_t)(r & 7);
-    int it = 0, ab = 0;
+    int it = 0;
     bool ok = true;
     for (int t = group; t < plan.n_tiles && ok; t += plan.groups) {
       for (int s = 0; s < nstages && ok; ++s, ++it) {
@@ -259,38 +311,25 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (lane == 0) good = mbar_wait(raw_full(slot), (it / RAW_STAGES) & 1) ? 1 : 0;
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) { if (lane == 0) atomicExch(status, 15); ok = false; break; }
-        const uint8_t* rawp = gen + X_BYTES + slot * RAW_STAGE_BYTES;
-        const uint4 sc = *reinterpret_cast<const uint4*>(rawp + RAW_BYTES + r * 16);
-        uint4 q[4];
-#pragma unroll
-        for (int sub = 0; sub < 4; ++sub)
-          q[sub] = *reinterpret_cast<const uint4*>(rawp + r * 128 + (((uint32_t)(sub * 2 + hb) ^ swz) << 4));
-#pragma unroll
-        for (int sub = 0; sub < 4; ++sub, ++ab) {
-          // scale of block (sub * 2 + hb): f16 bits -> f32 -> bf16, duplicated into both halves
-          const uint32_t sw = sub == 0 ? sc.x : sub == 1 ? sc.y : sub == 2 ? sc.z : sc.w;
-          const uint32_t db = f32_to_bf16_bits(f16_bits_to_f32((u16)(hb ? (sw >> 16) : (sw & 0xFFFFu))));
-          const uint32_t d2 = db | (db << 16);
-          const uint4 w = q[sub];
-          const uint4 c0 = deq8(w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, d2);                // elements 0-7
-          const uint4 c1 = deq8(w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu, d2);                // 8-15
-          const uint4 c2 = deq8((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, d2);  // 16-23
-          const uint4 c3 = deq8((w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu, d2);  // 24-31
-          const int buf = ab % A_BUFS;
-          if (lane == 0) good = mbar_wait(a_empty(buf), ((ab / A_BUFS) & 1) ^ 1) ? 1 : 0;
-          good = __shfl_sync(0xffffffffu, good, 0);
-          if (!good) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
-          uint8_t* arow = gen + X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + buf * A_BYTES + r * 128;
-          *reinterpret_cast<uint4*>(arow + (((uint32_t)(hb * 4 + 0) ^ swz) << 4)) = c0;
-          *reinterpret_cast<uint4*>(arow + (((uint32_t)(hb * 4 + 1) ^ swz) << 4)) = c1;
-          *reinterpret_cast<uint4*>(arow + (((uint32_t)(hb * 4 + 2) ^ swz) << 4)) = c2;
-          *reinterpret_cast<uint4*>(arow + (((uint32_t)(hb * 4 + 3) ^ swz) << 4)) = c3;
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(a_full(buf));
-        }
+        const uint32_t rawp = raw_base + slot * RAW_STAGE_BYTES;
+        const uint4 q0 = lds128(rawp + r * 128 + (((uint32_t)(2 * part) ^ swz) << 4));
+        const uint4 q1 = lds128(rawp + r * 128 + (((uint32_t)(2 * part + 1) ^ swz) << 4));
+        const uint32_t sw = lds32(rawp + RAW_BYTES + r * 16 + part * 4);   // f16 scales of blocks 2*part, 2*part+1
         __syncwarp();
-        if (ok && lane == 0) mbar_arrive(raw_empty(slot));
+        if (lane == 0) mbar_arrive(raw_empty(slot));                        // the stage now lives in registers
+        uint32_t v[32];
+        deq_block(q0, bf16x2_of_f16(sw & 0xFFFFu), v);
+        deq_block(q1, bf16x2_of_f16(sw >> 16), v + 16);
+        const int buf = it % A_STAGES;
+        if (lane == 0) good = mbar_wait(a_empty(buf), ((it / A_STAGES) & 1) ^ 1) ? 1 : 0;
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(A_COL0 + buf * A_STAGE_COLS + part * 32);
+        tmem_st32(ta, v);
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_full(buf));
       }
     }
   } else {
@@ -303,7 +342,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       const int acc = local & 1;
       const int n = t * TN + quarter * 32 + lane;
       int good = 1;
-      if (lane == 0) good = mbar_wait(t_full(acc), (local >> 1) & 1) ? 1 : 0;
+      if (lane == 0) good = mbar_wait_relaxed(t_full(acc), (local >> 1) & 1, 128) ? 1 : 0;
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -324,7 +363,9 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           finish32<MODE>(v, h * 32, M, n, N, out, ldo);
         }
       } else {
-        float* mine = ws + ((i64)ks * n_pad + n) * TM;
+        // partial sums are kept as [slice][tile][activation row][weight row of the tile]: a warp writes and reads
+        // 128 contiguous bytes per activation row
+        float* mine = ws + (((i64)ks * plan.n_tiles + t) * TM) * TN + quarter * 32 + lane;
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
           uint32_t rr[32];
@@ -335,8 +376,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             if (lane == 0) mbar_arrive(t_empty(acc));
           }
 #pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            *reinterpret_cast<uint4*>(mine + h * 32 + e) = make_uint4(rr[e], rr[e + 1], rr[e + 2], rr[e + 3]);
+          for (int e = 0; e < 32; ++e) __stcg(mine + (i64)(h * 32 + e) * TN, __uint_as_float(rr[e]));
         }
         // publish, count this warp in, and let the last warp of this (tile, quarter) add the slices up
         __threadfence();
@@ -346,21 +386,19 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         prev = __shfl_sync(0xffffffffu, prev, 0);
         if (prev == plan.ksplit - 1) {
           __threadfence();
+          const float* src0 = ws + ((i64)t * TM) * TN + quarter * 32 + lane;
+          const i64 slice_stride = (i64)plan.n_tiles * TM * TN;
 #pragma unroll 1
           for (int h = 0; h < 2; ++h) {
             float v[32];
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = 0.0f;
-            for (int s = 0; s < plan.ksplit; ++s) {
-              const float4* src = reinterpret_cast<const float4*>(ws + ((i64)s * n_pad + n) * TM + h * 32);
+            for (int e = 0; e < 32; ++e) v[e] = __ldcg(src0 + (i64)(h * 32 + e) * TN);
+            for (int s = 1; s < plan.ksplit; ++s) {      // slices are added in slice order
+              float p0[32];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const float4 p = __ldcg(src + e);
-                v[4 * e] = s ? fadd(v[4 * e], p.x) : p.x;
-                v[4 * e + 1] = s ? fadd(v[4 * e + 1], p.y) : p.y;
-                v[4 * e + 2] = s ? fadd(v[4 * e + 2], p.z) : p.z;
-                v[4 * e + 3] = s ? fadd(v[4 * e + 3], p.w) : p.w;
-              }
+              for (int e = 0; e < 32; ++e) p0[e] = __ldcg(src0 + s * slice_stride + (i64)(h * 32 + e) * TN);
+#pragma unroll
+              for (int e = 0; e < 32; ++e) v[e] = fadd(v[e], p0[e]);
             }
             finish32<MODE>(v, h * 32, M, n, N, out, ldo);
           }
@@ -369,12 +407,13 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
       }
     }
+    (void)n_pad;
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * TM) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
