@@ -274,19 +274,21 @@ int wkb_gemm_bf16_nt(const void* a, int64_t lda, const void* b, int64_t ldb, voi
                      int64_t ldr, void* stream);
 int wkb_gemm_status(void);
 
-/* W4A16 GEMM on the tensor cores for batched decode: out[m, n] = x[m, k] . W[n, k]^T with W resident as the
- * two Q4_0 planes of wkb_q_split whose rows are padded to k_pitch (a multiple of 256; the padding blocks
- * hold zero scales), x bf16 with row pitch ldx.  The weight the tensor core multiplies is exactly
+/* W4A16 GEMM on the tensor cores for batched decode: out[m, n] = x[m, k] . W[n, k]^T, x bf16 with row pitch ldx.
+ * W is resident in the tiled layout that wkb_q4_tile builds from the reference's raw Q4_0 rows (n rows of k/32
+ * 18-byte blocks, crates/wukong_runtime/src/quant.rs:13-16): [tile of 128 rows][stage of 256 K] -> one contiguous
+ * 18 KB image (nibble rows, then f16 scales), zero beyond n and k, wkb_q4_tiled_bytes(n, k) bytes in all -- every
+ * stage the kernel streams is one contiguous burst of HBM.  The weight the tensor core multiplies is exactly
  * bf16(bf16(d) * (nib - 8)); accumulation is fp32.  out_mode 0: f32 out[m, n]; 1: bf16 out[m, n];
- * 2: SwiGLU -- W rows interleaved (gate_0, up_0, gate_1, up_1, ...), bf16 out[m, n / 2] =
- * silu(gate) * up.  Rows are processed 64 at a time.  `workspace` (at least
- * wkb_gemm_q4_0_workspace_bytes(n, k_pitch), zero-filled once when allocated, one per stream) holds the
- * K-slice partial sums and their arrival counters; the result does not depend on arrival order.
+ * 2: SwiGLU -- W rows interleaved (gate_0, up_0, gate_1, up_1, ...), bf16 out[m, n / 2] = silu(gate) * up.
+ * Rows are processed 64 at a time.  `workspace` (at least wkb_gemm_q4_0_workspace_bytes(n, k), one per stream)
+ * holds the K-slice partial sums, which a second pass adds in slice order: results are run-to-run identical.
  * Counterpart in the reference: the W4A16 tile kernels of crates/wukong_codegen_gpu/src/ptx_int4.rs. */
-int64_t wkb_gemm_q4_0_workspace_bytes(int64_t n, int64_t k_pitch);
-int wkb_gemm_q4_0_bf16_nt(const void* qs, const void* d, int64_t k_pitch, const void* x_bf16, int64_t ldx, void* out,
-                          int64_t ldo, int out_mode, int64_t m, int64_t n, int64_t k, void* workspace,
-                          int64_t workspace_bytes, void* stream);
+int64_t wkb_q4_tiled_bytes(int64_t n, int64_t k);
+int wkb_q4_tile(const uint8_t* raw, int64_t n, int64_t k, void* tiled, void* stream);
+int64_t wkb_gemm_q4_0_workspace_bytes(int64_t n, int64_t k);
+int wkb_gemm_q4_0_bf16_nt(const void* w_tiled, const void* x_bf16, int64_t ldx, void* out, int64_t ldo, int out_mode,
+                          int64_t m, int64_t n, int64_t k, void* workspace, int64_t workspace_bytes, void* stream);
 /* The same GEMM over OCP E4M3FN codes (one byte per element, the codec of crates/wukong_runtime/src/fp8.rs
  * :66-164; the reference's GPU counterpart is ptx_fp8.rs `fp8_gemm_nt*`): tcgen05 kind::f8f6f4, fp32
  * accumulate, K % 16 == 0, pitches multiples of 16. */

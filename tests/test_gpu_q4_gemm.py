@@ -52,7 +52,7 @@ def run_case(dev, orc, rng, m, n, k, mode):
     exact, w_bf = reference_weights(orc, raw, n, k)
     w = dev.Q4Weight.from_raw(torch.from_numpy(raw).cuda(), n, k)
     xt = torch.from_numpy(xb.view(np.int16).reshape(m, k)).cuda().view(torch.bfloat16)
-    ws = dev.gemm_q4_workspace(w.n, w.k_pitch)
+    ws = dev.gemm_q4_workspace(w.n, w.k)
     out = dev.gemm_q4_0_bf16_nt(w, xt, mode=mode, workspace=ws)
     again = dev.gemm_q4_0_bf16_nt(w, xt, mode=mode, workspace=ws)   # the arrival counters must have been re-armed
     torch.cuda.synchronize()

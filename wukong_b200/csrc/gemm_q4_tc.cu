@@ -53,9 +53,6 @@ constexpr int A_STAGES = 3, A_STAGE_COLS = STAGE_K / 2, A_COL0 = 2 * TM;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int NUM_BARS = 1 + 2 * RAW_STAGES + 2 * A_STAGES + 4;
 constexpr int SMEM = X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + 1024 + 256;
-// The arrival counters sit in a fixed-size head of the workspace so that GEMMs of different shapes can share
-// one workspace: no partial sum ever lands where another shape keeps a counter.
-constexpr int COUNTER_BYTES = 65536;
 constexpr int DEQ_WARPS = 16, THREADS = 32 * (2 + DEQ_WARPS + 4);
 // instruction descriptor, kind::f16: D = f32, A = B = bf16 (the two operand formats must agree: an f16 A with a
 // bf16 B is rejected by the hardware as an illegal instruction)
@@ -63,6 +60,7 @@ constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TM >
 
 struct Plan {
   int n_tiles, kstages, ksplit, stages_per_slice, groups;
+  int kstages_pitch;   // stages per tile row in the resident layout (>= kstages)
 };
 
 // Choose the K split: a slice holds at most KS_MAX / STAGE_K stages; among the feasible splits take
@@ -73,7 +71,7 @@ inline Plan make_plan(i64 n, i64 k, i64 sms) {
   p.n_tiles = (int)((n + TN - 1) / TN);
   p.kstages = (int)((k + STAGE_K - 1) / STAGE_K);
   int best_cost = 1 << 30;
-  p.ksplit = 1; p.stages_per_slice = p.kstages; p.groups = 1;
+  p.ksplit = 1; p.stages_per_slice = p.kstages; p.groups = 1; p.kstages_pitch = p.kstages;
   for (int sps = KS_MAX / STAGE_K; sps >= 1; --sps) {
     int ks = (p.kstages + sps - 1) / sps;
     if (ks > sms) continue;
@@ -127,6 +125,11 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
+}
+// 1-D bulk copy global -> shared, completion counted on an mbarrier (addresses and size multiples of 16 bytes)
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 // MMA with the A operand in tensor memory (lane = row, a column holds two consecutive K elements)
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -203,9 +206,8 @@ __device__ __forceinline__ void finish32(const float (&v)[32], int m0, int M, in
 
 template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_q,
-                  const __grid_constant__ CUtensorMap map_d, void* out, i64 ldo, int M, int N, Plan plan,
-                  float* ws, int* counters, int* status) {
+gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ wt, void* out, i64 ldo, int M, int N,
+                  Plan plan, float* ws, int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -234,8 +236,6 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     for (int b = 0; b < 2; ++b) { mbar_init(t_full(b), 1); mbar_init(t_empty(b), 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_d) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -258,9 +258,9 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           const int slot = it % RAW_STAGES;
           if (!mbar_wait_relaxed(raw_empty(slot), ((it / RAW_STAGES) & 1) ^ 1, 64)) { atomicExch(status, 11); ok = false; break; }
           mbar_expect_tx(raw_full(slot), RAW_STAGE_BYTES);
-          const uint32_t dst = raw_base + slot * RAW_STAGE_BYTES;
-          tma_load_2d(dst, &map_q, raw_full(slot), (stage0 + s) * (STAGE_K / 2), t * TN);
-          tma_load_2d(dst + RAW_BYTES, &map_d, raw_full(slot), (stage0 + s) * (STAGE_K / 32), t * TN);
+          // one contiguous 18 KB stage image: (tile, stage) -> nibble rows already in their swizzled places, then scales
+          bulk_load(raw_base + slot * RAW_STAGE_BYTES, wt + ((i64)t * plan.kstages_pitch + stage0 + s) * RAW_STAGE_BYTES,
+                    RAW_STAGE_BYTES, raw_full(slot));
         }
       }
       if (!ok) {
@@ -363,9 +363,9 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           finish32<MODE>(v, h * 32, M, n, N, out, ldo);
         }
       } else {
-        // partial sums are kept as [slice][tile][activation row][weight row of the tile]: a warp writes and reads
-        // 128 contiguous bytes per activation row
-        float* mine = ws + (((i64)ks * plan.n_tiles + t) * TM) * TN + quarter * 32 + lane;
+        // partial sums go to the workspace as [slice][activation row][weight row]; a separate pass adds the
+        // slices in slice order, so the result does not depend on which CTA finished first
+        float* mine = ws + ((i64)ks * TM) * n_pad + n;
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
           uint32_t rr[32];
@@ -375,39 +375,13 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(t_empty(acc));
           }
+          const int mcount = min(32, M - h * 32);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) __stcg(mine + (i64)(h * 32 + e) * TN, __uint_as_float(rr[e]));
-        }
-        // publish, count this warp in, and let the last warp of this (tile, quarter) add the slices up
-        __threadfence();
-        __syncwarp();
-        int prev = 0;
-        if (lane == 0) prev = atomicAdd(&counters[t * 4 + quarter], 1);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        if (prev == plan.ksplit - 1) {
-          __threadfence();
-          const float* src0 = ws + ((i64)t * TM) * TN + quarter * 32 + lane;
-          const i64 slice_stride = (i64)plan.n_tiles * TM * TN;
-#pragma unroll 1
-          for (int h = 0; h < 2; ++h) {
-            float v[32];
-#pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = __ldcg(src0 + (i64)(h * 32 + e) * TN);
-            for (int s = 1; s < plan.ksplit; ++s) {      // slices are added in slice order
-              float p0[32];
-#pragma unroll
-              for (int e = 0; e < 32; ++e) p0[e] = __ldcg(src0 + s * slice_stride + (i64)(h * 32 + e) * TN);
-#pragma unroll
-              for (int e = 0; e < 32; ++e) v[e] = fadd(v[e], p0[e]);
-            }
-            finish32<MODE>(v, h * 32, M, n, N, out, ldo);
-          }
-          __syncwarp();
-          if (lane == 0) counters[t * 4 + quarter] = 0;  // ready for the next launch
+          for (int e = 0; e < 32; ++e)
+            if (e < mcount) __stcg(mine + (i64)(h * 32 + e) * n_pad, __uint_as_float(rr[e]));
         }
       }
     }
-    (void)n_pad;
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -417,18 +391,83 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   }
 }
 
-static int encode(CUtensorMap* map, CUtensorMapDataType dt, int esize, const void* ptr, i64 inner, i64 rows, i64 pitch_bytes,
-                  int box_inner, int box_rows, bool swizzle) {
+// ---- split-K second pass: out = finish(sum over slices in slice order) ----------------------------------------
+// One thread per (activation row, four consecutive weight rows): ksplit independent 16-byte loads, then the same
+// finishing as the in-kernel path (MODE 2: two (gate, up) pairs -> two bf16 outputs).
+template <int MODE>
+__global__ void __launch_bounds__(256) q4_splitk_reduce_kernel(const float* __restrict__ ws, int ksplit, int M, int N, i64 n_pad,
+                                                               void* out, i64 ldo) {
+  const i64 quads = n_pad >> 2;
+  const i64 total = (i64)M * quads;
+  for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
+    const int m = (int)(idx / quads);
+    const i64 n0 = (idx % quads) << 2;
+    if (n0 >= N) continue;
+    const float4* src = reinterpret_cast<const float4*>(ws + (i64)m * n_pad + n0);
+    const i64 slice = ((i64)TM * n_pad) >> 2;
+    float4 v = __ldcg(src);
+    for (int s0 = 1; s0 < ksplit; s0 += 4) {
+      float4 p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (s0 + j < ksplit) p[j] = __ldcg(src + (i64)(s0 + j) * slice);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (s0 + j < ksplit) { v.x = fadd(v.x, p[j].x); v.y = fadd(v.y, p[j].y); v.z = fadd(v.z, p[j].z); v.w = fadd(v.w, p[j].w); }
+    }
+    if (MODE == 2) {
+      const float y0 = fmul(silu1(v.x), v.y), y1 = fmul(silu1(v.z), v.w);
+      u16* o = reinterpret_cast<u16*>(out) + (i64)m * ldo + (n0 >> 1);
+      o[0] = f32_to_bf16_bits(y0);
+      if (n0 + 2 < N) o[1] = f32_to_bf16_bits(y1);
+    } else {
+      const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (n0 + j < N) {
+          if (MODE == 1) reinterpret_cast<u16*>(out)[(i64)m * ldo + n0 + j] = f32_to_bf16_bits(vv[j]);
+          else reinterpret_cast<float*>(out)[(i64)m * ldo + n0 + j] = vv[j];
+        }
+      }
+    }
+  }
+}
+
+// ---- resident layout: raw Q4_0 rows -> [tile of 128 rows][stage of 256 K][18 KB stage image] -----------------------
+// A stage image is what the kernel wants in shared memory: 128 rows x 128 B of nibbles with the 16-byte block chunks
+// already XOR-swizzled by (row & 7), then 128 rows x 8 f16 scales.  Rows past N and blocks past K are zero (scale 0).
+__global__ void __launch_bounds__(256) q4_tile_kernel(const u8* __restrict__ raw, i64 n, i64 nb, i64 n_tiles, i64 kstages,
+                                                      u8* __restrict__ out) {
+  const i64 total = n_tiles * kstages * TN * 8;
+  for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
+    const int b = (int)(idx & 7), r = (int)((idx >> 3) & (TN - 1));
+    const i64 ts = idx >> 10, s = ts % kstages, t = ts / kstages;
+    const i64 row = t * TN + r, kb = s * 8 + b;
+    u8* img = out + ts * RAW_STAGE_BYTES;
+    u8* qdst = img + r * 128 + ((b ^ (r & 7)) << 4);
+    u8* ddst = img + RAW_BYTES + r * 16 + b * 2;
+    if (row < n && kb < nb) {
+      const u8* src = raw + (row * nb + kb) * 18;
+      ddst[0] = src[0]; ddst[1] = src[1];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) qdst[j] = src[2 + j];
+    } else {
+      ddst[0] = 0; ddst[1] = 0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) qdst[j] = 0;
+    }
+  }
+}
+
+static int encode_x(CUtensorMap* map, const void* ptr, i64 k, i64 rows, i64 ldx) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return (int)cudaErrorNotSupported;
-  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows};
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)TM};
   cuuint32_t estr[2] = {1, 1};
-  (void)esize;
-  CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
@@ -439,38 +478,39 @@ using namespace wkb;
 
 extern "C" {
 
-int64_t wkb_gemm_q4_0_workspace_bytes(int64_t n, int64_t k_pitch) {
-  if (n <= 0 || k_pitch <= 0) return 256;
-  q4tc::Plan p = q4tc::make_plan(n, k_pitch, gemm_sm_count());
-  i64 counters = q4tc::COUNTER_BYTES;
-  i64 partial = p.ksplit > 1 ? (i64)p.ksplit * p.n_tiles * q4tc::TN * q4tc::TM * 4 : 0;
-  return counters + partial;
+int64_t wkb_q4_tiled_bytes(int64_t n, int64_t k) {
+  if (n <= 0 || k <= 0) return 0;
+  return ((n + q4tc::TN - 1) / q4tc::TN) * ((k + q4tc::STAGE_K - 1) / q4tc::STAGE_K) * q4tc::RAW_STAGE_BYTES;
 }
 
-int wkb_gemm_q4_0_bf16_nt(const void* qs, const void* d, int64_t k_pitch, const void* x_bf16, int64_t ldx, void* out,
-                          int64_t ldo, int out_mode, int64_t m, int64_t n, int64_t k, void* workspace,
-                          int64_t workspace_bytes, void* stream) {
+int wkb_q4_tile(const uint8_t* raw, int64_t n, int64_t k, void* tiled, void* stream) {
+  if (n <= 0 || k <= 0) return 0;
+  if (k % 32 != 0 || (((uintptr_t)tiled) & 15)) return (int)cudaErrorInvalidValue;
+  const i64 n_tiles = (n + q4tc::TN - 1) / q4tc::TN, kstages = (k + q4tc::STAGE_K - 1) / q4tc::STAGE_K;
+  const i64 total = n_tiles * kstages * q4tc::TN * 8;
+  i64 grid = (total + 255) / 256;
+  if (grid > gemm_sm_count() * 32) grid = gemm_sm_count() * 32;
+  q4tc::q4_tile_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(raw, n, k / 32, n_tiles, kstages, (u8*)tiled);
+  return (int)cudaGetLastError();
+}
+
+int64_t wkb_gemm_q4_0_workspace_bytes(int64_t n, int64_t k) {
+  if (n <= 0 || k <= 0) return 256;
+  q4tc::Plan p = q4tc::make_plan(n, k, gemm_sm_count());
+  return p.ksplit > 1 ? (i64)p.ksplit * q4tc::TM * p.n_tiles * q4tc::TN * 4 : 256;
+}
+
+int wkb_gemm_q4_0_bf16_nt(const void* w_tiled, const void* x_bf16, int64_t ldx, void* out, int64_t ldo, int out_mode,
+                          int64_t m, int64_t n, int64_t k, void* workspace, int64_t workspace_bytes, void* stream) {
   if (m <= 0 || n <= 0) return 0;
-  if (k <= 0 || k > k_pitch || k_pitch % q4tc::STAGE_K != 0 || k % 8 != 0 || ldx % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (k <= 0 || k % 32 != 0 || ldx % 8 != 0) return (int)cudaErrorInvalidValue;
   if (out_mode < 0 || out_mode > 2 || (out_mode == 2 && (n & 1))) return (int)cudaErrorInvalidValue;
-  if ((((uintptr_t)qs) | ((uintptr_t)d) | ((uintptr_t)x_bf16) | ((uintptr_t)workspace)) & 15) return (int)cudaErrorMisalignedAddress;
-  if (!workspace || workspace_bytes < wkb_gemm_q4_0_workspace_bytes(n, k_pitch)) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)w_tiled) | ((uintptr_t)x_bf16) | ((uintptr_t)workspace)) & 15) return (int)cudaErrorMisalignedAddress;
+  if (!workspace || workspace_bytes < wkb_gemm_q4_0_workspace_bytes(n, k)) return (int)cudaErrorInvalidValue;
   int* status = gemm_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
-  q4tc::Plan plan = q4tc::make_plan(n, k_pitch, gemm_sm_count());
-  // stages past the logical K hold only padding: do not visit them
-  plan.kstages = (int)((k + q4tc::STAGE_K - 1) / q4tc::STAGE_K);
-  {
-    q4tc::Plan full = plan;
-    plan.ksplit = (plan.kstages + full.stages_per_slice - 1) / full.stages_per_slice;
-    if (plan.ksplit < 1) plan.ksplit = 1;
-  }
-  CUtensorMap mq, md;
-  int rc = q4tc::encode(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, qs, k_pitch / 2, n, k_pitch / 2, 128, q4tc::TN, true);
-  if (rc) return rc;
-  rc = q4tc::encode(&md, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d, k_pitch / 32, n, k_pitch / 32 * 2, 8, q4tc::TN, false);
-  if (rc) return rc;
-  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, void*, i64, int, int, q4tc::Plan, float*, int*, int*);
+  q4tc::Plan plan = q4tc::make_plan(n, k, gemm_sm_count());
+  typedef void (*KernelFn)(const CUtensorMap, const uint8_t*, void*, i64, int, int, q4tc::Plan, float*, int*);
   static const KernelFn table[3] = {q4tc::gemm_q4_tc_kernel<0>, q4tc::gemm_q4_tc_kernel<1>, q4tc::gemm_q4_tc_kernel<2>};
   static bool attr_set[64][3] = {{false}};
   int dev = 0;
@@ -480,22 +520,29 @@ int wkb_gemm_q4_0_bf16_nt(const void* qs, const void* d, int64_t k_pitch, const 
     if (e != cudaSuccess) return (int)e;
     attr_set[dev][out_mode] = true;
   }
-  int* counters = reinterpret_cast<int*>(workspace);
-  if ((i64)plan.n_tiles * 16 > q4tc::COUNTER_BYTES) return (int)cudaErrorInvalidValue;
-  float* ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + q4tc::COUNTER_BYTES);
-  const i64 out_cols = out_mode == 2 ? n / 2 : n;
-  (void)out_cols;
+  float* ws = reinterpret_cast<float*>(workspace);
+  const i64 n_pad = (i64)plan.n_tiles * q4tc::TN;
   const int esz = out_mode == 0 ? 4 : 2;
   for (i64 m0 = 0; m0 < m; m0 += q4tc::TM) {
     const i64 mc = m - m0 < q4tc::TM ? m - m0 : q4tc::TM;
     CUtensorMap mx;
-    rc = q4tc::encode(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (const u16*)x_bf16 + m0 * ldx, k, mc, ldx * 2, 64, q4tc::TM, true);
+    int rc = q4tc::encode_x(&mx, (const u16*)x_bf16 + m0 * ldx, k, mc, ldx);
     if (rc) return rc;
     void* o = reinterpret_cast<uint8_t*>(out) + m0 * ldo * esz;
     table[out_mode]<<<plan.ksplit * plan.groups, q4tc::THREADS, q4tc::SMEM, as_stream(stream)>>>(
-        mx, mq, md, o, ldo, (int)mc, (int)n, plan, ws, counters, status);
+        mx, (const uint8_t*)w_tiled, o, ldo, (int)mc, (int)n, plan, ws, status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
+    if (plan.ksplit > 1) {
+      const i64 total = mc * (n_pad >> 2);
+      i64 grid = (total + 255) / 256;
+      if (grid > gemm_sm_count() * 8) grid = gemm_sm_count() * 8;
+      if (out_mode == 0) q4tc::q4_splitk_reduce_kernel<0><<<(int)grid, 256, 0, as_stream(stream)>>>(ws, plan.ksplit, (int)mc, (int)n, n_pad, o, ldo);
+      else if (out_mode == 1) q4tc::q4_splitk_reduce_kernel<1><<<(int)grid, 256, 0, as_stream(stream)>>>(ws, plan.ksplit, (int)mc, (int)n, n_pad, o, ldo);
+      else q4tc::q4_splitk_reduce_kernel<2><<<(int)grid, 256, 0, as_stream(stream)>>>(ws, plan.ksplit, (int)mc, (int)n, n_pad, o, ldo);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return (int)e;
+    }
   }
   return 0;
 }

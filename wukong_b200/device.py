@@ -76,32 +76,33 @@ def gemv_q4_0_bf16x(qs, d, x_bf16, n, k, out=None):
 
 
 class Q4Weight:
-    """Resident Q4_0 matrix [n, k] for the tensor-core GEMM: nibble plane [n, k_pitch/32, 16] u8 and scale
-    plane [n, k_pitch/32] f16, rows padded with zero blocks to k_pitch (a multiple of 256)."""
+    """Resident Q4_0 matrix [n, k] in the tiled layout of the tensor-core GEMM (wkb_q4_tile)."""
 
-    def __init__(self, qs, d, n, k, k_pitch):
-        self.qs, self.d, self.n, self.k, self.k_pitch = qs, d, n, k, k_pitch
+    def __init__(self, tiled, n, k):
+        self.tiled, self.n, self.k = tiled, n, k
 
     @staticmethod
     def from_raw(raw_u8, n, k):
         """`raw_u8`: device tensor of the n * (k/32) 18-byte blocks as the reference stores them."""
         if k % 32:
             raise ValueError("k must be a multiple of 32")
-        nb = k // 32
-        qs, d = q_split(raw_u8, n * nb, q4=True)
-        kp = (k + 255) // 256 * 256
-        if kp != k:
-            nbp = kp // 32
-            qs_p = torch.zeros(n, nbp, 16, dtype=torch.uint8, device=qs.device)
-            d_p = torch.zeros(n, nbp, dtype=torch.float16, device=qs.device)
-            qs_p[:, :nb] = qs.view(n, nb, 16)
-            d_p[:, :nb] = d.view(n, nb)
-            qs, d = qs_p, d_p
-        return Q4Weight(qs.view(n, kp // 32, 16), d.view(n, kp // 32), n, k, kp)
+        tiled = torch.empty(int(lib().wkb_q4_tiled_bytes(n, k)), dtype=torch.uint8, device=raw_u8.device)
+        check(lib().wkb_q4_tile(_p(raw_u8), n, k, _p(tiled), _s()), "wkb_q4_tile")
+        return Q4Weight(tiled, n, k)
+
+    @staticmethod
+    def from_planes(qs, d):
+        """qs uint8 [n, k/32, 16] nibble bytes, d float16 [n, k/32] scales (device tensors)."""
+        n, nb = d.shape
+        raw = torch.cat([d.contiguous().view(torch.uint8).view(n, nb, 2), qs.view(n, nb, 16)], dim=2).contiguous()
+        return Q4Weight.from_raw(raw.view(-1), n, nb * 32)
+
+    def weight_bytes(self):
+        return self.n * (self.k // 32) * 18
 
 
-def gemm_q4_workspace(n, k_pitch, device="cuda"):
-    return torch.zeros(int(lib().wkb_gemm_q4_0_workspace_bytes(n, k_pitch)), dtype=torch.uint8, device=device)
+def gemm_q4_workspace(n, k, device="cuda"):
+    return torch.zeros(int(lib().wkb_gemm_q4_0_workspace_bytes(n, k)), dtype=torch.uint8, device=device)
 
 
 def gemm_q4_0_bf16_nt(w, x_bf16, mode=0, out=None, workspace=None):
@@ -113,9 +114,9 @@ def gemm_q4_0_bf16_nt(w, x_bf16, mode=0, out=None, workspace=None):
     if out is None:
         out = torch.empty(m, cols, dtype=torch.float32 if mode == 0 else torch.bfloat16, device=x_bf16.device)
     if workspace is None:
-        workspace = gemm_q4_workspace(w.n, w.k_pitch, x_bf16.device)
-    check(lib().wkb_gemm_q4_0_bf16_nt(_p(w.qs), _p(w.d), w.k_pitch, _p(x_bf16), x_bf16.stride(0), _p(out), out.stride(0), mode,
-                                      m, w.n, k, _p(workspace), workspace.numel(), _s()), "wkb_gemm_q4_0_bf16_nt")
+        workspace = gemm_q4_workspace(w.n, w.k, x_bf16.device)
+    check(lib().wkb_gemm_q4_0_bf16_nt(_p(w.tiled), _p(x_bf16), x_bf16.stride(0), _p(out), out.stride(0), mode, m, w.n, k,
+                                      _p(workspace), workspace.numel(), _s()), "wkb_gemm_q4_0_bf16_nt")
     return out
 
 

@@ -131,15 +131,7 @@ class LlamaRankWeights:
             return qs, sc
 
         def make(qs, sc):
-            n, nb = sc.shape
-            k = nb * 32
-            kp = (k + 255) // 256 * 256
-            if kp != k:
-                qp = torch.zeros(n, kp // 32, 16, dtype=torch.uint8, device=device)
-                sp = torch.zeros(n, kp // 32, dtype=torch.float16, device=device)
-                qp[:, :nb], sp[:, :nb] = qs, sc
-                qs, sc = qp, sp
-            return dev.Q4Weight(qs.contiguous(), sc.contiguous(), n, k, kp)
+            return dev.Q4Weight.from_planes(qs.contiguous(), sc.contiguous())
 
         rows = lambda t, n: t[rank * (n // world):(rank + 1) * (n // world)]
         cols = lambda t, nb: t[:, rank * (nb // world):(rank + 1) * (nb // world)]
@@ -165,11 +157,7 @@ class LlamaRankWeights:
 
     def q4_bytes(self):
         """Algorithmic weight bytes one decode step streams on this rank (18 B per 32 weights)."""
-        tot = self.lm_head.n * (self.lm_head.k // 32) * 18
-        for lw in self.layers:
-            for key in ("wqkv", "wo", "wgu", "wdown"):
-                tot += lw[key].n * (lw[key].k // 32) * 18
-        return tot
+        return self.lm_head.weight_bytes() + sum(lw[key].weight_bytes() for lw in self.layers for key in ("wqkv", "wo", "wgu", "wdown"))
 
 
 class LlamaDecodeModel:
@@ -205,7 +193,7 @@ class LlamaDecodeModel:
         half = hd // 2
         inv = 1.0 / (np.float32(cfg.rope_base) ** (np.arange(half, dtype=np.float32) * np.float32(2.0 / hd)))
         self.inv_freq = torch.from_numpy(inv.astype(np.float32)).to(device)
-        ws_bytes = max(int(lib().wkb_gemm_q4_0_workspace_bytes(w.n, w.k_pitch))
+        ws_bytes = max(int(lib().wkb_gemm_q4_0_workspace_bytes(w.n, w.k))
                        for w in [weights.lm_head] + [lw[k] for lw in weights.layers for k in ("wqkv", "wo", "wgu", "wdown")])
         self.workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=device)
         self.scratch = dev.paged_attn_scratch(R, self.hq, hd, self.max_ctx, device)
@@ -214,7 +202,7 @@ class LlamaDecodeModel:
 
     def _gemm(self, w, x, ldx, out, ldo, mode, n, what):
         p = lambda t: t.data_ptr()
-        check(lib().wkb_gemm_q4_0_bf16_nt(p(w.qs), p(w.d), w.k_pitch, p(x), ldx, p(out), ldo, mode, n, w.n, w.k, p(self.workspace),
+        check(lib().wkb_gemm_q4_0_bf16_nt(p(w.tiled), p(x), ldx, p(out), ldo, mode, n, w.n, w.k, p(self.workspace),
                                           self.workspace.numel(), torch.cuda.current_stream().cuda_stream), what)
 
     # ---- phases (a caller that emulates several ranks on one device runs them in lockstep) ----

@@ -118,11 +118,9 @@ def case_gemm_q4(m, n, k, mode, hbm, tf, src):
     copies = max(2, L2_BYTES * 3 // bytes_w + 1)
     raw = torch.from_numpy(q4_weights(n, k, rng)).cuda()
     ws_ = [dev.Q4Weight.from_raw(raw, n, k) for _ in range(copies)]
-    for w in ws_[1:]:
-        w.qs, w.d = w.qs.clone(), w.d.clone()
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     out = torch.empty(m, n // 2 if mode == 2 else n, dtype=torch.float32 if mode == 0 else torch.bfloat16, device="cuda")
-    work = dev.gemm_q4_workspace(n, ws_[0].k_pitch)
+    work = dev.gemm_q4_workspace(n, k)
     us = time_graph(lambda i: dev.gemm_q4_0_bf16_nt(ws_[i % copies], x, mode=mode, out=out, workspace=work), copies * 2)
     alg = bytes_w + 2 * m * k + out.numel() * out.element_size()
     gbs = alg / us / 1e3
