@@ -256,7 +256,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
       for (int t = group; t < plan.n_tiles && ok; t += plan.groups) {
         for (int s = 0; s < nstages; ++s, ++it) {
           const int slot = it % RAW_STAGES;
-          if (!mbar_wait_relaxed(raw_empty(slot), ((it / RAW_STAGES) & 1) ^ 1, 64)) { atomicExch(status, 11); ok = false; break; }
+          if (!mbar_wait_parked(raw_empty(slot), ((it / RAW_STAGES) & 1) ^ 1)) { atomicExch(status, 11); ok = false; break; }
           mbar_expect_tx(raw_full(slot), RAW_STAGE_BYTES);
           // one contiguous 18 KB stage image: (tile, stage) -> nibble rows already in their swizzled places, then scales
           bulk_load(raw_base + slot * RAW_STAGE_BYTES, wt + ((i64)t * plan.kstages_pitch + stage0 + s) * RAW_STAGE_BYTES,
@@ -272,26 +272,31 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   } else if (warp == 1) {
     // ---------------- MMA issuer: A (dequantised weights) from tensor memory, B (activations) from shared memory ----------------
     if (lane == 0) {
-      bool ok = mbar_wait(x_full, 0);
+      bool ok = mbar_wait_parked(x_full, 0);
       if (!ok) atomicExch(status, 12);
       int as = 0, local = 0;
+      const uint64_t bdesc0 = make_sdesc(x_base);   // the start-address field counts 16-byte units: later operands are plain adds
       for (int t = group; t < plan.n_tiles && ok; t += plan.groups, ++local) {
         const int acc = local & 1;
-        if (!mbar_wait_relaxed(t_empty(acc), ((local >> 1) & 1) ^ 1, 32)) { atomicExch(status, 13); ok = false; break; }
+        if (!mbar_wait_parked(t_empty(acc), ((local >> 1) & 1) ^ 1)) { atomicExch(status, 13); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TM);
         for (int s = 0; s < nstages; ++s, ++as) {
           const int buf = as % A_STAGES;
-          if (!mbar_wait(a_full(buf), (as / A_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
+          if (!mbar_wait_parked(a_full(buf), (as / A_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t ta = tmem_base + (uint32_t)(A_COL0 + buf * A_STAGE_COLS);
-          const uint32_t sb = x_base + (uint32_t)(s * 4) * X_SUB_BYTES;
+          const uint64_t bd = bdesc0 + (uint64_t)((s * 4 * X_SUB_BYTES) >> 4);
+          if (s == 0) {
+            umma_bf16_ts(tmem_d, ta, bd, IDESC, 0u);   // first K step of the tile overwrites the accumulator
 #pragma unroll
-          for (int sub = 0; sub < 4; ++sub)
+            for (int j = 1; j < 16; ++j)
+              umma_bf16_ts(tmem_d, ta + (uint32_t)(j * 8), bd + (uint64_t)(((j >> 2) * X_SUB_BYTES + (j & 3) * 32) >> 4), IDESC, 1u);
+          } else {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_bf16_ts(tmem_d, ta + (uint32_t)(sub * 32 + k * 8), make_sdesc(sb + sub * X_SUB_BYTES + k * 32), IDESC,
-                           (s > 0 || sub > 0 || k > 0) ? 1u : 0u);
+            for (int j = 0; j < 16; ++j)
+              umma_bf16_ts(tmem_d, ta + (uint32_t)(j * 8), bd + (uint64_t)(((j >> 2) * X_SUB_BYTES + (j & 3) * 32) >> 4), IDESC, 1u);
+          }
           umma_commit(a_empty(buf));
         }
         if (ok) umma_commit(t_full(acc));
@@ -307,10 +312,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     for (int t = group; t < plan.n_tiles && ok; t += plan.groups) {
       for (int s = 0; s < nstages && ok; ++s, ++it) {
         const int slot = it % RAW_STAGES;
-        int good = 1;
-        if (lane == 0) good = mbar_wait(raw_full(slot), (it / RAW_STAGES) & 1) ? 1 : 0;
-        good = __shfl_sync(0xffffffffu, good, 0);
-        if (!good) { if (lane == 0) atomicExch(status, 15); ok = false; break; }
+        if (!mbar_wait_parked(raw_full(slot), (it / RAW_STAGES) & 1)) { if (lane == 0) atomicExch(status, 15); ok = false; break; }
         const uint32_t rawp = raw_base + slot * RAW_STAGE_BYTES;
         const uint4 q0 = lds128(rawp + r * 128 + (((uint32_t)(2 * part) ^ swz) << 4));
         const uint4 q1 = lds128(rawp + r * 128 + (((uint32_t)(2 * part + 1) ^ swz) << 4));
@@ -321,9 +323,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         deq_block(q0, bf16x2_of_f16(sw & 0xFFFFu), v);
         deq_block(q1, bf16x2_of_f16(sw >> 16), v + 16);
         const int buf = it % A_STAGES;
-        if (lane == 0) good = mbar_wait(a_empty(buf), ((it / A_STAGES) & 1) ^ 1) ? 1 : 0;
-        good = __shfl_sync(0xffffffffu, good, 0);
-        if (!good) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
+        if (!mbar_wait_parked(a_empty(buf), ((it / A_STAGES) & 1) ^ 1)) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(A_COL0 + buf * A_STAGE_COLS + part * 32);
         tmem_st32(ta, v);
@@ -341,10 +341,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     for (int t = group; t < plan.n_tiles && ok; t += plan.groups, ++local) {
       const int acc = local & 1;
       const int n = t * TN + quarter * 32 + lane;
-      int good = 1;
-      if (lane == 0) good = mbar_wait_relaxed(t_full(acc), (local >> 1) & 1, 128) ? 1 : 0;
-      good = __shfl_sync(0xffffffffu, good, 0);
-      if (!good) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
+      if (!mbar_wait_parked(t_full(acc), (local >> 1) & 1)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TM);
       if (plan.ksplit == 1) {

@@ -33,6 +33,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
+// Bounded wait that lets the hardware park the thread: each try may suspend for up to `hint_ns` and returns early
+// when the phase completes, so a waiting warp issues almost no instructions.  The limit is counted in tries.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns = 2000) {
+  for (uint32_t it = 0; it < (SPIN_LIMIT >> 6); ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
 // The same wait for a role that is not on the critical path: it sleeps between polls so that its polling does
 // not take issue slots and shared-memory bandwidth from the warps doing the work.  The limit is counted in polls.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, uint32_t sleep_ns) {
