@@ -9,6 +9,7 @@ the named shapes; the KV cache is filled with seeded normal values standing for 
 through host buffers every step (rows up, tokens down)."""
 import json
 import os
+import sys
 import time
 
 import bench as B
@@ -95,7 +96,7 @@ def run_ours(args):
     import torch.distributed as dist
     from wukong_b200 import _lib, device as dev
     from wukong_b200._lib import lib, check
-    from wukong_b200.llama import LlamaConfig, LlamaRankWeights, LlamaDecodeModel
+    from wukong_b200.llama import LlamaConfig, LlamaRankWeights, LlamaDecodeModel, DecodeStepRunner
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -137,31 +138,27 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    def capture(fn):
-        """CUDA graph of fn on `stream` (the all-reduces are captured with it); None if capture is refused."""
-        try:
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr, stream=stream):
-                fn()
-            return gr
-        except Exception as exc:       # fall back to eager launches, and say so in the output line
-            if rank == 0:
-                print("graph capture failed, running eagerly: %r" % (exc,), flush=True)
-            torch.cuda.synchronize()
-            return None
+    def note(msg):
+        if rank == 0:
+            print("[llama_int4] " + msg, file=sys.stderr, flush=True)
 
+    note("weights and KV resident on %d rank(s)" % world)
     with torch.cuda.stream(stream):
         d_rows.copy_(h_rows, non_blocking=True)
         for _ in range(2):
-            m.forward(BATCH)           # eager warm-up: first-use attribute calls, NCCL channel setup
+            m.forward(BATCH)           # eager warm-up: first-use attribute calls, process-group channel setup
     stream.synchronize()
-    g_fwd = capture(lambda: m.forward(BATCH))
-    run_fwd = g_fwd.replay if g_fwd is not None else (lambda: m.forward(BATCH))
+    note("eager forward done")
+    with torch.cuda.stream(stream):
+        fwd = DecodeStepRunner(m, BATCH, stream, with_advance=False)
+        resident = DecodeStepRunner(m, BATCH, stream, with_advance=True)
+    stream.synchronize()
+    note("step graphs captured (%d segment(s) per step)" % len(fwd.segments))
 
     def e2e_step():
         with torch.cuda.stream(stream):
             d_rows.copy_(h_rows, non_blocking=True)
-            run_fwd()
+            fwd.run()
             h_next.copy_(m.next_tok, non_blocking=True)
         stream.synchronize()
         hr[:BATCH] = h_next.numpy()
@@ -180,25 +177,18 @@ def run_ours(args):
     barrier()
     e2e_ms = B.max_over_ranks_ms(e0.elapsed_time(e1), world, "cuda")
 
-    # ---- device-resident loop: forward + on-device feedback per step, one graph
-    def step_resident():
-        m.forward(BATCH)
-        m.advance(BATCH)
-
+    note("e2e region done")
+    # ---- device-resident loop: forward + on-device feedback per step
     with torch.cuda.stream(stream):
         d_rows.copy_(h_rows, non_blocking=True)
-    stream.synchronize()
-    g_step = capture(step_resident)
-    run_step = g_step.replay if g_step is not None else step_resident
-    with torch.cuda.stream(stream):
         for _ in range(W):
-            run_step()
+            resident.run()
     barrier()
     d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         d0.record(stream)
         for _ in range(K):
-            run_step()
+            resident.run()
         d1.record(stream)
     barrier()
     clocks.stop()
@@ -214,8 +204,10 @@ def run_ours(args):
         with torch.cuda.stream(stream):
             fn()
             stream.synchronize()
-            gr = capture(fn)
-            run = gr.replay if gr is not None else fn
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                fn()
+            run = gr.replay
             run()
             a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a0.record(stream)
@@ -266,7 +258,7 @@ def run_ours(args):
                 "config": llama_config_dict(cfg, world, BATCH, CTX0),
                 "e2e": {"value": BATCH * K / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": int(h_rows.numel() * 4),
                         "d2h_bytes_per_step": int(h_next.numel() * 4), "ms_per_step": e2e_ms / K},
-                "gpu_launches": int((m.launches_per_forward + 1) * K), "graph": g_step is not None, "roofline": roofline,
+                "gpu_launches": int((m.launches_per_forward + 1) * K), "graph_segments_per_step": len(resident.segments), "roofline": roofline,
                 "cpu_baseline": cpu, "clocks": clocks.summary(),
                 "weights_bytes_per_gpu": int(weights.q4_bytes()), "kv_bytes_read_per_step_per_gpu": attn_bytes * cfg.n_layer}
         print(json.dumps(line), flush=True)

@@ -322,3 +322,66 @@ class LocalTensorParallel:
             ms[0].all_pairs[r].copy_(m.pairs)
         ms[0].head_pick(n)
         return ms[0].next_tok
+
+
+class DecodeStepRunner:
+    """One decode step as CUDA-graph replays.  With one rank the whole step (optionally with the on-device
+    feedback) is a single graph.  With several ranks the step is cut at the collectives: every run of kernels
+    between two sums over ranks is one graph, and the process-group calls are issued between the replays on the
+    same stream (no collective is recorded inside a graph)."""
+
+    def __init__(self, model, n, stream, with_advance=False):
+        self.m, self.n, self.stream, self.with_advance = model, n, stream, with_advance
+        m, L = model, model.cfg.n_layer
+        self.segments = []
+        if m.world == 1:
+            def whole():
+                m.forward(n)
+                if with_advance:
+                    m.advance(n)
+            self.segments.append(self._capture(whole))
+            return
+
+        def first():
+            m.begin(n)
+            m.attn_part(0, n)
+        self.segments.append(self._capture(first))
+        for li in range(L):
+            def mid(li=li):
+                m.after_attn(li, n)
+                m.mlp_part(li, n)
+            self.segments.append(self._capture(mid))
+
+            def nxt(li=li):
+                m.after_mlp(li, n)
+                if li + 1 < L:
+                    m.attn_part(li + 1, n)
+                else:
+                    m.head_local(n)
+            self.segments.append(self._capture(nxt))
+
+        def last():
+            m.head_pick(n)
+            if with_advance:
+                m.advance(n)
+        self.segments.append(self._capture(last))
+
+    def _capture(self, fn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=self.stream):
+            fn()
+        return g
+
+    def run(self):
+        """Enqueue one step on the current stream (the caller makes `stream` current)."""
+        m = self.m
+        if m.world == 1:
+            self.segments[0].replay()
+            return
+        segs = self.segments
+        segs[0].replay()
+        for i in range(1, len(segs) - 1):
+            m.reduce(m.part)
+            segs[i].replay()
+        m.gather(m.pairs, m.all_pairs)
+        segs[-1].replay()
