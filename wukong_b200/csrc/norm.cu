@@ -297,6 +297,139 @@ __global__ void __launch_bounds__(NT) norm_fast_kernel(const TIn* __restrict__ x
   }
 }
 
+// Warp-per-row variant for bf16 input whose row is VPL x 32 vectors of 8: the whole row sits packed in the
+// lane's registers (VPL 128-bit loads in flight per lane), reductions are warp shuffles only, no block barrier.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <typename TOut, int VPL>
+__global__ void __launch_bounds__(256, 2) norm_row_warp_kernel(const __nv_bfloat16* __restrict__ x, TOut* __restrict__ out,
+                                                            const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                            i64 rows, int cols, float eps, int op, int rows_per_warp) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const float inv_n = 1.0f / (float)cols;
+  for (int it = 0; it < rows_per_warp; ++it) {
+    const i64 r = warp * rows_per_warp + it;
+    if (r >= rows) return;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + r * (i64)cols);
+    uint4 w[VPL];
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) w[k] = __ldcs(xr + lane + 32 * k);   // read once: streaming
+    float scale = 1.0f, shift = 0.0f;
+    if (op == 0) {
+      float m = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < VPL; ++k) {
+        const uint32_t s4[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) m = fmaxf(m, fmaxf(u2f(s4[e] << 16), u2f(s4[e] & 0xffff0000u)));
+      }
+      m = warp_max(m);
+      const float l2e = 1.4426950408889634f;
+      float sum = 0.0f;
+#pragma unroll
+      for (int k = 0; k < VPL; ++k) {
+        const uint32_t s4[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          sum += exp2f((u2f(s4[e] << 16) - m) * l2e) + exp2f((u2f(s4[e] & 0xffff0000u) - m) * l2e);
+      }
+      sum = warp_sum(sum);
+      scale = 1.0f / sum;
+      shift = m;
+    } else {
+      float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+      for (int k = 0; k < VPL; ++k) {
+        const uint32_t s4[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = u2f(s4[e] << 16), b = u2f(s4[e] & 0xffff0000u);
+          s1 += a + b;
+          s2 = fmaf(a, a, fmaf(b, b, s2));
+        }
+      }
+      if (op == 1) {
+        // layernorm: mean first, then the centred second moment from the registers
+        const float mean = warp_sum(s1) * inv_n;
+        float q = 0.0f;
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) {
+          const uint32_t s4[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float a = u2f(s4[e] << 16) - mean, b = u2f(s4[e] & 0xffff0000u) - mean;
+            q = fmaf(a, a, fmaf(b, b, q));
+          }
+        }
+        scale = rsqrtf(warp_sum(q) * inv_n + eps);
+        shift = mean;
+      } else {
+        scale = rsqrtf(warp_sum(s2) * inv_n + eps);
+      }
+    }
+    TOut* orow = out + r * (i64)cols;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int vi = lane + 32 * k;
+      const uint32_t s4[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        o[2 * e] = u2f(s4[e] << 16);
+        o[2 * e + 1] = u2f(s4[e] & 0xffff0000u);
+      }
+      if (op == 0) {
+        const float l2e = 1.4426950408889634f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = exp2f((o[e] - shift) * l2e) * scale;
+      } else {
+        float g[8], b[8];
+        if (gamma) {
+          const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * vi], g1 = reinterpret_cast<const float4*>(gamma)[2 * vi + 1];
+          g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) g[e] = 1.0f;
+        }
+        if (beta) {
+          const float4 b0 = reinterpret_cast<const float4*>(beta)[2 * vi], b1 = reinterpret_cast<const float4*>(beta)[2 * vi + 1];
+          b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) b[e] = 0.0f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = fmaf((o[e] - shift) * scale, g[e], b[e]);
+      }
+      if (sizeof(TOut) == 2) {
+        const uint4 pk = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+        __stcs(reinterpret_cast<uint4*>(orow) + vi, pk);
+      } else {
+        float4* of = reinterpret_cast<float4*>(orow) + 2 * vi;
+        __stcs(of, make_float4(o[0], o[1], o[2], o[3]));
+        __stcs(of + 1, make_float4(o[4], o[5], o[6], o[7]));
+      }
+    }
+  }
+}
+
+template <typename TOut, int VPL>
+static int launch_row_warp(const void* x, void* out, const float* g, const float* b, i64 rows, i64 cols, float eps, int op,
+                           cudaStream_t st) {
+  // an equal number of rows for every warp: ceil(rows / (resident warps)) rows each
+  const i64 resident = (i64)WKB_SM_COUNT * (VPL >= 16 ? 16 : 32);
+  const int rpw = (int)((rows + resident - 1) / resident);
+  const i64 warps = (rows + rpw - 1) / rpw;
+  const i64 blocks = (warps + 7) / 8;
+  norm_row_warp_kernel<TOut, VPL><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (TOut*)out, g, b, rows, (int)cols, eps, op, rpw);
+  return (int)cudaGetLastError();
+}
+
 template <typename TIn, typename TOut>
 static int launch_fast(const void* x, void* out, const float* g, const float* b, i64 rows, i64 cols, float eps,
                        int op, cudaStream_t st) {
@@ -304,6 +437,11 @@ static int launch_fast(const void* x, void* out, const float* g, const float* b,
   if (cols % 8 != 0 || cols > 128 * 8 * 8) return (int)cudaErrorInvalidValue;
   if (op < 0 || op > 2) return (int)cudaErrorInvalidValue;
   if (((((uintptr_t)x) | ((uintptr_t)out)) & 15) != 0) return (int)cudaErrorMisalignedAddress;
+  if (sizeof(TIn) == 2 && ((((uintptr_t)g) | ((uintptr_t)b)) & 15) == 0) {
+    if (cols == 1024) return launch_row_warp<TOut, 4>(x, out, g, b, rows, cols, eps, op, st);
+    if (cols == 2048) return launch_row_warp<TOut, 8>(x, out, g, b, rows, cols, eps, op, st);
+    if (cols == 4096) return launch_row_warp<TOut, 16>(x, out, g, b, rows, cols, eps, op, st);
+  }
   int grid = (int)(rows < (i64)WKB_SM_COUNT * 16 ? rows : (i64)WKB_SM_COUNT * 16);
   if (cols <= 128 * 8) {
     norm_fast_kernel<TIn, TOut, 128, 1><<<grid, 128, 0, st>>>((const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
