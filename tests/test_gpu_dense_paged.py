@@ -202,7 +202,11 @@ def test_paged_append_and_decode(dev, orc):
             ref = orc.paged_attn_decode(q, kv.k[0].view(torch.int16).cpu().numpy().view(np.uint16),
                                         kv.v[0].view(torch.int16).cpu().numpy().view(np.uint16), 1, table, ctx, slots, q_heads,
                                         kv_heads, hd, page, mbps, scale, layout=1)
-            assert np.allclose(outs[-1], ref, rtol=1e-4, atol=1e-5), (q_heads, kv_heads, hd, np.abs(outs[-1] - ref).max())
+            # head_dim 128 with a GQA group runs on the tensor cores: the softmax weights are bf16 there (2^-9 each)
+            # (values are ~N(0,1), so a weighted mean of them carries up to ~2^-9 absolute)
+            mma_path = hd == 128 and q_heads != kv_heads
+            rtol, atol = (4e-3, 2e-3) if mma_path else (1e-4, 1e-5)
+            assert np.allclose(outs[-1], ref, rtol=rtol, atol=atol), (q_heads, kv_heads, hd, np.abs(outs[-1] - ref).max())
         assert outs[0].tobytes() == outs[1].tobytes(), "decode output depends on the physical page layout"
         for s in range(slots):
             if ctx[s] == 0:

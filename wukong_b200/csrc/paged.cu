@@ -217,6 +217,184 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   }
 }
 
+// ---- tensor-core variant for head_dim 128 with a GQA group of 2..8 query heads ------------------------------
+// At a group of 4 the lane-per-8-dims kernel above spends ~3 lane-instructions per KV byte (unpack + 4 heads of
+// FMAs + the reduce-scatter) and is bound by instruction issue at half the HBM rate.  Here the same unit of work
+// (row, kv head, chunk) per warp runs on mma.sync.m16n8k16 (bf16 x bf16 -> f32): the group's query heads are the
+// rows of the A operand, and the K / V fragments are exactly what 128-bit loads bring in:
+//   scores  S[head, token] : B fragment of lane (g, t) = K[token 8u+g][dims 32j+8t+4h .. +4]; the dim order inside a
+//           k-step is a fixed permutation applied to q as well (a dot product does not care).  q is split into
+//           bf16 hi + lo so the scores carry ~16 bits.
+//   output  O[head, dim]   : A fragment = the tile's probabilities straight from the S accumulators (rounded to bf16,
+//           and the same rounded values feed the normaliser); B fragment (tokens x dims) needs two tokens of one dim in
+//           a register: two byte-permutes of the rows of tokens 2t, 2t+1 loaded for dims 64s+8g..+8.
+// Lane (g, t) ends up owning dims [64s+16t, +16) of head g.  Everything is indexed by logical token position.
+// D(rows 0-7) += A(rows 0-7) . B for an A operand whose rows 8-15 are zero: only c0 / c1 are live accumulators, the
+// lower half of the result is discarded.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[2], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  float z0, z1;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, {%7, %8}, {%0, %1, %9, %9};"
+               : "+f"(d[0]), "+f"(d[1]), "=f"(z0), "=f"(z1) : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.0f));
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t byte_perm(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+template <int G>
+__global__ void __launch_bounds__(PA_WARPS * 32, 2) paged_attn_decode_mma_kernel(
+    const float* __restrict__ q, const uint4* __restrict__ kcache, const uint4* __restrict__ vcache,
+    const uint32_t* __restrict__ block_table, const int* __restrict__ row_slot, const int* __restrict__ row_ctx,
+    float* __restrict__ scratch, PagedGeo g, float scale_log2e) {
+  constexpr int HD = 128, LPT = HD / 8;   // 16 uint4 per token row
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gi = lane >> 2, t = lane & 3;
+  const i64 unit = (i64)blockIdx.x * PA_WARPS + warp;
+  const i64 units = (i64)g.rows * g.kv_heads * g.max_chunks;
+  if (unit >= units) return;
+  const int chunk = (int)(unit / ((i64)g.rows * g.kv_heads));
+  const int kvh = (int)(unit % g.kv_heads);
+  const int row = (int)((unit / g.kv_heads) % g.rows);
+  const int ctx = row_ctx[row];
+  const int t0 = chunk * g.chunk_tokens;
+  float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
+  const i64 head_stride = (i64)g.max_chunks * (HD + 4);
+  if (t0 >= ctx) {
+    if (lane < G) { float* s = sbase + lane * head_stride; s[HD] = -INFINITY; s[HD + 1] = 0.0f; }
+    return;
+  }
+  const int t1 = min(ctx, t0 + g.chunk_tokens);
+  const int last_tok = t1 - 1;
+  const uint32_t* bt = block_table + (i64)row_slot[row] * g.mbps;
+  const i64 page_units = (i64)g.kv_heads * g.page_tokens * LPT;
+  const i64 head_off = (i64)kvh * g.page_tokens * LPT;
+  auto row_index = [&](int tok) {   // uint4 index of the first 8 dims of a (clamped) token's row
+    tok = min(tok, last_tok);
+    return (i64)bt[tok >> g.page_shift] * page_units + head_off + (i64)(tok & (g.page_tokens - 1)) * LPT;
+  };
+  // query fragments: head gi (zero rows past the group), 8 k-steps (j, h), bf16 hi and lo of q * scale * log2(e)
+  uint32_t qh[4][2][2], ql[4][2][2];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float f[8];
+    if (gi < G) {
+      const float* qp = q + (i64)row * g.q_row_stride + ((i64)kvh * G + gi) * HD + 32 * j + 8 * t;
+      const float4 a = *reinterpret_cast<const float4*>(qp), b = *reinterpret_cast<const float4*>(qp + 4);
+      f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.0f;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float x0 = f[4 * h + 2 * c] * scale_log2e, x1 = f[4 * h + 2 * c + 1] * scale_log2e;
+        const uint32_t hi = pack2_bf16(x0, x1);
+        qh[j][h][c] = hi;
+        ql[j][h][c] = pack2_bf16(x0 - u2f(hi << 16), x1 - u2f(hi & 0xffff0000u));
+      }
+  }
+  float m = -INFINITY, l = 0.0f;
+  float acc[2][8][2];
+#pragma unroll
+  for (int sl = 0; sl < 2; ++sl)
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) { acc[sl][jj][0] = 0.0f; acc[sl][jj][1] = 0.0f; }
+
+  auto load_k = [&](int tile0, uint4 (&kw)[2][4]) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const i64 base = row_index(tile0 + 8 * u + gi);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) kw[u][j] = kcache[base + 4 * j + t];
+    }
+  };
+  uint4 kcur[2][4];
+  load_k(t0, kcur);
+  for (int tile0 = t0; tile0 < t1; tile0 += 16) {
+    // this tile's V rows (tokens 2t, 2t+1, 2t+8, 2t+9; dims 64*sl + 8*gi .. +8) and the next tile's K rows
+    uint4 vw[4][2];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const i64 base = row_index(tile0 + 2 * t + (a & 1) + 8 * (a >> 1));
+#pragma unroll
+      for (int sl = 0; sl < 2; ++sl) vw[a][sl] = vcache[base + 8 * sl + gi];
+    }
+    // ---- scores of 16 tokens for the group's heads
+    float sc[2][2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      sc[u][0] = 0.0f; sc[u][1] = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t kr[4] = {kcur[u][j].x, kcur[u][j].y, kcur[u][j].z, kcur[u][j].w};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mma_bf16_16816(sc[u], qh[j][h][0], qh[j][h][1], kr[2 * h], kr[2 * h + 1]);
+          mma_bf16_16816(sc[u], ql[j][h][0], ql[j][h][1], kr[2 * h], kr[2 * h + 1]);
+        }
+      }
+    }
+    // the K registers are free again: the next tile's K rows travel while this tile's softmax and values run
+    if (tile0 + 16 < t1) load_k(tile0 + 16, kcur);
+    // lane (gi, t) holds head gi's scores of tokens tile0 + 8u + 2t + {0, 1}
+    float s4[4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) s4[2 * u + c] = (tile0 + 8 * u + 2 * t + c < t1) ? sc[u][c] : -INFINITY;
+    float tm = fmaxf(fmaxf(s4[0], s4[1]), fmaxf(s4[2], s4[3]));
+    tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+    tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+    const float mn = fmaxf(m, tm);           // finite: every tile has a visible token
+    const float corr = exp2f(m - mn);
+    m = mn;
+    const uint32_t p01 = pack2_bf16(exp2f(s4[0] - mn), exp2f(s4[1] - mn));
+    const uint32_t p23 = pack2_bf16(exp2f(s4[2] - mn), exp2f(s4[3] - mn));
+    // the normaliser sums the same rounded weights the values are multiplied by
+    l = l * corr + ((u2f(p01 << 16) + u2f(p01 & 0xffff0000u)) + (u2f(p23 << 16) + u2f(p23 & 0xffff0000u)));
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl)
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) { acc[sl][jj][0] *= corr; acc[sl][jj][1] *= corr; }
+    // ---- values: 8 dims per slab and register pair, two tokens of one dim per B register
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl) {
+      const uint32_t x0[4] = {vw[0][sl].x, vw[0][sl].y, vw[0][sl].z, vw[0][sl].w};   // token 2t
+      const uint32_t x1[4] = {vw[1][sl].x, vw[1][sl].y, vw[1][sl].z, vw[1][sl].w};   // token 2t+1
+      const uint32_t y0[4] = {vw[2][sl].x, vw[2][sl].y, vw[2][sl].z, vw[2][sl].w};   // token 2t+8
+      const uint32_t y1[4] = {vw[3][sl].x, vw[3][sl].y, vw[3][sl].z, vw[3][sl].w};   // token 2t+9
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        mma_bf16_16816(acc[sl][2 * e], p01, p23, byte_perm(x0[e], x1[e], 0x5410u), byte_perm(y0[e], y1[e], 0x5410u));
+        mma_bf16_16816(acc[sl][2 * e + 1], p01, p23, byte_perm(x0[e], x1[e], 0x7632u), byte_perm(y0[e], y1[e], 0x7632u));
+      }
+    }
+  }
+  // ---- lane (gi, t) owns dims [64*sl + 16*t, +16) of head gi: c0 of pair jj is dim +jj, c1 is dim +8+jj
+  float lt = l + __shfl_xor_sync(0xffffffffu, l, 1);
+  lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+  if (gi < G) {
+    float* s = sbase + gi * head_stride;
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl) {
+      float* d = s + 64 * sl + 16 * t;
+      *reinterpret_cast<float4*>(d) = make_float4(acc[sl][0][0], acc[sl][1][0], acc[sl][2][0], acc[sl][3][0]);
+      *reinterpret_cast<float4*>(d + 4) = make_float4(acc[sl][4][0], acc[sl][5][0], acc[sl][6][0], acc[sl][7][0]);
+      *reinterpret_cast<float4*>(d + 8) = make_float4(acc[sl][0][1], acc[sl][1][1], acc[sl][2][1], acc[sl][3][1]);
+      *reinterpret_cast<float4*>(d + 12) = make_float4(acc[sl][4][1], acc[sl][5][1], acc[sl][6][1], acc[sl][7][1]);
+    }
+    if (t == 0) { s[HD] = m; s[HD + 1] = lt; }
+  }
+}
+
 // Merge a row-head's chunks in ascending order; out_dtype 0 = f32, 1 = bf16.
 template <int HD>
 __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const float* __restrict__ scratch, void* __restrict__ out,
@@ -287,6 +465,23 @@ __global__ void __launch_bounds__(256) paged_kv_append_kernel(const float* __res
   }
 }
 
+template <int G>
+static int launch_decode_mma(const float* q, const void* kc, const void* vc, const uint32_t* bt, const int* row_slot,
+                             const int* row_ctx, float* scratch, void* out, int out_dtype, i64 out_row_stride, PagedGeo g,
+                             float scale, cudaStream_t st) {
+  i64 units = (i64)g.rows * g.kv_heads * g.max_chunks;
+  i64 blocks = (units + PA_WARPS - 1) / PA_WARPS;
+  if (blocks > 0x7fffffff) return (int)cudaErrorInvalidValue;
+  paged_attn_decode_mma_kernel<G><<<(unsigned)blocks, PA_WARPS * 32, 0, st>>>(
+      q, (const uint4*)kc, (const uint4*)vc, bt, row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  i64 total = (i64)g.rows * g.q_heads * (128 / 4);
+  paged_attn_merge_kernel<128><<<(unsigned)((total + 127) / 128), 128, 0, st>>>(scratch, out, out_dtype, out_row_stride,
+                                                                                row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens);
+  return (int)cudaGetLastError();
+}
+
 template <int HD, int G>
 static int launch_decode(const float* q, const void* kc, const void* vc, const uint32_t* bt, const int* row_slot,
                          const int* row_ctx, float* scratch, void* out, int out_dtype, i64 out_row_stride, PagedGeo g,
@@ -344,8 +539,13 @@ int wkb_paged_attn_decode(const float* q, i64 q_row_stride, const void* kcache, 
 #define WKB_PA_CASE(HD_, G_) \
   if (head_dim == HD_ && G == G_) return launch_decode<HD_, G_>(q, kcache, vcache, block_table, row_slot, row_ctx, scratch, out, out_dtype, out_row_stride, g, scale, st);
   WKB_PA_CASE(64, 1) WKB_PA_CASE(64, 2) WKB_PA_CASE(64, 4)
-  WKB_PA_CASE(128, 1) WKB_PA_CASE(128, 2) WKB_PA_CASE(128, 4) WKB_PA_CASE(128, 8)
+  WKB_PA_CASE(128, 1)
 #undef WKB_PA_CASE
+  if (head_dim == 128 && chunk_tokens % 16 == 0) {
+    if (G == 2) return launch_decode_mma<2>(q, kcache, vcache, block_table, row_slot, row_ctx, scratch, out, out_dtype, out_row_stride, g, scale, st);
+    if (G == 4) return launch_decode_mma<4>(q, kcache, vcache, block_table, row_slot, row_ctx, scratch, out, out_dtype, out_row_stride, g, scale, st);
+    if (G == 8) return launch_decode_mma<8>(q, kcache, vcache, block_table, row_slot, row_ctx, scratch, out, out_dtype, out_row_stride, g, scale, st);
+  }
   return (int)cudaErrorInvalidValue;
 }
 
