@@ -331,12 +331,18 @@ __global__ void __launch_bounds__(256, 2) norm_row_warp_kernel(const __nv_bfloat
       m = warp_max(m);
       const float l2e = 1.4426950408889634f;
       float sum = 0.0f;
+      // one exponential per element: the results replace the inputs in the registers (packed bf16; the output
+      // is bf16 anyway), the normaliser sums the unrounded values
 #pragma unroll
       for (int k = 0; k < VPL; ++k) {
-        const uint32_t s4[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+        uint32_t s4[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          sum += exp2f((u2f(s4[e] << 16) - m) * l2e) + exp2f((u2f(s4[e] & 0xffff0000u) - m) * l2e);
+        for (int e = 0; e < 4; ++e) {
+          const float a = exp2f((u2f(s4[e] << 16) - m) * l2e), b = exp2f((u2f(s4[e] & 0xffff0000u) - m) * l2e);
+          sum += a + b;
+          s4[e] = pack_bf16x2(a, b);
+        }
+        w[k] = make_uint4(s4[0], s4[1], s4[2], s4[3]);
       }
       sum = warp_sum(sum);
       scale = 1.0f / sum;
@@ -384,9 +390,8 @@ __global__ void __launch_bounds__(256, 2) norm_row_warp_kernel(const __nv_bfloat
         o[2 * e + 1] = u2f(s4[e] & 0xffff0000u);
       }
       if (op == 0) {
-        const float l2e = 1.4426950408889634f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = exp2f((o[e] - shift) * l2e) * scale;
+        for (int e = 0; e < 8; ++e) o[e] *= scale;
       } else {
         float g[8], b[8];
         if (gamma) {
