@@ -145,75 +145,6 @@ __global__ void __launch_bounds__(128) gemv_q_contract_kernel(const uint4* __res
   }
 }
 
-// ---- in-register-dequant GEMV with bf16 activations, fp32 accumulate ----------------------------
-// y[j] = sum_b f32(d_jb) * sum_e (nib_jbe - 8) * x[32b+e].  Each nibble becomes the f32 value
-// 16+nib by placing it in the top mantissa bits of 16.0f (exact), so the per-element work is one
-// shift, one logic op and one FMA; sum_e (16+nib)*x - 24*sum_e x removes the offset once per block.
-// Products are exact (5-bit x 8-bit significands); fp32 accumulation order is free here (no CPU
-// kernel defines one for bf16 activations), lane-per-block with a warp-shuffle tree at the end.
-__global__ void __launch_bounds__(128) gemv_q4_bf16x_kernel(const uint4* __restrict__ qs, const u16* __restrict__ d,
-                                                            const u16* __restrict__ xb, i64 k, float* __restrict__ y,
-                                                            i64 n, int nb) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  float* xt = reinterpret_cast<float*>(smem);  // xt[e][b]: element e of block b
-  float* sxs = xt + 32 * nb;                   // 24 * sum of the block's x
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int i = threadIdx.x; i < nb * 32; i += blockDim.x) {
-    int b = i >> 5, e = i & 31;
-    xt[e * nb + b] = (i64)i < k ? bf16_bits_to_f32(xb[i]) : 0.0f;
-  }
-  __syncthreads();
-  for (int b = threadIdx.x; b < nb; b += blockDim.x) {
-    float s = 0.0f;
-    for (int e = 0; e < 32; ++e) s += xt[e * nb + b];
-    sxs[b] = 24.0f * s;
-  }
-  __syncthreads();
-  i64 nbatches = (n + GQ_RB - 1) / GQ_RB;
-  for (i64 batch = (i64)blockIdx.x * nwarps + warp; batch < nbatches; batch += (i64)gridDim.x * nwarps) {
-    i64 r0 = batch * GQ_RB;
-    float acc[GQ_RB];
-#pragma unroll
-    for (int r = 0; r < GQ_RB; ++r) acc[r] = 0.0f;
-    for (int b = lane; b < nb; b += 32) {
-      uint4 wq[GQ_RB];
-      float dw[GQ_RB], part[GQ_RB];
-#pragma unroll
-      for (int r = 0; r < GQ_RB; ++r) {
-        i64 row = r0 + r < n ? r0 + r : n - 1;
-        wq[r] = qs[row * nb + b];
-        dw[r] = f16_bits_to_f32(d[row * nb + b]);
-        part[r] = 0.0f;
-      }
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-#pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          // nibble p of word w: byte p/2 of the word, low half if p is even
-          int e = 4 * w + (p >> 1) + ((p & 1) ? 16 : 0);
-          float xv = xt[e * nb + b];
-#pragma unroll
-          for (int r = 0; r < GQ_RB; ++r) {
-            uint32_t word = w == 0 ? wq[r].x : w == 1 ? wq[r].y : w == 2 ? wq[r].z : wq[r].w;
-            int sh = 19 - 4 * p;
-            uint32_t pos = sh >= 0 ? (word << sh) : (word >> (-sh));
-            float m = u2f((pos & 0x00780000u) | 0x41800000u);  // 16 + nib, exact
-            part[r] = fmaf(m, xv, part[r]);
-          }
-        }
-      }
-      float corr = sxs[b];
-#pragma unroll
-      for (int r = 0; r < GQ_RB; ++r) acc[r] = fmaf(dw[r], part[r] - corr, acc[r]);
-    }
-#pragma unroll
-    for (int r = 0; r < GQ_RB; ++r) {
-      float v = warp_sum(acc[r]);
-      if (lane == 0 && r0 + r < n) y[r0 + r] = v;
-    }
-  }
-}
-
 // ---- packers (quant.rs:154-197): one thread per block, the scalar scan order --------------------
 template <bool Q4>
 __global__ void __launch_bounds__(128) quantize_kernel(const float* __restrict__ x, u8* __restrict__ q, i64 rows,
@@ -306,6 +237,96 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SX_OFF 
 
 static size_t contract_smem(int nb, int warps) { return (size_t)nb * (32 + 4 + 4) + (size_t)warps * GQ_RB * nb * 4; }
 
+// ---- y = W x, bf16 activation, every load issued before any arithmetic -----------------------------------------
+// A GEMV of these sizes (9-25 MB of weights) lasts a few microseconds at HBM speed, so what matters is that the
+// whole matrix is in flight at once: a warp owns R rows, a lane owns blocks lane, lane+32, ... of each, and all of
+// a pass's 16-byte block loads (and scale loads) are issued first; x (8-22 KB, L2-resident) is read straight from
+// global by the lane that needs it, 64 B per block, with no shared-memory staging and no barrier.
+// Per block: sum_e (16 + nib_e) * x_e in f32 (the nibble becomes the mantissa of 16 + nib, exact), minus 24 * sum_e x_e,
+// times the f16 scale.
+template <int R, int BPL>
+__global__ void __launch_bounds__(256) gemv_q4_lean_kernel(const uint4* __restrict__ qs, const u16* __restrict__ d,
+                                                           const uint4* __restrict__ xb, float* __restrict__ y, i64 n, int nb, i64 k) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const i64 r0 = warp * R;
+  if (r0 >= n) return;
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+  for (int b0 = 0; b0 < nb; b0 += 32 * BPL) {
+    uint4 wq[R][BPL];
+    u16 dw[R][BPL];
+    uint4 xv[BPL][4];
+#pragma unroll
+    for (int i = 0; i < BPL; ++i) {
+      const int b = min(b0 + lane + 32 * i, nb - 1);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const i64 row = r0 + r < n ? r0 + r : n - 1;
+        wq[r][i] = __ldcs(qs + row * nb + b);
+        dw[r][i] = d[row * nb + b];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < BPL; ++i) {
+      const int b = min(b0 + lane + 32 * i, nb - 1);
+      if ((i64)(b + 1) * 32 <= k) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) xv[i][c] = xb[(i64)b * 4 + c];
+      } else {
+        // ragged last block: elements past k count as zero
+        const u16* xs = reinterpret_cast<const u16*>(xb);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t ww[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const i64 i0 = (i64)b * 32 + 8 * c + 2 * e;
+            ww[e] = (i0 < k ? (uint32_t)xs[i0] : 0u) | ((i0 + 1 < k ? (uint32_t)xs[i0 + 1] : 0u) << 16);
+          }
+          xv[i][c] = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < BPL; ++i) {
+      const bool live = b0 + lane + 32 * i < nb;
+      float xf[32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t ww[4] = {xv[i][c].x, xv[i][c].y, xv[i][c].z, xv[i][c].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { xf[8 * c + 2 * e] = u2f(ww[e] << 16); xf[8 * c + 2 * e + 1] = u2f(ww[e] & 0xffff0000u); }
+      }
+      float sx = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) sx += xf[e];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const uint32_t words[4] = {wq[r][i].x, wq[r][i].y, wq[r][i].z, wq[r][i].w};
+        float part = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+#pragma unroll
+          for (int p = 0; p < 8; ++p) {
+            const int e = 4 * w + (p >> 1) + ((p & 1) ? 16 : 0);   // nibble p of word w is element e of the block
+            const int sh = 19 - 4 * p;
+            const uint32_t pos = sh >= 0 ? (words[w] << sh) : (words[w] >> (-sh));
+            part = fmaf(u2f((pos & 0x00780000u) | 0x41800000u), xf[e], part);
+          }
+        const float term = f16_bits_to_f32(dw[r][i]) * (part - 24.0f * sx);
+        acc[r] += live ? term : 0.0f;
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const float v = warp_sum(acc[r]);
+    if (lane == 0 && r0 + r < n) y[r0 + r] = v;
+  }
+}
+
 }  // namespace wkb
 
 using namespace wkb;
@@ -351,15 +372,14 @@ int wkb_gemv_q_contract(const void* qs, const void* d, const void* xq, const flo
 
 int wkb_gemv_q4_0_bf16x(const void* qs, const void* d, const void* x_bf16, float* y, i64 n, i64 k, void* stream) {
   if (n <= 0 || k <= 0) return 0;
-  int nb = (int)((k + 31) / 32);
-  size_t sm = (size_t)nb * 33 * 4;
-  if (sm > 200 * 1024) return (int)cudaErrorInvalidValue;
-  i64 nbatches = (n + GQ_RB - 1) / GQ_RB;
-  i64 blocks = (nbatches + 3) / 4;
-  if (blocks > (i64)WKB_SM_COUNT * 8) blocks = (i64)WKB_SM_COUNT * 8;
-  cudaError_t e = cudaFuncSetAttribute(gemv_q4_bf16x_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-  if (e != cudaSuccess) return (int)e;
-  gemv_q4_bf16x_kernel<<<(int)blocks, 128, sm, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const u16*)x_bf16, k, y, n, nb);
+  if ((((uintptr_t)qs) | ((uintptr_t)x_bf16)) & 15) return (int)cudaErrorMisalignedAddress;
+  const int nb = (int)((k + 31) / 32);
+  // two rows per warp; few rows: one row per warp so that the grid still covers the SMs
+  const bool one = n < (i64)WKB_SM_COUNT * 16;
+  const i64 warps = one ? n : (n + 1) / 2;
+  const i64 blocks = (warps + 7) / 8;
+  if (one) gemv_q4_lean_kernel<1, 4><<<(int)blocks, 256, 0, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const uint4*)x_bf16, y, n, nb, k);
+  else gemv_q4_lean_kernel<2, 4><<<(int)blocks, 256, 0, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const uint4*)x_bf16, y, n, nb, k);
   return (int)cudaGetLastError();
 }
 
