@@ -172,26 +172,35 @@ def case_paged_attn(hbm, tf, src):
             "note": "555 MB of KV per launch exceeds L2", "peak_source": "of " + src}
 
 
-def run(out=sys.stdout):
+def run(out=sys.stdout, only=None, reps_scale=1.0):
+    """Run the suite (or the cases whose name contains `only`) and print one JSON line per case."""
     require_gpu()
     hbm, tf, src = peaks()
-    results = []
+    plan = []
     for size in (1024, 4096, 8192):
-        results.append(case_gemm(size, hbm, tf, src))
+        plan.append(("gemm_bf16", lambda size=size: case_gemm(size, hbm, tf, src)))
     for (n, k) in ((4096, 4096), (11008, 4096)):
         for variant in ("contract", "bf16x"):
-            results.append(case_gemv_q4(n, k, variant, hbm, tf, src))
+            plan.append(("gemv_q4_0_" + variant, lambda n=n, k=k, variant=variant: case_gemv_q4(n, k, variant, hbm, tf, src)))
     for (n, k, mode) in ((6144, 4096, 0), (22016, 4096, 2), (4096, 11008, 0)):
-        results.append(case_gemm_q4(64, n, k, mode, hbm, tf, src))
-    for op in (2, 0):
-        results.append(case_norm(op, hbm, tf, src))
-    results.append(case_paged_attn(hbm, tf, src))
+        plan.append(("gemm_q4_0_bf16", lambda n=n, k=k, mode=mode: case_gemm_q4(64, n, k, mode, hbm, tf, src)))
+    for op, name in ((2, "rmsnorm_bf16"), (0, "softmax_bf16"), (1, "layernorm_bf16")):
+        plan.append((name, lambda op=op: case_norm(op, hbm, tf, src)))
+    plan.append(("paged_attn_decode", lambda: case_paged_attn(hbm, tf, src)))
+    results = []
+    for name, fn in plan:
+        if only and only not in name:
+            continue
+        r = fn()
+        results.append(r)
+        print(json.dumps(r), file=out, flush=True)
     if dev.gemm_status() != 0:
         raise RuntimeError("tensor-core GEMM reported an expired pipeline wait")
-    for r in results:
-        print(json.dumps(r), file=out, flush=True)
     return results
 
 
 if __name__ == "__main__":
-    run()
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None, help="run only the cases whose name contains this string")
+    run(only=ap.parse_args().case)
