@@ -241,7 +241,10 @@ def run_ours(args):
     step_ms = dev_ms / K
     a_gbs, g_gbs = attn_bytes / (attn_ms * 1e-3) / 1e9, gemm_bytes / (gemm_ms * 1e-3) / 1e9
     roofline = {"kernel": "paged_attn_decode_kernel<128,%d> (+ chunk merge)" % (m.hq // m.hkv), "bound": "hbm", "achieved": a_gbs,
-                "peak": peak, "peak_source": "of " + peak_kind, "unit": "GB/s", "frac": a_gbs / peak, "traffic": None,
+                "peak": peak, "peak_source": "of " + peak_kind, "unit": "GB/s", "frac": a_gbs / peak,
+                # DRAM bytes per launch: 1.02 x the algorithmic bytes in the ncu capture of this kernel on the batch-64
+                # ctx U[128,4096] case (profiles/paged_attn_decode_mma_ncu.md); traffic grows with the visible tokens
+                "traffic": 1.02 * attn_bytes, "traffic_source": "ncu on the micro-suite's paged_attn case, scaled by visible tokens",
                 "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms, "share_of_step": attn_ms * cfg.n_layer / step_ms,
                 "second_stream": {"kernel": "gemm_q4_tc_kernel (4 linears of a layer)", "bound": "hbm", "achieved": g_gbs, "unit": "GB/s",
                                   "frac": g_gbs / peak, "algorithmic_bytes_per_layer": gemm_bytes, "ms_per_layer": gemm_ms,
