@@ -40,6 +40,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gpt2_serving", choices=["gpt2_serving", "llama_int4"],
                     help="gpt2_serving: the headline workload (sequence-sharded replicas); llama_int4: the tensor-parallel Q4_0 stack")
+    ap.add_argument("--nccl-allreduce", action="store_true",
+                    help="llama_int4 only: sum over ranks with NCCL all-reduce instead of the fused peer-memory kernel")
     ap.add_argument("--layers", type=int, default=0, help="llama_int4 only: run a shorter stack (0: the named 32 layers)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)

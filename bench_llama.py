@@ -17,12 +17,12 @@ import bench as B
 BATCH, CTX0, PAGE = 64, 2048, 16
 
 
-def llama_config_dict(cfg, world, batch, ctx0):
+def llama_config_dict(cfg, world, batch, ctx0, how=""):
     return {"workload": "Llama-7B-shape Q4_0 block stack, batch %d decode at context %d (BASELINE configs[4])" % (batch, ctx0),
             "layers": cfg.n_layer, "d_model": cfg.d_model, "heads": cfg.n_head, "kv_heads": cfg.n_kv_head, "d_ff": cfg.d_ff,
             "vocab": cfg.vocab, "batch": batch, "context": ctx0, "weights": "Q4_0 (18 B per 32 weights), activations bf16",
             "kv": "paged bf16, %d-token pages, synthetic fill standing for the prefill" % PAGE,
-            "parallelism": "tp%d (heads / FFN columns / vocabulary split, 2 all-reduces per layer)" % world,
+            "parallelism": "tp%d (heads / FFN columns / vocabulary split, 2 sums over ranks per layer%s)" % (world, how),
             "l2": "per-step inputs (weights + KV, several GB per GPU) exceed the 126 MB L2; no flush needed"}
 
 
@@ -96,7 +96,7 @@ def run_ours(args):
     import torch.distributed as dist
     from wukong_b200 import _lib, device as dev
     from wukong_b200._lib import lib, check
-    from wukong_b200.llama import LlamaConfig, LlamaRankWeights, LlamaDecodeModel, DecodeStepRunner
+    from wukong_b200.llama import LlamaConfig, LlamaRankWeights, LlamaDecodeModel, DecodeStepRunner, PeerReduce
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -114,7 +114,8 @@ def run_ours(args):
     num_pages = BATCH * mbps
     reduce = (lambda t: dist.all_reduce(t)) if world > 1 else None
     gather = (lambda pairs, allp: dist.all_gather_into_tensor(allp, pairs)) if world > 1 else None
-    m = LlamaDecodeModel(cfg, weights, rank, world, BATCH, num_pages, mbps, PAGE, device, reduce, gather)
+    peer = PeerReduce(rank, world, BATCH, cfg.d_model, device) if (world > 1 and not args.nccl_allreduce) else None
+    m = LlamaDecodeModel(cfg, weights, rank, world, BATCH, num_pages, mbps, PAGE, device, reduce, gather, peer)
     g = torch.Generator(device=device)
     g.manual_seed(1 + rank)
     m.kv.k.normal_(generator=g)
@@ -258,7 +259,7 @@ def run_ours(args):
         line = {"metric": B.METRIC, "value": BATCH * K / (dev_ms * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "bf16 (Q4_0 weights dequantised in-register, fp32 accumulate)", "data": "synthetic",
-                "config": llama_config_dict(cfg, world, BATCH, CTX0),
+                "config": llama_config_dict(cfg, world, BATCH, CTX0, "" if world == 1 else (": NCCL all-reduce" if peer is None else ": fused peer-memory reduce + add + RMSNorm kernel")),
                 "e2e": {"value": BATCH * K / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": int(h_rows.numel() * 4),
                         "d2h_bytes_per_step": int(h_next.numel() * 4), "ms_per_step": e2e_ms / K},
                 "gpu_launches": int((m.launches_per_forward + 1) * K), "graph_segments_per_step": len(resident.segments), "roofline": roofline,
@@ -266,4 +267,7 @@ def run_ours(args):
                 "weights_bytes_per_gpu": int(weights.q4_bytes()), "kv_bytes_read_per_step_per_gpu": attn_bytes * cfg.n_layer}
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
+        if peer is not None:
+            peer.close()
         dist.destroy_process_group()

@@ -194,6 +194,24 @@ int wkb_rope_qk_f32(float* x, int64_t row_stride, const float* inv_freq, const i
  * half-precision recipe (fp32 statistics, one rounding on the way out). */
 int wkb_add_rmsnorm_bf16(float* x, const float* delta_or_null, const float* gamma_or_null, void* out_bf16, int64_t rows,
                          int64_t cols, float eps, void* stream);
+/* Tensor-parallel sum over ranks fused with the residual add and RMSNorm that follow it, over peer memory
+ * (one kernel per rank instead of an all-reduce plus a norm; the reference's counterpart is the all-reduce of its
+ * tensor-parallel block, crates/wukong_codegen_gpu/src/serving.rs:4161-4240).  parts[r] / flags[r] (HOST arrays
+ * of `world` device pointers, by rank) are every rank's fp32 [rows, cols] partial for this phase and every rank's
+ * flag row (>= world uint32, zeroed once), mapped into this process (wkb_ipc_* below, or any peer mapping).
+ * x += sum_r parts[r] (rank order on every rank); out = bf16(x / sqrt(mean(x^2) + eps) * gamma).
+ * `phase` in [0, phases_per_step) numbers the sums of one decode step; step_ptr is this rank's device step counter
+ * (wkb_tp_step_bump once per step, after the step's last sum).  Each rank alternates between two partial buffers.
+ * A wait that runs out (about a second) records 21 in the status word read by wkb_gemm_status. */
+int wkb_tp_reduce_add_rmsnorm(const void* const* parts, void* const* flags, int64_t rank, int64_t world, const void* step_ptr,
+                              int64_t phase, int64_t phases_per_step, float* x, const float* gamma_or_null, void* out_bf16,
+                              int64_t rows, int64_t cols, float eps, void* stream);
+int wkb_tp_step_bump(void* step_ptr, void* stream);
+/* CUDA IPC plumbing for the peer mappings: export the allocation containing `ptr` as a 64-byte handle plus the
+ * offset of `ptr` inside it; map a peer's allocation (add the peer's offset to the returned base). */
+int wkb_ipc_export(void* ptr, void* handle64, int64_t* offset);
+void* wkb_ipc_import(const void* handle64);
+int wkb_ipc_close(void* mapped_ptr);
 /* Greedy sampling with the vocabulary split over ranks: pack (value bits, idx_local + col_offset) of each
  * row's local arg-max into pairs[rows][2]; after gathering the ranks' pairs into [world][rows][2], pick the
  * row's token by the arg-max rule of wukong_rowargmax_i32 applied across ranks. */

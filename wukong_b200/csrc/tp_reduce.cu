@@ -1,0 +1,170 @@
+// Tensor-parallel sum over ranks fused with the residual add and RMSNorm that follow it, over peer memory.
+//
+// In the tensor-parallel Llama-shape block every rank ends its attention and its MLP with an fp32 [rows, d]
+// partial that must be summed over the ranks (the all-reduce of crates/wukong_codegen_gpu/src/serving.rs:4161-4240)
+// before `x += sum; xn = rmsnorm(x)`.  With NCCL that is a collective plus a norm kernel, and the collective cannot
+// be part of the step's CUDA graph.  Here it is ONE kernel per rank:
+//   1. block 0 publishes "my partial is complete" to every peer (a release store of the step's sequence number
+//      into the peer's flag row; the partial was written by the preceding GEMM on the same stream);
+//   2. every block waits (acquire loads, bounded) until all peers have published this sequence number;
+//   3. a block then owns rows: it reads the row of every rank's partial -- plain loads through the peer mappings,
+//      over NVLink -- adds them in rank order (so all ranks compute bit-identical sums and the replicated residual
+//      stream stays identical), adds the residual, computes the RMS statistic and writes x and the bf16 normed row.
+// Buffers: each rank owns two partial buffers (attention, MLP) used alternately; a rank can run at most one phase
+// ahead of its slowest peer (it cannot pass a phase without that peer's flag), so a partial buffer is never
+// rewritten while a peer may still read it.  Sequence numbers come from a per-rank device step counter plus the
+// phase index baked into the launch, so the launches can live in a CUDA graph.
+// Peer memory is mapped with CUDA IPC (no multicast objects); loads are plain ld.global, never TMA.
+// Waits are bounded (about a second): on expiry the block records it in `status`, skips the sum and returns.
+#include "common.cuh"
+#include "wkb_device.h"
+#include <cstring>
+#include <cuda.h>
+
+namespace wkb {
+int* gemm_status_word();
+
+constexpr int TP_MAX_WORLD = 8;
+constexpr uint32_t TP_SPIN_LIMIT = 1u << 22;   // x ~200 ns sleep: about a second
+
+struct TpPeers {
+  const float* part[TP_MAX_WORLD];   // every rank's partial buffer for this phase (own entry included), by rank
+  uint32_t* flags[TP_MAX_WORLD];     // every rank's flag row: flags[r][sender] = last sequence number published
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) tp_reduce_add_rmsnorm_kernel(TpPeers peers, int rank, int world, const uint32_t* __restrict__ step_ptr,
+                                                                    int phase, int phases_per_step, float* __restrict__ x,
+                                                                    const float* __restrict__ gamma, u16* __restrict__ out, int rows,
+                                                                    int cols, float eps, int* status) {
+  __shared__ float red[8];
+  __shared__ int s_ok;
+  const uint32_t seq = (*step_ptr) * (uint32_t)phases_per_step + (uint32_t)phase + 1u;
+  if (blockIdx.x == 0 && threadIdx.x < world && (int)threadIdx.x != rank) {
+    __threadfence_system();
+    st_release_sys(peers.flags[threadIdx.x] + rank, seq);
+  }
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int p = 0; p < world && ok; ++p) {
+      if (p == rank) continue;
+      const uint32_t* f = peers.flags[rank] + p;
+      uint32_t it = 0;
+      // sequence numbers only grow; a peer one phase ahead has already published a larger one
+      while ((int32_t)(ld_acquire_sys(f) - seq) < 0) {
+        if (++it > TP_SPIN_LIMIT) { ok = 0; break; }
+        __nanosleep(200);
+      }
+    }
+    if (!ok) atomicExch(status, 21);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int nvec = cols >> 2;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    float4* xr = reinterpret_cast<float4*>(x + (i64)r * cols);
+    float q = 0.0f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      float4 s = __ldcg(reinterpret_cast<const float4*>(peers.part[0] + (i64)r * cols) + i);
+      for (int p = 1; p < world; ++p) {
+        const float4 d = __ldcg(reinterpret_cast<const float4*>(peers.part[p] + (i64)r * cols) + i);
+        s.x += d.x; s.y += d.y; s.z += d.z; s.w += d.w;
+      }
+      float4 v = xr[i];
+      v.x += s.x; v.y += s.y; v.z += s.z; v.w += s.w;
+      xr[i] = v;
+      q = fmaf(v.x, v.x, q); q = fmaf(v.y, v.y, q); q = fmaf(v.z, v.z, q); q = fmaf(v.w, v.w, q);
+    }
+    q = warp_sum(q);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = q;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float inv = rsqrtf(tot / (float)cols + eps);
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const float4 v = xr[i];
+      const float4 g = gamma ? reinterpret_cast<const float4*>(gamma)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+      uint2 o;
+      o.x = (uint32_t)f32_to_bf16_bits(v.x * inv * g.x) | ((uint32_t)f32_to_bf16_bits(v.y * inv * g.y) << 16);
+      o.y = (uint32_t)f32_to_bf16_bits(v.z * inv * g.z) | ((uint32_t)f32_to_bf16_bits(v.w * inv * g.w) << 16);
+      reinterpret_cast<uint2*>(out + (i64)r * cols)[i] = o;
+    }
+  }
+}
+
+__global__ void tp_step_bump_kernel(uint32_t* step_ptr) { *step_ptr += 1u; }
+
+}  // namespace wkb
+
+using namespace wkb;
+
+extern "C" {
+
+// Export the allocation that contains `p`: the handle names the whole allocation, *offset is where p sits in it
+// (memory handed out by a caching allocator is usually an interior pointer of a larger cudaMalloc block).
+int wkb_ipc_export(void* p, void* handle64, i64* offset) {
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range = nullptr;
+  if (!range) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess)
+      return (int)cudaErrorNotSupported;
+    range = (RangeFn)fn;
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (range(&base, &size, (CUdeviceptr)p) != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, (void*)base);
+  if (e != cudaSuccess) return (int)e;
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  *offset = (i64)((CUdeviceptr)p - base);
+  return 0;
+}
+void* wkb_ipc_import(const void* handle64) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return nullptr;
+  return p;
+}
+int wkb_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+
+int wkb_tp_reduce_add_rmsnorm(const void* const* parts, void* const* flags, i64 rank, i64 world, const void* step_ptr, i64 phase,
+                              i64 phases_per_step, float* x, const float* gamma_or_null, void* out_bf16, i64 rows, i64 cols, float eps,
+                              void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (world < 1 || world > TP_MAX_WORLD || rank < 0 || rank >= world || cols % 4 != 0) return (int)cudaErrorInvalidValue;
+  int* status = gemm_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  TpPeers peers;
+  for (int p = 0; p < TP_MAX_WORLD; ++p) {
+    peers.part[p] = p < world ? (const float*)parts[p] : nullptr;
+    peers.flags[p] = p < world ? (uint32_t*)flags[p] : nullptr;
+  }
+  const int grid = (int)(rows < (i64)WKB_SM_COUNT ? rows : (i64)WKB_SM_COUNT);
+  tp_reduce_add_rmsnorm_kernel<<<grid, 256, 0, as_stream(stream)>>>(peers, (int)rank, (int)world, (const uint32_t*)step_ptr, (int)phase,
+                                                                    (int)phases_per_step, x, gamma_or_null, (u16*)out_bf16, (int)rows,
+                                                                    (int)cols, eps, status);
+  return (int)cudaGetLastError();
+}
+
+int wkb_tp_step_bump(void* step_ptr, void* stream) {
+  tp_step_bump_kernel<<<1, 1, 0, as_stream(stream)>>>((uint32_t*)step_ptr);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -160,16 +160,61 @@ class LlamaRankWeights:
         return self.lm_head.weight_bytes() + sum(lw[key].weight_bytes() for lw in self.layers for key in ("wqkv", "wo", "wgu", "wdown"))
 
 
+class PeerReduce:
+    """Peer-memory plumbing of the fused sum-over-ranks + add + RMSNorm kernel (wkb_tp_reduce_add_rmsnorm): every rank
+    owns two fp32 partial buffers [rows, cols] and a flag row, exports them with CUDA IPC, and maps its peers'.
+    `dist` must be an initialised torch.distributed process group with one rank per GPU of the node."""
+
+    def __init__(self, rank, world, rows, cols, device):
+        import ctypes
+        import torch.distributed as dist
+        L = lib()
+        self.rank, self.world = rank, world
+        self.part = [torch.zeros((rows, cols), dtype=torch.float32, device=device) for _ in range(2)]
+        self.flags = torch.zeros(256, dtype=torch.int32, device=device)
+        self.step = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize()
+        mine = []
+        for t in self.part + [self.flags]:
+            handle, off = (ctypes.c_char * 64)(), ctypes.c_int64(0)
+            check(L.wkb_ipc_export(t.data_ptr(), handle, ctypes.byref(off)), "wkb_ipc_export")
+            mine.append((bytes(handle.raw), int(off.value)))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+        self._mapped = []
+        ptrs = [[0] * world for _ in range(3)]
+        for r in range(world):
+            for b in range(3):
+                if r == rank:
+                    ptrs[b][r] = (self.part + [self.flags])[b].data_ptr()
+                else:
+                    handle, off = everyone[r][b]
+                    base = L.wkb_ipc_import((ctypes.c_char * 64).from_buffer_copy(handle))
+                    if not base:
+                        raise RuntimeError("cannot map the buffers of rank %d (CUDA IPC)" % r)
+                    self._mapped.append(base)
+                    ptrs[b][r] = base + off
+        arr = lambda v: (ctypes.c_void_p * world)(*v)
+        self.part_ptrs = [arr(ptrs[0]), arr(ptrs[1])]   # by buffer, then by rank
+        self.flag_ptrs = arr(ptrs[2])
+        dist.barrier()
+
+    def close(self):
+        for base in self._mapped:
+            lib().wkb_ipc_close(base)
+        self._mapped = []
+
+
 class LlamaDecodeModel:
     """One rank of the tensor-parallel decode model.  `forward(n)` runs rows 0..n-1 of the row buffers
     (token, position, slot, visible keys); `reduce(t)` must sum `t` over the ranks in place (None: one rank);
     `gather(pairs, all_pairs)` must gather the ranks' arg-max candidates (None: one rank)."""
 
     def __init__(self, cfg, weights, rank, world, bcap, num_pages, max_blocks_per_seq, page_tokens=16, device="cuda",
-                 reduce=None, gather=None):
+                 reduce=None, gather=None, peer=None):
         cfg.check_world(world)
         self.cfg, self.w, self.rank, self.world, self.bcap, self.device = cfg, weights, rank, world, bcap, device
-        self.reduce, self.gather = reduce, gather
+        self.reduce, self.gather, self.peer = reduce, gather, peer
         self.page_tokens, self.mbps, self.max_ctx = page_tokens, max_blocks_per_seq, max_blocks_per_seq * page_tokens
         d, hd, R = cfg.d_model, cfg.head_dim, bcap
         self.hq, self.hkv, self.f = cfg.n_head // world, cfg.n_kv_head // world, cfg.d_ff // world
@@ -183,6 +228,8 @@ class LlamaDecodeModel:
         f32 = dict(dtype=torch.float32, device=device)
         bf = dict(dtype=torch.bfloat16, device=device)
         self.x, self.part = torch.zeros((R, d), **f32), torch.zeros((R, d), **f32)
+        # with the peer-memory reduce the two projections write straight into the buffers the peers read
+        self.part_attn, self.part_mlp = (peer.part[0], peer.part[1]) if peer is not None else (self.part, self.part)
         self.xn = torch.zeros((R, d), **bf)
         self.qkv = torch.zeros((R, self.qkv_w), **f32)
         self.att = torch.zeros((R, self.hq * hd), **bf)
@@ -223,20 +270,29 @@ class LlamaDecodeModel:
         check(L.wkb_paged_attn_decode(p(self.qkv), self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
                                       p(self.row_ctx), p(self.att), 1, self.hq * hd, n, self.hq, self.hkv, hd, self.page_tokens, self.mbps,
                                       self.max_ctx, self.scale, p(self.scratch), s), "attention")
-        self._gemm(lw["wo"], self.att, self.hq * hd, self.part, cfg.d_model, 0, n, "o_proj")
+        self._gemm(lw["wo"], self.att, self.hq * hd, self.part_attn, cfg.d_model, 0, n, "o_proj")
+
+    def _peer_reduce(self, which, phase, gain, n, what):
+        pr, s, p = self.peer, torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
+        check(lib().wkb_tp_reduce_add_rmsnorm(pr.part_ptrs[which], pr.flag_ptrs, self.rank, self.world, p(pr.step), phase,
+                                              2 * self.cfg.n_layer, p(self.x), p(gain), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), what)
 
     def after_attn(self, li, n):
         L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
+        if self.peer is not None:
+            return self._peer_reduce(0, 2 * li, self.w.layers[li]["norm2"], n, "reduce_norm2")
         check(L.wkb_add_rmsnorm_bf16(p(self.x), p(self.part), p(self.w.layers[li]["norm2"]), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), "norm2")
 
     def mlp_part(self, li, n):
         lw = self.w.layers[li]
         self._gemm(lw["wgu"], self.xn, self.cfg.d_model, self.h, self.f, 2, n, "gate_up")
-        self._gemm(lw["wdown"], self.h, self.f, self.part, self.cfg.d_model, 0, n, "down")
+        self._gemm(lw["wdown"], self.h, self.f, self.part_mlp, self.cfg.d_model, 0, n, "down")
 
     def after_mlp(self, li, n):
         L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
         gain = self.w.layers[li + 1]["norm1"] if li + 1 < self.cfg.n_layer else self.w.norm_f
+        if self.peer is not None:
+            return self._peer_reduce(1, 2 * li + 1, gain, n, "reduce_norm_next")
         check(L.wkb_add_rmsnorm_bf16(p(self.x), p(self.part), p(gain), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), "norm_next")
 
     def head_local(self, n):
@@ -248,16 +304,18 @@ class LlamaDecodeModel:
     def head_pick(self, n):
         L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
         check(L.wkb_argmax_pick(p(self.all_pairs), self.world, self.bcap, p(self.next_tok), s), "argmax_pick")
+        if self.peer is not None:
+            check(L.wkb_tp_step_bump(p(self.peer.step), s), "step_bump")
 
     def forward(self, n):
         self.begin(n)
         for li in range(self.cfg.n_layer):
             self.attn_part(li, n)
-            if self.reduce is not None:
+            if self.reduce is not None and self.peer is None:
                 self.reduce(self.part)
             self.after_attn(li, n)
             self.mlp_part(li, n)
-            if self.reduce is not None:
+            if self.reduce is not None and self.peer is None:
                 self.reduce(self.part)
             self.after_mlp(li, n)
         self.head_local(n)
@@ -342,6 +400,24 @@ class DecodeStepRunner:
             self.segments.append(self._capture(whole))
             return
 
+        if m.peer is not None:
+            def body():
+                m.begin(n)
+                for li in range(L):
+                    m.attn_part(li, n)
+                    m.after_attn(li, n)
+                    m.mlp_part(li, n)
+                    m.after_mlp(li, n)
+                m.head_local(n)
+            self.segments.append(self._capture(body))
+
+            def tail():
+                m.head_pick(n)
+                if with_advance:
+                    m.advance(n)
+            self.segments.append(self._capture(tail))
+            return
+
         def first():
             m.begin(n)
             m.attn_part(0, n)
@@ -379,6 +455,11 @@ class DecodeStepRunner:
             self.segments[0].replay()
             return
         segs = self.segments
+        if m.peer is not None:
+            segs[0].replay()
+            m.gather(m.pairs, m.all_pairs)
+            segs[1].replay()
+            return
         segs[0].replay()
         for i in range(1, len(segs) - 1):
             m.reduce(m.part)
