@@ -1,0 +1,64 @@
+"""Child program of tests/test_gpu_tp_peer.py (run under torch.distributed.run, one rank per GPU): the same
+tensor-parallel Llama-shape decode steps once with NCCL all-reduces and once with the fused peer-memory
+reduce + add + RMSNorm kernel; the two must agree (bit for bit on two ranks, where the sum has two terms)."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch
+import torch.distributed as dist
+
+from wukong_b200 import device as dev
+from wukong_b200.llama import LlamaConfig, LlamaRankWeights, LlamaDecodeModel, PeerReduce
+
+
+def main():
+    world, rank, local = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    device = "cuda:%d" % local
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = LlamaConfig(n_layer=2, d_model=1024, n_head=8, n_kv_head=4, d_ff=2816, vocab=2048)
+    w = LlamaRankWeights.synth_device(cfg, rank, world, 0, device)
+    B, mbps = 16, 4
+
+    def make(peer):
+        m = LlamaDecodeModel(cfg, w, rank, world, B, B * mbps, mbps, 16, device, lambda t: dist.all_reduce(t),
+                             lambda a, b: dist.all_gather_into_tensor(b, a), peer)
+        g = torch.Generator(device=device)
+        g.manual_seed(5 + rank)
+        m.kv.k.normal_(generator=g)
+        m.kv.v.normal_(generator=g)
+        m.block_table.copy_(torch.arange(B * mbps, dtype=torch.int32, device=device).view(B, mbps))
+        m.row_token.copy_(torch.arange(B, dtype=torch.int32, device=device) * 37 % cfg.vocab)
+        m.row_pos.fill_(20)
+        m.row_ctx.fill_(21)
+        return m
+
+    peer = PeerReduce(rank, world, B, cfg.d_model, device)
+    ma, mb = make(None), make(peer)
+    for _ in range(3):
+        ta = ma.forward(B).clone()
+        ma.advance(B)
+        tb = mb.forward(B).clone()
+        mb.advance(B)
+        torch.cuda.synchronize()
+        assert dev.gemm_status() == 0
+        assert torch.equal(ta, tb), "tokens differ between the NCCL and the peer-memory path"
+        scale = ma.x.abs().max().item()
+        diff = (ma.x - mb.x).abs().max().item()
+        assert diff <= (0.0 if world == 2 else 1e-5 * scale), (diff, scale)
+    # every rank holds the same residual stream and the same tokens
+    ref = mb.next_tok.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(ref, mb.next_tok)
+    dist.barrier()
+    peer.close()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("tp_peer_check ok", flush=True)
+
+
+if __name__ == "__main__":
+    main()
