@@ -241,7 +241,7 @@ def run_ours(args):
     peak, peak_kind = B.hbm_peak()
     step_ms = dev_ms / K
     a_gbs, g_gbs = attn_bytes / (attn_ms * 1e-3) / 1e9, gemm_bytes / (gemm_ms * 1e-3) / 1e9
-    roofline = {"kernel": "paged_attn_decode_kernel<128,%d> (+ chunk merge)" % (m.hq // m.hkv), "bound": "hbm", "achieved": a_gbs,
+    roofline = {"kernel": ("paged_attn_decode_mma_kernel<%d> (+ chunk merge)" if m.hq != m.hkv else "paged_attn_decode_kernel<128,%d> (+ chunk merge)") % (m.hq // m.hkv), "bound": "hbm", "achieved": a_gbs,
                 "peak": peak, "peak_source": "of " + peak_kind, "unit": "GB/s", "frac": a_gbs / peak,
                 # DRAM bytes per launch: 1.02 x the algorithmic bytes in the ncu capture of this kernel on the batch-64
                 # ctx U[128,4096] case (profiles/paged_attn_decode_mma_ncu.md); traffic grows with the visible tokens
