@@ -129,6 +129,17 @@ void wukong_embedding_f32_parallel(float* out, const float* weight, const int32_
 void wukong_rowargmax_i32(const float* x, int32_t* out, int64_t rows, int64_t cols);
 void wukong_rowargmax_i32_parallel(const float* x, int32_t* out, int64_t rows, int64_t cols);
 
+/* Selection, sampling, RNG (crates/wukong_runtime/src/topk.rs:161-221, random.rs:88-104).  One strict total
+ * order: descending = NaN largest, larger first, ties (signed zeros, NaNs) to the lower index; ascending = smaller
+ * first, NaN last, stable.  topk writes k = min(n, nv, ni) (value, index) pairs and returns k; the input is read
+ * before any output is written.  sample_categorical is the inverse CDF over the positive finite weights with the
+ * running mass summed in f64 in index order (-1 when nothing has mass).  rand_fill: out[i] = top 24 bits of
+ * Philox4x32-10(key = seed, counter = ctr0 + i) word 0, times 2^-24. */
+int64_t wukong_topk_f32(const float* x, int64_t n, float* vals, int64_t nv, int64_t* idx, int64_t ni);
+int64_t wukong_argsort_f32(const float* x, int64_t n, int64_t* idx, int64_t ni, int64_t descending);
+int64_t wukong_sample_categorical_f32(const float* p, int64_t n, float u);
+void wukong_rand_fill_f32(float* out, int64_t n, int64_t seed, int64_t ctr0);
+
 /* ===================================== PART 2: device-resident API ============================ */
 /* The reference's GPU path crosses host<->device on every call (crates/wukong_codegen_gpu/src/gpu.rs
  * :1647-1663); these entries are what replaces it.  All pointers are DEVICE pointers. */
@@ -212,6 +223,14 @@ int wkb_tp_step_bump(void* step_ptr, void* stream);
 int wkb_ipc_export(void* ptr, void* handle64, int64_t* offset);
 void* wkb_ipc_import(const void* handle64);
 int wkb_ipc_close(void* mapped_ptr);
+/* Sampling beyond greedy on device rows: per-row top-k (k <= 4096; k rounds over the row held in shared memory),
+ * full argsort (bitonic network; scratch of wkb_argsort_scratch_bytes(n)), per-row categorical draw with the
+ * reference's f64 index-order sums, Philox fill.  Same total orders and bits as the PART 1 entries. */
+int wkb_rand_fill_f32(float* out, int64_t n, int64_t seed, int64_t ctr0, void* stream);
+int wkb_topk_rows_f32(const float* x, int64_t ld, int64_t rows, int64_t cols, int64_t k, float* vals, int64_t* idx, void* stream);
+int64_t wkb_argsort_scratch_bytes(int64_t n);
+int wkb_argsort_f32(const float* x, int64_t n, float* vals_or_null, int64_t* idx, int64_t m, int64_t descending, void* scratch, void* stream);
+int wkb_sample_categorical_rows_f32(const float* p, int64_t ld, int64_t rows, int64_t cols, const float* u, int64_t* out, void* stream);
 /* Greedy sampling with the vocabulary split over ranks: pack (value bits, idx_local + col_offset) of each
  * row's local arg-max into pairs[rows][2]; after gathering the ranks' pairs into [world][rows][2], pick the
  * row's token by the arg-max rule of wukong_rowargmax_i32 applied across ranks. */

@@ -92,6 +92,12 @@ def _declare(L):
         "wko_rope_pos_f32": (None, [vp, vp, vp, vp, i64, i64, i64]),
         "wko_embedding_f32": (None, [vp, vp, vp, i64, i64, i64]),
         "wko_rowargmax_i32": (None, [vp, vp, i64, i64]),
+        "wko_philox4x32_10": (None, [vp, vp, vp]),
+        "wko_rand_u32": (C.c_uint32, [C.c_uint64, C.c_uint64]),
+        "wko_rand_fill_f32": (None, [vp, i64, i64, i64]),
+        "wko_topk_f32": (i64, [vp, i64, vp, i64, vp, i64]),
+        "wko_argsort_f32": (i64, [vp, i64, vp, i64, i64]),
+        "wko_sample_categorical_f32": (i64, [vp, i64, C.c_float]),
         "wko_set_threads": (None, [C.c_int]),
         "wko_get_threads": (C.c_int, []),
     }
@@ -330,3 +336,38 @@ def to_bf16_bits(x):
 
 def from_bf16_bits(b):
     return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def philox4x32_10(ctr4, key2):
+    c, k, o = np.asarray(ctr4, np.uint32), np.asarray(key2, np.uint32), np.zeros(4, np.uint32)
+    lib().wko_philox4x32_10(p(c), p(k), p(o))
+    return o
+
+
+def rand_u32(seed, ctr):
+    return int(lib().wko_rand_u32(seed & 0xFFFFFFFFFFFFFFFF, ctr & 0xFFFFFFFFFFFFFFFF))
+
+
+def rand_fill(n, seed, ctr0):
+    out = np.full(max(n, 0), 7.0, np.float32)
+    lib().wko_rand_fill_f32(p(out), n, seed, ctr0)
+    return out
+
+
+def topk(x, k):
+    x = f32a(x).ravel()
+    vals, idx = np.full(k, 9.0, np.float32), np.full(k, 9, np.int64)
+    got = lib().wko_topk_f32(p(x), x.size, p(vals), k, p(idx), k)
+    return int(got), vals, idx
+
+
+def argsort(x, m, descending=False):
+    x = f32a(x).ravel()
+    idx = np.full(m, 9, np.int64)
+    got = lib().wko_argsort_f32(p(x), x.size, p(idx), m, int(descending))
+    return int(got), idx
+
+
+def sample_categorical(w, u):
+    w = f32a(w).ravel()
+    return int(lib().wko_sample_categorical_f32(p(w) if w.size else None, w.size, float(u)))

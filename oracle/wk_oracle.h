@@ -112,6 +112,14 @@ void wko_rope_pos_f32(const float* x, const float* inv_freq, const int32_t* pos,
 void wko_embedding_f32(float* out, const float* weight, const int32_t* ids, i64 t, i64 h, i64 v);
 void wko_rowargmax_i32(const float* x, int32_t* out, i64 rows, i64 cols);
 
+/* selection, sampling, RNG: topk.rs:22-136, random.rs:24-104 of the reference runtime */
+void wko_philox4x32_10(const uint32_t* ctr4, const uint32_t* key2, uint32_t* out4);
+uint32_t wko_rand_u32(uint64_t seed, uint64_t ctr);
+void wko_rand_fill_f32(float* out, i64 n, i64 seed, i64 ctr0);
+i64 wko_topk_f32(const float* x, i64 n, float* vals, i64 nv, i64* idx, i64 ni);
+i64 wko_argsort_f32(const float* x, i64 n, i64* idx, i64 ni, i64 descending);
+i64 wko_sample_categorical_f32(const float* p, i64 n, float u);
+
 // ---- threading knob for the timed CPU baseline (rows/units split across threads; results are
 // bit-identical to the single-thread run because units are independent) ----
 void wko_set_threads(int n);

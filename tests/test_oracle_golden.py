@@ -439,3 +439,53 @@ def test_llama_block_example_golden(orc):
     from wukong_b200 import wk_programs
     out = wk_programs.llama_block(OracleRT(orc), **wk_programs.llama_block_inputs())
     assert [int(t) for t in fx.rust_round(out[[0, 64, 256, 511]] * np.float32(10000.0))] == [-1227, 1204, 593, -404]
+
+
+# ---- selection, sampling and the counter-based RNG (crates/wukong_runtime/src/topk.rs, random.rs) ----------
+def test_philox_known_answers_and_builtin_mapping(orc):
+    """Random123's published known-answer vectors for philox4x32-10 and the (seed, counter) mapping the reference
+    pins in random.rs:109-155."""
+    M = 0xFFFFFFFF
+    kat = [([0, 0, 0, 0], [0, 0], [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]),
+           ([M] * 4, [M] * 2, [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]),
+           ([0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344], [0xa4093822, 0x299f31d0], [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1])]
+    for ctr, key, want in kat:
+        assert [int(v) for v in orc.philox4x32_10(ctr, key)] == want
+    assert orc.rand_u32(0, 0) == 0x6627e8d5 and orc.rand_u32(0, 1) == 0xf8e4cca4 and orc.rand_u32(1, 0) == 0xe3e80670
+    assert orc.rand_u32(42, 7) == 0x5bbd83b1 and orc.rand_u32(0xDEADBEEFCAFEF00D, 0x123456789ABCDEF0) == 0xdecbb6f2
+    assert orc.rand_u32(0xFFFFFFFFFFFFFFFF, 3) == 0x8e8fd014
+    f = orc.rand_fill(5, 42, -2)                      # the counter wraps: lane 2 is counter 0
+    assert f[2] == np.float32((orc.rand_u32(42, 0) >> 8) / 16777216.0)
+    assert orc.rand_fill(1, 0, 0)[0] == np.float32(6694888.0 / 16777216.0)
+    assert orc.rand_fill(1, 42, 7)[0] == np.float32(6012291.0 / 16777216.0)
+    assert orc.rand_fill(0, 1, 1).size == 0
+
+
+def test_topk_argsort_total_order(orc):
+    """topk.rs:244-286: NaN largest, ties (signed zeros, NaNs) to the lower index; ascending sort is stable, NaN last."""
+    nan = np.nan
+    x = np.array([1.0, nan, 3.0, -0.0, 3.0, 0.0, nan, -5.0], np.float32)
+    k, vals, idx = orc.topk(x, 5)
+    assert k == 5 and idx.tolist() == [1, 6, 2, 4, 0]
+    assert np.isnan(vals[:2]).all() and vals[2:].tolist() == [3.0, 3.0, 1.0]
+    k, vals, idx = orc.topk(np.array([0.0, -0.0, 0.0], np.float32), 3)
+    assert idx.tolist() == [0, 1, 2] and np.signbit(vals[1])
+    assert orc.topk(np.zeros(0, np.float32), 3)[0] == 0
+    y = np.array([2.0, nan, -1.0, 2.0, 0.5, -1.0], np.float32)
+    assert orc.argsort(y, 6)[1].tolist() == [2, 5, 4, 0, 3, 1]
+    assert orc.argsort(y, 6, True)[1].tolist() == [1, 0, 3, 4, 2, 5]
+    m, short = orc.argsort(y, 2)
+    assert m == 2 and short.tolist() == [2, 5]
+    m, long = orc.argsort(y[:3], 8)
+    assert m == 3 and long.tolist() == [2, 0, 1, 9, 9, 9, 9, 9]
+
+
+def test_sample_categorical_inverse_cdf(orc):
+    """topk.rs:309-323: mass = the weight when positive and finite, first index whose running mass exceeds u * total."""
+    p = [0.0, 1.0, np.nan, 2.0, -4.0, np.inf, 1.0]
+    want = {0.0: 1, 0.2499: 1, 0.25: 3, 0.7499: 3, 0.75: 6, 1.0: 6, 7.0: 6, -3.0: 1}
+    for u, i in want.items():
+        assert orc.sample_categorical(p, u) == i, u
+    assert orc.sample_categorical(p, np.nan) == 1
+    assert orc.sample_categorical([0.0, -1.0, np.nan], 0.5) == -1
+    assert orc.sample_categorical([], 0.5) == -1

@@ -455,6 +455,69 @@ void wukong_rowargmax_i32(const float* x, int32_t* out, i64 rows, i64 cols) {
 }
 void wukong_rowargmax_i32_parallel(const float* x, int32_t* out, i64 rows, i64 cols) { wukong_rowargmax_i32(x, out, rows, cols); }
 
+// ---- selection / sampling / RNG (topk.rs:161-221, random.rs:88-104 of the reference runtime) ----
+i64 wukong_topk_f32(const float* x, i64 n, float* vals, i64 nv, i64* idx, i64 ni) {
+  if (n < 0) n = 0;
+  i64 k = n;
+  if (nv < k) k = nv < 0 ? 0 : nv;
+  if (ni < k) k = ni < 0 ? 0 : ni;
+  if (k <= 0) return 0;
+  Arena& A = g_arena;
+  A.begin(pad((size_t)n * 4) + pad((size_t)k * 4) + pad((size_t)k * 8) + pad((size_t)wkb_argsort_scratch_bytes(n)));
+  float* dx = A.up(x, (size_t)n);           // the input is snapshotted here: outputs may overlap it
+  float* dv = A.out<float>((size_t)k);
+  i64* di = A.out<i64>((size_t)k);
+  if (k <= 64) {
+    check_launch(wkb_topk_rows_f32(dx, n, 1, n, k, dv, di, A.stream), "topk");
+  } else {
+    void* scratch = A.take((size_t)wkb_argsort_scratch_bytes(n));
+    check_launch(wkb_argsort_f32(dx, n, dv, di, k, 1, scratch, A.stream), "topk(sort)");
+  }
+  A.down(vals, dv, (size_t)k);
+  A.down(idx, di, (size_t)k);
+  A.sync();
+  return k;
+}
+
+i64 wukong_argsort_f32(const float* x, i64 n, i64* idx, i64 ni, i64 descending) {
+  if (n < 0) n = 0;
+  i64 m = ni < n ? (ni < 0 ? 0 : ni) : n;
+  if (m <= 0) return 0;
+  Arena& A = g_arena;
+  A.begin(pad((size_t)n * 4) + pad((size_t)m * 8) + pad((size_t)wkb_argsort_scratch_bytes(n)));
+  float* dx = A.up(x, (size_t)n);
+  i64* di = A.out<i64>((size_t)m);
+  void* scratch = A.take((size_t)wkb_argsort_scratch_bytes(n));
+  check_launch(wkb_argsort_f32(dx, n, nullptr, di, m, descending, scratch, A.stream), "argsort");
+  A.down(idx, di, (size_t)m);
+  A.sync();
+  return m;
+}
+
+i64 wukong_sample_categorical_f32(const float* p, i64 n, float u) {
+  if (n <= 0 || !p) return -1;
+  Arena& A = g_arena;
+  A.begin(pad((size_t)n * 4) + pad(8) + pad(8));
+  float* dp = A.up(p, (size_t)n);
+  float* du = A.up(&u, 1);
+  i64* dout = A.out<i64>(1);
+  check_launch(wkb_sample_categorical_rows_f32(dp, n, 1, n, du, dout, A.stream), "sample_categorical");
+  i64 r = -1;
+  A.down(&r, dout, 1);
+  A.sync();
+  return r;
+}
+
+void wukong_rand_fill_f32(float* out, i64 n, i64 seed, i64 ctr0) {
+  if (n <= 0) return;
+  Arena& A = g_arena;
+  A.begin(pad((size_t)n * 4));
+  float* d = A.out<float>((size_t)n);
+  check_launch(wkb_rand_fill_f32(d, n, seed, ctr0, A.stream), "rand_fill");
+  A.down(out, d, (size_t)n);
+  A.sync();
+}
+
 // Library identity / device probe used by the Python loader.
 int wkb_device_count(void) {
   int n = 0;

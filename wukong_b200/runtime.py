@@ -177,3 +177,22 @@ def embedding(out, weight, ids, t, h, v):
 
 def rowargmax(x, out, rows, cols):
     lib().wukong_rowargmax_i32(_p(_f32(x)), _p(out), rows, cols)
+
+
+# ---- selection / sampling / RNG builtins (topk_f32, argsort_f32, sample_categorical, rand_fill_f32) ----
+def topk(x, vals, idx):
+    """Writes the k = min(len(x), len(vals), len(idx)) largest elements (value, int64 index) in descending order; returns k."""
+    return int(lib().wukong_topk_f32(_p(_f32(x)), x.size, _p(_f32(vals)), vals.size, _p(idx), idx.size))
+
+
+def argsort(x, idx, descending=False):
+    return int(lib().wukong_argsort_f32(_p(_f32(x)), x.size, _p(idx), idx.size, int(descending)))
+
+
+def sample_categorical(p, u):
+    p = _f32(p)
+    return int(lib().wukong_sample_categorical_f32(_p(p) if p.size else None, p.size, float(u)))
+
+
+def rand_fill(out, seed, ctr0):
+    lib().wukong_rand_fill_f32(_p(_f32(out)), out.size, seed, ctr0)
