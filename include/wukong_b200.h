@@ -200,6 +200,12 @@ int wkb_rope_bf16(const void* x, const float* inv_freq, const int* pos, void* ou
  * row_stride floats; same pairing and sin / cos sequence as wkb_rope_f32, position from pos[row]. */
 int wkb_rope_qk_f32(float* x, int64_t row_stride, const float* inv_freq, const int* pos, int64_t rows, int64_t heads,
                     int64_t half, void* stream);
+/* The two above fused with the paged KV append (wkb_paged_kv_append): one pass over fused QKV rows
+ * [q heads | k heads | v heads]; q rotated in place, k rotated and v copied into their bf16 pages at row_pos
+ * (which is also the RoPE position); rows with row_pos < 0 are untouched. */
+int wkb_rope_qk_paged_append(float* qkv, int64_t row_stride, const float* inv_freq, const uint32_t* block_table, const int* row_slot,
+                             const int* row_pos, void* kcache, void* vcache, int64_t rows, int64_t q_heads, int64_t kv_heads,
+                             int64_t half, int64_t page_tokens, int64_t max_blocks_per_seq, void* stream);
 /* Residual add fused with RMSNorm: x += delta (delta may be null), out = bf16(x / sqrt(mean(x^2) + eps) * gamma);
  * cols % 4 == 0.  The norm is the RMSNORM op of crates/wukong_runtime/src/norm.rs:50-54 in the
  * half-precision recipe (fp32 statistics, one rounding on the way out). */

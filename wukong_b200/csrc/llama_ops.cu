@@ -14,39 +14,49 @@
 
 namespace wkb {
 
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
-                                                          const float* __restrict__ gamma, u16* __restrict__ out,
-                                                          i64 rows, int cols, float eps) {
-  __shared__ float red[8];
-  const int nvec = cols >> 2;
+// One CTA per row; a thread keeps its NV float4 of the row in registers between the statistic and the write-back,
+// so the row is read once (x and delta) and written once (x and the bf16 normed row).
+template <int NV>
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                                           const float* __restrict__ gamma, u16* __restrict__ out,
+                                                           i64 rows, int cols, float eps) {
+  __shared__ float red[32];
+  const int nvec = cols >> 2, nwarps = blockDim.x >> 5;
   for (i64 r = blockIdx.x; r < rows; r += gridDim.x) {
     float4* xr = reinterpret_cast<float4*>(x + r * (i64)cols);
     const float4* dr = delta ? reinterpret_cast<const float4*>(delta + r * (i64)cols) : nullptr;
+    float4 v[NV];
     float q = 0.0f;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-      float4 v = xr[i];
-      if (dr) {
-        const float4 d = dr[i];
-        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
-        xr[i] = v;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < nvec) {
+        v[k] = xr[i];
+        if (dr) {
+          const float4 d = dr[i];
+          v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+        }
+        q = fmaf(v[k].x, v[k].x, q); q = fmaf(v[k].y, v[k].y, q); q = fmaf(v[k].z, v[k].z, q); q = fmaf(v[k].w, v[k].w, q);
       }
-      q = fmaf(v.x, v.x, q); q = fmaf(v.y, v.y, q); q = fmaf(v.z, v.z, q); q = fmaf(v.w, v.w, q);
     }
     q = warp_sum(q);
     __syncthreads();
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = q;
     __syncthreads();
     float tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) tot += red[w];
+    for (int w = 0; w < nwarps; ++w) tot += red[w];
     const float inv = rsqrtf(tot / (float)cols + eps);
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-      const float4 v = xr[i];  // this thread's own earlier write
-      const float4 g = gamma ? reinterpret_cast<const float4*>(gamma)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
-      uint2 o;
-      o.x = (uint32_t)f32_to_bf16_bits(v.x * inv * g.x) | ((uint32_t)f32_to_bf16_bits(v.y * inv * g.y) << 16);
-      o.y = (uint32_t)f32_to_bf16_bits(v.z * inv * g.z) | ((uint32_t)f32_to_bf16_bits(v.w * inv * g.w) << 16);
-      reinterpret_cast<uint2*>(out + r * (i64)cols)[i] = o;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < nvec) {
+        if (dr) xr[i] = v[k];
+        const float4 g = gamma ? reinterpret_cast<const float4*>(gamma)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+        uint2 o;
+        o.x = (uint32_t)f32_to_bf16_bits(v[k].x * inv * g.x) | ((uint32_t)f32_to_bf16_bits(v[k].y * inv * g.y) << 16);
+        o.y = (uint32_t)f32_to_bf16_bits(v[k].z * inv * g.z) | ((uint32_t)f32_to_bf16_bits(v[k].w * inv * g.w) << 16);
+        reinterpret_cast<uint2*>(out + r * (i64)cols)[i] = o;
+      }
     }
   }
 }
@@ -63,6 +73,45 @@ __global__ void __launch_bounds__(256) rope_qk_kernel(float* x, i64 row_stride, 
     const float a = p[j], b = p[j + half];
     p[j] = ffma(b, -s, fmul(a, c));
     p[j + half] = ffma(a, s, fmul(b, c));
+  }
+}
+
+// RoPE and the KV append in one pass over a fused QKV row: a thread owns the pair (j, j + half) of one head.
+// Query heads are rotated in place; key heads are rotated and rounded straight into their page; value heads are
+// rounded into theirs.  Same pairing, sin / cos and page addressing as rope_qk_kernel and paged_kv_append_kernel
+// (pages are bf16 [page][kv_head][token][dim]); a row with pos < 0 is inactive and touches nothing.
+__global__ void __launch_bounds__(256) rope_append_kernel(float* qkv, i64 row_stride, const float* __restrict__ inv_freq,
+                                                          const uint32_t* __restrict__ block_table, const int* __restrict__ row_slot,
+                                                          const int* __restrict__ row_pos, u16* __restrict__ kcache,
+                                                          u16* __restrict__ vcache, i64 rows, int hq, int hkv, int half,
+                                                          int page_tokens, int mbps) {
+  const int heads = hq + 2 * hkv, hd = 2 * half;
+  const i64 total = rows * heads * half;
+  for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
+    const int j = (int)(idx % half);
+    const i64 rh = idx / half;
+    const int hh = (int)(rh % heads);
+    const i64 r = rh / heads;
+    const int pos = row_pos[r];
+    if (pos < 0) continue;
+    float* p = qkv + r * row_stride + (i64)hh * hd;
+    float a = p[j], b = p[j + half];
+    if (hh < hq + hkv) {
+      const float theta = fmul((float)pos, inv_freq[j]);
+      const float c = sincos1(theta, true), s = sincos1(theta, false);
+      const float ra = ffma(b, -s, fmul(a, c)), rb = ffma(a, s, fmul(b, c));
+      a = ra; b = rb;
+    }
+    if (hh < hq) {
+      p[j] = a; p[j + half] = b;
+    } else {
+      const int kvh = hh < hq + hkv ? hh - hq : hh - hq - hkv;
+      const uint32_t page = block_table[(i64)row_slot[r] * mbps + pos / page_tokens];
+      const i64 dst = (((i64)page * hkv + kvh) * page_tokens + pos % page_tokens) * hd;
+      u16* cache = hh < hq + hkv ? kcache : vcache;
+      cache[dst + j] = f32_to_bf16_bits(a);
+      cache[dst + j + half] = f32_to_bf16_bits(b);
+    }
   }
 }
 
@@ -105,8 +154,18 @@ int wkb_add_rmsnorm_bf16(float* x, const float* delta_or_null, const float* gamm
   if (cols % 4 != 0) return (int)cudaErrorInvalidValue;
   if ((((uintptr_t)x) | ((uintptr_t)delta_or_null) | ((uintptr_t)gamma_or_null) | ((uintptr_t)out_bf16)) & 15)
     return (int)cudaErrorMisalignedAddress;
-  const int grid = (int)(rows < (i64)WKB_SM_COUNT * 8 ? rows : (i64)WKB_SM_COUNT * 8);
-  add_rmsnorm_kernel<<<grid, 256, 0, as_stream(stream)>>>(x, delta_or_null, gamma_or_null, (u16*)out_bf16, rows, (int)cols, eps);
+  const int grid = (int)(rows < (i64)WKB_SM_COUNT * 2 ? rows : (i64)WKB_SM_COUNT * 2);
+  const i64 nvec = cols / 4;
+  // as many threads as the row has float4 (up to 1024), then 2 or 4 or 8 vectors per thread
+  int threads = (int)(((nvec < 1024 ? nvec : 1024) + 31) / 32 * 32);
+  const i64 per = (nvec + threads - 1) / threads;
+  cudaStream_t st = as_stream(stream);
+  u16* o = (u16*)out_bf16;
+  if (per <= 1) add_rmsnorm_kernel<1><<<grid, threads, 0, st>>>(x, delta_or_null, gamma_or_null, o, rows, (int)cols, eps);
+  else if (per <= 2) add_rmsnorm_kernel<2><<<grid, threads, 0, st>>>(x, delta_or_null, gamma_or_null, o, rows, (int)cols, eps);
+  else if (per <= 4) add_rmsnorm_kernel<4><<<grid, threads, 0, st>>>(x, delta_or_null, gamma_or_null, o, rows, (int)cols, eps);
+  else if (per <= 8) add_rmsnorm_kernel<8><<<grid, threads, 0, st>>>(x, delta_or_null, gamma_or_null, o, rows, (int)cols, eps);
+  else return (int)cudaErrorInvalidValue;   // rows wider than 32768 columns
   return (int)cudaGetLastError();
 }
 
@@ -118,6 +177,21 @@ int wkb_rope_qk_f32(float* x, i64 row_stride, const float* inv_freq, const int* 
   i64 grid = (total + 255) / 256;
   if (grid > (i64)WKB_SM_COUNT * 16) grid = (i64)WKB_SM_COUNT * 16;
   rope_qk_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(x, row_stride, inv_freq, pos, rows, heads, half);
+  return (int)cudaGetLastError();
+}
+
+int wkb_rope_qk_paged_append(float* qkv, i64 row_stride, const float* inv_freq, const uint32_t* block_table, const int* row_slot,
+                             const int* row_pos, void* kcache, void* vcache, i64 rows, i64 q_heads, i64 kv_heads, i64 half,
+                             i64 page_tokens, i64 max_blocks_per_seq, void* stream) {
+  if (rows <= 0) return 0;
+  if (q_heads < 0 || kv_heads <= 0 || half <= 0 || page_tokens <= 0 || row_stride < (q_heads + 2 * kv_heads) * 2 * half)
+    return (int)cudaErrorInvalidValue;
+  const i64 total = rows * (q_heads + 2 * kv_heads) * half;
+  i64 grid = (total + 255) / 256;
+  if (grid > (i64)WKB_SM_COUNT * 16) grid = (i64)WKB_SM_COUNT * 16;
+  rope_append_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(qkv, row_stride, inv_freq, block_table, row_slot, row_pos, (u16*)kcache,
+                                                               (u16*)vcache, rows, (int)q_heads, (int)kv_heads, (int)half,
+                                                               (int)page_tokens, (int)max_blocks_per_seq);
   return (int)cudaGetLastError();
 }
 

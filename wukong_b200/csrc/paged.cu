@@ -412,9 +412,11 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const float* __re
   if (nch > max_chunks) nch = max_chunks;
   const float* s = scratch + rh * (i64)max_chunks * (HD + 4);
   float mm = -INFINITY;
+#pragma unroll 4
   for (int c = 0; c < nch; ++c) mm = fmaxf(mm, s[(i64)c * (HD + 4) + HD]);
   float lsum = 0.0f;
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
   for (int c = 0; c < nch; ++c) {
     const float* sc = s + (i64)c * (HD + 4);
     float w = exp2f(sc[HD] - mm);

@@ -5,8 +5,7 @@ memory, streams, graph capture and the process group):
 
     RMSNorm (fused with the previous residual add)            wkb_add_rmsnorm_bf16
     fused QKV projection, W4A16 on the tensor cores            wkb_gemm_q4_0_bf16_nt
-    RoPE in place on the q / k heads at the rows' positions    wkb_rope_qk_f32
-    K / V append through the block table                       wkb_paged_kv_append
+    RoPE on q / k at the rows' positions + K / V append       wkb_rope_qk_paged_append
     paged GQA decode attention                                 wkb_paged_attn_decode
     output projection (this rank's K slice)                    wkb_gemm_q4_0_bf16_nt
     -- sum over ranks --
@@ -263,10 +262,9 @@ class LlamaDecodeModel:
         L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
         cfg, lw, hd = self.cfg, self.w.layers[li], self.cfg.head_dim
         self._gemm(lw["wqkv"], self.xn, cfg.d_model, self.qkv, self.qkv_w, 0, n, "qkv")
-        check(L.wkb_rope_qk_f32(p(self.qkv), self.qkv_w, p(self.inv_freq), p(self.row_pos), n, self.hq + self.hkv, hd // 2, s), "rope")
-        k_ptr, v_ptr = p(self.qkv) + 4 * self.hq * hd, p(self.qkv) + 4 * (self.hq + self.hkv) * hd
-        check(L.wkb_paged_kv_append(k_ptr, v_ptr, self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
-                                    p(self.row_pos), n, self.hkv, hd, self.page_tokens, self.mbps, s), "kv_append")
+        check(L.wkb_rope_qk_paged_append(p(self.qkv), self.qkv_w, p(self.inv_freq), p(self.block_table), p(self.row_slot), p(self.row_pos),
+                                         p(self.kv.k[li]), p(self.kv.v[li]), n, self.hq, self.hkv, hd // 2, self.page_tokens, self.mbps, s),
+              "rope_append")
         check(L.wkb_paged_attn_decode(p(self.qkv), self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
                                       p(self.row_ctx), p(self.att), 1, self.hq * hd, n, self.hq, self.hkv, hd, self.page_tokens, self.mbps,
                                       self.max_ctx, self.scale, p(self.scratch), s), "attention")
@@ -324,8 +322,8 @@ class LlamaDecodeModel:
         else:
             self.all_pairs[0].copy_(self.pairs)
         self.head_pick(n)
-        # per layer: 2 norms, 4 GEMMs, rope, append, attention (2 kernels); embedding + first norm; head: GEMM, arg-max, pack, pick
-        self.launches_per_forward = self.cfg.n_layer * 10 + 2 + 4
+        # per layer: 2 norms, 4 GEMMs (+ their split-K second passes, not counted), rope + append, attention (2 kernels); embedding + first norm; head: GEMM, arg-max, pack, pick
+        self.launches_per_forward = self.cfg.n_layer * 9 + 2 + 4
         return self.next_tok
 
     def advance(self, n):
