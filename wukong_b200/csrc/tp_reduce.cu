@@ -9,7 +9,8 @@
 //   2. every block waits (acquire loads, bounded) until all peers have published this sequence number;
 //   3. a block then owns rows: it reads the row of every rank's partial -- plain loads through the peer mappings,
 //      over NVLink -- adds them in rank order (so all ranks compute bit-identical sums and the replicated residual
-//      stream stays identical), adds the residual, computes the RMS statistic and writes x and the bf16 normed row.
+//      stream stays identical), adds the residual, computes the RMS statistic and writes x and the bf16 normed row
+//      (the row stays in registers between the statistic and the write-back).
 // Buffers: each rank owns two partial buffers (attention, MLP) used alternately; a rank can run at most one phase
 // ahead of its slowest peer (it cannot pass a phase without that peer's flag), so a partial buffer is never
 // rewritten while a peer may still read it.  Sequence numbers come from a per-rank device step counter plus the
@@ -41,11 +42,12 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-__global__ void __launch_bounds__(256) tp_reduce_add_rmsnorm_kernel(TpPeers peers, int rank, int world, const uint32_t* __restrict__ step_ptr,
+template <int NV>
+__global__ void __launch_bounds__(1024) tp_reduce_add_rmsnorm_kernel(TpPeers peers, int rank, int world, const uint32_t* __restrict__ step_ptr,
                                                                     int phase, int phases_per_step, float* __restrict__ x,
                                                                     const float* __restrict__ gamma, u16* __restrict__ out, int rows,
                                                                     int cols, float eps, int* status) {
-  __shared__ float red[8];
+  __shared__ float red[32];
   __shared__ int s_ok;
   const uint32_t seq = (*step_ptr) * (uint32_t)phases_per_step + (uint32_t)phase + 1u;
   if (blockIdx.x == 0 && threadIdx.x < world && (int)threadIdx.x != rank) {
@@ -69,36 +71,43 @@ __global__ void __launch_bounds__(256) tp_reduce_add_rmsnorm_kernel(TpPeers peer
   }
   __syncthreads();
   if (!s_ok) return;
-  const int nvec = cols >> 2;
+  const int nvec = cols >> 2, nwarps = blockDim.x >> 5;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     float4* xr = reinterpret_cast<float4*>(x + (i64)r * cols);
+    float4 v[NV];
     float q = 0.0f;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-      float4 s = __ldcg(reinterpret_cast<const float4*>(peers.part[0] + (i64)r * cols) + i);
-      for (int p = 1; p < world; ++p) {
-        const float4 d = __ldcg(reinterpret_cast<const float4*>(peers.part[p] + (i64)r * cols) + i);
-        s.x += d.x; s.y += d.y; s.z += d.z; s.w += d.w;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < nvec) {
+        float4 s = __ldcg(reinterpret_cast<const float4*>(peers.part[0] + (i64)r * cols) + i);
+        for (int p = 1; p < world; ++p) {
+          const float4 d = __ldcg(reinterpret_cast<const float4*>(peers.part[p] + (i64)r * cols) + i);
+          s.x += d.x; s.y += d.y; s.z += d.z; s.w += d.w;
+        }
+        v[k] = xr[i];
+        v[k].x += s.x; v[k].y += s.y; v[k].z += s.z; v[k].w += s.w;
+        q = fmaf(v[k].x, v[k].x, q); q = fmaf(v[k].y, v[k].y, q); q = fmaf(v[k].z, v[k].z, q); q = fmaf(v[k].w, v[k].w, q);
       }
-      float4 v = xr[i];
-      v.x += s.x; v.y += s.y; v.z += s.z; v.w += s.w;
-      xr[i] = v;
-      q = fmaf(v.x, v.x, q); q = fmaf(v.y, v.y, q); q = fmaf(v.z, v.z, q); q = fmaf(v.w, v.w, q);
     }
     q = warp_sum(q);
     __syncthreads();
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = q;
     __syncthreads();
     float tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) tot += red[w];
+    for (int w = 0; w < nwarps; ++w) tot += red[w];
     const float inv = rsqrtf(tot / (float)cols + eps);
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-      const float4 v = xr[i];
-      const float4 g = gamma ? reinterpret_cast<const float4*>(gamma)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
-      uint2 o;
-      o.x = (uint32_t)f32_to_bf16_bits(v.x * inv * g.x) | ((uint32_t)f32_to_bf16_bits(v.y * inv * g.y) << 16);
-      o.y = (uint32_t)f32_to_bf16_bits(v.z * inv * g.z) | ((uint32_t)f32_to_bf16_bits(v.w * inv * g.w) << 16);
-      reinterpret_cast<uint2*>(out + (i64)r * cols)[i] = o;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < nvec) {
+        xr[i] = v[k];
+        const float4 g = gamma ? reinterpret_cast<const float4*>(gamma)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+        uint2 o;
+        o.x = (uint32_t)f32_to_bf16_bits(v[k].x * inv * g.x) | ((uint32_t)f32_to_bf16_bits(v[k].y * inv * g.y) << 16);
+        o.y = (uint32_t)f32_to_bf16_bits(v[k].z * inv * g.z) | ((uint32_t)f32_to_bf16_bits(v[k].w * inv * g.w) << 16);
+        reinterpret_cast<uint2*>(out + (i64)r * cols)[i] = o;
+      }
     }
   }
 }
@@ -156,9 +165,18 @@ int wkb_tp_reduce_add_rmsnorm(const void* const* parts, void* const* flags, i64 
     peers.flags[p] = p < world ? (uint32_t*)flags[p] : nullptr;
   }
   const int grid = (int)(rows < (i64)WKB_SM_COUNT ? rows : (i64)WKB_SM_COUNT);
-  tp_reduce_add_rmsnorm_kernel<<<grid, 256, 0, as_stream(stream)>>>(peers, (int)rank, (int)world, (const uint32_t*)step_ptr, (int)phase,
-                                                                    (int)phases_per_step, x, gamma_or_null, (u16*)out_bf16, (int)rows,
-                                                                    (int)cols, eps, status);
+  const i64 nvec = cols / 4;
+  const int threads = (int)(((nvec < 1024 ? nvec : 1024) + 31) / 32 * 32);
+  const i64 per = (nvec + threads - 1) / threads;
+  cudaStream_t st = as_stream(stream);
+#define WKB_TP_LAUNCH(NV_) tp_reduce_add_rmsnorm_kernel<NV_><<<grid, threads, 0, st>>>(peers, (int)rank, (int)world, (const uint32_t*)step_ptr, \
+    (int)phase, (int)phases_per_step, x, gamma_or_null, (u16*)out_bf16, (int)rows, (int)cols, eps, status)
+  if (per <= 1) WKB_TP_LAUNCH(1);
+  else if (per <= 2) WKB_TP_LAUNCH(2);
+  else if (per <= 4) WKB_TP_LAUNCH(4);
+  else if (per <= 8) WKB_TP_LAUNCH(8);
+  else return (int)cudaErrorInvalidValue;
+#undef WKB_TP_LAUNCH
   return (int)cudaGetLastError();
 }
 
