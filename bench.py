@@ -69,25 +69,36 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.samples, self.proc = index, [], None
+        self.t_begin = self.t_end = None
 
-    def start(self):
+    def launch(self):
+        """Start nvidia-smi streaming samples (it needs a moment to come up, so this is called well before the
+        timed region; `start` / `stop` then mark the region whose samples count)."""
+        if self.proc is not None:
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
             self.proc = None
 
+    def start(self):
+        self.launch()
+        self.t_begin = time.perf_counter()
+
     def _read(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 6:
-                self.samples.append(parts)
+                self.samples.append((time.perf_counter(), parts))
 
     def stop(self):
+        self.t_end = time.perf_counter()
         if self.proc:
+            time.sleep(0.06)            # let the sample that covers the end of the region arrive
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -97,7 +108,10 @@ class ClockSampler:
     def summary(self):
         sm, mx, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for p in self.samples:
+        inside = [p for (t, p) in self.samples if self.t_begin is not None and self.t_begin <= t <= (self.t_end or t) + 0.06]
+        # a region shorter than the sampling period may hold no sample: then the nearest ones around it stand in
+        chosen = inside or [p for (_, p) in self.samples[-3:]]
+        for p in chosen:
             try:
                 sm.append(int(p[0]))
                 mx = max(mx, int(p[1]))
@@ -216,6 +230,8 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     _lib.require_gpu()
     torch.cuda.set_device(local)
+    clocks = ClockSampler(local)
+    clocks.launch()                 # streams from here on; start() / stop() mark the timed regions
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     K, W, S = args.steps, args.warmup, args.seqs
@@ -261,7 +277,6 @@ def run_ours(args):
     def max_over_ranks(ms):
         return max_over_ranks_ms(ms, world, "cuda")
 
-    clocks = ClockSampler(local)
 
     # ---- e2e: the public serving API, host buffers in and out every step
     for _ in range(W):
