@@ -27,7 +27,7 @@ def test_gemm_tc_matches_order_contract_gemm(dev, orc):
     import torch
     rng = np.random.default_rng(0)
     for (m, n, k) in [(1, 1, 8), (128, 128, 64), (130, 70, 200), (64, 768, 768), (512, 2304, 768), (33, 1000, 3072),
-                      (257, 129, 72)]:
+                      (257, 129, 72), (512, 768, 3072)]:   # the last two K = 3072 shapes take the split-K path
         a = rng.standard_normal((m, k)).astype(np.float32)
         b = rng.standard_normal((n, k)).astype(np.float32)
         bias = rng.standard_normal(n).astype(np.float32)
@@ -48,6 +48,12 @@ def test_gemm_tc_matches_order_contract_gemm(dev, orc):
         refb = orc.sgemm_half_nt(ab, bb, m, k, n, bias=bias, act=2)
         got = cb.float().cpu().numpy()
         assert np.allclose(got, refb, rtol=2e-2, atol=2e-2)
+    # split-K with the output aliasing the residual (x = x + proj(h)), exact on small integers
+    a = torch.randint(-3, 4, (512, 3072), device="cuda").to(torch.bfloat16)
+    b = torch.randint(-3, 4, (768, 3072), device="cuda").to(torch.bfloat16)
+    xres = torch.randint(-5, 6, (512, 768), device="cuda").float()
+    want = a.float() @ b.float().T + xres
+    assert torch.equal(dev.gemm_bf16_nt(a, b, residual=xres, out=xres), want)
     assert dev.gemm_status() == 0
     # linearity at a size the oracle does not run: C(a1 + a2) == C(a1) + C(a2) for exactly representable inputs
     a1 = torch.randint(-4, 5, (1024, 4096), device="cuda").to(torch.bfloat16)

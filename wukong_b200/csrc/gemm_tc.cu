@@ -69,6 +69,8 @@ struct GemmEpi {
   int act;                 // 0 identity, 1 relu, 2 gelu, 3 silu
   int out_bf16;            // 0: f32 C, 1: bf16 C
   int* arg_idx;            // arg-max mode: per-(row, column tile) winning column (values go to C)
+  int ksplit;              // > 1: work item = (tile, K slice); slice s writes its raw fp32 partial at c + s * slice_stride
+  i64 slice_stride;        // elements between the partial outputs of consecutive K slices
 };
 
 // GELU for bf16 output: x * sigmoid(2u), u = sqrt(2/pi)(x + 0.044715 x^3), with the hardware exp2 and
@@ -115,9 +117,11 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int ksplit = epi.ksplit > 1 ? epi.ksplit : 1;
+  const int num_tiles = tiles_m * tiles_n * ksplit;   // work items: the K slice is the fastest index
   constexpr int BK = F8 ? BK_BYTES : BK_BYTES / 2;  // elements of K per stage
-  const int kiters = (K + BK - 1) / BK;
+  const int kiters_all = (K + BK - 1) / BK;
+  const int kper = (kiters_all + ksplit - 1) / ksplit;   // the host picks ksplit so that no slice is empty
   if (threadIdx.x == 0) WKB_TRACE(0);
 
   if (threadIdx.x == 0) {
@@ -142,15 +146,16 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       int it = 0, issued_from = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x) {
+        const int t = w / ksplit, k0 = (w % ksplit) * kper, kiters = min(kper, kiters_all - k0);
         const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
         for (int kk = 0; kk < kiters; ++kk, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1)) { atomicExch(status, 1); ok = false; break; }
           mbar_expect_tx(full_bar(s), STAGE_BYTES);
           const uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_A_BYTES;
-          tma_load_2d(sa, &map_a, full_bar(s), kk * BK, m0);
-          tma_load_2d(sb, &map_b, full_bar(s), kk * BK, n0);
+          tma_load_2d(sa, &map_a, full_bar(s), (k0 + kk) * BK, m0);
+          tma_load_2d(sb, &map_b, full_bar(s), (k0 + kk) * BK, n0);
         }
       }
       if (!ok) {
@@ -164,7 +169,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       int it = 0, local = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x, ++local) {
+        const int kiters = min(kper, kiters_all - (w % ksplit) * kper);
         const int buf = local & 1;
         // the epilogue must have drained this accumulator buffer (two tiles ago)
         if (!mbar_wait(tempty_bar(buf), ((local >> 1) & 1) ^ 1)) { atomicExch(status, 4); ok = false; break; }
@@ -194,7 +200,11 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     (void)stage;
     int local = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+    void* const c_all = c;
+    for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x, ++local) {
+      const int t = w / ksplit;
+      // a K slice's partial goes to its own plane of the split workspace (fp32, identity epilogue)
+      c = reinterpret_cast<float*>(c_all) + (i64)(w % ksplit) * epi.slice_stride;
       const int buf = local & 1;
       const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
       const int row = m0 + quarter * 32 + lane;
@@ -386,6 +396,55 @@ int* gemm_status_word() {
   return words[dev];
 }
 
+// Split-K second pass of the dense GEMM: c = act(sum over slices (slice order) + bias) (+ residual), f32 or bf16.
+__global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* __restrict__ ws, int ksplit, i64 slice_stride, int M, int N,
+                                                                 void* __restrict__ c, i64 ldc, int c_bf16, const float* __restrict__ bias,
+                                                                 int act, const float* __restrict__ residual, i64 ldr) {
+  const i64 quads = (i64)(N >> 2), total = (i64)M * quads;
+  for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
+    const int m = (int)(idx / quads), n0 = (int)(idx % quads) << 2;
+    const float4* src = reinterpret_cast<const float4*>(ws + (i64)m * N + n0);
+    float4 v = __ldcg(src);
+    for (int s = 1; s < ksplit; ++s) {
+      const float4 p = __ldcg(reinterpret_cast<const float4*>(ws + (i64)s * slice_stride + (i64)m * N + n0));
+      v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+    }
+    float y[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float t = y[j] + (bias ? bias[n0 + j] : 0.0f);
+      t = (act == 2 && c_bf16) ? gelu_fast(t) : act_apply(act, t);
+      if (residual) t += residual[(i64)m * ldr + n0 + j];
+      y[j] = t;
+    }
+    if (c_bf16) {
+      uint2 o;
+      o.x = (uint32_t)f32_to_bf16_bits(y[0]) | ((uint32_t)f32_to_bf16_bits(y[1]) << 16);
+      o.y = (uint32_t)f32_to_bf16_bits(y[2]) | ((uint32_t)f32_to_bf16_bits(y[3]) << 16);
+      *reinterpret_cast<uint2*>(reinterpret_cast<u16*>(c) + (i64)m * ldc + n0) = o;
+    } else {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(c) + (i64)m * ldc + n0) = make_float4(y[0], y[1], y[2], y[3]);
+    }
+  }
+}
+
+// Per-device split-K workspace, allocated on first use outside stream capture (a captured launch that finds none
+// simply does not split).
+constexpr size_t SPLITK_WS_BYTES = (size_t)32 << 20;
+static float* splitk_workspace(cudaStream_t st) {
+  static float* ws[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ws[dev]) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return nullptr;
+    float* p = nullptr;
+    if (cudaMalloc((void**)&p, SPLITK_WS_BYTES) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    ws[dev] = p;
+  }
+  return ws[dev];
+}
+
 i64 gemm_sm_count() { return sm_count(); }
 
 }  // namespace wkb
@@ -438,6 +497,37 @@ int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i6
   }
   GemmEpi epi{bias, residual, ldr, (int)act, c_bf16, nullptr};
   i64 tiles = wide ? tiles_wide : ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  // Few tiles and a long K (the decode MLP's down projection: 24 tiles, K = 3072): cut K into slices so that most SMs
+  // pull operands, fp32 partials to a workspace, one finishing pass.  Results do not depend on scheduling.
+  const i64 kiters = (k + 63) / 64;
+  if (!wide && tiles * 2 <= sm_count() && kiters >= 32 && n % 4 == 0 && ldc % 4 == 0 && (residual == nullptr || ldr % 4 == 0)) {
+    i64 ks = sm_count() / tiles;
+    if (ks > 4) ks = 4;
+    if (ks > kiters / 8) ks = kiters / 8;
+    const i64 kper = (kiters + ks - 1) / ks;
+    ks = (kiters + kper - 1) / kper;
+    float* ws = ks > 1 && (size_t)(ks * m * n * 4) <= SPLITK_WS_BYTES ? splitk_workspace(as_stream(stream)) : nullptr;
+    if (ws) {
+      KernelFn plain = table[0][0];
+      if (!attr_set[dev & 63][0]) {
+        cudaError_t e = cudaFuncSetAttribute(plain, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        attr_set[dev & 63][0] = true;
+      }
+      GemmEpi part{nullptr, nullptr, 0, 0, 0, nullptr, (int)ks, m * n};
+      const i64 items = tiles * ks;
+      plain<<<(unsigned)(items < sm_count() ? items : sm_count()), GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(
+          ma, mb, ws, n, (int)m, (int)n, (int)k, part, status);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return (int)e;
+      const i64 total = m * (n / 4);
+      i64 g = (total + 255) / 256;
+      if (g > sm_count() * 8) g = sm_count() * 8;
+      gemm_splitk_finish_kernel<<<(unsigned)g, 256, 0, as_stream(stream)>>>(ws, (int)ks, m * n, (int)m, (int)n, c, ldc, c_bf16, bias, (int)act,
+                                                                         residual, ldr);
+      return (int)cudaGetLastError();
+    }
+  }
   unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
   kern<<<grid, GEMM_THREADS, smem, as_stream(stream)>>>(ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
   return (int)cudaGetLastError();

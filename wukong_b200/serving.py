@@ -136,7 +136,11 @@ class DecodeModel:
         else:
             check(L.wkb_gemm_bf16_nt_argmax(p(self.hs), d, p(self.w["wte"]), d, n_sample, cfg.vocab, d, None, p(self.part_val),
                                             p(self.part_idx), p(self.next_tok), s), "lm_head_argmax")
-        self.launches_per_forward = launches + len(self.layers) + 4   # the attention call is two kernels
+        # the attention call is two kernels; a GEMM with few tiles and K >= 2048 (the down projection) adds its
+        # split-K finishing pass
+        tiles = lambda m, nn: ((m + 127) // 128) * ((nn + 127) // 128)
+        split = 1 if (2 * tiles(n, d) <= 148 and f >= 2048) else 0
+        self.launches_per_forward = launches + len(self.layers) * (1 + split) + 4
         return self.next_tok
 
 
