@@ -206,11 +206,20 @@ int wkb_rope_qk_f32(float* x, int64_t row_stride, const float* inv_freq, const i
 int wkb_rope_qk_paged_append(float* qkv, int64_t row_stride, const float* inv_freq, const uint32_t* block_table, const int* row_slot,
                              const int* row_pos, void* kcache, void* vcache, int64_t rows, int64_t q_heads, int64_t kv_heads,
                              int64_t half, int64_t page_tokens, int64_t max_blocks_per_seq, void* stream);
+/* wkb_rope_qk_paged_append reading the fused QKV row as the K-slice partials of its projection (out_mode 3 of
+ * wkb_gemm_q4_0_bf16_nt): rotated q heads go to q_out (row pitch row_stride), k and v into their pages. */
+int wkb_rope_qk_paged_append_slices(float* q_out, int64_t row_stride, const float* slices, int64_t nslices, int64_t slice_stride,
+                                    int64_t ld, const float* inv_freq, const uint32_t* block_table, const int* row_slot,
+                                    const int* row_pos, void* kcache, void* vcache, int64_t rows, int64_t q_heads, int64_t kv_heads,
+                                    int64_t half, int64_t page_tokens, int64_t max_blocks_per_seq, void* stream);
 /* Residual add fused with RMSNorm: x += delta (delta may be null), out = bf16(x / sqrt(mean(x^2) + eps) * gamma);
  * cols % 4 == 0.  The norm is the RMSNORM op of crates/wukong_runtime/src/norm.rs:50-54 in the
  * half-precision recipe (fp32 statistics, one rounding on the way out). */
 int wkb_add_rmsnorm_bf16(float* x, const float* delta_or_null, const float* gamma_or_null, void* out_bf16, int64_t rows,
                          int64_t cols, float eps, void* stream);
+/* The same with delta given as nslices planes (pitch ld, slice_stride apart) that are added in plane order. */
+int wkb_add_slices_rmsnorm_bf16(float* x, const float* slices, int64_t nslices, int64_t slice_stride, int64_t ld,
+                                const float* gamma_or_null, void* out_bf16, int64_t rows, int64_t cols, float eps, void* stream);
 /* Tensor-parallel sum over ranks fused with the residual add and RMSNorm that follow it, over peer memory
  * (one kernel per rank instead of an all-reduce plus a norm; the reference's counterpart is the all-reduce of its
  * tensor-parallel block, crates/wukong_codegen_gpu/src/serving.rs:4161-4240).  parts[r] / flags[r] (HOST arrays
@@ -330,6 +339,10 @@ int wkb_gemm_status(void);
 int64_t wkb_q4_tiled_bytes(int64_t n, int64_t k);
 int wkb_q4_tile(const uint8_t* raw, int64_t n, int64_t k, void* tiled, void* stream);
 int64_t wkb_gemm_q4_0_workspace_bytes(int64_t n, int64_t k);
+/* out_mode 3 (m <= 64): no second pass -- the fp32 K-slice partials stay in the workspace as
+ * [slices][64][ld] (this call reports the layout) for a consumer that adds them in slice order while it does its
+ * own work: wkb_add_slices_rmsnorm_bf16, wkb_rope_qk_paged_append_slices.  `out` is ignored. */
+void wkb_gemm_q4_0_partial_layout(int64_t n, int64_t k, int64_t* slices, int64_t* slice_stride, int64_t* ld);
 int wkb_gemm_q4_0_bf16_nt(const void* w_tiled, const void* x_bf16, int64_t ldx, void* out, int64_t ldo, int out_mode,
                           int64_t m, int64_t n, int64_t k, void* workspace, int64_t workspace_bytes, void* stream);
 /* The same GEMM over OCP E4M3FN codes (one byte per element, the codec of crates/wukong_runtime/src/fp8.rs

@@ -104,3 +104,37 @@ def test_q4_gemm_llama_shapes(dev, orc):
     run_case(dev, orc, rng, 64, 6144, 4096, 0)
     run_case(dev, orc, rng, 64, 2 * 2752, 4096, 2)
     run_case(dev, orc, rng, 64, 4096, 2752, 0)
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 4096, 2752), (17, 512, 4096), (64, 256, 256)])
+def test_q4_gemm_partials_folded_into_add_rmsnorm(dev, orc, m, n, k):
+    """out_mode 3 leaves the K-slice partials in the workspace; adding them in slice order inside the
+    residual-add + RMSNorm kernel must give the residual stream and normed row of the two-kernel route."""
+    import ctypes
+    import torch
+    from wukong_b200._lib import lib, check
+    rng = np.random.default_rng(31 + m + n + k)
+    raw = synth_q4(rng, n, k)
+    w = dev.Q4Weight.from_raw(torch.from_numpy(raw).cuda(), n, k)
+    xb = orc.to_bf16_bits(rng.standard_normal((m, k)).astype(np.float32))
+    xt = torch.from_numpy(xb.view(np.int16).reshape(m, k)).cuda().view(torch.bfloat16)
+    ws = dev.gemm_q4_workspace(w.n, w.k)
+    full = dev.gemm_q4_0_bf16_nt(w, xt, mode=0, workspace=ws)
+    res = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).cuda()
+    gain = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+    s = torch.cuda.current_stream().cuda_stream
+    x_a, out_a = res.clone(), torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    check(lib().wkb_add_rmsnorm_bf16(x_a.data_ptr(), full.data_ptr(), gain.data_ptr(), out_a.data_ptr(), m, n, 1e-5, s), "add_rmsnorm")
+    a, b, c = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+    lib().wkb_gemm_q4_0_partial_layout(n, k, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+    assert a.value >= 1 and a.value * b.value * 4 <= ws.numel() and c.value >= n
+    dummy = torch.empty(1, device="cuda")
+    check(lib().wkb_gemm_q4_0_bf16_nt(w.tiled.data_ptr(), xt.data_ptr(), k, dummy.data_ptr(), n, 3, m, n, k, ws.data_ptr(), ws.numel(), s), "gemm mode 3")
+    x_b, out_b = res.clone(), torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    check(lib().wkb_add_slices_rmsnorm_bf16(x_b.data_ptr(), ws.data_ptr(), a.value, b.value, c.value, gain.data_ptr(), out_b.data_ptr(),
+                                            m, n, 1e-5, s), "add_slices_rmsnorm")
+    torch.cuda.synchronize()
+    assert dev.gemm_status() == 0
+    # the same slices are added in the same order; only the place of the residual in the sum differs
+    assert torch.allclose(x_a, x_b, rtol=0, atol=4e-6 * float(full.abs().max() + res.abs().max()))
+    assert (out_a.float() - out_b.float()).abs().max() <= 2.0 ** -7 * out_a.float().abs().max()

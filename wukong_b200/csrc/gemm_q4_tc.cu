@@ -169,6 +169,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 
 // Finish 32 activation rows (m0 .. m0+31) of weight row n held one per register.
 // MODE 0: f32 out[m, n]; 1: bf16 out[m, n]; 2: SwiGLU, bf16 out[m, n / 2] from (gate = even n, up = odd n).
+// (MODE 3 never finishes in the kernel: the K-slice partials are the result, left in the workspace for a consumer
+// that adds them up itself.)
 template <int MODE>
 __device__ __forceinline__ void finish32(const float (&v)[32], int m0, int M, int n, int N, void* out, i64 ldo) {
   const int mcount = min(32, M - m0);
@@ -344,7 +346,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
       if (!mbar_wait_parked(t_full(acc), (local >> 1) & 1)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TM);
-      if (plan.ksplit == 1) {
+      if (plan.ksplit == 1 && MODE != 3) {
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
           uint32_t rr[32];
@@ -494,22 +496,30 @@ int wkb_q4_tile(const uint8_t* raw, int64_t n, int64_t k, void* tiled, void* str
 int64_t wkb_gemm_q4_0_workspace_bytes(int64_t n, int64_t k) {
   if (n <= 0 || k <= 0) return 256;
   q4tc::Plan p = q4tc::make_plan(n, k, gemm_sm_count());
-  return p.ksplit > 1 ? (i64)p.ksplit * q4tc::TM * p.n_tiles * q4tc::TN * 4 : 256;
+  return (i64)p.ksplit * q4tc::TM * p.n_tiles * q4tc::TN * 4;   // one slice is the least: out_mode 3 always goes through it
+}
+
+void wkb_gemm_q4_0_partial_layout(int64_t n, int64_t k, int64_t* slices, int64_t* slice_stride, int64_t* ld) {
+  q4tc::Plan p = q4tc::make_plan(n, k, gemm_sm_count());
+  *slices = p.ksplit;
+  *ld = (i64)p.n_tiles * q4tc::TN;
+  *slice_stride = (i64)q4tc::TM * (*ld);
 }
 
 int wkb_gemm_q4_0_bf16_nt(const void* w_tiled, const void* x_bf16, int64_t ldx, void* out, int64_t ldo, int out_mode,
                           int64_t m, int64_t n, int64_t k, void* workspace, int64_t workspace_bytes, void* stream) {
   if (m <= 0 || n <= 0) return 0;
   if (k <= 0 || k % 32 != 0 || ldx % 8 != 0) return (int)cudaErrorInvalidValue;
-  if (out_mode < 0 || out_mode > 2 || (out_mode == 2 && (n & 1))) return (int)cudaErrorInvalidValue;
+  if (out_mode < 0 || out_mode > 3 || (out_mode == 2 && (n & 1)) || (out_mode == 3 && m > q4tc::TM)) return (int)cudaErrorInvalidValue;
   if ((((uintptr_t)w_tiled) | ((uintptr_t)x_bf16) | ((uintptr_t)workspace)) & 15) return (int)cudaErrorMisalignedAddress;
   if (!workspace || workspace_bytes < wkb_gemm_q4_0_workspace_bytes(n, k)) return (int)cudaErrorInvalidValue;
   int* status = gemm_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
   q4tc::Plan plan = q4tc::make_plan(n, k, gemm_sm_count());
   typedef void (*KernelFn)(const CUtensorMap, const uint8_t*, void*, i64, int, int, q4tc::Plan, float*, int*);
-  static const KernelFn table[3] = {q4tc::gemm_q4_tc_kernel<0>, q4tc::gemm_q4_tc_kernel<1>, q4tc::gemm_q4_tc_kernel<2>};
-  static bool attr_set[64][3] = {{false}};
+  static const KernelFn table[4] = {q4tc::gemm_q4_tc_kernel<0>, q4tc::gemm_q4_tc_kernel<1>, q4tc::gemm_q4_tc_kernel<2>,
+                                    q4tc::gemm_q4_tc_kernel<3>};
+  static bool attr_set[64][4] = {{false}};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev][out_mode]) {
@@ -530,7 +540,7 @@ int wkb_gemm_q4_0_bf16_nt(const void* w_tiled, const void* x_bf16, int64_t ldx, 
         mx, (const uint8_t*)w_tiled, o, ldo, (int)mc, (int)n, plan, ws, status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (plan.ksplit > 1) {
+    if (plan.ksplit > 1 && out_mode != 3) {
       const i64 total = mc * (n_pad >> 2);
       i64 grid = (total + 255) / 256;
       if (grid > gemm_sm_count() * 8) grid = gemm_sm_count() * 8;

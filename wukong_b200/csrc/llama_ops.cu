@@ -19,12 +19,13 @@ namespace wkb {
 template <int NV>
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                                            const float* __restrict__ gamma, u16* __restrict__ out,
-                                                           i64 rows, int cols, float eps) {
+                                                           i64 rows, int cols, float eps, int nsl, i64 slice_stride, i64 dld) {
   __shared__ float red[32];
   const int nvec = cols >> 2, nwarps = blockDim.x >> 5;
   for (i64 r = blockIdx.x; r < rows; r += gridDim.x) {
     float4* xr = reinterpret_cast<float4*>(x + r * (i64)cols);
-    const float4* dr = delta ? reinterpret_cast<const float4*>(delta + r * (i64)cols) : nullptr;
+    // delta: nsl planes of pitch dld, added in plane order (the K-slice partials of a split GEMM, or one plain matrix)
+    const float4* dr = delta ? reinterpret_cast<const float4*>(delta + r * dld) : nullptr;
     float4 v[NV];
     float q = 0.0f;
 #pragma unroll
@@ -33,7 +34,11 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
       if (i < nvec) {
         v[k] = xr[i];
         if (dr) {
-          const float4 d = dr[i];
+          float4 d = __ldcg(dr + i);
+          for (int sl = 1; sl < nsl; ++sl) {
+            const float4 e = __ldcg(reinterpret_cast<const float4*>(delta + sl * slice_stride + r * dld) + i);
+            d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+          }
           v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
         }
         q = fmaf(v[k].x, v[k].x, q); q = fmaf(v[k].y, v[k].y, q); q = fmaf(v[k].z, v[k].z, q); q = fmaf(v[k].w, v[k].w, q);
@@ -80,7 +85,8 @@ __global__ void __launch_bounds__(256) rope_qk_kernel(float* x, i64 row_stride, 
 // Query heads are rotated in place; key heads are rotated and rounded straight into their page; value heads are
 // rounded into theirs.  Same pairing, sin / cos and page addressing as rope_qk_kernel and paged_kv_append_kernel
 // (pages are bf16 [page][kv_head][token][dim]); a row with pos < 0 is inactive and touches nothing.
-__global__ void __launch_bounds__(256) rope_append_kernel(float* qkv, i64 row_stride, const float* __restrict__ inv_freq,
+__global__ void __launch_bounds__(256) rope_append_kernel(float* qkv, i64 row_stride, const float* __restrict__ src, int nsl,
+                                                          i64 slice_stride, i64 sld, const float* __restrict__ inv_freq,
                                                           const uint32_t* __restrict__ block_table, const int* __restrict__ row_slot,
                                                           const int* __restrict__ row_pos, u16* __restrict__ kcache,
                                                           u16* __restrict__ vcache, i64 rows, int hq, int hkv, int half,
@@ -95,7 +101,15 @@ __global__ void __launch_bounds__(256) rope_append_kernel(float* qkv, i64 row_st
     const int pos = row_pos[r];
     if (pos < 0) continue;
     float* p = qkv + r * row_stride + (i64)hh * hd;
-    float a = p[j], b = p[j + half];
+    float a, b;
+    if (src) {
+      // the projection's K-slice partials, added in slice order
+      const float* sp = src + r * sld + (i64)hh * hd;
+      a = __ldcg(sp + j); b = __ldcg(sp + j + half);
+      for (int sl = 1; sl < nsl; ++sl) { a += __ldcg(sp + sl * slice_stride + j); b += __ldcg(sp + sl * slice_stride + j + half); }
+    } else {
+      a = p[j]; b = p[j + half];
+    }
     if (hh < hq + hkv) {
       const float theta = fmul((float)pos, inv_freq[j]);
       const float c = sincos1(theta, true), s = sincos1(theta, false);
@@ -148,12 +162,11 @@ using namespace wkb;
 
 extern "C" {
 
-int wkb_add_rmsnorm_bf16(float* x, const float* delta_or_null, const float* gamma_or_null, void* out_bf16, i64 rows,
-                         i64 cols, float eps, void* stream) {
+static int launch_add_rmsnorm(float* x, const float* delta, int nsl, i64 slice_stride, i64 dld, const float* gamma, void* out_bf16, i64 rows,
+                              i64 cols, float eps, void* stream) {
   if (rows <= 0 || cols <= 0) return 0;
-  if (cols % 4 != 0) return (int)cudaErrorInvalidValue;
-  if ((((uintptr_t)x) | ((uintptr_t)delta_or_null) | ((uintptr_t)gamma_or_null) | ((uintptr_t)out_bf16)) & 15)
-    return (int)cudaErrorMisalignedAddress;
+  if (cols % 4 != 0 || dld % 4 != 0 || slice_stride % 4 != 0) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)gamma) | ((uintptr_t)out_bf16)) & 15) return (int)cudaErrorMisalignedAddress;
   const int grid = (int)(rows < (i64)WKB_SM_COUNT * 2 ? rows : (i64)WKB_SM_COUNT * 2);
   const i64 nvec = cols / 4;
   // as many threads as the row has float4 (up to 1024), then 2 or 4 or 8 vectors per thread
@@ -161,12 +174,25 @@ int wkb_add_rmsnorm_bf16(float* x, const float* delta_or_null, const float* gamm
   const i64 per = (nvec + threads - 1) / threads;
   cudaStream_t st = as_stream(stream);
   u16* o = (u16*)out_bf16;
-  if (per <= 1) add_rmsnorm_kernel<1><<<grid, threads, 0, st>>>(x, delta_or_null, gamma_or_null, o, rows, (int)cols, eps);
-  else if (per <= 2) add_rmsnorm_kernel<2><<<grid, threads, 0, st>>>(x, delta_or_null, gamma_or_null, o, rows, (int)cols, eps);
-  else if (per <= 4) add_rmsnorm_kernel<4><<<grid, threads, 0, st>>>(x, delta_or_null, gamma_or_null, o, rows, (int)cols, eps);
-  else if (per <= 8) add_rmsnorm_kernel<8><<<grid, threads, 0, st>>>(x, delta_or_null, gamma_or_null, o, rows, (int)cols, eps);
+#define WKB_ARN(NV_) add_rmsnorm_kernel<NV_><<<grid, threads, 0, st>>>(x, delta, gamma, o, rows, (int)cols, eps, nsl, slice_stride, dld)
+  if (per <= 1) WKB_ARN(1);
+  else if (per <= 2) WKB_ARN(2);
+  else if (per <= 4) WKB_ARN(4);
+  else if (per <= 8) WKB_ARN(8);
   else return (int)cudaErrorInvalidValue;   // rows wider than 32768 columns
+#undef WKB_ARN
   return (int)cudaGetLastError();
+}
+
+int wkb_add_rmsnorm_bf16(float* x, const float* delta_or_null, const float* gamma_or_null, void* out_bf16, i64 rows,
+                         i64 cols, float eps, void* stream) {
+  return launch_add_rmsnorm(x, delta_or_null, 1, 0, cols, gamma_or_null, out_bf16, rows, cols, eps, stream);
+}
+
+int wkb_add_slices_rmsnorm_bf16(float* x, const float* slices, i64 nslices, i64 slice_stride, i64 ld, const float* gamma_or_null,
+                                void* out_bf16, i64 rows, i64 cols, float eps, void* stream) {
+  if (nslices < 1 || !slices) return (int)cudaErrorInvalidValue;
+  return launch_add_rmsnorm(x, slices, (int)nslices, slice_stride, ld, gamma_or_null, out_bf16, rows, cols, eps, stream);
 }
 
 int wkb_rope_qk_f32(float* x, i64 row_stride, const float* inv_freq, const int* pos, i64 rows, i64 heads, i64 half,
@@ -189,9 +215,26 @@ int wkb_rope_qk_paged_append(float* qkv, i64 row_stride, const float* inv_freq, 
   const i64 total = rows * (q_heads + 2 * kv_heads) * half;
   i64 grid = (total + 255) / 256;
   if (grid > (i64)WKB_SM_COUNT * 16) grid = (i64)WKB_SM_COUNT * 16;
-  rope_append_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(qkv, row_stride, inv_freq, block_table, row_slot, row_pos, (u16*)kcache,
-                                                               (u16*)vcache, rows, (int)q_heads, (int)kv_heads, (int)half,
+  rope_append_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(qkv, row_stride, nullptr, 0, 0, 0, inv_freq, block_table, row_slot, row_pos,
+                                                               (u16*)kcache, (u16*)vcache, rows, (int)q_heads, (int)kv_heads, (int)half,
                                                                (int)page_tokens, (int)max_blocks_per_seq);
+  return (int)cudaGetLastError();
+}
+
+int wkb_rope_qk_paged_append_slices(float* q_out, i64 row_stride, const float* slices, i64 nslices, i64 slice_stride, i64 ld,
+                                    const float* inv_freq, const uint32_t* block_table, const int* row_slot, const int* row_pos,
+                                    void* kcache, void* vcache, i64 rows, i64 q_heads, i64 kv_heads, i64 half, i64 page_tokens,
+                                    i64 max_blocks_per_seq, void* stream) {
+  if (rows <= 0) return 0;
+  if (!slices || nslices < 1 || q_heads < 0 || kv_heads <= 0 || half <= 0 || page_tokens <= 0 || row_stride < q_heads * 2 * half ||
+      ld < (q_heads + 2 * kv_heads) * 2 * half)
+    return (int)cudaErrorInvalidValue;
+  const i64 total = rows * (q_heads + 2 * kv_heads) * half;
+  i64 grid = (total + 255) / 256;
+  if (grid > (i64)WKB_SM_COUNT * 16) grid = (i64)WKB_SM_COUNT * 16;
+  rope_append_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(q_out, row_stride, slices, (int)nslices, slice_stride, ld, inv_freq, block_table,
+                                                               row_slot, row_pos, (u16*)kcache, (u16*)vcache, rows, (int)q_heads,
+                                                               (int)kv_heads, (int)half, (int)page_tokens, (int)max_blocks_per_seq);
   return (int)cudaGetLastError();
 }
 

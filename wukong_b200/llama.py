@@ -245,6 +245,14 @@ class LlamaDecodeModel:
         self.scratch = dev.paged_attn_scratch(R, self.hq, hd, self.max_ctx, device)
         self.scale = 1.0 / math.sqrt(hd)
         self.launches_per_forward = 0
+        # one rank, at most 64 rows: the split-K second passes are folded into the kernels that consume the results
+        self.fold_slices = world == 1 and reduce is None and peer is None and bcap <= 64
+
+    def _partial_layout(self, w):
+        import ctypes
+        a, b, c = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+        lib().wkb_gemm_q4_0_partial_layout(w.n, w.k, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
+        return int(a.value), int(b.value), int(c.value)
 
     def _gemm(self, w, x, ldx, out, ldo, mode, n, what):
         p = lambda t: t.data_ptr()
@@ -261,36 +269,53 @@ class LlamaDecodeModel:
     def attn_part(self, li, n):
         L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
         cfg, lw, hd = self.cfg, self.w.layers[li], self.cfg.head_dim
-        self._gemm(lw["wqkv"], self.xn, cfg.d_model, self.qkv, self.qkv_w, 0, n, "qkv")
-        check(L.wkb_rope_qk_paged_append(p(self.qkv), self.qkv_w, p(self.inv_freq), p(self.block_table), p(self.row_slot), p(self.row_pos),
-                                         p(self.kv.k[li]), p(self.kv.v[li]), n, self.hq, self.hkv, hd // 2, self.page_tokens, self.mbps, s),
-              "rope_append")
+        if self.fold_slices:
+            nsl, sst, sld = self._partial_layout(lw["wqkv"])
+            self._gemm(lw["wqkv"], self.xn, cfg.d_model, self.qkv, self.qkv_w, 3, n, "qkv")
+            check(L.wkb_rope_qk_paged_append_slices(p(self.qkv), self.qkv_w, p(self.workspace), nsl, sst, sld, p(self.inv_freq),
+                                                    p(self.block_table), p(self.row_slot), p(self.row_pos), p(self.kv.k[li]), p(self.kv.v[li]),
+                                                    n, self.hq, self.hkv, hd // 2, self.page_tokens, self.mbps, s), "rope_append")
+        else:
+            self._gemm(lw["wqkv"], self.xn, cfg.d_model, self.qkv, self.qkv_w, 0, n, "qkv")
+            check(L.wkb_rope_qk_paged_append(p(self.qkv), self.qkv_w, p(self.inv_freq), p(self.block_table), p(self.row_slot), p(self.row_pos),
+                                             p(self.kv.k[li]), p(self.kv.v[li]), n, self.hq, self.hkv, hd // 2, self.page_tokens, self.mbps, s),
+                  "rope_append")
         check(L.wkb_paged_attn_decode(p(self.qkv), self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
                                       p(self.row_ctx), p(self.att), 1, self.hq * hd, n, self.hq, self.hkv, hd, self.page_tokens, self.mbps,
                                       self.max_ctx, self.scale, p(self.scratch), s), "attention")
-        self._gemm(lw["wo"], self.att, self.hq * hd, self.part_attn, cfg.d_model, 0, n, "o_proj")
+        self._gemm(lw["wo"], self.att, self.hq * hd, self.part_attn, cfg.d_model, 3 if self.fold_slices else 0, n, "o_proj")
 
     def _peer_reduce(self, which, phase, gain, n, what):
         pr, s, p = self.peer, torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
         check(lib().wkb_tp_reduce_add_rmsnorm(pr.part_ptrs[which], pr.flag_ptrs, self.rank, self.world, p(pr.step), phase,
                                               2 * self.cfg.n_layer, p(self.x), p(gain), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), what)
 
+    def _add_slices_norm(self, w, gain, n, what):
+        nsl, sst, sld = self._partial_layout(w)
+        p = lambda t: t.data_ptr()
+        check(lib().wkb_add_slices_rmsnorm_bf16(p(self.x), p(self.workspace), nsl, sst, sld, p(gain), p(self.xn), n, self.cfg.d_model,
+                                                self.cfg.eps, torch.cuda.current_stream().cuda_stream), what)
+
     def after_attn(self, li, n):
         L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
         if self.peer is not None:
             return self._peer_reduce(0, 2 * li, self.w.layers[li]["norm2"], n, "reduce_norm2")
+        if self.fold_slices:
+            return self._add_slices_norm(self.w.layers[li]["wo"], self.w.layers[li]["norm2"], n, "norm2")
         check(L.wkb_add_rmsnorm_bf16(p(self.x), p(self.part), p(self.w.layers[li]["norm2"]), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), "norm2")
 
     def mlp_part(self, li, n):
         lw = self.w.layers[li]
         self._gemm(lw["wgu"], self.xn, self.cfg.d_model, self.h, self.f, 2, n, "gate_up")
-        self._gemm(lw["wdown"], self.h, self.f, self.part_mlp, self.cfg.d_model, 0, n, "down")
+        self._gemm(lw["wdown"], self.h, self.f, self.part_mlp, self.cfg.d_model, 3 if self.fold_slices else 0, n, "down")
 
     def after_mlp(self, li, n):
         L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
         gain = self.w.layers[li + 1]["norm1"] if li + 1 < self.cfg.n_layer else self.w.norm_f
         if self.peer is not None:
             return self._peer_reduce(1, 2 * li + 1, gain, n, "reduce_norm_next")
+        if self.fold_slices:
+            return self._add_slices_norm(self.w.layers[li]["wdown"], gain, n, "norm_next")
         check(L.wkb_add_rmsnorm_bf16(p(self.x), p(self.part), p(gain), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), "norm_next")
 
     def head_local(self, n):
