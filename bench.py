@@ -372,7 +372,7 @@ def run_ours(args):
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            tok_s, dt, desc = cpu_decode_tok_s(weights, cfg, 24, 1, 8, threads)
+            tok_s, dt, desc = cpu_decode_tok_s(weights, cfg, 64, 1, 16, threads)      # about 10-15 s of host work
             cpu = {"value": tok_s, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc, "seconds": dt}
         line = {
             "metric": METRIC, "value": world * S * K / (dev_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
