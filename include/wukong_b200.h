@@ -357,6 +357,35 @@ int64_t wkb_gemm_argmax_tiles(int64_t n);
 int wkb_gemm_bf16_nt_argmax(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k,
                             const float* bias, float* part_val, int* part_idx, int* out, void* stream);
 
+/* ---- checkpoint containers (GGUF versions 2 and 3, safetensors) ----------------------------------------------
+ * Host readers with the names, arguments, check order and codes of the reference runtime entries
+ * (crates/wukong_runtime/src/gguf.rs:809-851 read, :902-918 query, :1026-1062 metadata, :1086-1110 strings;
+ * crates/wukong_runtime/src/safetensors.rs:379-407).  dtype codes: 0 f32, 1 f64, 2 f16, 3 bf16, 4 i8, 5 i16,
+ * 6 i32, 7 i64, 8 u8, 9 u16, 10 u32, 11 u64 (crates/wukong_runtime/src/fileio.rs:45-67).  A read returns the
+ * element count, or -1 (open), -2 (I/O), -3 (dtype), -4 (shape or count), -5 (no such name), -6 (malformed
+ * header), -7 (a ggml type with no decoder); rank < 0 means a flat destination, else dims[0..rank) is its shape,
+ * outermost first.  A block-quantized GGUF tensor dequantizes into f32 (Q4_0 Q4_1 Q5_0 Q5_1 Q8_0, the K-quants
+ * Q2_K..Q6_K and Q8_K, IQ4_NL / IQ4_XS; ggml's reference arithmetic) or loads its raw block bytes into u8;
+ * F16 / BF16 widen exactly into f32. */
+int64_t wukong_rt_gguf_read(const char* path, const char* name, void* data, int64_t len, int64_t dtype, const int64_t* dims,
+                            int64_t rank);
+/* what: 0 find (index in the tensor table), 1 rank, 2 dim k (outermost first), 3 ggml type id. */
+int64_t wukong_rt_gguf_query(const char* path, const char* name, int64_t what, int64_t k);
+/* what: 0 value type id (9 for an array), 1 length (string bytes / array items / 1), 2 value i as i64 or dflt. */
+int64_t wukong_rt_gguf_meta(const char* path, const char* key, int64_t what, int64_t i, int64_t dflt);
+double wukong_rt_gguf_meta_f64(const char* path, const char* key, int64_t i, double dflt);
+int64_t wukong_rt_gguf_meta_str(const char* path, const char* key, int64_t i, char* buf, int64_t len);
+int64_t wukong_rt_st_read(const char* path, const char* name, void* data, int64_t len, int64_t dtype, const int64_t* dims,
+                          int64_t rank);
+/* The same reads with a DEVICE destination: the payload crosses PCIe as the file's own bytes (pinned double
+ * buffer) and is dequantized or widened by a kernel on `stream`; values are bit-identical to the host readers'. */
+int64_t wkb_gguf_read_device(const char* path, const char* name, void* dev_data, int64_t len, int64_t dtype, const int64_t* dims,
+                             int64_t rank, void* stream);
+int64_t wkb_st_read_device(const char* path, const char* name, void* dev_data, int64_t len, int64_t dtype, const int64_t* dims,
+                           int64_t rank, void* stream);
+/* Dequantize `blocks` device-resident blocks of a ggml type into f32 (the kernel the device reads use). */
+int wkb_ggml_dequant_f32(int64_t ggml_type_id, const void* raw_dev, int64_t blocks, float* out_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -50,6 +50,8 @@ def _types_from_header(header=_HEADER):
                 return i64
             if base[0] == "float":
                 return f32
+            if base[0] == "double":
+                return C.c_double
             if base[0] == "int":
                 return ci
             raise WukongB200Error("unparsed parameter %r of %s" % (decl, name))

@@ -46,6 +46,21 @@ class LlamaConfig:
         return self.n_layer * (2 * d * self.n_head * hd + 2 * d * self.n_kv_head * hd + 3 * d * self.d_ff)
 
 
+def llama_config_from_gguf(path):
+    """The block-stack shape from a GGUF file's `llama.*` metadata and its embedding table."""
+    from . import model_io as io
+    need = lambda key: io.gguf_meta_i64(path, key, 0, -1)
+    n_layer, d, heads, ff = (need("llama." + k) for k in ("block_count", "embedding_length", "attention.head_count", "feed_forward_length"))
+    if min(n_layer, d, heads, ff) <= 0:
+        raise io.ModelIOError(-5, "llama.* metadata of %r" % path)
+    kv = io.gguf_meta_i64(path, "llama.attention.head_count_kv", 0, heads)
+    vocab = io.gguf_dim(path, "token_embd.weight", 0)
+    if vocab < 0:
+        raise io.ModelIOError(vocab, "token_embd.weight")
+    return LlamaConfig(n_layer, d, heads, kv, ff, vocab, io.gguf_meta_f64(path, "llama.rope.freq_base", 0, 10000.0),
+                       io.gguf_meta_f64(path, "llama.attention.layer_norm_rms_epsilon", 0, 1e-5))
+
+
 def synth_q4_raw(rng, n, k, sigma=0.02):
     """Raw Q4_0 rows [n, k/32, 18]: uniform nibbles, f16 scale |N(0, sigma)|."""
     nb = k // 32
@@ -152,6 +167,53 @@ class LlamaRankWeights:
             out.layers.append(dict(norm1=torch.ones(d, device=device), norm2=torch.ones(d, device=device),
                                    wqkv=make(qkv_q, qkv_s), wo=make(cols(o_q, nq // 32), cols(o_s, nq // 32)),
                                    wgu=make(gu_q, gu_s), wdown=make(cols(d_q, F // 32), cols(d_s, F // 32))))
+        return out
+
+    @staticmethod
+    def from_gguf(path, cfg=None, rank=0, world=1, device="cuda", unpermute_qk=False):
+        """One rank's weights from a GGUF checkpoint with llama.cpp's tensor names (`token_embd.weight`,
+        `blk.N.attn_q.weight` ... `output.weight`).  The linears must be Q4_0: their block rows cross PCIe raw and
+        are sliced for this rank and re-tiled on the device; the embedding and the norm gains may be any type the
+        reader turns into f32 (dequantized on the GPU).  RoPE here pairs element i with i + head_dim/2; a file whose
+        converter re-ordered the Q / K rows for adjacent pairs is restored with `unpermute_qk`."""
+        from . import model_io as io
+        cfg = cfg or llama_config_from_gguf(path)
+        cfg.check_world(world)
+        d, hd, F = cfg.d_model, cfg.head_dim, cfg.d_ff
+
+        def f32(name, shape):
+            return io.gguf_read_device(path, name, torch.empty(shape, dtype=torch.float32, device=device))
+
+        def raw(name, n, k):
+            if io.gguf_type(path, name) != 2:
+                raise io.ModelIOError(-3, "gguf tensor %r must be Q4_0 for the W4A16 GEMM" % name)
+            t = torch.empty((n, k // 32 * 18), dtype=torch.uint8, device=device)
+            return io.gguf_read_device(path, name, t).view(n, k // 32, 18)
+
+        def unpermute(t, heads):
+            if not unpermute_qk:
+                return t
+            n, nb, _ = t.shape
+            return t.view(heads, hd // 2, 2, nb, 18).transpose(1, 2).reshape(n, nb, 18)
+
+        rows = lambda t: t[rank * (t.shape[0] // world):(rank + 1) * (t.shape[0] // world)]
+        cols = lambda t: t[:, rank * (t.shape[1] // world):(rank + 1) * (t.shape[1] // world)]
+        q4 = lambda t: dev.Q4Weight.from_raw(t.contiguous().view(-1), t.shape[0], t.shape[1] * 32)
+        out = LlamaRankWeights()
+        out.embed, out.norm_f = f32("token_embd.weight", (cfg.vocab, d)), f32("output_norm.weight", (d,))
+        head = "output.weight" if io.gguf_find(path, "output.weight") >= 0 else "token_embd.weight"     # tied embeddings
+        out.lm_head = q4(rows(raw(head, cfg.vocab, d)))
+        for i in range(cfg.n_layer):
+            b = "blk.%d." % i
+            wq = unpermute(raw(b + "attn_q.weight", cfg.n_head * hd, d), cfg.n_head)
+            wk = unpermute(raw(b + "attn_k.weight", cfg.n_kv_head * hd, d), cfg.n_kv_head)
+            wv = raw(b + "attn_v.weight", cfg.n_kv_head * hd, d)
+            gate, up = rows(raw(b + "ffn_gate.weight", F, d)), rows(raw(b + "ffn_up.weight", F, d))
+            out.layers.append(dict(norm1=f32(b + "attn_norm.weight", (d,)), norm2=f32(b + "ffn_norm.weight", (d,)),
+                                   wqkv=q4(torch.cat([rows(wq), rows(wk), rows(wv)])),
+                                   wo=q4(cols(raw(b + "attn_output.weight", d, cfg.n_head * hd))),
+                                   wgu=q4(torch.stack([gate, up], dim=1).reshape(-1, d // 32, 18)),
+                                   wdown=q4(cols(raw(b + "ffn_down.weight", d, F)))))
         return out
 
     def q4_bytes(self):
