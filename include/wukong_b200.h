@@ -275,6 +275,18 @@ int wkb_paged_attn_decode(const float* q, int64_t q_row_stride, const void* kcac
                           int out_dtype, int64_t out_row_stride, int64_t rows, int64_t q_heads, int64_t kv_heads,
                           int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq, int64_t max_ctx,
                           float scale, float* scratch, void* stream);
+/* Prefill / chunked prefill against the same cache (causal, GQA; the reference's counterpart is the flash prefill of
+ * crates/wukong_codegen_gpu/src/ptx_flash.rs under the chunked scheduler of serving.rs:1346-1595).  `tiles` is a
+ * DEVICE array of n_tiles (first row, row count) int32 pairs; the rows of a tile are consecutive query tokens of ONE
+ * sequence, at most wkb_paged_attn_prefill_tile_rows(q_heads, kv_heads) = 16 / (q_heads / kv_heads) of them.  Row r
+ * sees its sequence's first row_ctx[r] keys (0: the row is not written).  Keys are streamed once per tile instead of
+ * once per row.  head_dim in {64, 128}; q_heads / kv_heads in {1, 2, 4, 8}; out_dtype 0 f32, 1 bf16. */
+int64_t wkb_paged_attn_prefill_tile_rows(int64_t q_heads, int64_t kv_heads);
+int wkb_paged_attn_prefill(const float* q, int64_t q_row_stride, const void* kcache, const void* vcache,
+                           const uint32_t* block_table, const int* row_slot, const int* row_ctx, const int* tiles,
+                           int64_t n_tiles, void* out, int out_dtype, int64_t out_row_stride, int64_t q_heads,
+                           int64_t kv_heads, int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq, float scale,
+                           void* stream);
 int wkb_paged_kv_append(const float* ksrc, const float* vsrc, int64_t src_row_stride, void* kcache, void* vcache,
                         const uint32_t* block_table, const int* row_slot, const int* row_pos, int64_t rows,
                         int64_t kv_heads, int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq,

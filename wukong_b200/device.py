@@ -190,3 +190,31 @@ def paged_attn_decode(q, q_row_stride, kv, layer, block_table, row_slot, row_ctx
                                       kv.kv_heads, kv.head_dim, kv.page_tokens, mbps, max_ctx, scale, _p(scratch), _s()),
           "wkb_paged_attn_decode")
     return out
+
+
+def prefill_tiles(row_slot, tile_rows, min_run=1):
+    """Host helper: cut the runs of equal slot in `row_slot` (numpy int32, rows laid out sequence by sequence) into
+    tiles of at most `tile_rows` rows -> int32 [n_tiles, 2] of (first row, row count).  Runs shorter than `min_run`
+    rows are left out (the caller sends those rows through the decode kernel)."""
+    import numpy as np
+    rs = np.asarray(row_slot)
+    n = rs.shape[0]
+    if n == 0:
+        return np.zeros((0, 2), np.int32)
+    starts = np.flatnonzero(np.concatenate([[True], rs[1:] != rs[:-1]]))
+    ends = np.concatenate([starts[1:], [n]])
+    out = []
+    for a, b in zip(starts.tolist(), ends.tolist()):
+        if b - a < min_run:
+            continue
+        out.extend((r, min(tile_rows, b - r)) for r in range(a, b, tile_rows))
+    return np.asarray(out, np.int32).reshape(-1, 2)
+
+
+def paged_attn_prefill(q, q_row_stride, kv, layer, block_table, row_slot, row_ctx, tiles, out, q_heads, mbps, scale):
+    """Causal attention of prompt-chunk rows against the paged cache; `tiles` is a device int32 [n_tiles, 2]."""
+    check(lib().wkb_paged_attn_prefill(_p(q), q_row_stride, _p(kv.k[layer]), _p(kv.v[layer]), _p(block_table), _p(row_slot),
+                                       _p(row_ctx), _p(tiles), tiles.shape[0], _p(out), int(out.dtype == torch.bfloat16),
+                                       out.stride(0), q_heads, kv.kv_heads, kv.head_dim, kv.page_tokens, mbps, scale, _s()),
+          "wkb_paged_attn_prefill")
+    return out

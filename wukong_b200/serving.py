@@ -86,6 +86,10 @@ class DecodeModel:
         self.row_token, self.row_pos = torch.zeros(R, **i32), torch.full((R,), -1, **i32)
         self.row_slot, self.row_ctx = torch.zeros(R, **i32), torch.zeros(R, **i32)
         self.sample_rows = torch.zeros(R, **i32)
+        # prompt chunks: rows of runs of one sequence go through the tiled prefill kernel (keys streamed once per
+        # tile); row_ctx_dec is row_ctx with those rows zeroed, for the row-per-token kernel that takes the rest
+        self.row_ctx_dec, self.tiles = torch.zeros(R, **i32), torch.zeros(2 * R, **i32)
+        self.tile_rows = int(lib().wkb_paged_attn_prefill_tile_rows(cfg.n_head, cfg.n_head))
         self.block_table = torch.zeros((bcap, max_blocks_per_seq), **i32)
         self.x = torch.zeros((R, d), dtype=torch.float32, device=device)
         self.h = torch.zeros((R, d), dtype=torch.bfloat16, device=device)
@@ -106,8 +110,9 @@ class DecodeModel:
         self.launches_per_forward = 0
 
     # -- one forward over the first n rows; n_sample rows (indices in sample_rows) reach the LM head
-    def forward(self, n, n_sample):
+    def forward(self, n, n_sample, n_tiles=0):
         cfg, L, s = self.cfg, lib(), torch.cuda.current_stream().cuda_stream
+        ctx_dec = self.row_ctx_dec if n_tiles else self.row_ctx
         d, f, p = cfg.d_model, cfg.d_ff, (lambda t: t.data_ptr())
         launches = 0
         check(L.wkb_embed_tok_pos_bf16(p(self.x), p(self.w["wte"]), p(self.w["wpe"]), p(self.row_token), p(self.row_pos), n, d,
@@ -120,8 +125,12 @@ class DecodeModel:
                                         p(self.block_table), p(self.row_slot), p(self.row_pos), n, cfg.n_head, cfg.head_dim,
                                         self.page_tokens, self.mbps, s), "kv_append")
             check(L.wkb_paged_attn_decode(p(self.qkv), 3 * d, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
-                                          p(self.row_ctx), p(self.att), 1, d, n, cfg.n_head, cfg.n_head, cfg.head_dim, self.page_tokens,
+                                          p(ctx_dec), p(self.att), 1, d, n, cfg.n_head, cfg.n_head, cfg.head_dim, self.page_tokens,
                                           self.mbps, self.max_ctx, self.scale, p(self.scratch), s), "attn")
+            if n_tiles:
+                check(L.wkb_paged_attn_prefill(p(self.qkv), 3 * d, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
+                                               p(self.row_ctx), p(self.tiles), n_tiles, p(self.att), 1, d, cfg.n_head, cfg.n_head,
+                                               cfg.head_dim, self.page_tokens, self.mbps, self.scale, s), "attn_prefill")
             check(L.wkb_gemm_bf16_nt(p(self.att), d, p(lw["w_o"]), d, p(self.x), d, 0, n, d, d, p(lw["b_o"]), 0, p(self.x), d, s), "o_proj")
             check(L.wkb_norm_fast(p(self.x), 0, p(self.h), 1, p(lw["ln2_g"]), p(lw["ln2_b"]), n, d, cfg.eps, 1, s), "ln2")
             check(L.wkb_gemm_bf16_nt(p(self.h), d, p(lw["w_fc"]), d, p(self.ff), f, 1, n, f, d, p(lw["b_fc"]), 2, None, 0, s), "fc")
@@ -140,7 +149,7 @@ class DecodeModel:
         # split-K finishing pass
         tiles = lambda m, nn: ((m + 127) // 128) * ((nn + 127) // 128)
         split = 1 if (2 * tiles(n, d) <= 148 and f >= 2048) else 0
-        self.launches_per_forward = launches + len(self.layers) * (1 + split) + 4
+        self.launches_per_forward = launches + len(self.layers) * (1 + split + (1 if n_tiles else 0)) + 4
         return self.next_tok
 
 
@@ -155,11 +164,13 @@ class Engine:
         self.sched = Scheduler(bcap, num_pages, page_tokens, max_blocks_per_seq, self.model.max_rows, prefill_chunk)
         R = self.model.max_rows
         pin = lambda n, dt=torch.int32: torch.zeros(n, dtype=dt).pin_memory()
-        # one pinned staging block: token | pos | slot | ctx | sample_rows
-        self.h_rows = pin(5 * R)
-        self.d_rows = torch.zeros(5 * R, dtype=torch.int32, device=device)
+        # one pinned staging block: token | pos | slot | ctx | sample_rows | ctx of the row-per-token kernel | prefill tiles
+        self.h_rows = pin(8 * R)
+        self.d_rows = torch.zeros(8 * R, dtype=torch.int32, device=device)
         m = self.model
-        m.row_token, m.row_pos, m.row_slot, m.row_ctx, m.sample_rows = (self.d_rows[i * R:(i + 1) * R] for i in range(5))
+        m.row_token, m.row_pos, m.row_slot, m.row_ctx, m.sample_rows, m.row_ctx_dec = (self.d_rows[i * R:(i + 1) * R] for i in range(6))
+        m.tiles = self.d_rows[6 * R:8 * R]
+        self.use_prefill_kernel = True
         self.h_table = pin(bcap * max_blocks_per_seq)
         self.h_next = pin(bcap)
         self.uploaded_epoch = -1
@@ -191,6 +202,16 @@ class Engine:
             hr[4 * R:4 * R + self.bcap] = np.arange(self.bcap)   # graph path: the head runs on every decode row
         else:
             hr[4 * R:4 * R + sampled_slots.size] = s.sample_row[sampled_slots]
+        n_tiles = 0
+        if not decode_only and self.use_prefill_kernel and m.tile_rows:
+            tiles = dev.prefill_tiles(s.row_slot[:n], m.tile_rows, min_run=2)
+            n_tiles = tiles.shape[0]
+            if n_tiles:
+                ctx_dec = s.row_ctx[:n].copy()
+                for r0, cnt in tiles:
+                    ctx_dec[r0:r0 + cnt] = 0
+                hr[5 * R:5 * R + n] = ctx_dec; hr[5 * R + n:6 * R] = 0
+                hr[6 * R:6 * R + 2 * n_tiles] = tiles.reshape(-1)
         with torch.cuda.stream(self.stream):
             self.d_rows.copy_(self.h_rows, non_blocking=True)
             self.h2d_bytes += self.h_rows.numel() * 4
@@ -215,7 +236,7 @@ class Engine:
                 m.forward(self.bcap, self.bcap)
                 nrows_head = self.bcap
             else:
-                m.forward(n, max(1, sampled_slots.size))
+                m.forward(n, max(1, sampled_slots.size), n_tiles)
                 nrows_head = sampled_slots.size
             self.kernel_launches += m.launches_per_forward
             self.h_next.copy_(m.next_tok, non_blocking=True)
