@@ -172,6 +172,42 @@ def case_paged_attn(hbm, tf, src):
             "note": "555 MB of KV per launch exceeds L2", "peak_source": "of " + src}
 
 
+def case_paged_prefill(H, HKV, D, seqs, hist, chunk, hbm, tf, src):
+    """Prompt chunks of `chunk` tokens on top of `hist` cached tokens, `seqs` sequences: the tiled kernel, with the
+    row-per-token kernel it replaces timed beside it.  Rated against the tensor peak (useful flops: QK^T and PV over
+    the causal triangle, 4 * head_dim per (query, visible key, head)) and by the key bytes it streams."""
+    rng = np.random.default_rng(0)
+    page = 16
+    total = hist + chunk
+    mbps = (total + page - 1) // page
+    pool = seqs * mbps
+    table = rng.permutation(pool).astype(np.uint32).reshape(seqs, mbps)
+    kv = dev.PagedKV(1, pool, HKV, D, page)
+    kv.k.normal_()
+    kv.v.normal_()
+    rows = seqs * chunk
+    q = torch.randn(rows, H * D, device="cuda")
+    bt = torch.from_numpy(table.view(np.int32)).cuda()
+    rs = np.repeat(np.arange(seqs, dtype=np.int32), chunk)
+    rc = np.tile(np.arange(hist + 1, total + 1, dtype=np.int32), seqs)
+    tile_rows = 16 // (H // HKV)
+    tiles = dev.prefill_tiles(rs, tile_rows)
+    row_slot, row_ctx, d_tiles = torch.from_numpy(rs).cuda(), torch.from_numpy(rc).cuda(), torch.from_numpy(tiles).cuda()
+    out = torch.empty(rows, H * D, dtype=torch.bfloat16, device="cuda")
+    scale = 1.0 / math.sqrt(D)
+    us = time_graph(lambda i: dev.paged_attn_prefill(q, H * D, kv, 0, bt, row_slot, row_ctx, d_tiles, out, H, mbps, scale), 10)
+    scratch = dev.paged_attn_scratch(rows, H, D, total)
+    us_rows = time_graph(lambda i: dev.paged_attn_decode(q, H * D, kv, 0, bt, row_slot, row_ctx, out, rows, H, mbps, total, scale, scratch), 5)
+    pairs = float(rc.sum())                                   # (query, visible key) pairs per head
+    flops = pairs * H * 4 * D
+    key_bytes = float(sum(int(rc[r0:r0 + n].max()) for r0, n in tiles)) * HKV * 2 * D * 2
+    return {"case": "paged_attn_prefill", "shape": {"q_heads": H, "kv_heads": HKV, "d": D, "sequences": seqs, "cached": hist, "chunk": chunk},
+            "us": us, "achieved": flops / us / 1e6, "unit": "TFLOP/s", "bound": "tensor", "peak": tf, "frac": flops / us / 1e6 / tf,
+            "useful_flops": flops, "key_bytes_streamed": key_bytes, "key_stream_gbs": key_bytes / us / 1e3, "prompt_tok_per_s": rows / us * 1e6,
+            "row_per_token_us": us_rows, "speedup_vs_row_per_token": us_rows / us,
+            "note": "mma.sync (legacy tensor path) with q as bf16 hi + lo: 1.5x the useful flops are issued", "peak_source": "of " + src}
+
+
 def run(out=sys.stdout, only=None, reps_scale=1.0):
     """Run the suite (or the cases whose name contains `only`) and print one JSON line per case."""
     require_gpu()
@@ -187,6 +223,8 @@ def run(out=sys.stdout, only=None, reps_scale=1.0):
     for op, name in ((2, "rmsnorm_bf16"), (0, "softmax_bf16"), (1, "layernorm_bf16")):
         plan.append((name, lambda op=op: case_norm(op, hbm, tf, src)))
     plan.append(("paged_attn_decode", lambda: case_paged_attn(hbm, tf, src)))
+    for (H, HKV, D, seqs, hist, chunk) in ((12, 12, 64, 64, 0, 512), (32, 8, 128, 16, 0, 512), (32, 8, 128, 16, 2048, 256)):
+        plan.append(("paged_attn_prefill", lambda a=(H, HKV, D, seqs, hist, chunk): case_paged_prefill(*a, hbm, tf, src)))
     results = []
     for name, fn in plan:
         if only and only not in name:
