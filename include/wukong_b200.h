@@ -275,6 +275,19 @@ int wkb_paged_attn_decode(const float* q, int64_t q_row_stride, const void* kcac
                           int out_dtype, int64_t out_row_stride, int64_t rows, int64_t q_heads, int64_t kv_heads,
                           int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq, int64_t max_ctx,
                           float scale, float* scratch, void* stream);
+/* int8 KV cache (the reference's lossy storage option: crates/wukong_codegen_gpu/src/paged_attention.rs:1305-1326,
+ * paged_kv.rs:153-178): per (token, KV head) scale = max|x| / 127 (1 for an all-zero row), value = round(x / scale)
+ * half away from zero, clamped to +-127 -- bytes and scales identical to the reference's quantizer.  Slabs per layer:
+ * int8 [num_pages][kv_heads][page_tokens][head_dim], f32 scales [num_pages][kv_heads][page_tokens].  The decode call
+ * has the contract of wkb_paged_attn_decode (same scratch); head_dim in {64, 128}; q_heads / kv_heads in {1, 2, 4}. */
+int wkb_paged_kv_append_int8(const float* ksrc, const float* vsrc, int64_t src_row_stride, void* kq, void* vq, float* kscale,
+                             float* vscale, const uint32_t* block_table, const int* row_slot, const int* row_pos, int64_t rows,
+                             int64_t kv_heads, int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq, void* stream);
+int wkb_paged_attn_decode_int8(const float* q, int64_t q_row_stride, const void* kq, const void* vq, const float* kscale,
+                               const float* vscale, const uint32_t* block_table, const int* row_slot, const int* row_ctx,
+                               void* out, int out_dtype, int64_t out_row_stride, int64_t rows, int64_t q_heads, int64_t kv_heads,
+                               int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq, int64_t max_ctx, float scale,
+                               float* scratch, void* stream);
 /* Prefill / chunked prefill against the same cache (causal, GQA; the reference's counterpart is the flash prefill of
  * crates/wukong_codegen_gpu/src/ptx_flash.rs under the chunked scheduler of serving.rs:1346-1595).  `tiles` is a
  * DEVICE array of n_tiles (first row, row count) int32 pairs; the rows of a tile are consecutive query tokens of ONE

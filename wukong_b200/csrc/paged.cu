@@ -565,3 +565,5 @@ int wkb_paged_kv_append(const float* ksrc, const float* vsrc, i64 src_row_stride
   return (int)cudaGetLastError();
 }
 }
+
+#include "paged_int8.cuh"

@@ -218,3 +218,30 @@ def paged_attn_prefill(q, q_row_stride, kv, layer, block_table, row_slot, row_ct
                                        out.stride(0), q_heads, kv.kv_heads, kv.head_dim, kv.page_tokens, mbps, scale, _s()),
           "wkb_paged_attn_prefill")
     return out
+
+
+class PagedKVInt8:
+    """Per-layer int8 K/V slabs [layers][pages][kv_heads][page_tokens][head_dim] with f32 scales
+    [layers][pages][kv_heads][page_tokens] (one per token and KV head)."""
+
+    def __init__(self, layers, num_pages, kv_heads, head_dim, page_tokens=16, device="cuda"):
+        self.layers, self.num_pages, self.kv_heads, self.head_dim, self.page_tokens = layers, num_pages, kv_heads, head_dim, page_tokens
+        shape = (layers, num_pages, kv_heads, page_tokens, head_dim)
+        self.k = torch.zeros(shape, dtype=torch.int8, device=device)
+        self.v = torch.zeros(shape, dtype=torch.int8, device=device)
+        self.k_scale = torch.ones(shape[:-1], dtype=torch.float32, device=device)
+        self.v_scale = torch.ones(shape[:-1], dtype=torch.float32, device=device)
+
+
+def paged_kv_append_int8(kv, layer, ksrc, vsrc, src_row_stride, block_table, row_slot, row_pos, rows, mbps):
+    check(lib().wkb_paged_kv_append_int8(_p(ksrc), _p(vsrc), src_row_stride, _p(kv.k[layer]), _p(kv.v[layer]), _p(kv.k_scale[layer]),
+                                         _p(kv.v_scale[layer]), _p(block_table), _p(row_slot), _p(row_pos), rows, kv.kv_heads,
+                                         kv.head_dim, kv.page_tokens, mbps, _s()), "wkb_paged_kv_append_int8")
+
+
+def paged_attn_decode_int8(q, q_row_stride, kv, layer, block_table, row_slot, row_ctx, out, rows, q_heads, mbps, max_ctx, scale, scratch):
+    check(lib().wkb_paged_attn_decode_int8(_p(q), q_row_stride, _p(kv.k[layer]), _p(kv.v[layer]), _p(kv.k_scale[layer]),
+                                           _p(kv.v_scale[layer]), _p(block_table), _p(row_slot), _p(row_ctx), _p(out),
+                                           int(out.dtype == torch.bfloat16), out.stride(0), rows, q_heads, kv.kv_heads, kv.head_dim,
+                                           kv.page_tokens, mbps, max_ctx, scale, _p(scratch), _s()), "wkb_paged_attn_decode_int8")
+    return out

@@ -172,6 +172,39 @@ def case_paged_attn(hbm, tf, src):
             "note": "555 MB of KV per launch exceeds L2", "peak_source": "of " + src}
 
 
+def case_paged_attn_int8(hbm, tf, src):
+    """The paged_attn_decode case over the int8 cache (same batch, heads and context draw)."""
+    rng = np.random.default_rng(0)
+    B, H, HKV, D, page, pool = 64, 32, 8, 128, 16, 65536
+    ctx = rng.integers(128, 4097, B).astype(np.int32)
+    mbps = 256
+    perm = rng.permutation(pool).astype(np.uint32)
+    table = np.zeros((B, mbps), np.uint32)
+    nxt = 0
+    for b in range(B):
+        n = (int(ctx[b]) + page - 1) // page
+        table[b, :n] = perm[nxt:nxt + n]
+        nxt += n
+    kv = dev.PagedKVInt8(1, pool, HKV, D, page)
+    kv.k.copy_(torch.randint(-127, 128, kv.k.shape, dtype=torch.int8, device="cuda"))
+    kv.v.copy_(torch.randint(-127, 128, kv.v.shape, dtype=torch.int8, device="cuda"))
+    kv.k_scale.uniform_(0.005, 0.03)
+    kv.v_scale.uniform_(0.005, 0.03)
+    q = torch.randn(B, H * D, device="cuda")
+    bt = torch.from_numpy(table.view(np.int32)).cuda()
+    row_slot = torch.arange(B, dtype=torch.int32, device="cuda")
+    row_ctx = torch.from_numpy(ctx).cuda()
+    out = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
+    scratch = dev.paged_attn_scratch(B, H, D, 4096)
+    fn = lambda i: dev.paged_attn_decode_int8(q, H * D, kv, 0, bt, row_slot, row_ctx, out, B, H, mbps, 4096, 1.0 / math.sqrt(D), scratch)
+    us = time_graph(fn, 10)
+    alg = float(ctx.sum()) * 2 * HKV * (D + 4) + B * H * D * (4 + 2) + B * mbps * 4
+    gbs = alg / us / 1e3
+    return {"case": "paged_attn_decode_int8", "shape": {"batch": B, "q_heads": H, "kv_heads": HKV, "d": D, "ctx": "U[128,4096]"}, "us": us,
+            "achieved": gbs, "unit": "GB/s", "bound": "hbm", "peak": hbm, "frac": gbs / hbm, "algorithmic_bytes": alg,
+            "note": "int8 values + f32 scale per (token, kv head): 286 MB per launch, above L2", "peak_source": "of " + src}
+
+
 def case_paged_prefill(H, HKV, D, seqs, hist, chunk, hbm, tf, src):
     """Prompt chunks of `chunk` tokens on top of `hist` cached tokens, `seqs` sequences: the tiled kernel, with the
     row-per-token kernel it replaces timed beside it.  Rated against the tensor peak (useful flops: QK^T and PV over
@@ -223,6 +256,7 @@ def run(out=sys.stdout, only=None, reps_scale=1.0):
     for op, name in ((2, "rmsnorm_bf16"), (0, "softmax_bf16"), (1, "layernorm_bf16")):
         plan.append((name, lambda op=op: case_norm(op, hbm, tf, src)))
     plan.append(("paged_attn_decode", lambda: case_paged_attn(hbm, tf, src)))
+    plan.append(("paged_attn_decode_int8", lambda: case_paged_attn_int8(hbm, tf, src)))
     for (H, HKV, D, seqs, hist, chunk) in ((12, 12, 64, 64, 0, 512), (32, 8, 128, 16, 0, 512), (32, 8, 128, 16, 2048, 256)):
         plan.append(("paged_attn_prefill", lambda a=(H, HKV, D, seqs, hist, chunk): case_paged_prefill(*a, hbm, tf, src)))
     results = []
