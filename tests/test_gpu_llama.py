@@ -101,3 +101,58 @@ def test_llama_tensor_parallel_split_matches_unsharded(env, orc):
     assert tp.models[0].kv.k[0].shape[1] == cfg.n_kv_head // 2
     full = llama.LlamaRankWeights.from_raw(cfg, w).q4_bytes()
     assert sum(m.w.q4_bytes() for m in tp.models) == full
+
+
+def test_llama_chunked_prefill_matches_token_by_token_oracle(env, orc):
+    """Prompt chunks (several positions of a sequence in one step, on the tiled prefill attention) give the logits the
+    oracle computes token by token, and the decode steps that follow continue from the same cache."""
+    torch, llama = env
+    from oracle.llama_model import OracleLlama
+    from wukong_b200 import device as dev
+    cfg = small_cfg(llama)
+    w = llama.synth_llama_raw(cfg, seed=11, sigma=0.008)
+    rng = np.random.default_rng(9)
+    lens = [9, 3, 5]                                    # prompt lengths: 17 rows in the first step
+    prompts = [list(rng.integers(0, cfg.vocab, n)) for n in lens]
+    S, R, mbps = len(lens), 24, 4
+    model = llama.LlamaDecodeModel(cfg, llama.LlamaRankWeights.from_raw(cfg, w), 0, 1, bcap=R, num_pages=64, max_blocks_per_seq=mbps)
+    oracle = OracleLlama(cfg, w, orc, "bf16")
+    table = np.zeros((R, mbps), np.int32)
+    table[:S] = rng.permutation(64).astype(np.int32)[:S * mbps].reshape(S, mbps)
+    model.block_table.copy_(torch.from_numpy(table).cuda())
+    # the oracle, one token at a time
+    kc, vc = zip(*[oracle.new_cache(16) for _ in range(S)])
+    ref = {}
+    for t in range(max(lens)):
+        live = [s for s in range(S) if t < lens[s]]
+        _, lg = oracle.step([prompts[s][t] for s in live], [t] * len(live), [kc[s] for s in live], [vc[s] for s in live])
+        for i, s in enumerate(live):
+            ref[(s, t)] = lg[i]
+    # ours: the whole prompts in one step
+    slot = np.concatenate([np.full(n, s, np.int32) for s, n in enumerate(lens)])
+    pos = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+    tok = np.concatenate([np.asarray(p, np.int32) for p in prompts])
+    n = slot.shape[0]
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.int32)).cuda()
+    pad = lambda a, fill: np.concatenate([np.asarray(a, np.int32), np.full(R - len(a), fill, np.int32)])
+    model.row_token.copy_(i32(pad(tok, 0))); model.row_pos.copy_(i32(pad(pos, -1)))
+    model.row_slot.copy_(i32(pad(slot, 0))); model.row_ctx.copy_(i32(pad(pos + 1, 0)))
+    model.set_prefill_rows(slot)
+    model.forward(n)
+    torch.cuda.synchronize()
+    assert dev.gemm_status() == 0
+    got = model.logits.cpu().numpy()[:n]
+    want = np.stack([ref[(int(slot[r]), int(pos[r]))] for r in range(n)])
+    check_hist([(want, got, want.argmax(1), got.argmax(1))], 8e-3)
+    # decode continues from the cache the chunks wrote
+    model.set_prefill_rows(None)
+    toks = [int(ref[(s, lens[s] - 1)].argmax()) for s in range(S)]
+    for step in range(2):
+        poss = [lens[s] + step for s in range(S)]
+        nxt, lg = oracle.step(toks, poss, list(kc), list(vc))
+        model.row_token.copy_(i32(pad(np.asarray(toks), 0))); model.row_pos.copy_(i32(pad(np.asarray(poss), -1)))
+        model.row_slot.copy_(i32(pad(np.arange(S), 0))); model.row_ctx.copy_(i32(pad(np.asarray(poss) + 1, 0)))
+        model.forward(S)
+        torch.cuda.synchronize()
+        check_hist([(lg, model.logits.cpu().numpy()[:S], np.asarray(nxt), model.next_tok.cpu().numpy()[:S])], 8e-3)
+        toks = [int(t) for t in nxt]

@@ -307,6 +307,7 @@ class LlamaDecodeModel:
         self.scratch = dev.paged_attn_scratch(R, self.hq, hd, self.max_ctx, device)
         self.scale = 1.0 / math.sqrt(hd)
         self.launches_per_forward = 0
+        self.prefill_tiles = None       # set by set_prefill_rows for a step whose rows are prompt chunks
         # one rank, at most 64 rows: the split-K second passes are folded into the kernels that consume the results
         self.fold_slices = world == 1 and reduce is None and peer is None and bcap <= 64
 
@@ -320,6 +321,17 @@ class LlamaDecodeModel:
         p = lambda t: t.data_ptr()
         check(lib().wkb_gemm_q4_0_bf16_nt(p(w.tiled), p(x), ldx, p(out), ldo, mode, n, w.n, w.k, p(self.workspace),
                                           self.workspace.numel(), torch.cuda.current_stream().cuda_stream), what)
+
+    def set_prefill_rows(self, row_slot_host):
+        """Chunked prefill: the step's rows are laid out sequence by sequence (several consecutive positions of a
+        sequence per step, at most `bcap` rows in all); `row_slot_host` is the host copy of row_slot for the live rows.
+        Attention then runs on the tiled prefill kernel.  Pass None to go back to one row per sequence."""
+        if row_slot_host is None:
+            self.prefill_tiles = None
+            return
+        tile_rows = int(lib().wkb_paged_attn_prefill_tile_rows(self.hq, self.hkv))
+        tiles = dev.prefill_tiles(np.asarray(row_slot_host, np.int32), tile_rows)
+        self.prefill_tiles = torch.from_numpy(tiles).to(self.block_table.device)
 
     # ---- phases (a caller that emulates several ranks on one device runs them in lockstep) ----
     def begin(self, n):
@@ -342,9 +354,16 @@ class LlamaDecodeModel:
             check(L.wkb_rope_qk_paged_append(p(self.qkv), self.qkv_w, p(self.inv_freq), p(self.block_table), p(self.row_slot), p(self.row_pos),
                                              p(self.kv.k[li]), p(self.kv.v[li]), n, self.hq, self.hkv, hd // 2, self.page_tokens, self.mbps, s),
                   "rope_append")
-        check(L.wkb_paged_attn_decode(p(self.qkv), self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
-                                      p(self.row_ctx), p(self.att), 1, self.hq * hd, n, self.hq, self.hkv, hd, self.page_tokens, self.mbps,
-                                      self.max_ctx, self.scale, p(self.scratch), s), "attention")
+        if self.prefill_tiles is not None:
+            # prompt chunks: several rows per sequence, keys streamed once per tile (the tiles must cover every live row)
+            check(L.wkb_paged_attn_prefill(p(self.qkv), self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table),
+                                           p(self.row_slot), p(self.row_ctx), p(self.prefill_tiles), self.prefill_tiles.shape[0],
+                                           p(self.att), 1, self.hq * hd, self.hq, self.hkv, hd, self.page_tokens, self.mbps,
+                                           self.scale, s), "prefill attention")
+        else:
+            check(L.wkb_paged_attn_decode(p(self.qkv), self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
+                                          p(self.row_ctx), p(self.att), 1, self.hq * hd, n, self.hq, self.hkv, hd, self.page_tokens, self.mbps,
+                                          self.max_ctx, self.scale, p(self.scratch), s), "attention")
         self._gemm(lw["wo"], self.att, self.hq * hd, self.part_attn, cfg.d_model, 3 if self.fold_slices else 0, n, "o_proj")
 
     def _peer_reduce(self, which, phase, gain, n, what):
