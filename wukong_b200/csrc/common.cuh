@@ -262,6 +262,34 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------------------------------
+// The kernels of a decode step are short (5-100 us) and strictly ordered on one stream, so the gap between two of them
+// (drain, launch, block scheduling, prologue) is a visible share of the step.  A kernel launched through launch_pdl
+// may become resident while its predecessor is still running; it must call pdl_wait() -- every thread, before its
+// first access to global memory -- which returns once the predecessor has completed and its writes are visible, and
+// it calls pdl_trigger() to let its own successor be scheduled early.  With WKB_PDL=0 in the environment launch_pdl
+// is a plain launch and both calls are no-ops in effect.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("WKB_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int ceil_div_i(i64 a, i64 b) { return (int)((a + b - 1) / b); }
 static inline cudaStream_t as_stream(void* s) { return (cudaStream_t)s; }
 

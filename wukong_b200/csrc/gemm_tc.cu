@@ -131,6 +131,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
   }
+  // everything above touches only this CTA's shared memory; tensor memory is claimed and operands are read only once
+  // the preceding kernel of the stream has completed
+  pdl_wait();
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -139,6 +142,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
   if (threadIdx.x == 0) WKB_TRACE(1);
 
   if (warp == 0) {
@@ -350,6 +354,8 @@ static int make_map(CUtensorMap* map, const void* ptr, i64 rows, i64 k, i64 ld, 
 // column, a pinned row (value +inf from a NaN at column 0, index 0) wins outright by its index rule.
 __global__ void __launch_bounds__(128) argmax_tiles_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int tiles,
                                                            int* __restrict__ out, int rows) {
+  pdl_wait();
+  pdl_trigger();
   int lane = threadIdx.x & 31;
   int row = (int)(((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
   if (row >= rows) return;
@@ -400,6 +406,8 @@ int* gemm_status_word() {
 __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* __restrict__ ws, int ksplit, i64 slice_stride, int M, int N,
                                                                  void* __restrict__ c, i64 ldc, int c_bf16, const float* __restrict__ bias,
                                                                  int act, const float* __restrict__ residual, i64 ldr) {
+  pdl_wait();
+  pdl_trigger();
   const i64 quads = (i64)(N >> 2), total = (i64)M * quads;
   for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
     const int m = (int)(idx / quads), n0 = (int)(idx % quads) << 2;
@@ -516,21 +524,18 @@ int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i6
       }
       GemmEpi part{nullptr, nullptr, 0, 0, 0, nullptr, (int)ks, m * n};
       const i64 items = tiles * ks;
-      plain<<<(unsigned)(items < sm_count() ? items : sm_count()), GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(
-          ma, mb, ws, n, (int)m, (int)n, (int)k, part, status);
-      cudaError_t e = cudaGetLastError();
+      cudaError_t e = launch_pdl(plain, (unsigned)(items < sm_count() ? items : sm_count()), GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb,
+                                 (void*)ws, n, (int)m, (int)n, (int)k, part, status);
       if (e != cudaSuccess) return (int)e;
       const i64 total = m * (n / 4);
       i64 g = (total + 255) / 256;
       if (g > sm_count() * 8) g = sm_count() * 8;
-      gemm_splitk_finish_kernel<<<(unsigned)g, 256, 0, as_stream(stream)>>>(ws, (int)ks, m * n, (int)m, (int)n, c, ldc, c_bf16, bias, (int)act,
-                                                                         residual, ldr);
-      return (int)cudaGetLastError();
+      return (int)launch_pdl(gemm_splitk_finish_kernel, (unsigned)g, 256, 0, as_stream(stream), (const float*)ws, (int)ks, m * n, (int)m, (int)n, c,
+                             ldc, c_bf16, bias, (int)act, residual, ldr);
     }
   }
   unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, GEMM_THREADS, smem, as_stream(stream)>>>(ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(kern, grid, GEMM_THREADS, smem, as_stream(stream), ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
 }
 
 // E4M3 x E4M3 -> fp32 accumulate: same kernel with kind::f8f6f4 MMAs and 128 elements of K per stage.
@@ -599,11 +604,11 @@ int wkb_gemm_bf16_nt_argmax(const void* a, i64 lda, const void* b, i64 ldb, i64 
   GemmEpi epi{bias, nullptr, 0, 0, 0, part_idx};
   i64 tiles_n = (n + BN - 1) / BN, tiles = tiles_n * ((m + BM - 1) / BM);
   unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream)>>>(ma, mb, part_val, 0, (int)m, (int)n, (int)k, epi, status);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(kern, grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb, (void*)part_val, (i64)0, (int)m, (int)n, (int)k, epi,
+                             status);
   if (e != cudaSuccess) return (int)e;
-  argmax_tiles_kernel<<<(unsigned)((m * 32 + 127) / 128), 128, 0, as_stream(stream)>>>(part_val, part_idx, (int)tiles_n, out, (int)m);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(argmax_tiles_kernel, (unsigned)((m * 32 + 127) / 128), 128, 0, as_stream(stream), (const float*)part_val,
+                         (const int*)part_idx, (int)tiles_n, out, (int)m);
 }
 
 // Reads (and clears) the bounded-wait status of the tensor-core GEMM on the current device:

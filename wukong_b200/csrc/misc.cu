@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(256) rope_bf16_kernel(const u16* x, const floa
 template <typename T>
 __global__ void __launch_bounds__(256) embedding_kernel(T* __restrict__ out, const T* __restrict__ weight,
                                                         const int* __restrict__ ids, i64 t, i64 h, i64 v) {
+  pdl_wait();
+  pdl_trigger();
   i64 total = t * h;
   i64 stride = (i64)gridDim.x * blockDim.x;
   for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
@@ -63,6 +65,8 @@ __global__ void __launch_bounds__(256) embed_tok_pos_kernel(float* __restrict__ 
                                                             const u16* __restrict__ wpe, const int* __restrict__ ids,
                                                             const int* __restrict__ pos, i64 t, i64 h, i64 v,
                                                             i64 npos) {
+  pdl_wait();
+  pdl_trigger();
   i64 total = t * h;
   i64 stride = (i64)gridDim.x * blockDim.x;
   for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
@@ -126,6 +130,8 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* a, const floa
 // one position on (inactive rows, pos < 0, stay inactive).  Lets a run of decode steps replay with
 // no host round trip (the block table must already cover the positions ahead).
 __global__ void decode_advance_kernel(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, int n) {
+  pdl_wait();
+  pdl_trigger();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n && row_pos[i] >= 0) {
     row_token[i] = next_tok[i];
@@ -164,15 +170,15 @@ int wkb_rope_bf16(const void* x, const float* inv_freq, const int* pos, void* ou
 
 int wkb_embedding_f32(float* out, const float* weight, const int* ids, i64 t, i64 h, i64 v, void* stream) {
   if (t <= 0 || h <= 0) return 0;
-  embedding_kernel<float><<<grid_for(t * h, 256), 256, 0, as_stream(stream)>>>(out, weight, ids, t, h, v < 0 ? 0 : v);
+  launch_pdl(embedding_kernel<float>, grid_for(t * h, 256), 256, 0, as_stream(stream), out, weight, ids, t, h, v < 0 ? 0 : v);
   return (int)cudaGetLastError();
 }
 
 int wkb_embed_tok_pos_bf16(float* out, const void* wte, const void* wpe, const int* ids, const int* pos, i64 t, i64 h,
                            i64 v, i64 npos, void* stream) {
   if (t <= 0 || h <= 0) return 0;
-  embed_tok_pos_kernel<<<grid_for(t * h, 256), 256, 0, as_stream(stream)>>>(out, (const u16*)wte, (const u16*)wpe, ids,
-                                                                            pos, t, h, v, npos);
+  launch_pdl(embed_tok_pos_kernel, grid_for(t * h, 256), 256, 0, as_stream(stream), out, (const u16*)wte, (const u16*)wpe, ids, pos, t, h, v,
+             npos);
   return (int)cudaGetLastError();
 }
 
@@ -192,7 +198,7 @@ int wkb_rowargmax_strided_i32(const float* x, int* out, i64 rows, i64 cols, i64 
 
 int wkb_decode_advance(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, i64 n, void* stream) {
   if (n <= 0) return 0;
-  decode_advance_kernel<<<(int)((n + 255) / 256), 256, 0, as_stream(stream)>>>(row_token, row_pos, row_ctx, next_tok, (int)n);
+  launch_pdl(decode_advance_kernel, (int)((n + 255) / 256), 256, 0, as_stream(stream), row_token, row_pos, row_ctx, next_tok, (int)n);
   return (int)cudaGetLastError();
 }
 

@@ -210,6 +210,8 @@ __global__ void __launch_bounds__(NT) norm_fast_kernel(const TIn* __restrict__ x
                                                        const float* __restrict__ beta, i64 rows, int cols,
                                                        float eps, int op) {
   __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
   const int nvec = cols >> 3;
   for (i64 r = blockIdx.x; r < rows; r += gridDim.x) {
     const TIn* xr = x + r * (i64)cols;
@@ -449,13 +451,13 @@ static int launch_fast(const void* x, void* out, const float* g, const float* b,
   }
   int grid = (int)(rows < (i64)WKB_SM_COUNT * 16 ? rows : (i64)WKB_SM_COUNT * 16);
   if (cols <= 128 * 8) {
-    norm_fast_kernel<TIn, TOut, 128, 1><<<grid, 128, 0, st>>>((const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
+    launch_pdl(norm_fast_kernel<TIn, TOut, 128, 1>, grid, 128, 0, st, (const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
   } else if (cols <= 128 * 8 * 2) {
-    norm_fast_kernel<TIn, TOut, 128, 2><<<grid, 128, 0, st>>>((const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
+    launch_pdl(norm_fast_kernel<TIn, TOut, 128, 2>, grid, 128, 0, st, (const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
   } else if (cols <= 128 * 8 * 4) {
-    norm_fast_kernel<TIn, TOut, 128, 4><<<grid, 128, 0, st>>>((const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
+    launch_pdl(norm_fast_kernel<TIn, TOut, 128, 4>, grid, 128, 0, st, (const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
   } else {
-    norm_fast_kernel<TIn, TOut, 128, 8><<<grid, 128, 0, st>>>((const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
+    launch_pdl(norm_fast_kernel<TIn, TOut, 128, 8>, grid, 128, 0, st, (const TIn*)x, (TOut*)out, g, b, rows, (int)cols, eps, op);
   }
   return (int)cudaGetLastError();
 }

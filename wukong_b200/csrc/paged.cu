@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   constexpr bool PREFETCH_V = (HD == 64) || (G <= 2);
   constexpr bool DOUBLE_BUFFER = (HD == 64 && G <= 2) || (HD == 128 && G == 1);
   static_assert(TILE == 32, "tile is one token per lane");
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int grp = lane / LPT, j = lane % LPT;
   const i64 unit = (i64)blockIdx.x * PA_WARPS + warp;
@@ -253,6 +255,8 @@ __global__ void __launch_bounds__(PA_WARPS * 32, 2) paged_attn_decode_mma_kernel
     const uint32_t* __restrict__ block_table, const int* __restrict__ row_slot, const int* __restrict__ row_ctx,
     float* __restrict__ scratch, PagedGeo g, float scale_log2e) {
   constexpr int HD = 128, LPT = HD / 8;   // 16 uint4 per token row
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gi = lane >> 2, t = lane & 3;
   const i64 unit = (i64)blockIdx.x * PA_WARPS + warp;
@@ -401,6 +405,8 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const float* __re
                                                                int out_dtype, i64 out_row_stride,
                                                                const int* __restrict__ row_ctx, int rows, int q_heads,
                                                                int max_chunks, int chunk_tokens) {
+  pdl_wait();
+  pdl_trigger();
   i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x;
   i64 total = (i64)rows * q_heads * (HD / 4);
   if (idx >= total) return;
@@ -444,6 +450,8 @@ __global__ void __launch_bounds__(256) paged_kv_append_kernel(const float* __res
                                                               u16* __restrict__ vcache, const uint32_t* __restrict__ block_table,
                                                               const int* __restrict__ row_slot, const int* __restrict__ row_pos,
                                                               int rows, int kv_heads, int hd, int page_tokens, int mbps) {
+  pdl_wait();
+  pdl_trigger();
   int per_row = kv_heads * hd / 8;
   i64 total = (i64)rows * per_row;
   i64 stride = (i64)gridDim.x * blockDim.x;
@@ -474,14 +482,12 @@ static int launch_decode_mma(const float* q, const void* kc, const void* vc, con
   i64 units = (i64)g.rows * g.kv_heads * g.max_chunks;
   i64 blocks = (units + PA_WARPS - 1) / PA_WARPS;
   if (blocks > 0x7fffffff) return (int)cudaErrorInvalidValue;
-  paged_attn_decode_mma_kernel<G><<<(unsigned)blocks, PA_WARPS * 32, 0, st>>>(
-      q, (const uint4*)kc, (const uint4*)vc, bt, row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(paged_attn_decode_mma_kernel<G>, (unsigned)blocks, PA_WARPS * 32, 0, st, q, (const uint4*)kc, (const uint4*)vc, bt,
+                             row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f);
   if (e != cudaSuccess) return (int)e;
   i64 total = (i64)g.rows * g.q_heads * (128 / 4);
-  paged_attn_merge_kernel<128><<<(unsigned)((total + 127) / 128), 128, 0, st>>>(scratch, out, out_dtype, out_row_stride,
-                                                                                row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(paged_attn_merge_kernel<128>, (unsigned)((total + 127) / 128), 128, 0, st, (const float*)scratch, out, out_dtype,
+                         out_row_stride, row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens);
 }
 
 template <int HD, int G>
@@ -491,14 +497,12 @@ static int launch_decode(const float* q, const void* kc, const void* vc, const u
   i64 units = (i64)g.rows * g.kv_heads * g.max_chunks;
   i64 blocks = (units + PA_WARPS - 1) / PA_WARPS;
   if (blocks > 0x7fffffff) return (int)cudaErrorInvalidValue;
-  paged_attn_decode_kernel<HD, G><<<(unsigned)blocks, PA_WARPS * 32, 0, st>>>(
-      q, (const uint4*)kc, (const uint4*)vc, bt, row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(paged_attn_decode_kernel<HD, G>, (unsigned)blocks, PA_WARPS * 32, 0, st, q, (const uint4*)kc, (const uint4*)vc, bt,
+                             row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f);
   if (e != cudaSuccess) return (int)e;
   i64 total = (i64)g.rows * g.q_heads * (HD / 4);
-  paged_attn_merge_kernel<HD><<<(unsigned)((total + 127) / 128), 128, 0, st>>>(scratch, out, out_dtype, out_row_stride,
-                                                                                row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(paged_attn_merge_kernel<HD>, (unsigned)((total + 127) / 128), 128, 0, st, (const float*)scratch, out, out_dtype,
+                         out_row_stride, row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens);
 }
 
 }  // namespace wkb
@@ -559,10 +563,9 @@ int wkb_paged_kv_append(const float* ksrc, const float* vsrc, i64 src_row_stride
   i64 total = rows * kv_heads * head_dim / 8;
   i64 blocks = (total + 255) / 256;
   if (blocks > (i64)WKB_SM_COUNT * 16) blocks = (i64)WKB_SM_COUNT * 16;
-  paged_kv_append_kernel<<<(int)blocks, 256, 0, as_stream(stream)>>>(ksrc, vsrc, src_row_stride, (u16*)kcache, (u16*)vcache,
-                                                                     block_table, row_slot, row_pos, (int)rows, (int)kv_heads,
-                                                                     (int)head_dim, (int)page_tokens, (int)max_blocks_per_seq);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(paged_kv_append_kernel, (int)blocks, 256, 0, as_stream(stream), ksrc, vsrc, src_row_stride, (u16*)kcache,
+                         (u16*)vcache, block_table, row_slot, row_pos, (int)rows, (int)kv_heads, (int)head_dim, (int)page_tokens,
+                         (int)max_blocks_per_seq);
 }
 }
 
