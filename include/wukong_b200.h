@@ -270,6 +270,9 @@ int wkb_decode_advance(int* row_token, int* row_pos, int* row_ctx, const int* ne
  * The decode call needs `scratch` of wkb_paged_attn_scratch_bytes(...) bytes; max_ctx bounds row_ctx.
  * head_dim in {64, 128}; q_heads / kv_heads in {1, 2, 4} (and 8 at head_dim 128); out_dtype 0 f32, 1 bf16. */
 int64_t wkb_paged_attn_scratch_bytes(int64_t rows, int64_t q_heads, int64_t head_dim, int64_t max_ctx);
+/* Kernels one wkb_paged_attn_decode call of this shape launches (1: every row is one unit that writes its own output; 2: units + chunk merge). */
+int64_t wkb_paged_attn_decode_launches(int64_t rows, int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t max_ctx, int out_dtype,
+                                       int64_t out_row_stride);
 int wkb_paged_attn_decode(const float* q, int64_t q_row_stride, const void* kcache, const void* vcache,
                           const uint32_t* block_table, const int* row_slot, const int* row_ctx, void* out,
                           int out_dtype, int64_t out_row_stride, int64_t rows, int64_t q_heads, int64_t kv_heads,

@@ -45,7 +45,9 @@ template <int HD, int G>
 __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
     const float* __restrict__ q, const uint4* __restrict__ kcache, const uint4* __restrict__ vcache,
     const uint32_t* __restrict__ block_table, const int* __restrict__ row_slot, const int* __restrict__ row_ctx,
-    float* __restrict__ scratch, PagedGeo g, float scale_log2e) {
+    float* __restrict__ scratch, PagedGeo g, float scale_log2e, void* __restrict__ out, int out_dtype, i64 out_row_stride) {
+  // out != nullptr: the launch has one chunk per row, so the unit normalises and writes the row itself (the arithmetic
+  // of the merge kernel for a single chunk) and no scratch record or merge launch is needed
   constexpr int LPT = HD / 8;       // lanes per token
   constexpr int TPW = 32 / LPT;     // tokens per warp step
   constexpr int STEPS = LPT;        // steps per tile (so the reduce-scatter is square)
@@ -69,8 +71,27 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   const int t0 = chunk * g.chunk_tokens;
   float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
   const i64 head_stride = (i64)g.max_chunks * (HD + 4);
+  auto write_row = [&](int h, const float (&v)[8]) {   // 8 dims j*8.. of head kvh*G + h, by the lanes of token group 0
+    const i64 off = (i64)row * out_row_stride + ((i64)kvh * G + h) * HD + j * 8;
+    if (out_dtype == 0) {
+      float4* d = reinterpret_cast<float4*>(static_cast<float*>(out) + off);
+      d[0] = make_float4(v[0], v[1], v[2], v[3]);
+      d[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+      uint4 pk;
+      pk.x = (uint32_t)f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
+      pk.y = (uint32_t)f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
+      pk.z = (uint32_t)f32_to_bf16_bits(v[4]) | ((uint32_t)f32_to_bf16_bits(v[5]) << 16);
+      pk.w = (uint32_t)f32_to_bf16_bits(v[6]) | ((uint32_t)f32_to_bf16_bits(v[7]) << 16);
+      *reinterpret_cast<uint4*>(static_cast<u16*>(out) + off) = pk;
+    }
+  };
   if (t0 >= ctx) {  // nothing visible in this chunk: mark it empty
-    if (lane < G) { float* s = sbase + lane * head_stride; s[HD] = -INFINITY; s[HD + 1] = 0.0f; }
+    if (out) {
+      const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (grp == 0)
+        for (int h = 0; h < G; ++h) write_row(h, zero);
+    } else if (lane < G) { float* s = sbase + lane * head_stride; s[HD] = -INFINITY; s[HD + 1] = 0.0f; }
     return;
   }
   const int t1 = min(ctx, t0 + g.chunk_tokens);
@@ -210,6 +231,14 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
       for (int e = 0; e < 8; ++e) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], ofs);
     }
     float lt = warp_sum(l[h]);
+    if (out) {
+      const float inv = lt != 0.0f ? 1.0f / lt : 0.0f;
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = acc[h][e] * inv;
+      if (grp == 0) write_row(h, v);
+      continue;
+    }
     float* s = sbase + h * head_stride;
     if (grp == 0) {
       *reinterpret_cast<float4*>(s + j * 8) = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
@@ -497,9 +526,12 @@ static int launch_decode(const float* q, const void* kc, const void* vc, const u
   i64 units = (i64)g.rows * g.kv_heads * g.max_chunks;
   i64 blocks = (units + PA_WARPS - 1) / PA_WARPS;
   if (blocks > 0x7fffffff) return (int)cudaErrorInvalidValue;
+  // one unit per (row, kv head): it writes the row itself (128-bit stores: a bf16 row pitch must be a multiple of 8)
+  const bool direct = g.max_chunks == 1 && (out_dtype == 0 || out_row_stride % 8 == 0);
   cudaError_t e = launch_pdl(paged_attn_decode_kernel<HD, G>, (unsigned)blocks, PA_WARPS * 32, 0, st, q, (const uint4*)kc, (const uint4*)vc, bt,
-                             row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f);
-  if (e != cudaSuccess) return (int)e;
+                             row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f, direct ? out : (void*)nullptr, out_dtype,
+                             out_row_stride);
+  if (e != cudaSuccess || direct) return (int)e;
   i64 total = (i64)g.rows * g.q_heads * (HD / 4);
   return (int)launch_pdl(paged_attn_merge_kernel<HD>, (unsigned)((total + 127) / 128), 128, 0, st, (const float*)scratch, out, out_dtype,
                          out_row_stride, row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens);
@@ -509,12 +541,44 @@ static int launch_decode(const float* q, const void* kc, const void* vc, const u
 
 using namespace wkb;
 
+// How finely a sequence is split depends on the launch shape only (never on the data): few (row, kv head) pairs need
+// the split for parallelism, many pairs are better off amortising the per-unit set-up over longer runs.
+static void pa_plan(i64 rows, i64 kv_heads, i64 head_dim, int G, i64 max_ctx, int* chunk_tokens_out, i64* chunks_out) {
+  // Aim for about 2048 units at full context, between 128 and 512 tokens each (measured on batch 64 x 8 KV heads at
+  // context 2048: 128 / 256 / 512 / 1024-token units give 128 / 122 / 115 / 112 us per launch, 2048 gives 197 us; on
+  // ragged contexts up to 4096, 512 beats 1024).
+  i64 want = rows * kv_heads * (max_ctx > 0 ? max_ctx : 1) / 2048;
+  int chunk_tokens = PA_CHUNK_MIN;
+  while (chunk_tokens < 512 && chunk_tokens * 2 <= want) chunk_tokens *= 2;
+  // Two chunks of 512 where one of 1024 would do (contexts up to 1024 with plenty of rows): take the single chunk --
+  // the SIMT kernels then write the rows themselves and the merge launch disappears (same time per launch measured
+  // on 512 rows x 12 heads with contexts up to 896).
+  const bool simt = head_dim == 64 || G == 1;
+  if (simt && chunk_tokens == 512 && max_ctx > 512 && max_ctx <= 1024) chunk_tokens = 1024;
+  i64 chunks = (max_ctx + chunk_tokens - 1) / chunk_tokens;
+  if (chunks < 1) chunks = 1;
+  *chunk_tokens_out = chunk_tokens;
+  *chunks_out = chunks;
+}
+
 extern "C" {
 
 i64 wkb_paged_attn_scratch_bytes(i64 rows, i64 q_heads, i64 head_dim, i64 max_ctx) {
   i64 chunks = (max_ctx + PA_CHUNK_MIN - 1) / PA_CHUNK_MIN;   // worst case: the smallest split
   if (chunks < 1) chunks = 1;
   return rows * q_heads * chunks * (head_dim + 4) * 4;
+}
+
+// Kernels one wkb_paged_attn_decode call launches: 1 when every row is a single unit that writes its own output
+// (SIMT kernels, one chunk), else 2 (units + chunk merge).
+i64 wkb_paged_attn_decode_launches(i64 rows, i64 q_heads, i64 kv_heads, i64 head_dim, i64 max_ctx, int out_dtype, i64 out_row_stride) {
+  if (rows <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return 0;
+  const int G = (int)(q_heads / kv_heads);
+  int chunk_tokens;
+  i64 chunks;
+  pa_plan(rows, kv_heads, head_dim, G, max_ctx, &chunk_tokens, &chunks);
+  const bool simt = head_dim == 64 || G == 1;
+  return (simt && chunks == 1 && (out_dtype == 0 || out_row_stride % 8 == 0)) ? 1 : 2;
 }
 
 int wkb_paged_attn_decode(const float* q, i64 q_row_stride, const void* kcache, const void* vcache,
@@ -530,19 +594,11 @@ int wkb_paged_attn_decode(const float* q, i64 q_row_stride, const void* kcache, 
   if ((q_row_stride % 4) != 0 || ((((uintptr_t)q) | ((uintptr_t)scratch) | ((uintptr_t)kcache) | ((uintptr_t)vcache)) & 15) != 0)
     return (int)cudaErrorMisalignedAddress;
   if (out_row_stride % 4 != 0 || (((uintptr_t)out) & 15) != 0) return (int)cudaErrorMisalignedAddress;
-  // How finely a sequence is split depends on the launch shape only (never on the data): few
-  // (row, kv head) pairs need the split for parallelism, many pairs are better off amortising the
-  // per-unit set-up over longer runs.
-  // Aim for about 2048 units at full context, between 128 and 512 tokens each (measured on batch 64 x 8 KV heads at
-  // context 2048: 128 / 256 / 512 / 1024-token units give 128 / 122 / 115 / 112 us per launch, 2048 gives 197 us; on
-  // ragged contexts up to 4096, 512 beats 1024).
-  i64 want = rows * kv_heads * (max_ctx > 0 ? max_ctx : 1) / 2048;
-  int chunk_tokens = PA_CHUNK_MIN;
-  while (chunk_tokens < 512 && chunk_tokens * 2 <= want) chunk_tokens *= 2;
-  i64 chunks = (max_ctx + chunk_tokens - 1) / chunk_tokens;
-  if (chunks < 1) chunks = 1;
-  PagedGeo g{(int)rows, (int)q_heads, (int)kv_heads, (int)page_tokens, page_shift, (int)max_blocks_per_seq, (int)chunks, chunk_tokens, q_row_stride};
   int G = (int)(q_heads / kv_heads);
+  int chunk_tokens;
+  i64 chunks;
+  pa_plan(rows, kv_heads, head_dim, G, max_ctx, &chunk_tokens, &chunks);
+  PagedGeo g{(int)rows, (int)q_heads, (int)kv_heads, (int)page_tokens, page_shift, (int)max_blocks_per_seq, (int)chunks, chunk_tokens, q_row_stride};
   cudaStream_t st = as_stream(stream);
 #define WKB_PA_CASE(HD_, G_) \
   if (head_dim == HD_ && G == G_) return launch_decode<HD_, G_>(q, kcache, vcache, block_table, row_slot, row_ctx, scratch, out, out_dtype, out_row_stride, g, scale, st);

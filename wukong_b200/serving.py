@@ -149,7 +149,8 @@ class DecodeModel:
         # split-K finishing pass
         tiles = lambda m, nn: ((m + 127) // 128) * ((nn + 127) // 128)
         split = 1 if (2 * tiles(n, d) <= 148 and f >= 2048) else 0
-        self.launches_per_forward = launches + len(self.layers) * (1 + split + (1 if n_tiles else 0)) + 4
+        attn = int(L.wkb_paged_attn_decode_launches(n, cfg.n_head, cfg.n_head, cfg.head_dim, self.max_ctx, 1, d)) - 1   # beyond the one counted above
+        self.launches_per_forward = launches + len(self.layers) * (attn + split + (1 if n_tiles else 0)) + 4
         return self.next_tok
 
 
