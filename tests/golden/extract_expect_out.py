@@ -21,7 +21,9 @@ FIXTURES = [
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: extract_expect_out.py <path of the reference checkout>")
+    ref = sys.argv[1]
     out = {}
     for name in FIXTURES:
         path = os.path.join(ref, "tests", "run", name + ".wk")
