@@ -544,10 +544,10 @@ using namespace wkb;
 // How finely a sequence is split depends on the launch shape only (never on the data): few (row, kv head) pairs need
 // the split for parallelism, many pairs are better off amortising the per-unit set-up over longer runs.
 static void pa_plan(i64 rows, i64 kv_heads, i64 head_dim, int G, i64 max_ctx, int* chunk_tokens_out, i64* chunks_out) {
-  // Aim for about 2048 units at full context, between 128 and 512 tokens each (measured on batch 64 x 8 KV heads at
+  // Aim for about 1024 units at full context, between 128 and 512 tokens each (measured on batch 64 x 8 KV heads at
   // context 2048: 128 / 256 / 512 / 1024-token units give 128 / 122 / 115 / 112 us per launch, 2048 gives 197 us; on
-  // ragged contexts up to 4096, 512 beats 1024).
-  i64 want = rows * kv_heads * (max_ctx > 0 ? max_ctx : 1) / 2048;
+  // ragged contexts up to 4096, 512 beats 1024; with 4 or 2 KV heads per GPU, 256 / 512-token units beat 128 / 256).
+  i64 want = rows * kv_heads * (max_ctx > 0 ? max_ctx : 1) / 1024;
   int chunk_tokens = PA_CHUNK_MIN;
   while (chunk_tokens < 512 && chunk_tokens * 2 <= want) chunk_tokens *= 2;
   // Two chunks of 512 where one of 1024 would do (contexts up to 1024 with plenty of rows): take the single chunk --

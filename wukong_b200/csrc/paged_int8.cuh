@@ -237,7 +237,7 @@ int wkb_paged_attn_decode_int8(const float* q, i64 q_row_stride, const void* kq,
   if ((q_row_stride % 4) != 0 || ((((uintptr_t)q) | ((uintptr_t)scratch)) & 15) != 0 || ((((uintptr_t)kq) | ((uintptr_t)vq)) & 7) != 0)
     return (int)cudaErrorMisalignedAddress;
   if (out_row_stride % 4 != 0 || (((uintptr_t)out) & 15) != 0) return (int)cudaErrorMisalignedAddress;
-  i64 want = rows * kv_heads * (max_ctx > 0 ? max_ctx : 1) / 2048;      // the bf16 path's split rule
+  i64 want = rows * kv_heads * (max_ctx > 0 ? max_ctx : 1) / 1024;      // the bf16 path's split rule
   int chunk_tokens = PA_CHUNK_MIN;
   while (chunk_tokens < 512 && chunk_tokens * 2 <= want) chunk_tokens *= 2;
   i64 chunks = (max_ctx + chunk_tokens - 1) / chunk_tokens;
