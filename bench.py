@@ -1,14 +1,19 @@
-"""Benchmark of the decode hot path: GPT-2-124M-shape batched greedy decode serving, bf16 weights,
-paged KV with 16-token pages, 512 concurrent sequences per GPU (prompts uniform in [32, 512]).
+"""Benchmark of the decode hot path: GPT-2-124M-shape batched greedy decode serving, bf16 weights, paged KV with
+16-token pages, 512 concurrent sequences (prompts uniform in [32, 512]) sharded by sequence over the GPUs.
 
-    python bench.py --gpus N --steps K --warmup W            # this library (one replica per GPU)
+    python bench.py --gpus N --steps K --warmup W            # this library, one replica per GPU
     python bench.py --impl reference --steps K --warmup W    # the CPU port of the reference kernels
-    python bench.py --workload llama_int4 --gpus N ...        # second workload: tensor-parallel Q4_0 Llama-shape stack
+    python bench.py --workload llama_int4 --gpus N ...       # only the second workload: tensor-parallel Q4_0 Llama-shape stack
 
-A step is one decode step of every resident sequence (one token each).  `value` is measured with
-all inputs resident in HBM (a self-feeding CUDA graph per step); `e2e` is measured through the public
-serving API (`Engine.step`: pinned-host row / block-table upload, graph replay, token download, host
-scheduling).  Weights, prompts and their values are synthetic (seeded) stand-ins of the same shapes.
+A step is one decode step of every resident sequence (one token each).  The job is the fixed 512-sequence batch:
+with N GPUs every rank serves 512 / N of them as an independent replica (no collective on the data path), so
+`value` is a strong-scaling number; the per-GPU-512 (weak) figure is reported beside it under `weak` when N > 1.
+`value` is measured with all inputs resident in HBM (a self-feeding CUDA graph per step); `e2e` through the public
+serving API (`Engine.step`: pinned-host row / block-table upload, graph replay, token download, host scheduling).
+Extra keys of the line: `continuous_batching` (a second timed region with admissions, prompt chunks and retirements
+inside it), `tp_llama_int4` (the tensor-parallel Llama-shape int4 step on the same N GPUs: fused peer-memory reduce
+and the NCCL all-reduce baseline) and, at N = 1, `microsuite` (per-kernel roofline fractions of the kernel
+micro-suite).  Weights, prompts and their values are synthetic (seeded) stand-ins of the same shapes.
 """
 import argparse
 import json
@@ -22,11 +27,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-SEQS_PER_GPU = 512
+GLOBAL_SEQS = 512
 PROMPT_LO, PROMPT_HI = 32, 512
 GEN_NOMINAL = 128
 PAGE = 16
-MBPS = 56                      # block-table columns: 896 tokens per sequence at most
+N_POS = 1024                   # learned positions of the GPT-2 shape: no sequence may grow past this
+CPU_SAMPLE_SEQS = 16           # the one CPU sample definition: a step = one decode step of 16 of the workload's sequences
 METRIC, UNIT = "decode_tokens_per_s", "tok/s"
 
 
@@ -36,10 +42,12 @@ def parse():
     ap.add_argument("--steps", type=int, default=48)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--seqs", type=int, default=SEQS_PER_GPU, help="sequences per GPU (default: the named workload)")
+    ap.add_argument("--seqs", type=int, default=0, help="sequences per GPU (default: 512 / number of GPUs, the named workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the continuous-batching region, the tensor-parallel "
+                    "Llama-shape step, the weak-scaling figure and the micro-suite (for profiling runs)")
     ap.add_argument("--workload", default="gpt2_serving", choices=["gpt2_serving", "llama_int4"],
-                    help="gpt2_serving: the headline workload (sequence-sharded replicas); llama_int4: the tensor-parallel Q4_0 stack")
+                    help="gpt2_serving: the headline workload (sequence-sharded replicas); llama_int4: only the tensor-parallel Q4_0 stack")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="llama_int4 only: sum over ranks with NCCL all-reduce instead of the fused peer-memory kernel")
     ap.add_argument("--layers", type=int, default=0, help="llama_int4 only: run a shorter stack (0: the named 32 layers)")
@@ -49,14 +57,14 @@ def parse():
     return a
 
 
-def workload_config(args, n_gpus):
+def workload_config(seqs_per_gpu, n_gpus):
     return {
-        "workload": "GPT-2-124M-shape batched greedy decode serving (BASELINE configs[3])",
+        "workload": "GPT-2-124M-shape batched greedy decode serving, %d concurrent sequences sharded over the GPUs" % (seqs_per_gpu * n_gpus),
         "layers": 12, "d_model": 768, "heads": 12, "d_ff": 3072, "vocab": 50257,
-        "sequences_per_gpu": args.seqs, "global_sequences": args.seqs * n_gpus,
+        "sequences_per_gpu": seqs_per_gpu, "global_sequences": seqs_per_gpu * n_gpus,
         "prompt_len": "uniform[%d,%d]" % (PROMPT_LO, PROMPT_HI), "greedy_steps_nominal": GEN_NOMINAL,
         "kv": "paged bf16, %d-token pages" % PAGE, "parallelism": "replicas x%d (sequence sharded, no collective)" % n_gpus,
-        "l2": "per-step inputs (249 MB weights + multi-GB KV) exceed the 126 MB L2; no flush needed",
+        "l2": "per-step inputs (249 MB weights + KV of every resident sequence) exceed the 126 MB L2; no flush needed",
     }
 
 
@@ -69,16 +77,16 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.samples, self.proc = index, [], None
-        self.t_begin = self.t_end = None
+        self.regions = []
 
     def launch(self):
         """Start nvidia-smi streaming samples (it needs a moment to come up, so this is called well before the
-        timed region; `start` / `stop` then mark the region whose samples count)."""
+        timed regions; `start` / `stop` then mark the regions whose samples count)."""
         if self.proc is not None:
             return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -87,7 +95,7 @@ class ClockSampler:
 
     def start(self):
         self.launch()
-        self.t_begin = time.perf_counter()
+        self.regions.append([time.perf_counter(), None])
 
     def _read(self):
         for line in self.proc.stdout:
@@ -96,19 +104,23 @@ class ClockSampler:
                 self.samples.append((time.perf_counter(), parts))
 
     def stop(self):
-        self.t_end = time.perf_counter()
+        if self.regions and self.regions[-1][1] is None:
+            self.regions[-1][1] = time.perf_counter()
+
+    def close(self):
         if self.proc:
-            time.sleep(0.06)            # let the sample that covers the end of the region arrive
+            time.sleep(0.05)            # let the sample that covers the end of the last region arrive
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except Exception:
                 pass
+            self.proc = None
 
     def summary(self):
         sm, mx, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        inside = [p for (t, p) in self.samples if self.t_begin is not None and self.t_begin <= t <= (self.t_end or t) + 0.06]
+        inside = [p for (t, p) in self.samples if any(b <= t <= (e or t) + 0.03 for b, e in self.regions)]
         # a region shorter than the sampling period may hold no sample: then the nearest ones around it stand in
         chosen = inside or [p for (_, p) in self.samples[-3:]]
         for p in chosen:
@@ -128,14 +140,16 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # CPU port of the reference kernels (the oracle), timed on the host cores
 # ------------------------------------------------------------------------------------------------
-def cpu_decode_tok_s(weights, cfg, steps, warmup, seqs, threads):
-    """Decode steps of `seqs` sequences on the CPU oracle model; contexts drawn from the workload's
-    distribution at mid-generation, KV caches pre-filled with seeded random bf16 values (only the
-    decode step is timed).  Returns (tok/s, seconds, description)."""
+def cpu_decode_tok_s(weights, cfg, steps, warmup, threads):
+    """Decode steps of CPU_SAMPLE_SEQS sequences on the CPU oracle model; contexts drawn from the workload's
+    distribution at mid-generation, KV caches pre-filled with seeded random bf16 values (only the decode step is
+    timed).  Returns (tok/s, seconds, description).  Both the `cpu_baseline` key of this library's line and the
+    reference arm time exactly this sample."""
     import numpy as np
     from oracle import binding as orc
     from oracle.gpt2_model import OracleGPT2
     orc.set_threads(threads)
+    seqs = CPU_SAMPLE_SEQS
     model = OracleGPT2(cfg, weights, orc)
     rng = np.random.default_rng(1234)
     ctx = rng.integers(PROMPT_LO, PROMPT_HI + 1, seqs) + GEN_NOMINAL // 2
@@ -155,7 +169,8 @@ def cpu_decode_tok_s(weights, cfg, steps, warmup, seqs, threads):
         toks = [int(t) for t in nxt]
         pos = [p + 1 for p in pos]
     dt = time.perf_counter() - t0
-    desc = "%d sequences x %d decode steps, ctx uniform[%d,%d]+%d, random bf16 KV" % (seqs, steps, PROMPT_LO, PROMPT_HI, GEN_NOMINAL // 2)
+    desc = "%d of the workload's sequences x %d decode steps, ctx uniform[%d,%d]+%d, random bf16 KV" % (
+        seqs, steps, PROMPT_LO, PROMPT_HI, GEN_NOMINAL // 2)
     return seqs * steps / dt, dt, desc
 
 
@@ -169,15 +184,14 @@ def run_reference(args):
     cfg = GPT2Config()
     weights = synth_weights(cfg, 0)
     threads = os.cpu_count() or 1
-    total = args.steps + args.warmup
-    seqs = max(1, min(8, int(150.0 / (total * 0.05))))     # ~0.05 s per token-forward on 8 threads: stay within minutes
-    tok_s, dt, desc = cpu_decode_tok_s(weights, cfg, args.steps, args.warmup, seqs, threads)
+    steps = min(args.steps, 64)             # about 0.2 s per 16-sequence step: the run stays within a few minutes
+    tok_s, dt, desc = cpu_decode_tok_s(weights, cfg, steps, min(args.warmup, 3), threads)
     n_gpus = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     line = {
         "impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, n_gpus),
-        "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "warmup": args.warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(GLOBAL_SEQS // n_gpus, n_gpus),
+        "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc, "seconds": dt},
         "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -187,12 +201,12 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------
 # this library, one replica per GPU
 # ------------------------------------------------------------------------------------------------
-def shard_prompts(rank, seqs, vocab):
+def shard_prompts(rank, seqs, vocab, stream=0):
     """This rank's shard of the workload: `seqs` prompts drawn from a rank-specific seeded stream, so
     the global job is world x seqs distinct sequences and no two ranks share one (replicas exchange
     nothing on the data path)."""
     import numpy as np
-    rng = np.random.default_rng(100 + rank)
+    rng = np.random.default_rng(100 + rank + 1000 * stream)
     lens = rng.integers(PROMPT_LO, PROMPT_HI + 1, seqs)
     return [rng.integers(0, vocab, int(L)) for L in lens]
 
@@ -217,49 +231,64 @@ def hbm_peak():
         return 6650.0, "fallback"
 
 
-def run_ours(args):
+class Dist:
+    """The few process-group calls the bench needs (barrier, max over ranks); one rank: no-ops."""
+
+    def __init__(self, world, rank, local):
+        self.world, self.rank, self.local = world, rank, local
+
+    def barrier(self):
+        import torch
+        torch.cuda.synchronize()
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_ms(self, ms):
+        return max_over_ranks_ms(ms, self.world, "cuda")
+
+    def sum_int(self, v):
+        if self.world == 1:
+            return int(v)
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([int(v)], dtype=torch.int64, device="cuda")
+        dist.all_reduce(t)
+        return int(t.item())
+
+
+def measure_serving(args, S, D, weights, cfg, clocks, label):
+    """The decode benchmark on this rank's S sequences: prefill (untimed), the e2e region through Engine.step, the
+    device-resident region, and the dominant kernel timed alone.  Returns a dict of rank-reduced results."""
     import numpy as np
     import torch
-    import torch.distributed as dist
-    from wukong_b200 import _lib, device as dev
+    from wukong_b200 import device as dev
     from wukong_b200._lib import lib, check
-    from wukong_b200.serving import GPT2Config, synth_weights, Engine
+    from wukong_b200.serving import Engine
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    _lib.require_gpu()
-    torch.cuda.set_device(local)
-    clocks = ClockSampler(local)
-    clocks.launch()                 # streams from here on; start() / stop() mark the timed regions
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    K, W, S = args.steps, args.warmup, args.seqs
-
-    cfg = GPT2Config()
-    weights = synth_weights(cfg, 0)
-    num_pages = S * MBPS
-    eng = Engine(cfg, weights, bcap=S, num_pages=num_pages, max_blocks_per_seq=MBPS, max_rows=max(8192, S),
-                 prefill_chunk=512, page_tokens=PAGE, device="cuda:%d" % local)
+    K, W = args.steps, args.warmup
+    need = 2 * (K + W) + 40                        # decode positions the two timed regions consume per sequence
+    gen_len = max(GEN_NOMINAL, need + 64)          # nobody retires inside these two regions (the continuous-batching region is separate)
+    if PROMPT_HI + gen_len > N_POS:
+        raise SystemExit("steps + warmup too large for the %d learned positions: need %d decode positions" % (N_POS, need))
+    mbps = max(56, (PROMPT_HI + gen_len + 8 + PAGE - 1) // PAGE)
+    eng = Engine(cfg, weights, bcap=S, num_pages=S * mbps, max_blocks_per_seq=mbps, max_rows=max(8192, S),
+                 prefill_chunk=512, page_tokens=PAGE, device="cuda:%d" % D.local)
     m, sched = eng.model, eng.sched
-    prompts = shard_prompts(rank, S, cfg.vocab)
+    prompts = shard_prompts(D.rank, S, cfg.vocab)
     lens = np.array([p.size for p in prompts])
-    budget = MBPS * PAGE - PROMPT_HI - 8          # decode positions available to every sequence
-    need = 2 * (K + W) + 40
-    if need > budget:
-        raise SystemExit("steps + warmup too large for the block-table width: need %d decode positions, have %d" % (need, budget))
-    gen_len = max(GEN_NOMINAL, need + 64)         # nobody retires inside the measurement
     for pr in prompts:
         eng.enqueue(pr, gen_len)
 
-    # ---- prefill (untimed): run engine steps until every sequence is decoding
+    # ---- prefill (untimed): engine steps until every sequence is decoding
     t_pre = time.perf_counter()
     pre_steps = 0
     while True:
         n = sched.plan_step()
-        decode_only = n <= S and np.array_equal(sched.sample_row[sched.row_slot[:n]], np.arange(n, dtype=np.int32)) and n == S
-        # undo is impossible, so run this planned step through the engine's own machinery
-        sched_commit_via_engine(eng, n)
+        decode_only = n == S and np.array_equal(sched.sample_row[sched.row_slot[:n]], np.arange(n, dtype=np.int32))
+        eng._planned = n                           # the plan was inspected first; the engine runs exactly this plan
+        eng.step()
         pre_steps += 1
         if decode_only:
             break
@@ -268,21 +297,11 @@ def run_ours(args):
     torch.cuda.synchronize()
     t_pre = time.perf_counter() - t_pre
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def max_over_ranks(ms):
-        return max_over_ranks_ms(ms, world, "cuda")
-
-
     # ---- e2e: the public serving API, host buffers in and out every step
     for _ in range(W):
         eng.step()
     h2d0, d2h0 = eng.h2d_bytes, eng.d2h_bytes
-    barrier()
+    D.barrier()
     clocks.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(eng.stream)
@@ -290,8 +309,9 @@ def run_ours(args):
     for _ in range(K):
         emitted += eng.step()
     e1.record(eng.stream)
-    barrier()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    D.barrier()
+    clocks.stop()
+    e2e_ms = D.max_ms(e0.elapsed_time(e1))
     h2d_step, d2h_step = (eng.h2d_bytes - h2d0) // K, (eng.d2h_bytes - d2h0) // K
     assert emitted == S * K, (emitted, S * K)
 
@@ -316,18 +336,19 @@ def run_ours(args):
     with torch.cuda.stream(eng.stream):
         for _ in range(W):
             graph.replay()
-    barrier()
+    D.barrier()
+    clocks.start()
     d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(eng.stream):
         d0.record(eng.stream)
         for _ in range(K):
             graph.replay()
         d1.record(eng.stream)
-    barrier()
+    D.barrier()
     clocks.stop()
-    dev_ms = max_over_ranks(d0.elapsed_time(d1))
+    dev_ms = D.max_ms(d0.elapsed_time(d1))
     if dev.gemm_status() != 0:
-        raise SystemExit("tensor-core GEMM reported an expired pipeline wait")
+        raise SystemExit("a kernel reported an expired wait or a refused KV position")
     launches_per_step = m.launches_per_forward + 1
 
     # ---- dominant kernel (paged decode attention) timed alone on the same state, same stream
@@ -340,7 +361,7 @@ def run_ours(args):
         def attn(li):
             s = torch.cuda.current_stream().cuda_stream
             check(lib().wkb_paged_attn_decode(p(m.qkv), 3 * d, p(m.kv.k[li]), p(m.kv.v[li]), p(m.block_table), p(m.row_slot), p(m.row_ctx),
-                                              p(m.att), 1, d, S, cfg.n_head, cfg.n_head, cfg.head_dim, PAGE, MBPS, m.max_ctx, m.scale,
+                                              p(m.att), 1, d, S, cfg.n_head, cfg.n_head, cfg.head_dim, PAGE, mbps, m.max_ctx, m.scale,
                                               p(m.scratch), s), "attn")
         for li in range(cfg.n_layer):
             attn(li)
@@ -360,40 +381,146 @@ def run_ours(args):
     attn_bytes = float(ctx_end.sum()) * 2 * d * 2 + S * d * (4 + 2) + S * 4 * 2
     peak, peak_kind = hbm_peak()
     achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
-    # DRAM traffic per launch: 1.04 x the algorithmic bytes, from the ncu capture summarised in
-    # profiles/paged_attn_decode_ncu.md (taken at 128 sequences; traffic grows with the visible tokens)
-    roofline = {"kernel": "paged_attn_decode_kernel<64,1> (+ chunk merge)", "bound": "hbm", "achieved": achieved, "peak": peak,
+    # DRAM traffic per launch: an ncu capture of this kernel at 128 sequences read and wrote 1.04 x its algorithmic
+    # bytes (every K/V byte once, plus the output rows); the traffic grows with the visible tokens, so that factor is
+    # applied to this launch's algorithmic bytes
+    roofline = {"kernel": "paged_attn_decode_kernel<64,1>", "bound": "hbm", "achieved": achieved, "peak": peak,
                 "peak_source": "of " + peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": 1.04 * attn_bytes,
                 "traffic_source": "ncu at 128 sequences, scaled by visible tokens",
                 "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms,
                 "share_of_step": attn_ms * cfg.n_layer / (dev_ms / K)}
+    # whole-step algorithmic bytes: every weight once + K/V of every visible token over the 12 layers
+    step_bytes = 2.0 * cfg.n_params() - 2.0 * cfg.n_pos * d + float(ctx_end.sum()) * 2 * d * 2 * cfg.n_layer
+    total_seqs = D.sum_int(S)
+    out = {"label": label, "seqs_per_gpu": S, "global_seqs": total_seqs, "dev_ms": dev_ms, "e2e_ms": e2e_ms,
+           "value": total_seqs * K / (dev_ms * 1e-3), "e2e_value": total_seqs * K / (e2e_ms * 1e-3),
+           "h2d": int(h2d_step), "d2h": int(d2h_step), "launches_per_step": int(launches_per_step), "roofline": roofline,
+           "whole_step_hbm_frac": step_bytes / (dev_ms / K * 1e-3) / 1e9 / peak,
+           "prefill": {"steps": pre_steps, "seconds": t_pre, "prompt_tokens": int(lens.sum())}, "mean_ctx": float(ctx_end.mean())}
+    del graph, ag, eng, m, sched
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_continuous_batching(args, S, D, weights, cfg, clocks):
+    """A second timed region in which the scheduler does its whole job: 2 x S requests of 128 greedy tokens each against
+    S slots, so prompt chunks, admissions into freed slots and retirements all happen inside the timing (the reference's
+    goodput bench has the same shape: crates/wukong_codegen_gpu/src/serving.rs:3845-3992).  Goodput counts generated
+    tokens only; the prompt tokens pushed through the model in the same time are reported beside it."""
+    import numpy as np
+    import torch
+    from wukong_b200 import device as dev
+    from wukong_b200.serving import Engine
+    mbps = (PROMPT_HI + GEN_NOMINAL + 8 + PAGE - 1) // PAGE
+    eng = Engine(cfg, weights, bcap=S, num_pages=S * mbps, max_blocks_per_seq=mbps, max_rows=max(8192, S),
+                 prefill_chunk=512, page_tokens=PAGE, device="cuda:%d" % D.local)
+    warm = shard_prompts(D.rank, min(S, 8), cfg.vocab, stream=2)
+    for pr in warm:                                # untimed warm-up: captures the graph, touches every kernel
+        eng.enqueue(pr, 4)
+    eng.run_until_idle()
+    prompts = shard_prompts(D.rank, 2 * S, cfg.vocab, stream=1)
+    for pr in prompts:
+        eng.enqueue(pr, GEN_NOMINAL)
+    base_emitted, base_done = eng.sched.emitted(), eng.sched.completed()
+    D.barrier()
+    clocks.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(eng.stream)
+    steps = eng.run_until_idle()
+    e1.record(eng.stream)
+    D.barrier()
+    clocks.stop()
+    ms = D.max_ms(e0.elapsed_time(e1))
+    gen = D.sum_int(eng.sched.emitted() - base_emitted)
+    prompt_tokens = D.sum_int(int(sum(p.size for p in prompts)))
+    done = D.sum_int(eng.sched.completed() - base_done)
+    if dev.gemm_status() != 0:
+        raise SystemExit("a kernel reported an expired wait or a refused KV position")
+    out = {"value": gen / (ms * 1e-3), "unit": "generated tok/s (whole job, admissions, prompt chunks and retirements inside the timed region)",
+           "requests": done, "generated_tokens": gen, "prompt_tokens": prompt_tokens, "prompt_tok_per_s": prompt_tokens / (ms * 1e-3),
+           "engine_steps_rank0": steps, "seconds": ms * 1e-3, "slots_per_gpu": S, "requests_per_gpu": 2 * S, "tokens_per_request": GEN_NOMINAL}
+    del eng
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from wukong_b200 import _lib
+    from wukong_b200.serving import GPT2Config, synth_weights
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    _lib.require_gpu()
+    torch.cuda.set_device(local)
+    clocks = ClockSampler(local)
+    clocks.launch()                 # streams from here on; start() / stop() mark the timed regions
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    D = Dist(world, rank, local)
+    K, W = args.steps, args.warmup
+    S = args.seqs or max(1, GLOBAL_SEQS // world)
+    cfg = GPT2Config()
+    weights = synth_weights(cfg, 0)
+
+    def note(msg):
+        if rank == 0:
+            print("[bench] " + msg, file=sys.stderr, flush=True)
+
+    main = measure_serving(args, S, D, weights, cfg, clocks, "strong")
+    note("serving regions done: %.3f ms/step" % (main["dev_ms"] / K))
+    extras = {}
+    if not args.no_extras:
+        if world > 1 and not args.seqs:
+            weak = measure_serving(args, GLOBAL_SEQS, D, weights, cfg, clocks, "weak")
+            extras["weak"] = {"value": weak["value"], "unit": UNIT, "sequences_per_gpu": GLOBAL_SEQS, "global_sequences": weak["global_seqs"],
+                              "ms_per_step": weak["dev_ms"] / K, "e2e_value": weak["e2e_value"], "roofline_frac": weak["roofline"]["frac"],
+                              "whole_step_hbm_frac": weak["whole_step_hbm_frac"]}
+            note("weak-scaling figure done")
+        extras["continuous_batching"] = measure_continuous_batching(args, S, D, weights, cfg, clocks)
+        note("continuous-batching region done")
+        import bench_llama
+        try:
+            extras["tp_llama_int4"] = bench_llama.measure_both(args, D, clocks, note)
+        except Exception as exc:            # the headline line must still be printed
+            extras["tp_llama_int4"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+        if world == 1:
+            from wukong_b200 import microbench
+            try:
+                with open(os.devnull, "w") as sink:
+                    res = microbench.run(out=sink)
+                extras["microsuite"] = [{k: r[k] for k in ("case", "shape", "us", "achieved", "unit", "bound", "frac", "peak_source") if k in r} for r in res]
+            except Exception as exc:
+                extras["microsuite"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+            note("micro-suite done")
+    clocks.close()
 
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            tok_s, dt, desc = cpu_decode_tok_s(weights, cfg, 64, 1, 16, threads)      # about 10-15 s of host work
+            tok_s, dt, desc = cpu_decode_tok_s(weights, cfg, min(K, 64), 3, threads)      # the reference arm's sample definition
             cpu = {"value": tok_s, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc, "seconds": dt}
         line = {
-            "metric": METRIC, "value": world * S * K / (dev_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": workload_config(args, world),
-            "e2e": {"value": world * S * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d_step),
-                    "d2h_bytes_per_step": int(d2h_step), "ms_per_step": e2e_ms / K},
-            "gpu_launches": int(launches_per_step * K), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(),
-            "prefill": {"steps": pre_steps, "seconds": t_pre, "prompt_tokens": int(lens.sum())},
-            "mean_ctx": float(ctx_end.mean()),
+            "metric": METRIC, "value": main["value"], "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": main["dev_ms"] / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(S, world),
+            "e2e": {"value": main["e2e_value"], "unit": UNIT, "h2d_bytes_per_step": main["h2d"],
+                    "d2h_bytes_per_step": main["d2h"], "ms_per_step": main["e2e_ms"] / K},
+            "gpu_launches": int(main["launches_per_step"] * K), "roofline": main["roofline"], "cpu_baseline": cpu, "clocks": clocks.summary(),
+            "whole_step_hbm_frac": main["whole_step_hbm_frac"], "prefill": main["prefill"], "mean_ctx": main["mean_ctx"],
         }
+        line.update(extras)
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
-
-
-def sched_commit_via_engine(eng, n_planned):
-    """Run a step whose rows were already planned (used by the prefill loop, which inspects the plan
-    before running it)."""
-    eng._planned = n_planned
-    eng.step()
 
 
 if __name__ == "__main__":

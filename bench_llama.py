@@ -18,7 +18,7 @@ BATCH, CTX0, PAGE = 64, 2048, 16
 
 
 def llama_config_dict(cfg, world, batch, ctx0, how=""):
-    return {"workload": "Llama-7B-shape Q4_0 block stack, batch %d decode at context %d (BASELINE configs[4])" % (batch, ctx0),
+    return {"workload": "Llama-7B-shape Q4_0 block stack, batch %d decode at context %d after a synthetic-fill prefill" % (batch, ctx0),
             "layers": cfg.n_layer, "d_model": cfg.d_model, "heads": cfg.n_head, "kv_heads": cfg.n_kv_head, "d_ff": cfg.d_ff,
             "vocab": cfg.vocab, "batch": batch, "context": ctx0, "weights": "Q4_0 (18 B per 32 weights), activations bf16",
             "kv": "paged bf16, %d-token pages, synthetic fill standing for the prefill" % PAGE,
@@ -90,33 +90,105 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args):
+class _Dist:
+    def __init__(self, world, rank, local):
+        self.world, self.rank, self.local = world, rank, local
+
+
+def _barrier(D):
+    import torch
+    torch.cuda.synchronize()
+    if D.world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        torch.cuda.synchronize()
+
+
+def _status_over_ranks(D):
+    """The library's device status word, worst over the ranks (a rank whose flag wait ran out must not be hidden by
+    rank 0 printing its own clean status)."""
+    import torch
+    from wukong_b200 import device as dev
+    st = int(dev.gemm_status())
+    if D.world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([st], dtype=torch.int32, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        st = int(t.item())
+    return st
+
+
+def check_fused_reduce_equals_nccl(D, cfg_full, weights, note):
+    """Before anything is timed on several ranks: two layers of the stack at full width, three decode steps, once
+    with NCCL all-reduces and once with the fused peer-memory reduce + add + RMSNorm kernel.  Tokens must be equal
+    and the residual streams must agree (bit for bit on two ranks, where each sum has two terms; to fp32
+    re-association otherwise).  Raises on a mismatch."""
+    import torch
+    import torch.distributed as dist
+    from wukong_b200.llama import LlamaConfig, LlamaDecodeModel, PeerReduce
+    device = "cuda:%d" % D.local
+    cfg = LlamaConfig(n_layer=2, d_model=cfg_full.d_model, n_head=cfg_full.n_head, n_kv_head=cfg_full.n_kv_head, d_ff=cfg_full.d_ff,
+                      vocab=cfg_full.vocab, rope_base=cfg_full.rope_base, eps=cfg_full.eps)
+
+    class TwoLayers:                       # a view of the first two layers of the resident weights
+        layers, embed, norm_f, lm_head = weights.layers[:2], weights.embed, weights.norm_f, weights.lm_head
+    Bc, mbps = 16, 4
+
+    def make(peer):
+        m = LlamaDecodeModel(cfg, TwoLayers, D.rank, D.world, Bc, Bc * mbps, mbps, PAGE, device, lambda t: dist.all_reduce(t),
+                             lambda a, b: dist.all_gather_into_tensor(b, a), peer)
+        g = torch.Generator(device=device)
+        g.manual_seed(5 + D.rank)
+        m.kv.k.normal_(generator=g)
+        m.kv.v.normal_(generator=g)
+        m.block_table.copy_(torch.arange(Bc * mbps, dtype=torch.int32, device=device).view(Bc, mbps))
+        m.row_token.copy_(torch.arange(Bc, dtype=torch.int32, device=device) * 37 % cfg.vocab)
+        m.row_pos.fill_(20)
+        m.row_ctx.fill_(21)
+        return m
+
+    peer = PeerReduce(D.rank, D.world, Bc, cfg.d_model, device)
+    ma, mb = make(None), make(peer)
+    _barrier(D)                            # every rank's buffers and mappings exist before the first peer kernel starts
+    for _ in range(3):
+        ta = ma.forward(Bc).clone()
+        ma.advance(Bc)
+        tb = mb.forward(Bc).clone()
+        mb.advance(Bc)
+        torch.cuda.synchronize()
+        if _status_over_ranks(D) != 0:
+            raise RuntimeError("a kernel reported an expired wait during the fused-reduce check")
+        if not torch.equal(ta, tb):
+            raise RuntimeError("tokens differ between the NCCL and the fused peer-memory path")
+        scale = ma.x.abs().max().item()
+        diff = (ma.x - mb.x).abs().max().item()
+        if diff > (0.0 if D.world == 2 else 1e-5 * scale):
+            raise RuntimeError("residual streams differ between the NCCL and the fused path: %g (scale %g)" % (diff, scale))
+    _barrier(D)
+    peer.close()
+    del ma, mb, peer
+    torch.cuda.empty_cache()
+    note("fused peer-memory reduce == NCCL all-reduce path on %d ranks (2 layers, 3 steps)" % D.world)
+
+
+def measure(args, D, clocks, note, use_nccl, cfg, weights):
+    """The Llama-shape int4 decode benchmark on the initialised process group: e2e region, device-resident region and
+    the two HBM streams timed alone.  Returns the pieces of a bench line (rank-reduced times)."""
     import numpy as np
     import torch
     import torch.distributed as dist
-    from wukong_b200 import _lib, device as dev
     from wukong_b200._lib import lib, check
-    from wukong_b200.llama import LlamaConfig, LlamaRankWeights, LlamaDecodeModel, DecodeStepRunner, PeerReduce
+    from wukong_b200.llama import LlamaDecodeModel, DecodeStepRunner, PeerReduce
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    _lib.require_gpu()
-    torch.cuda.set_device(local)
+    world, rank, local = D.world, D.rank, D.local
     device = "cuda:%d" % local
-    clocks = B.ClockSampler(local)
-    clocks.launch()                 # streams from here on; start() / stop() mark the timed regions
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     K, W = args.steps, args.warmup
-    cfg = LlamaConfig(n_layer=args.layers) if args.layers else LlamaConfig()
-    weights = LlamaRankWeights.synth_device(cfg, rank, world, 0, device)
     positions = CTX0 + 2 * (K + W) + 8          # the e2e region and the resident loop both move every sequence on
     mbps = (positions + PAGE - 1) // PAGE
     num_pages = BATCH * mbps
     reduce = (lambda t: dist.all_reduce(t)) if world > 1 else None
     gather = (lambda pairs, allp: dist.all_gather_into_tensor(allp, pairs)) if world > 1 else None
-    peer = PeerReduce(rank, world, BATCH, cfg.d_model, device) if (world > 1 and not args.nccl_allreduce) else None
+    peer = PeerReduce(rank, world, BATCH, cfg.d_model, device) if (world > 1 and not use_nccl) else None
     m = LlamaDecodeModel(cfg, weights, rank, world, BATCH, num_pages, mbps, PAGE, device, reduce, gather, peer)
     g = torch.Generator(device=device)
     g.manual_seed(1 + rank)
@@ -135,17 +207,8 @@ def run_ours(args):
     hr[2 * BATCH:] = CTX0 + 1
     stream = torch.cuda.Stream(device=device)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def note(msg):
-        if rank == 0:
-            print("[llama_int4] " + msg, file=sys.stderr, flush=True)
-
     note("weights and KV resident on %d rank(s)" % world)
+    _barrier(D)                                    # no rank starts a peer kernel before every rank's buffers exist
     with torch.cuda.stream(stream):
         d_rows.copy_(h_rows, non_blocking=True)
         for _ in range(2):
@@ -169,14 +232,15 @@ def run_ours(args):
 
     for _ in range(W):
         e2e_step()
-    barrier()
+    _barrier(D)
     clocks.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(K):
         e2e_step()
     e1.record(stream)
-    barrier()
+    _barrier(D)
+    clocks.stop()
     e2e_ms = B.max_over_ranks_ms(e0.elapsed_time(e1), world, "cuda")
 
     note("e2e region done")
@@ -185,18 +249,20 @@ def run_ours(args):
         d_rows.copy_(h_rows, non_blocking=True)
         for _ in range(W):
             resident.run()
-    barrier()
+    _barrier(D)
+    clocks.start()
     d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         d0.record(stream)
         for _ in range(K):
             resident.run()
         d1.record(stream)
-    barrier()
+    _barrier(D)
     clocks.stop()
     dev_ms = B.max_over_ranks_ms(d0.elapsed_time(d1), world, "cuda")
-    if dev.gemm_status() != 0:
-        raise SystemExit("tensor-core GEMM reported an expired pipeline wait")
+    status = _status_over_ranks(D)
+    if status != 0:
+        raise SystemExit("a kernel reported status %d (expired wait or refused KV position) on some rank" % status)
 
     # ---- the two HBM streams timed alone on the same state: paged attention (KV) and the four linears (weights)
     p = lambda t: t.data_ptr()
@@ -242,33 +308,98 @@ def run_ours(args):
     peak, peak_kind = B.hbm_peak()
     step_ms = dev_ms / K
     a_gbs, g_gbs = attn_bytes / (attn_ms * 1e-3) / 1e9, gemm_bytes / (gemm_ms * 1e-3) / 1e9
-    roofline = {"kernel": ("paged_attn_decode_mma_kernel<%d> (+ chunk merge)" if m.hq != m.hkv else "paged_attn_decode_kernel<128,%d> (+ chunk merge)") % (m.hq // m.hkv), "bound": "hbm", "achieved": a_gbs,
+    # DRAM bytes per attention launch: an ncu capture of this kernel on the batch-64, ctx U[128,4096] case of the
+    # micro-suite read and wrote 1.02 x its algorithmic bytes; the traffic grows with the visible tokens
+    roofline = {"kernel": "paged GQA decode attention, group of %d" % (m.hq // m.hkv), "bound": "hbm", "achieved": a_gbs,
                 "peak": peak, "peak_source": "of " + peak_kind, "unit": "GB/s", "frac": a_gbs / peak,
-                # DRAM bytes per launch: 1.02 x the algorithmic bytes in the ncu capture of this kernel on the batch-64
-                # ctx U[128,4096] case (profiles/paged_attn_decode_mma_ncu.md); traffic grows with the visible tokens
                 "traffic": 1.02 * attn_bytes, "traffic_source": "ncu on the micro-suite's paged_attn case, scaled by visible tokens",
                 "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms, "share_of_step": attn_ms * cfg.n_layer / step_ms,
-                "second_stream": {"kernel": "gemm_q4_tc_kernel (4 linears of a layer)", "bound": "hbm", "achieved": g_gbs, "unit": "GB/s",
+                "second_stream": {"kernel": "W4A16 GEMM (4 linears of a layer)", "bound": "hbm", "achieved": g_gbs, "unit": "GB/s",
                                   "frac": g_gbs / peak, "algorithmic_bytes_per_layer": gemm_bytes, "ms_per_layer": gemm_ms,
                                   "share_of_step": gemm_ms * cfg.n_layer / step_ms}}
+    how = "" if world == 1 else (": NCCL all-reduce" if peer is None else ": fused peer-memory reduce + add + RMSNorm kernel")
+    out = {"value": BATCH * K / (dev_ms * 1e-3), "ms_per_step": step_ms, "e2e_value": BATCH * K / (e2e_ms * 1e-3), "e2e_ms_per_step": e2e_ms / K,
+           "h2d": int(h_rows.numel() * 4), "d2h": int(h_next.numel() * 4), "launches_per_step": m.launches_per_forward + 1,
+           "segments": len(resident.segments), "roofline": roofline, "how": how,
+           "weights_bytes_per_gpu": int(weights.q4_bytes()), "kv_bytes_read_per_step_per_gpu": attn_bytes * cfg.n_layer}
+    _barrier(D)
+    if peer is not None:
+        peer.close()
+    del fwd, resident, m
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_both(args, D, clocks, note):
+    """The `tp_llama_int4` key of the serving benchmark's line: the tensor-parallel step on the same GPUs, with the
+    fused reduce (checked against the NCCL path first) and with NCCL all-reduces."""
+    import torch
+    from wukong_b200.llama import LlamaConfig, LlamaRankWeights
+    cfg = LlamaConfig(n_layer=args.layers) if args.layers else LlamaConfig()
+    weights = LlamaRankWeights.synth_device(cfg, D.rank, D.world, 0, "cuda:%d" % D.local)
+    res = {"metric": B.METRIC, "unit": B.UNIT, "scaling": "strong", "n_gpus": D.world,
+           "config": llama_config_dict(cfg, D.world, BATCH, CTX0)}
+    if D.world > 1:
+        check_fused_reduce_equals_nccl(D, cfg, weights, note)
+        res["fused_equals_nccl"] = True
+    r = measure(args, D, clocks, note, False, cfg, weights)
+    res.update({"value": r["value"], "ms_per_step": r["ms_per_step"], "e2e_value": r["e2e_value"], "roofline": r["roofline"],
+                "reduce": r["how"].lstrip(": ") or "none (one rank)", "graph_segments_per_step": r["segments"]})
+    if D.world > 1:
+        n = measure(args, D, clocks, note, True, cfg, weights)
+        res["nccl_allreduce"] = {"value": n["value"], "ms_per_step": n["ms_per_step"], "e2e_value": n["e2e_value"],
+                                 "graph_segments_per_step": n["segments"]}
+    del weights
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from wukong_b200 import _lib
+    from wukong_b200.llama import LlamaConfig, LlamaRankWeights
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    _lib.require_gpu()
+    torch.cuda.set_device(local)
+    clocks = B.ClockSampler(local)
+    clocks.launch()                 # streams from here on; start() / stop() mark the timed regions
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    D = _Dist(world, rank, local)
+
+    def note(msg):
+        if rank == 0:
+            print("[llama_int4] " + msg, file=sys.stderr, flush=True)
+
+    cfg = LlamaConfig(n_layer=args.layers) if args.layers else LlamaConfig()
+    weights = LlamaRankWeights.synth_device(cfg, rank, world, 0, "cuda:%d" % local)
+    if world > 1 and not args.nccl_allreduce:
+        check_fused_reduce_equals_nccl(D, cfg, weights, note)
+    r = measure(args, D, clocks, note, args.nccl_allreduce, cfg, weights)
+    clocks.close()
+    K, W = args.steps, args.warmup
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             tok_s, sample = cpu_llama_tok_s(cfg, BATCH, CTX0, threads)
             cpu = {"value": tok_s, "unit": B.UNIT, "cores": threads, "kind": "port", "sample": sample}
-        line = {"metric": B.METRIC, "value": BATCH * K / (dev_ms * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": K, "warmup": W,
-                "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        line = {"metric": B.METRIC, "value": r["value"], "unit": B.UNIT, "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "bf16 (Q4_0 weights dequantised in-register, fp32 accumulate)", "data": "synthetic",
-                "config": llama_config_dict(cfg, world, BATCH, CTX0, "" if world == 1 else (": NCCL all-reduce" if peer is None else ": fused peer-memory reduce + add + RMSNorm kernel")),
-                "e2e": {"value": BATCH * K / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": int(h_rows.numel() * 4),
-                        "d2h_bytes_per_step": int(h_next.numel() * 4), "ms_per_step": e2e_ms / K},
-                "gpu_launches": int((m.launches_per_forward + 1) * K), "graph_segments_per_step": len(resident.segments), "roofline": roofline,
+                "config": llama_config_dict(cfg, world, BATCH, CTX0, r["how"]),
+                "e2e": {"value": r["e2e_value"], "unit": B.UNIT, "h2d_bytes_per_step": r["h2d"],
+                        "d2h_bytes_per_step": r["d2h"], "ms_per_step": r["e2e_ms_per_step"]},
+                "gpu_launches": int(r["launches_per_step"] * K), "graph_segments_per_step": r["segments"], "roofline": r["roofline"],
                 "cpu_baseline": cpu, "clocks": clocks.summary(),
-                "weights_bytes_per_gpu": int(weights.q4_bytes()), "kv_bytes_read_per_step_per_gpu": attn_bytes * cfg.n_layer}
+                "weights_bytes_per_gpu": r["weights_bytes_per_gpu"], "kv_bytes_read_per_step_per_gpu": r["kv_bytes_read_per_step_per_gpu"]}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
-        if peer is not None:
-            peer.close()
         dist.destroy_process_group()

@@ -233,6 +233,10 @@ int wkb_tp_reduce_add_rmsnorm(const void* const* parts, void* const* flags, int6
                               int64_t phase, int64_t phases_per_step, float* x, const float* gamma_or_null, void* out_bf16,
                               int64_t rows, int64_t cols, float eps, void* stream);
 int wkb_tp_step_bump(void* step_ptr, void* stream);
+/* Flag-wait limit of later wkb_tp_reduce_add_rmsnorm launches (process-wide; <= 0: the default, one second).  A rank
+ * whose wait runs out records 21, leaves x / out untouched and marks itself dead in every flag row, so every later
+ * phase on every rank ends with 22 at once; zero the flag rows to start again. */
+void wkb_tp_set_wait_limit_ms(int64_t ms);
 /* CUDA IPC plumbing for the peer mappings: export the allocation containing `ptr` as a 64-byte handle plus the
  * offset of `ptr` inside it; map a peer's allocation (add the peer's offset to the returned base). */
 int wkb_ipc_export(void* ptr, void* handle64, int64_t* offset);
@@ -258,8 +262,15 @@ int wkb_rowargmax_i32(const float* x, int* out, int64_t rows, int64_t cols, void
 /* Same with a row pitch ld >= cols (padded logits). */
 int wkb_rowargmax_strided_i32(const float* x, int* out, int64_t rows, int64_t cols, int64_t ld, void* stream);
 int wkb_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream);
-/* Decode feedback on the device: row_token = next_tok, row_pos += 1, row_ctx += 1 for active rows. */
-int wkb_decode_advance(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, int64_t n, void* stream);
+/* Host-side deadline on a stream, after the reference's `sync_within` (crates/wukong_codegen_gpu/src/gpu.rs:250-262,
+ * :302): 0 = all work queued on the stream has completed, -1 = timeout_ms passed with work still in flight (nothing is
+ * cancelled), > 0 = a CUDA error.  wkb_device_sleep_ms queues a kernel that holds the stream for about ms (<= 2000)
+ * milliseconds and then ends by itself: a way to exercise the deadline. */
+int wkb_stream_sync_within(void* stream, int64_t timeout_ms);
+int wkb_device_sleep_ms(int64_t ms, void* stream);
+/* Decode feedback on the device: row_token = next_tok, row_pos += 1, row_ctx += 1 for active rows.  A row already at
+ * max_pos (the last position its block-table row covers; < 0: no limit) is parked instead: pos = -1, ctx = 0. */
+int wkb_decode_advance(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, int64_t n, int64_t max_pos, void* stream);
 
 /* Paged KV cache (behaviour of crates/wukong_codegen_gpu/src/paged_kv.rs:84-151,428-628 and
  * paged_attention.rs:395-534,1343-1410; kernels and HBM layout are this library's own).
@@ -325,8 +336,10 @@ void wkb_blockmgr_flat_table(void* h, uint32_t* out);
 void wkb_blockmgr_ctx_lens(void* h, int32_t* out);
 
 /* Continuous-batching scheduler (host; behaviour of serving.rs:1346-1595): first-fit admission with
- * a 64-request look-ahead, plan -> run -> commit per step.  plan_step returns the row count, 0 when
- * idle, -1 when pages ran out (nothing changed), -3 when the previous step was not committed. */
+ * a 64-request look-ahead, plan -> run -> commit per step.  plan_step admits first (admission is kept whatever
+ * follows), then plans the rows of every slot whose pages fit, decode rows before prompt chunks; a slot that cannot get
+ * a page sits the step out.  It returns the row count, 0 when idle, -1 when sequences are resident but no row at all can
+ * get a page (terminal unless the caller releases a slot), -3 when the previous step was not committed. */
 void* wkb_sched_new(int64_t bcap, int64_t num_blocks, int64_t block_size, int64_t max_blocks_per_seq,
                     int64_t max_rows, int64_t prefill_chunk);
 void wkb_sched_delete(void* h);
@@ -352,6 +365,21 @@ int64_t wkb_sched_output(void* h, int64_t request, int32_t* out, int64_t cap);
 int wkb_gemm_bf16_nt(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int c_bf16,
                      int64_t m, int64_t n, int64_t k, const float* bias, int64_t act, const float* residual,
                      int64_t ldr, void* stream);
+/* Whether a shape splits K is a function of (m, n, k) only; a split shape keeps fp32 partials in a workspace.  This entry
+ * uses one default workspace per device, shared by every stream and host thread: at most one split-shaped GEMM may be
+ * in flight per device through it.  wkb_gemm_init allocates that workspace (32 MiB) and the status word; call it once
+ * per device before capturing into a CUDA graph -- a split-shaped call that finds no workspace while its stream is
+ * capturing returns cudaErrorNotReady (600) and launches nothing.  wkb_gemm_bf16_nt_ws is the same GEMM with a caller
+ * workspace of at least wkb_gemm_workspace_bytes(m, n, k) bytes (0: the shape does not split), one per stream. */
+int wkb_gemm_init(void);
+int64_t wkb_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int wkb_gemm_bf16_nt_ws(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int c_bf16,
+                        int64_t m, int64_t n, int64_t k, const float* bias, int64_t act, const float* residual,
+                        int64_t ldr, void* workspace, int64_t workspace_bytes, void* stream);
+/* Reads and clears the library's device status word of the current device (synchronises): 0, or the code of the last
+ * event -- 1-4 / 11-17 a bounded pipeline wait of the dense / W4A16 GEMM ran out, 21 the tensor-parallel reduce's flag
+ * wait ran out, 31 a KV append met a position past its block-table row (the row was skipped).  The word is one per
+ * device, shared by every stream and thread: concurrent users see each other's codes and the read clears them all. */
 int wkb_gemm_status(void);
 
 /* W4A16 GEMM on the tensor cores for batched decode: out[m, n] = x[m, k] . W[n, k]^T, x bf16 with row pitch ldx.

@@ -1,0 +1,222 @@
+"""GPU parity at the benchmark configurations themselves (the other GPU tests use small shapes so the oracle is
+quick): the paged GQA attention case of the micro-suite, one full-width GPT-2-124M-shape decode step, one
+full-width Llama-7B-shape int4 layer plus LM head at batch 64 and context 2048 (one rank, and split over two
+emulated ranks), and the dense GEMM at 4096^3 / 8192^3.  The reference gates its own paged attention the same two
+ways on its real geometry (f64 tolerance and bit-identity across two page layouts:
+crates/wukong_codegen_gpu/src/paged_attention.rs:2047-2119, crates/wukong_codegen_gpu/src/serving.rs:2944)."""
+import math
+
+import numpy as np
+import pytest
+
+from tolerances import check_logits, clear_winner
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+    from wukong_b200 import _lib, device
+    _lib.require_gpu()
+    return torch, device
+
+
+def u16(t):
+    import torch
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def test_paged_attention_microsuite_case_vs_f64_oracle_and_second_layout(env, orc):
+    """Batch 64, contexts uniform in [128, 4096], 32 query / 8 KV heads of dim 128, 16-token pages drawn as a seeded
+    permutation of a 65 536-page pool: every output against the oracle's f64 attention over the same cache bytes, and
+    bit-identical output after the same history is moved to a different set of physical pages."""
+    torch, dev = env
+    from wukong_b200.microbench import build_paged_attn_case
+    c = build_paged_attn_case(seed=0, torch_seed=1234)
+    B, H, HKV, D, page, mbps, kv = c["B"], c["H"], c["HKV"], c["D"], c["page"], c["mbps"], c["kv"]
+    out = torch.empty(B, H * D, dtype=torch.float32, device="cuda")
+    scratch = dev.paged_attn_scratch(B, H, D, c["max_ctx"])
+    dev.paged_attn_decode(c["q"], H * D, kv, 0, c["bt"], c["row_slot"], c["row_ctx"], out, B, H, mbps, c["max_ctx"], c["scale"], scratch)
+    got = out.cpu().numpy()
+    ref = orc.paged_attn_decode(c["q"].cpu().numpy(), u16(kv.k[0]), u16(kv.v[0]), 1, c["table"], c["ctx"], B, H, HKV, D, page, mbps,
+                                c["scale"], layout=1)
+    # head_dim 128 with a GQA group runs on the tensor cores with bf16 softmax weights (2^-9 each); values are ~N(0,1),
+    # so a weighted mean of them carries up to ~2^-9 absolute -- the same bar as the small-shape test of this kernel
+    assert np.allclose(got, ref, rtol=4e-3, atol=2e-3), float(np.abs(got - ref).max())
+    # second physical layout: the same logical pages at other pool positions
+    rng = np.random.default_rng(77)
+    used = c["pages_used"]
+    old = np.concatenate([c["table"][b, :(int(c["ctx"][b]) + page - 1) // page] for b in range(B)]).astype(np.int64)
+    assert old.size == used
+    new = rng.permutation(c["pool"])[:used].astype(np.int64)
+    kv2 = dev.PagedKV(1, c["pool"], HKV, D, page)
+    kv2.k.fill_(float("nan")); kv2.v.fill_(float("nan"))
+    o_t, n_t = torch.from_numpy(old).cuda(), torch.from_numpy(new).cuda()
+    kv2.k[0].index_copy_(0, n_t, kv.k[0].index_select(0, o_t))
+    kv2.v[0].index_copy_(0, n_t, kv.v[0].index_select(0, o_t))
+    table2 = np.zeros_like(c["table"])
+    nxt = 0
+    for b in range(B):
+        n = (int(c["ctx"][b]) + page - 1) // page
+        table2[b, :n] = new[nxt:nxt + n]
+        nxt += n
+    out2 = torch.empty_like(out)
+    dev.paged_attn_decode(c["q"], H * D, kv2, 0, torch.from_numpy(table2.view(np.int32)).cuda(), c["row_slot"], c["row_ctx"], out2, B, H,
+                          mbps, c["max_ctx"], c["scale"], scratch)
+    assert torch.equal(out.view(torch.int32), out2.view(torch.int32)), "output depends on the physical page layout"
+    assert not np.isnan(got).any()
+    # bf16 output (what the serving step consumes) is the rounding of the f32 output
+    outb = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
+    dev.paged_attn_decode(c["q"], H * D, kv, 0, c["bt"], c["row_slot"], c["row_ctx"], outb, B, H, mbps, c["max_ctx"], c["scale"], scratch)
+    assert np.array_equal(u16(outb), orc.to_bf16_bits(got).reshape(B, -1))
+
+
+def test_gpt2_124m_shape_decode_steps_vs_oracle_model(env, orc):
+    """Two decode steps of the full-width GPT-2-124M-shape model (12 layers, d 768, 12 heads, FFN 3072, vocabulary 50257,
+    bf16 weights, seed 0) for 8 sequences with contexts in [32, 512] over a seeded KV cache in permuted pages: logits
+    within the stated bf16 bar of the oracle model's, greedy tokens equal wherever the oracle's winner is clear."""
+    torch, dev = env
+    from oracle.gpt2_model import OracleGPT2
+    from wukong_b200.serving import GPT2Config, synth_weights, DecodeModel
+    cfg = GPT2Config()
+    w = synth_weights(cfg, 0)
+    S, page, mbps = 8, 16, 36
+    rng = np.random.default_rng(21)
+    ctx = np.concatenate([[32, 512], rng.integers(32, 513, S - 2)]).astype(np.int32)
+    num_pages = S * mbps
+    m = DecodeModel(cfg, w, bcap=S, num_pages=num_pages, max_blocks_per_seq=mbps, page_tokens=page)
+    m.keep_logits = True
+    g = torch.Generator(device="cuda"); g.manual_seed(3)
+    m.kv.k.normal_(0.0, 0.5, generator=g)
+    m.kv.v.normal_(0.0, 0.5, generator=g)
+    table = rng.permutation(num_pages).astype(np.int32).reshape(S, mbps)
+    m.block_table.copy_(torch.from_numpy(table))
+    d = cfg.d_model
+    # the oracle's contiguous caches: [positions, heads * head_dim] bf16 bits, gathered through the block table
+    model = OracleGPT2(cfg, w, orc)
+    kcs, vcs = [], []
+    for s in range(S):
+        kc, vc = model.new_cache(int(ctx[s]) + 4)
+        npg = kc[0].shape[0] // page
+        pages = torch.from_numpy(table[s, :npg].astype(np.int64)).cuda()
+        for li in range(cfg.n_layer):
+            # device pages are [page][head][token][dim]; the oracle's cache rows are [token][head * dim]
+            kc[li][:] = u16(m.kv.k[li].index_select(0, pages).permute(0, 2, 1, 3)).reshape(npg * page, d)
+            vc[li][:] = u16(m.kv.v[li].index_select(0, pages).permute(0, 2, 1, 3)).reshape(npg * page, d)
+        kcs.append(kc); vcs.append(vc)
+    toks = rng.integers(0, cfg.vocab, S).astype(np.int32)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.int32)).cuda()
+    worst = 0.0
+    for step in range(2):
+        pos = ctx + step
+        m.row_token.copy_(i32(toks)); m.row_pos.copy_(i32(pos)); m.row_slot.copy_(i32(np.arange(S))); m.row_ctx.copy_(i32(pos + 1))
+        m.sample_rows.copy_(i32(np.arange(S)))
+        m.forward(S, S)
+        torch.cuda.synchronize()
+        assert dev.gemm_status() == 0
+        got = m.logits.cpu().numpy()[:S, :cfg.vocab]
+        got_tok = m.next_tok.cpu().numpy()[:S]
+        ref_tok, ref = model.step([int(t) for t in toks], [int(p) for p in pos], kcs, vcs)
+        worst = max(worst, check_logits(got, ref, what="gpt2 step %d" % step))
+        clear = clear_winner(ref)
+        assert clear.sum() >= S // 2
+        assert np.array_equal(got_tok[clear], np.asarray(ref_tok)[clear])
+        toks = np.asarray(ref_tok, np.int32)
+    # the fused arg-max LM head (what the serving step runs) picks the tokens of the materialised logits
+    m.keep_logits = False
+    m.row_token.copy_(i32(toks)); m.row_pos.copy_(i32(ctx + 1)); m.row_ctx.copy_(i32(ctx + 2))
+    fused = m.forward(S, S).clone()
+    m.keep_logits = True
+    plain = m.forward(S, S).clone()
+    assert torch.equal(fused[:S], plain[:S])
+    print("gpt2-124M-shape logits: worst error = %.3f of the allowance" % worst)
+
+
+def _llama_full_width_layer(torch, dev, orc, world):
+    from oracle.llama_model import OracleLlama
+    from wukong_b200 import llama
+    cfg = llama.LlamaConfig(n_layer=1)           # one layer of the 7B shape at full width: d 4096, 32 / 8 heads, FFN 11008, vocab 32000
+    w = llama.synth_llama_raw(cfg, seed=4, sigma=0.02)
+    B, CTX, page = 64, 2048, 16
+    mbps = (CTX + 1 + page - 1) // page
+    num_pages = B * mbps
+    rng = np.random.default_rng(8)
+    table = rng.permutation(num_pages).astype(np.int32).reshape(B, mbps)
+    hd, hkv = cfg.head_dim, cfg.n_kv_head
+    g = torch.Generator(device="cuda"); g.manual_seed(9)
+    kfull = torch.randn((num_pages, hkv, page, hd), device="cuda", generator=g).to(torch.bfloat16)
+    vfull = torch.randn((num_pages, hkv, page, hd), device="cuda", generator=g).to(torch.bfloat16)
+    toks = rng.integers(0, cfg.vocab, B).astype(np.int32)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.int32)).cuda()
+    rows = (i32(toks), i32(np.full(B, CTX)), i32(np.arange(B)), i32(np.full(B, CTX + 1)), torch.from_numpy(table).cuda())
+    if world == 1:
+        model = llama.LlamaDecodeModel(cfg, llama.LlamaRankWeights.from_raw(cfg, w), 0, 1, bcap=B, num_pages=num_pages, max_blocks_per_seq=mbps)
+        model.kv.k[0].copy_(kfull); model.kv.v[0].copy_(vfull)
+        model.row_token.copy_(rows[0]); model.row_pos.copy_(rows[1]); model.row_slot.copy_(rows[2]); model.row_ctx.copy_(rows[3])
+        model.block_table.copy_(rows[4])
+        got_tok = model.forward(B).cpu().numpy()
+        torch.cuda.synchronize()
+        got = model.logits.cpu().numpy()[:B]
+    else:
+        tp = llama.LocalTensorParallel(cfg, w, world, bcap=B, num_pages=num_pages, max_blocks_per_seq=mbps)
+        per = hkv // world
+        for r, mm in enumerate(tp.models):
+            mm.kv.k[0].copy_(kfull[:, r * per:(r + 1) * per]); mm.kv.v[0].copy_(vfull[:, r * per:(r + 1) * per])
+        tp.set_rows(*rows)
+        got_tok = tp.forward(B).cpu().numpy()
+        torch.cuda.synchronize()
+        got = np.concatenate([mm.logits.cpu().numpy()[:B] for mm in tp.models], axis=1)
+    assert dev.gemm_status() == 0
+    # the oracle's caches: float32 [positions, kv_heads * head_dim] holding the bf16 values, through the block table
+    def gather(full, s):
+        pages = torch.from_numpy(table[s].astype(np.int64)).cuda()
+        return full.index_select(0, pages).permute(0, 2, 1, 3).reshape(mbps * page, hkv * hd).float().cpu().numpy()
+    out = {}
+    for operand, rel in (("bf16", 8e-3), ("exact", 2e-2)):
+        oracle = OracleLlama(cfg, w, orc, operand)
+        kcs = [[gather(kfull, s)] for s in range(B)]
+        vcs = [[gather(vfull, s)] for s in range(B)]
+        ref_tok, ref = oracle.step([int(t) for t in toks], [CTX] * B, kcs, vcs)
+        out[operand] = check_logits(got, ref, rel, what="llama %s world %d" % (operand, world))
+        clear = clear_winner(ref, rel)
+        assert np.array_equal(got_tok[:B][clear], np.asarray(ref_tok)[clear])
+        del oracle
+    print("llama-7B-shape layer, %d rank(s): worst error = %.3f (bf16-operand oracle, 8e-3) / %.3f (exact dequant, 2e-2) of the allowance"
+          % (world, out["bf16"], out["exact"]))
+
+
+def test_llama_7b_shape_int4_layer_batch64_ctx2048_vs_oracle(env, orc):
+    """One full-width layer of the Llama-7B-shape Q4_0 stack plus final norm, LM head and arg-max, batch 64 at context
+    2048 over a seeded N(0,1) cache in permuted pages, against the oracle model: within 8e-3 when the oracle holds each
+    weight as the bf16 operand the tensor core multiplies, within the stated 2e-2 against the exact dequantisation."""
+    torch, dev = env
+    _llama_full_width_layer(torch, dev, orc, 1)
+
+
+def test_llama_7b_shape_int4_layer_two_emulated_ranks_vs_oracle(env, orc):
+    """The same layer split over two tensor-parallel ranks (heads, FFN columns and vocabulary rows; O / down by K slices;
+    KV heads sharded), both ranks run in lockstep on one device."""
+    torch, dev = env
+    _llama_full_width_layer(torch, dev, orc, 2)
+
+
+@pytest.mark.parametrize("size", [4096, 8192])
+def test_dense_gemm_microsuite_sizes_exact_on_small_integers(env, size):
+    """The bf16 GEMM at the micro-suite's 4096^3 and 8192^3: on small-integer operands every product and partial sum is
+    exact in fp32, so the tensor-core result must equal the integer result bit for bit whatever the summation order;
+    plus linearity in A."""
+    torch, dev = env
+    g = torch.Generator(device="cuda"); g.manual_seed(size)
+    a1 = torch.randint(-4, 5, (size, size), device="cuda", generator=g).to(torch.bfloat16)
+    a2 = torch.randint(-4, 5, (size, size), device="cuda", generator=g).to(torch.bfloat16)
+    b = torch.randint(-4, 5, (size, size), device="cuda", generator=g).to(torch.bfloat16)
+    c1 = dev.gemm_bf16_nt(a1, b)
+    # integer reference in slabs of K (int32 matmul is not available on the device; fp64 of integers is exact)
+    want = torch.zeros(size, size, dtype=torch.float64, device="cuda")
+    for k0 in range(0, size, 2048):
+        want += a1[:, k0:k0 + 2048].double() @ b[:, k0:k0 + 2048].double().T
+    assert torch.equal(c1.double(), want)
+    c12 = dev.gemm_bf16_nt(a1 + a2, b)
+    assert torch.equal(c12, c1 + dev.gemm_bf16_nt(a2, b))
+    assert dev.gemm_status() == 0

@@ -5,14 +5,15 @@ carved its whole arena at start-up, or a plug-in invoked from inside another run
 region.  `wkb_gemv_q4_0_f32_noalloc` serves them by keeping the per-call activation scratch in a
 fixed device array of the library.  This file is collected last on purpose, so a failure here cannot
 hide the result of any other test.  Two calls in a row check that the array, which keeps the previous
-call's contents, is fully rewritten; the oversize refusal is checked too."""
+call's contents, is fully rewritten; both calls are also held to the CPU oracle's GEMV bit for bit; the oversize
+refusal is checked too."""
 import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
 
 
-def test_noalloc_gemv_matches_regular_entry_twice():
+def test_noalloc_gemv_matches_regular_entry_twice(orc):
     import torch
     from wukong_b200 import _lib, lib, device as dev
     _lib.require_gpu()
@@ -27,7 +28,8 @@ def test_noalloc_gemv_matches_regular_entry_twice():
         raw.reshape(-1, 18)[:, 1] = sc >> 8
         qs, d = dev.q_split(torch.from_numpy(raw).cuda(), n * nb, q4=True)
         for call in range(2):   # the second call sees the first call's scratch contents
-            x = torch.from_numpy((rng.standard_normal(k) * (1 + 9 * call)).astype(np.float32)).cuda()
+            x_host = (rng.standard_normal(k) * (1 + 9 * call)).astype(np.float32)
+            x = torch.from_numpy(x_host).cuda()
             xq, dx, sx = dev.quantize_act(x)
             want = dev.gemv_q_contract(qs, d, xq, dx, sx, n, k, q4=True)
             got = torch.full((n,), 7.0, device="cuda")
@@ -35,6 +37,9 @@ def test_noalloc_gemv_matches_regular_entry_twice():
             torch.cuda.synchronize()
             assert rc == 0
             assert torch.equal(got.view(torch.int32), want.view(torch.int32)), (n, k, call)   # bit for bit
+            # and against the CPU oracle's GEMV on the raw blocks (an independent implementation of the same contract)
+            st, ref = orc.gemv_q(raw, x_host, n)
+            assert st == 0 and got.cpu().numpy().tobytes() == ref.tobytes(), (n, k, call)
     # beyond the fixed scratch: refused, output untouched
     y = torch.full((4,), 7.0, device="cuda")
     rc = L.wkb_gemv_q4_0_f32_noalloc(qs.data_ptr(), d.data_ptr(), x.data_ptr(), y.data_ptr(), 4, 32768 + 32, s)

@@ -38,13 +38,18 @@ def main():
 
     peer = PeerReduce(rank, world, B, cfg.d_model, device)
     ma, mb = make(None), make(peer)
+    torch.cuda.synchronize()
+    dist.barrier()                      # every rank's buffers and mappings exist before the first peer kernel starts
+    torch.cuda.synchronize()
     for _ in range(3):
         ta = ma.forward(B).clone()
         ma.advance(B)
         tb = mb.forward(B).clone()
         mb.advance(B)
         torch.cuda.synchronize()
-        assert dev.gemm_status() == 0
+        st = torch.tensor([dev.gemm_status()], dtype=torch.int32, device=device)
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)            # a wait that ran out on any rank fails every rank
+        assert int(st.item()) == 0
         assert torch.equal(ta, tb), "tokens differ between the NCCL and the peer-memory path"
         scale = ma.x.abs().max().item()
         diff = (ma.x - mb.x).abs().max().item()

@@ -17,20 +17,13 @@
 
 namespace {
 
+// Staging memory and stream of one (host thread, device) pair.
 struct Arena {
   char* base = nullptr;
   size_t cap = 0, used = 0;
   cudaStream_t stream = nullptr;
-  int device = -1;
   void begin(size_t need) {
-    int dev;
-    WKB_CUDA_CHECK(cudaGetDevice(&dev));
-    if (!stream || dev != device) {
-      WKB_CUDA_CHECK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
-      device = dev;
-      base = nullptr;
-      cap = 0;
-    }
+    if (!stream) WKB_CUDA_CHECK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     need += 4096;
     if (need > cap) {
       if (base) WKB_CUDA_CHECK(cudaFree(base));
@@ -60,7 +53,32 @@ struct Arena {
   void sync() { WKB_CUDA_CHECK(cudaStreamSynchronize(stream)); }
 };
 
-thread_local Arena g_arena;
+// One arena per device for each host thread, kept when the thread switches devices and released at thread exit
+// (with the owning device made current for the release).
+struct ArenaSet {
+  static constexpr int MAX_DEV = 64;
+  Arena per_device[MAX_DEV];
+  Arena& current() {
+    int dev;
+    WKB_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEV) { fprintf(stderr, "wukong_b200: device index %d out of range\n", dev); abort(); }
+    return per_device[dev];
+  }
+  ~ArenaSet() {
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) return;   // the runtime is already gone (process exit)
+    for (int d = 0; d < MAX_DEV; ++d) {
+      Arena& a = per_device[d];
+      if (!a.stream && !a.base) continue;
+      if (cudaSetDevice(d) != cudaSuccess) continue;
+      if (a.stream) { cudaStreamSynchronize(a.stream); cudaStreamDestroy(a.stream); }
+      if (a.base) cudaFree(a.base);
+    }
+    cudaSetDevice(prev);
+    cudaGetLastError();
+  }
+};
+thread_local ArenaSet g_arenas;
 
 static inline size_t pad(size_t b) { return (b + 255) & ~(size_t)255; }
 static void check_launch(int code, const char* what) {
@@ -77,7 +95,7 @@ static void gemm_host(const void* a, int adt, const void* b, int bdt, float* c, 
   if (m <= 0 || k <= 0 || n <= 0) return;  // gemm.rs:1018-1020: nothing written
   size_t ea = adt == 0 ? 4 : 2, eb = bdt == 0 ? 4 : 2;
   size_t na = (size_t)m * k, nbb = (size_t)k * n, nc = (size_t)m * n;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad(na * ea) + pad(nbb * eb) + pad(nc * 4) + pad((size_t)n * 4));
   void* da = A.take(na * ea);
   void* db = A.take(nbb * eb);
@@ -96,7 +114,7 @@ static i64 gemv_half_host(const u16* w, i64 nw, const float* x, i64 nx, float* y
   if ((__int128)ny * (__int128)nx != (__int128)nw) return -2;
   if (ny == 0) return 0;
   if (nx == 0) { memset(y, 0, (size_t)ny * 4); return 0; }
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)nw * 2) + pad((size_t)nx * 4) + pad((size_t)ny * 4));
   u16* dw = A.up(w, (size_t)nw);
   float* dx = A.up(x, (size_t)nx);
@@ -121,7 +139,7 @@ static i64 gemv_q_host(const u8* w, i64 nw, const float* x, i64 nx, float* y, i6
   if (ny == 0) return 0;
   if (nx == 0) { memset(y, 0, (size_t)ny * 4); return 0; }
   i64 nb = (nx + 31) / 32, nblocks = ny * nb;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   size_t qb = (size_t)nblocks * (bb - 2);
   A.begin(pad((size_t)nw) + pad(qb) + pad((size_t)nblocks * 2) + pad((size_t)nx * 4) + pad((size_t)nb * 32) +
           2 * pad((size_t)nb * 4) + pad((size_t)ny * 4));
@@ -147,7 +165,7 @@ static i64 quantize_host(const float* x, i64 nx, u8* q, i64 nq, i64 k, int q4) {
   i64 rows = nx / k;
   if (!q_need(rows, k, q4 ? 18 : 34, nq)) return -2;
   if (rows == 0) return 0;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)nx * 4) + pad((size_t)nq));
   float* dx = A.up(x, (size_t)nx);
   u8* dq = A.out<u8>((size_t)nq);
@@ -163,7 +181,7 @@ static i64 dequant_int4_host(const u8* q, i64 nq, const float* scale, i64 ns, co
   uint64_t n = (uint64_t)nout, g = (uint64_t)group, groups = (n + g - 1) / g;
   if ((uint64_t)nq != (n + 1) / 2 || (uint64_t)ns != groups || (nz >= 0 && (uint64_t)nz != groups)) return -2;
   if (n == 0) return 0;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)nq) + 2 * pad((size_t)groups * 4) + pad((size_t)n * 4));
   u8* dq = A.up(q, (size_t)nq);
   float* dsc = A.up(scale, (size_t)groups);
@@ -231,7 +249,7 @@ void wukong_sgemm_f16_tn_parallel(const u16* a, const u16* b, float* c, i64 m, i
 // ---- GEMV (gemv.rs:197-326, gemv_half.rs:465-529) ----
 void wukong_sgemv_alpha(const float* a, const float* x, float* y, i64 m, i64 n, float alpha) {
   if (m <= 0 || n <= 0) return;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)m * n * 4) + pad((size_t)n * 4) + pad((size_t)m * 4));
   float* da = A.up(a, (size_t)m * n);
   float* dx = A.up(x, (size_t)n);
@@ -267,7 +285,7 @@ i64 wukong_dequant_u4_f32(const u8* q, i64 nq, const float* scale, i64 ns, const
 // ---- elementwise (vmath.rs:1063-1130, :2022-2050; velem.rs:212-236) ----
 void wukong_vmath_f32(const float* x, float* out, i64 n, i64 op) {
   if (n <= 0) return;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(2 * pad((size_t)n * 4));
   float* dx = A.up(x, (size_t)n);
   float* dout = A.out<float>((size_t)n);
@@ -278,7 +296,7 @@ void wukong_vmath_f32(const float* x, float* out, i64 n, i64 op) {
 void wukong_vmath_f32_parallel(const float* x, float* out, i64 n, i64 op) { wukong_vmath_f32(x, out, n, op); }
 void wukong_vmath2_f32(const float* x, const float* y, float* out, i64 n, i64 op) {
   if (n <= 0) return;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(3 * pad((size_t)n * 4));
   float* dx = A.up(x, (size_t)n);
   float* dy = A.up(y, (size_t)n);
@@ -290,7 +308,7 @@ void wukong_vmath2_f32(const float* x, const float* y, float* out, i64 n, i64 op
 void wukong_velem_f32(const float* x, const float* y, float* out, i64 n, float a, float b, float c, i64 op) {
   if (n <= 0) return;
   bool use_y = (op & (256 | 512 | 1024)) != 0;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(3 * pad((size_t)n * 4));
   float* dx = A.up(x, (size_t)n);
   float* dy = use_y ? A.up(y, (size_t)n) : nullptr;
@@ -307,7 +325,7 @@ static void norm_host(const float* x, float* out, const float* gamma, const floa
   if (rows <= 0 || cols <= 0) return;
   if (affine ? (op != 1 && op != 2) : (op < 0 || op > 4)) return;  // unknown code: nothing written
   size_t n = (size_t)rows * cols;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(2 * pad(n * 4) + 2 * pad((size_t)cols * 4));
   float* dx = A.up(x, n);
   float* dg = A.up(gamma, (size_t)cols);
@@ -341,7 +359,7 @@ i64 wukong_attention_kv_f32(const float* q, i64 nq, const float* k, i64 nk, cons
   __int128 q_ext = ((__int128)sq - 1) * q_stride + q_row;
   __int128 kv_ext = skv == 0 ? 0 : ((__int128)skv - 1) * kv_stride + kv_row;
   if (q_ext > nq || q_ext > no || kv_ext > nk || kv_ext > nv) return -2;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(2 * pad((size_t)q_ext * 4) + 2 * pad((size_t)kv_ext * 4 + 16));
   float* dq = A.up(q, (size_t)q_ext);
   float* dk = kv_ext ? A.up(k, (size_t)kv_ext) : (float*)A.take(16);
@@ -369,7 +387,7 @@ i64 wukong_attention_kv_batch_f32(const float* q, i64 nq, const float* k, i64 nk
   if (q_ext > nq || q_ext > no || kv_ext > nk || kv_ext > nv || batch > nl || batch > np) return -2;
   for (i64 b = 0; b < batch; ++b)
     if (kv_lens[b] < 0 || (i64)kv_lens[b] > skv) return -1;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(2 * pad((size_t)q_ext * 4) + 2 * pad((size_t)kv_ext * 4 + 16) + 2 * pad((size_t)batch * 4));
   float* dq = A.up(q, (size_t)q_ext);
   float* dk = kv_ext ? A.up(k, (size_t)kv_ext) : (float*)A.take(16);
@@ -403,7 +421,7 @@ i64 wukong_kv_append_f32(float* cache, i64 ncache, const float* row, i64 nrow, i
 void wukong_attention_f32(const float* q, const float* k, const float* v, float* o, i64 s, i64 d, float scale, i64 causal) {
   if (s <= 0 || d <= 0) return;
   size_t n = (size_t)s * d;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(4 * pad(n * 4));
   float* dq = A.up(q, n);
   float* dk = A.up(k, n);
@@ -418,7 +436,7 @@ void wukong_attention_f32(const float* q, const float* k, const float* v, float*
 void wukong_rope_f32(const float* x, const float* inv_freq, float* out, i64 rows, i64 half) {
   if (rows <= 0 || half <= 0) return;
   size_t n = (size_t)rows * half * 2;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(2 * pad(n * 4) + pad((size_t)half * 4));
   float* dx = A.up(x, n);
   float* df = A.up(inv_freq, (size_t)half);
@@ -432,7 +450,7 @@ void wukong_rope_f32_parallel(const float* x, const float* inv_freq, float* out,
 void wukong_embedding_f32(float* out, const float* weight, const int32_t* ids, i64 t, i64 h, i64 v) {
   if (t <= 0 || h <= 0) return;
   i64 vv = v < 0 ? 0 : v;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)t * h * 4) + pad((size_t)vv * h * 4 + 16) + pad((size_t)t * 4));
   float* dw = vv ? A.up(weight, (size_t)vv * h) : (float*)A.take(16);
   int* di = A.up(ids, (size_t)t);
@@ -445,7 +463,7 @@ void wukong_embedding_f32_parallel(float* out, const float* weight, const int32_
 
 void wukong_rowargmax_i32(const float* x, int32_t* out, i64 rows, i64 cols) {
   if (rows <= 0 || cols <= 0) return;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)rows * cols * 4) + pad((size_t)rows * 4));
   float* dx = A.up(x, (size_t)rows * cols);
   int* dout = A.out<int>((size_t)rows);
@@ -462,7 +480,7 @@ i64 wukong_topk_f32(const float* x, i64 n, float* vals, i64 nv, i64* idx, i64 ni
   if (nv < k) k = nv < 0 ? 0 : nv;
   if (ni < k) k = ni < 0 ? 0 : ni;
   if (k <= 0) return 0;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)n * 4) + pad((size_t)k * 4) + pad((size_t)k * 8) + pad((size_t)wkb_argsort_scratch_bytes(n)));
   float* dx = A.up(x, (size_t)n);           // the input is snapshotted here: outputs may overlap it
   float* dv = A.out<float>((size_t)k);
@@ -483,7 +501,7 @@ i64 wukong_argsort_f32(const float* x, i64 n, i64* idx, i64 ni, i64 descending) 
   if (n < 0) n = 0;
   i64 m = ni < n ? (ni < 0 ? 0 : ni) : n;
   if (m <= 0) return 0;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)n * 4) + pad((size_t)m * 8) + pad((size_t)wkb_argsort_scratch_bytes(n)));
   float* dx = A.up(x, (size_t)n);
   i64* di = A.out<i64>((size_t)m);
@@ -496,7 +514,7 @@ i64 wukong_argsort_f32(const float* x, i64 n, i64* idx, i64 ni, i64 descending) 
 
 i64 wukong_sample_categorical_f32(const float* p, i64 n, float u) {
   if (n <= 0 || !p) return -1;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)n * 4) + pad(8) + pad(8));
   float* dp = A.up(p, (size_t)n);
   float* du = A.up(&u, 1);
@@ -510,7 +528,7 @@ i64 wukong_sample_categorical_f32(const float* p, i64 n, float u) {
 
 void wukong_rand_fill_f32(float* out, i64 n, i64 seed, i64 ctr0) {
   if (n <= 0) return;
-  Arena& A = g_arena;
+  Arena& A = g_arenas.current();
   A.begin(pad((size_t)n * 4));
   float* d = A.out<float>((size_t)n);
   check_launch(wkb_rand_fill_f32(d, n, seed, ctr0, A.stream), "rand_fill");

@@ -208,8 +208,11 @@ int64_t wkb_sched_enqueue(void* h, const int32_t* prompt, int64_t prompt_len, in
 
 // Admit, then lay out this step's rows.  Outputs (caller-owned, capacities max_rows / bcap):
 //   row_token, row_pos, row_slot, row_ctx  per row;  sample_row[slot] = row to sample or -1.
-// Returns the number of rows (0: idle), or -1 when a page is needed and none is free (nothing is
-// changed in that case: the step can be retried after sequences retire).
+// Admission (slot assignment and the prompt's page reservation) happens first and is kept whatever follows.
+// Slots whose rows need more pages than are free are left out of this step, decode rows being served before
+// prompt chunks; they run again once other sequences retire and release pages.  Returns the number of rows
+// (0: idle), or -1 when sequences are resident but not one row can get a page: no step was planned, and the
+// state can only move on if the caller releases a slot (the reference returns Err(OutOfBlocks) here too).
 int64_t wkb_sched_plan_step(void* h, int32_t* row_token, int32_t* row_pos, int32_t* row_slot, int32_t* row_ctx,
                             int32_t* sample_row) {
   auto* s = (Scheduler*)h;
@@ -227,18 +230,26 @@ int64_t wkb_sched_plan_step(void* h, int32_t* row_token, int32_t* row_pos, int32
       f.samples = f.planned == left;
       budget -= f.planned;
     }
-  // pass 2: every planned row must have a page before anything is committed
+  // pass 2: hand the free pages out, decode rows first; a slot that cannot get its pages sits this step out
   {
-    int64_t need = 0;
-    for (int64_t slot = 0; slot < s->bcap; ++slot) {
-      auto& f = s->slots[(size_t)slot];
-      if (f.planned == 0) continue;
-      int64_t have = (int64_t)s->mgr.tables[(size_t)slot].size();
-      int64_t want = s->mgr.blocks_for(s->mgr.ctx[(size_t)slot] + f.planned);
-      if (want > s->mgr.mbps) return -1;
-      need += std::max<int64_t>(0, want - have);
+    int64_t free_left = (int64_t)s->mgr.free_list.size(), planned_rows = 0, wanted_rows = 0;
+    for (int pass = 0; pass < 2; ++pass)
+      for (int64_t slot = 0; slot < s->bcap; ++slot) {
+        auto& f = s->slots[(size_t)slot];
+        const bool decode = f.id >= 0 && f.fed >= (int64_t)f.prompt.size();
+        if (f.planned == 0 || decode != (pass == 0)) continue;
+        wanted_rows += f.planned;
+        int64_t have = (int64_t)s->mgr.tables[(size_t)slot].size();
+        int64_t want = s->mgr.blocks_for(s->mgr.ctx[(size_t)slot] + f.planned);
+        int64_t extra = std::max<int64_t>(0, want - have);
+        if (want > s->mgr.mbps || extra > free_left) { f.planned = 0; f.samples = false; continue; }
+        free_left -= extra;
+        planned_rows += f.planned;
+      }
+    if (wanted_rows > 0 && planned_rows == 0) {
+      for (auto& f : s->slots) { f.planned = 0; f.samples = false; }
+      return -1;
     }
-    if (need > (int64_t)s->mgr.free_list.size()) return -1;
   }
   // pass 3: lay the rows out
   for (int64_t slot = 0; slot < s->bcap; ++slot) {

@@ -16,6 +16,10 @@ typedef uint16_t u16;
 
 #define WKB_SM_COUNT 148
 
+// Codes of the library's device status word beyond the pipeline-wait codes of the tensor-core kernels (read and cleared
+// by wkb_gemm_status): a KV append met a position past its block-table row (the row was skipped, nothing written).
+#define WKB_STATUS_KV_POS_RANGE 31
+
 // Fatal-error policy of the `void` entry points: the runtime ABI has no status to return there, and
 // a kernel library that silently computes nothing is worse than one that stops (the reference's own
 // entries abort rather than unwind).  Checked entries return their status instead.

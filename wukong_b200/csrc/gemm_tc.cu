@@ -48,20 +48,6 @@ __host__ __device__ constexpr uint32_t make_idesc(int bn, bool f8) {
   return (1u << 4) | (f8 ? 0u : ((1u << 7) | (1u << 10))) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-#ifdef WKB_GEMM_TRACE
-// Diagnostic build only: CTA (0,0) records globaltimer stamps (ns) after the status word.
-__device__ __forceinline__ void trace_stamp(int* status, int slot) {
-  if (blockIdx.x == 0 && blockIdx.y == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    reinterpret_cast<unsigned long long*>(status)[1 + slot] = t;
-  }
-}
-#define WKB_TRACE(slot) trace_stamp(status, slot)
-#else
-#define WKB_TRACE(slot)
-#endif
-
 struct GemmEpi {
   const float* bias;       // [N] or null
   const float* residual;   // [M, ldr] f32 or null (added after the activation)
@@ -122,7 +108,6 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr int BK = F8 ? BK_BYTES : BK_BYTES / 2;  // elements of K per stage
   const int kiters_all = (K + BK - 1) / BK;
   const int kper = (kiters_all + ksplit - 1) / ksplit;   // the host picks ksplit so that no slice is empty
-  if (threadIdx.x == 0) WKB_TRACE(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -143,7 +128,6 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
   pdl_trigger();
-  if (threadIdx.x == 0) WKB_TRACE(1);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -195,7 +179,6 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         if (ok) umma_commit(tfull_bar(buf));
       }
-      WKB_TRACE(2);
     }
   } else {
     // ---------------- epilogue warps 2..5: TMEM lane quarter (warp % 4) ----------------
@@ -217,7 +200,6 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) { if (lane == 0) atomicExch(status, 3); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (threadIdx.x == 64 && local == 0) WKB_TRACE(3);
       float best_v = -INFINITY;
       int best_i = -1;
       bool pinned = false;
@@ -325,10 +307,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   }
-  if (threadIdx.x == 64) WKB_TRACE(4);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (threadIdx.x == 0) WKB_TRACE(5);
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -436,21 +416,40 @@ __global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const float* __
   }
 }
 
-// Per-device split-K workspace, allocated on first use outside stream capture (a captured launch that finds none
-// simply does not split).
+// Default split-K workspace, one per device: allocated by wkb_gemm_init (or by the first eligible call that is not
+// inside a stream capture).  Whether a shape splits is a pure function of (m, n, k); a split shape that finds no
+// workspace is an error, never a silent change of algorithm (the summation order, hence the output bits, would
+// otherwise depend on the call history).
 constexpr size_t SPLITK_WS_BYTES = (size_t)32 << 20;
-static float* splitk_workspace(cudaStream_t st) {
+static float* splitk_workspace(cudaStream_t st, bool may_allocate) {
   static float* ws[64] = {nullptr};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!ws[dev]) {
+  if (!ws[dev] && may_allocate) {
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return nullptr;
+    if (st && (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone)) return nullptr;
     float* p = nullptr;
     if (cudaMalloc((void**)&p, SPLITK_WS_BYTES) != cudaSuccess) { cudaGetLastError(); return nullptr; }
     ws[dev] = p;
   }
   return ws[dev];
+}
+
+// K slices of a shape (1: no split).  Few 128 x 128 tiles and a long K (the decode MLP's down projection: 24 tiles,
+// K = 3072): cut K so that most SMs pull operands.
+static i64 splitk_slices(i64 m, i64 n, i64 k) {
+  const i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  const i64 tiles_wide = ((n + BN_WIDE - 1) / BN_WIDE) * ((m + BM - 1) / BM);
+  const i64 kiters = (k + 63) / 64;
+  if (tiles_wide >= 2 * sm_count() || tiles * 2 > sm_count() || kiters < 32 || n % 4 != 0) return 1;
+  i64 ks = sm_count() / tiles;
+  if (ks > 4) ks = 4;
+  if (ks > kiters / 8) ks = kiters / 8;
+  if (ks < 1) ks = 1;
+  const i64 kper = (kiters + ks - 1) / ks;
+  ks = (kiters + kper - 1) / kper;
+  if (ks > 1 && (size_t)(ks * m * n * 4) > SPLITK_WS_BYTES) return 1;
+  return ks;
 }
 
 i64 gemm_sm_count() { return sm_count(); }
@@ -461,8 +460,9 @@ using namespace wkb;
 
 extern "C" {
 
-int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i64 ldc, int c_bf16, i64 m, i64 n, i64 k,
-                     const float* bias, i64 act, const float* residual, i64 ldr, void* stream) {
+// Shared body of the two bf16 entries.  `ws` holds the fp32 K-slice partials of a split shape (ws_bytes of it).
+static int gemm_bf16_nt_impl(const void* a, i64 lda, const void* b, i64 ldb, void* c, i64 ldc, int c_bf16, i64 m, i64 n, i64 k,
+                             const float* bias, i64 act, const float* residual, i64 ldr, float* ws, i64 ws_bytes, cudaStream_t st) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   if (k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return (int)cudaErrorInvalidValue;
   if ((((uintptr_t)a) | ((uintptr_t)b)) & 15) return (int)cudaErrorMisalignedAddress;
@@ -505,37 +505,64 @@ int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i6
   }
   GemmEpi epi{bias, residual, ldr, (int)act, c_bf16, nullptr};
   i64 tiles = wide ? tiles_wide : ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
-  // Few tiles and a long K (the decode MLP's down projection: 24 tiles, K = 3072): cut K into slices so that most SMs
-  // pull operands, fp32 partials to a workspace, one finishing pass.  Results do not depend on scheduling.
-  const i64 kiters = (k + 63) / 64;
-  if (!wide && tiles * 2 <= sm_count() && kiters >= 32 && n % 4 == 0 && ldc % 4 == 0 && (residual == nullptr || ldr % 4 == 0)) {
-    i64 ks = sm_count() / tiles;
-    if (ks > 4) ks = 4;
-    if (ks > kiters / 8) ks = kiters / 8;
-    const i64 kper = (kiters + ks - 1) / ks;
-    ks = (kiters + kper - 1) / kper;
-    float* ws = ks > 1 && (size_t)(ks * m * n * 4) <= SPLITK_WS_BYTES ? splitk_workspace(as_stream(stream)) : nullptr;
-    if (ws) {
-      KernelFn plain = table[0][0];
-      if (!attr_set[dev & 63][0]) {
-        cudaError_t e = cudaFuncSetAttribute(plain, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        attr_set[dev & 63][0] = true;
-      }
-      GemmEpi part{nullptr, nullptr, 0, 0, 0, nullptr, (int)ks, m * n};
-      const i64 items = tiles * ks;
-      cudaError_t e = launch_pdl(plain, (unsigned)(items < sm_count() ? items : sm_count()), GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb,
-                                 (void*)ws, n, (int)m, (int)n, (int)k, part, status);
+  // Split-K: fp32 partials of each K slice to the workspace, one finishing pass with the epilogue.  The decision
+  // depends on the shape (and the pitches' alignment) only, and the slices are summed in slice order.
+  const i64 ks = splitk_slices(m, n, k);
+  if (ks > 1 && ldc % 4 == 0 && (residual == nullptr || ldr % 4 == 0)) {
+    if (!ws || ws_bytes < ks * m * n * 4 || (((uintptr_t)ws) & 15)) return (int)cudaErrorInvalidValue;
+    KernelFn plain = table[0][0];
+    if (!attr_set[dev & 63][0]) {
+      cudaError_t e = cudaFuncSetAttribute(plain, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
       if (e != cudaSuccess) return (int)e;
-      const i64 total = m * (n / 4);
-      i64 g = (total + 255) / 256;
-      if (g > sm_count() * 8) g = sm_count() * 8;
-      return (int)launch_pdl(gemm_splitk_finish_kernel, (unsigned)g, 256, 0, as_stream(stream), (const float*)ws, (int)ks, m * n, (int)m, (int)n, c,
-                             ldc, c_bf16, bias, (int)act, residual, ldr);
+      attr_set[dev & 63][0] = true;
     }
+    GemmEpi part{nullptr, nullptr, 0, 0, 0, nullptr, (int)ks, m * n};
+    const i64 items = tiles * ks;
+    cudaError_t e = launch_pdl(plain, (unsigned)(items < sm_count() ? items : sm_count()), GEMM_THREADS, SMEM_BYTES, st, ma, mb,
+                               (void*)ws, n, (int)m, (int)n, (int)k, part, status);
+    if (e != cudaSuccess) return (int)e;
+    const i64 total = m * (n / 4);
+    i64 g = (total + 255) / 256;
+    if (g > sm_count() * 8) g = sm_count() * 8;
+    return (int)launch_pdl(gemm_splitk_finish_kernel, (unsigned)g, 256, 0, st, (const float*)ws, (int)ks, m * n, (int)m, (int)n, c,
+                           ldc, c_bf16, bias, (int)act, residual, ldr);
   }
   unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
-  return (int)launch_pdl(kern, grid, GEMM_THREADS, smem, as_stream(stream), ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
+  return (int)launch_pdl(kern, grid, GEMM_THREADS, smem, st, ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
+}
+
+// Allocates this device's default split-K workspace (32 MiB) and the status word.  Call once per device before
+// capturing wkb_gemm_bf16_nt into a CUDA graph; without it the first split-shaped call outside a capture allocates.
+int wkb_gemm_init(void) {
+  if (!gemm_status_word()) return (int)cudaErrorMemoryAllocation;
+  return splitk_workspace(nullptr, true) ? 0 : (int)cudaErrorMemoryAllocation;
+}
+
+// Bytes of workspace wkb_gemm_bf16_nt_ws needs for this shape (0: the shape does not split K).
+i64 wkb_gemm_workspace_bytes(i64 m, i64 n, i64 k) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  const i64 ks = splitk_slices(m, n, k);
+  return ks > 1 ? ks * m * n * 4 : 0;
+}
+
+int wkb_gemm_bf16_nt_ws(const void* a, i64 lda, const void* b, i64 ldb, void* c, i64 ldc, int c_bf16, i64 m, i64 n, i64 k,
+                        const float* bias, i64 act, const float* residual, i64 ldr, void* workspace, i64 workspace_bytes, void* stream) {
+  return gemm_bf16_nt_impl(a, lda, b, ldb, c, ldc, c_bf16, m, n, k, bias, act, residual, ldr, (float*)workspace, workspace_bytes,
+                           as_stream(stream));
+}
+
+// The same with this device's default workspace, which every stream and host thread shares: only one split-shaped
+// GEMM may be in flight per device through this entry (use wkb_gemm_bf16_nt_ws with a workspace per stream otherwise).
+// A split-shaped call that finds no workspace while its stream is capturing returns cudaErrorNotReady: call
+// wkb_gemm_init first.
+int wkb_gemm_bf16_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i64 ldc, int c_bf16, i64 m, i64 n, i64 k,
+                     const float* bias, i64 act, const float* residual, i64 ldr, void* stream) {
+  float* ws = nullptr;
+  if (m > 0 && n > 0 && k > 0 && splitk_slices(m, n, k) > 1) {
+    ws = splitk_workspace(as_stream(stream), true);
+    if (!ws) return (int)cudaErrorNotReady;
+  }
+  return gemm_bf16_nt_impl(a, lda, b, ldb, c, ldc, c_bf16, m, n, k, bias, act, residual, ldr, ws, (i64)SPLITK_WS_BYTES, as_stream(stream));
 }
 
 // E4M3 x E4M3 -> fp32 accumulate: same kernel with kind::f8f6f4 MMAs and 128 elements of K per stage.
@@ -623,10 +650,4 @@ int wkb_gemm_status(void) {
   return v;
 }
 
-#ifdef WKB_GEMM_TRACE
-int wkb_gemm_trace(void* host256) {
-  int* status = gemm_status_word();
-  return status ? (int)cudaMemcpy(host256, status, 256, cudaMemcpyDeviceToHost) : -1;
-}
-#endif
 }

@@ -14,6 +14,8 @@
 
 namespace wkb {
 
+int* gemm_status_word();   // the library's device status word (gemm_tc.cu)
+
 // One CTA per row; a thread keeps its NV float4 of the row in registers between the statistic and the write-back,
 // so the row is read once (x and delta) and written once (x and the bf16 normed row).
 template <int NV>
@@ -90,7 +92,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(float* qkv, i64 row_st
                                                           const uint32_t* __restrict__ block_table, const int* __restrict__ row_slot,
                                                           const int* __restrict__ row_pos, u16* __restrict__ kcache,
                                                           u16* __restrict__ vcache, i64 rows, int hq, int hkv, int half,
-                                                          int page_tokens, int mbps) {
+                                                          int page_tokens, int mbps, int* __restrict__ status) {
   const int heads = hq + 2 * hkv, hd = 2 * half;
   const i64 total = rows * heads * half;
   for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
@@ -100,6 +102,10 @@ __global__ void __launch_bounds__(256) rope_append_kernel(float* qkv, i64 row_st
     const i64 r = rh / heads;
     const int pos = row_pos[r];
     if (pos < 0) continue;
+    if (pos / page_tokens >= mbps) {   // beyond the block-table row: the row is skipped whole and reported
+      if (j == 0 && hh == 0 && status) atomicExch(status, WKB_STATUS_KV_POS_RANGE);
+      continue;
+    }
     float* p = qkv + r * row_stride + (i64)hh * hd;
     float a, b;
     if (src) {
@@ -217,7 +223,7 @@ int wkb_rope_qk_paged_append(float* qkv, i64 row_stride, const float* inv_freq, 
   if (grid > (i64)WKB_SM_COUNT * 16) grid = (i64)WKB_SM_COUNT * 16;
   rope_append_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(qkv, row_stride, nullptr, 0, 0, 0, inv_freq, block_table, row_slot, row_pos,
                                                                (u16*)kcache, (u16*)vcache, rows, (int)q_heads, (int)kv_heads, (int)half,
-                                                               (int)page_tokens, (int)max_blocks_per_seq);
+                                                               (int)page_tokens, (int)max_blocks_per_seq, gemm_status_word());
   return (int)cudaGetLastError();
 }
 
@@ -234,7 +240,7 @@ int wkb_rope_qk_paged_append_slices(float* q_out, i64 row_stride, const float* s
   if (grid > (i64)WKB_SM_COUNT * 16) grid = (i64)WKB_SM_COUNT * 16;
   rope_append_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(q_out, row_stride, slices, (int)nslices, slice_stride, ld, inv_freq, block_table,
                                                                row_slot, row_pos, (u16*)kcache, (u16*)vcache, rows, (int)q_heads,
-                                                               (int)kv_heads, (int)half, (int)page_tokens, (int)max_blocks_per_seq);
+                                                               (int)kv_heads, (int)half, (int)page_tokens, (int)max_blocks_per_seq, gemm_status_word());
   return (int)cudaGetLastError();
 }
 

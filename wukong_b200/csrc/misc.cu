@@ -5,6 +5,8 @@
 // rowargmax: ascending scan semantics, strict compare, lowest index on a tie, a NaN at column 0 pins
 // the result to 0 and later NaNs never win (rowarg.rs:1-30, reduce.rs:631-639).
 #include "common.cuh"
+#include <chrono>
+#include <thread>
 #include "wkb_device.h"
 
 namespace wkb {
@@ -129,14 +131,29 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float* a, const floa
 // Device-side feedback of a decode step: the sampled token becomes the next input and the row moves
 // one position on (inactive rows, pos < 0, stay inactive).  Lets a run of decode steps replay with
 // no host round trip (the block table must already cover the positions ahead).
-__global__ void decode_advance_kernel(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, int n) {
+// A row whose next position would pass max_pos (the last position its block-table row covers) is parked instead:
+// pos = -1, ctx = 0, so every later step skips it.
+__global__ void decode_advance_kernel(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, int n, int max_pos) {
   pdl_wait();
   pdl_trigger();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n && row_pos[i] >= 0) {
     row_token[i] = next_tok[i];
-    row_pos[i] += 1;
-    row_ctx[i] += 1;
+    if (row_pos[i] >= max_pos) { row_pos[i] = -1; row_ctx[i] = 0; }
+    else { row_pos[i] += 1; row_ctx[i] += 1; }
+  }
+}
+
+// One thread that sleeps until `ns` nanoseconds have passed on the device clock (at most 2 s; the poll count is
+// bounded as well).  It exists so that the host-side deadline of wkb_stream_sync_within can be exercised without
+// any kernel that fails to finish.
+__global__ void device_sleep_kernel(unsigned long long ns) {
+  unsigned long long t0, now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (unsigned it = 0; it < (1u << 22); ++it) {
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - t0 >= ns) break;
+    __nanosleep(1000);
   }
 }
 
@@ -196,9 +213,35 @@ int wkb_rowargmax_strided_i32(const float* x, int* out, i64 rows, i64 cols, i64 
   return (int)cudaGetLastError();
 }
 
-int wkb_decode_advance(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, i64 n, void* stream) {
+int wkb_decode_advance(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, i64 n, i64 max_pos, void* stream) {
   if (n <= 0) return 0;
-  launch_pdl(decode_advance_kernel, (int)((n + 255) / 256), 256, 0, as_stream(stream), row_token, row_pos, row_ctx, next_tok, (int)n);
+  if (max_pos < 0 || max_pos > 0x7ffffffe) max_pos = 0x7ffffffe;
+  launch_pdl(decode_advance_kernel, (int)((n + 255) / 256), 256, 0, as_stream(stream), row_token, row_pos, row_ctx, next_tok, (int)n, (int)max_pos);
+  return (int)cudaGetLastError();
+}
+
+// Host-side deadline on a stream (the counterpart of the reference's `sync_within`, crates/wukong_codegen_gpu/src/
+// gpu.rs:250-262, :302, which turns a launch that does not finish into an error instead of a hung process): polls
+// the stream without blocking in the driver.  0 = everything queued on the stream has completed; -1 = the deadline
+// passed with work still in flight (the stream is left as it is: the caller decides whether to keep waiting, tear
+// the context down or report); > 0 = the CUDA error the stream reported.
+int wkb_stream_sync_within(void* stream, i64 timeout_ms) {
+  const auto t0 = std::chrono::steady_clock::now();
+  const auto limit = std::chrono::milliseconds(timeout_ms < 0 ? 0 : timeout_ms);
+  for (unsigned spins = 0;; ++spins) {
+    const cudaError_t e = cudaStreamQuery(as_stream(stream));
+    if (e == cudaSuccess) return 0;
+    if (e != cudaErrorNotReady) return (int)e;
+    if (std::chrono::steady_clock::now() - t0 >= limit) return -1;
+    if (spins > 2000) std::this_thread::sleep_for(std::chrono::microseconds(50));   // spin first: steps last ~2 ms
+  }
+}
+
+// Queues a kernel that occupies the stream for about `ms` milliseconds (clamped to [0, 2000]).
+int wkb_device_sleep_ms(i64 ms, void* stream) {
+  if (ms < 0) ms = 0;
+  if (ms > 2000) ms = 2000;
+  device_sleep_kernel<<<1, 1, 0, as_stream(stream)>>>((unsigned long long)ms * 1000000ull);
   return (int)cudaGetLastError();
 }
 

@@ -27,6 +27,7 @@ namespace wkb {
 
 constexpr int PA_CHUNK_MIN = 128;   // smallest split of the logical sequence (sizes the scratch)
 constexpr int PA_WARPS = 4;
+int* gemm_status_word();   // the library's device status word (gemm_tc.cu)
 
 __device__ __forceinline__ void unpack8(const uint4& w, float f[8]) {
   f[0] = u2f(w.x << 16); f[1] = u2f(w.x & 0xffff0000u);
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
   const int chunk = (int)(unit / ((i64)g.rows * g.kv_heads));
   const int kvh = (int)(unit % g.kv_heads);
   const int row = (int)((unit / g.kv_heads) % g.rows);
-  const int ctx = row_ctx[row];
+  const int ctx = min(row_ctx[row], g.mbps * g.page_tokens);   // never walk past the block-table row
   const int t0 = chunk * g.chunk_tokens;
   float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
   const i64 head_stride = (i64)g.max_chunks * (HD + 4);
@@ -294,7 +295,7 @@ __global__ void __launch_bounds__(PA_WARPS * 32, 2) paged_attn_decode_mma_kernel
   const int chunk = (int)(unit / ((i64)g.rows * g.kv_heads));
   const int kvh = (int)(unit % g.kv_heads);
   const int row = (int)((unit / g.kv_heads) % g.rows);
-  const int ctx = row_ctx[row];
+  const int ctx = min(row_ctx[row], g.mbps * g.page_tokens);   // never walk past the block-table row
   const int t0 = chunk * g.chunk_tokens;
   float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
   const i64 head_stride = (i64)g.max_chunks * (HD + 4);
@@ -433,7 +434,7 @@ template <int HD>
 __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const float* __restrict__ scratch, void* __restrict__ out,
                                                                int out_dtype, i64 out_row_stride,
                                                                const int* __restrict__ row_ctx, int rows, int q_heads,
-                                                               int max_chunks, int chunk_tokens) {
+                                                               int max_chunks, int chunk_tokens, int table_tokens) {
   pdl_wait();
   pdl_trigger();
   i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x;
@@ -442,7 +443,7 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const float* __re
   int dq = (int)(idx % (HD / 4));
   i64 rh = idx / (HD / 4);
   int row = (int)(rh / q_heads), h = (int)(rh % q_heads);
-  int ctx = row_ctx[row];
+  int ctx = min(row_ctx[row], table_tokens);
   int nch = ctx <= 0 ? 0 : (ctx + chunk_tokens - 1) / chunk_tokens;
   if (nch > max_chunks) nch = max_chunks;
   const float* s = scratch + rh * (i64)max_chunks * (HD + 4);
@@ -478,7 +479,7 @@ __global__ void __launch_bounds__(256) paged_kv_append_kernel(const float* __res
                                                               i64 src_row_stride, u16* __restrict__ kcache,
                                                               u16* __restrict__ vcache, const uint32_t* __restrict__ block_table,
                                                               const int* __restrict__ row_slot, const int* __restrict__ row_pos,
-                                                              int rows, int kv_heads, int hd, int page_tokens, int mbps) {
+                                                              int rows, int kv_heads, int hd, int page_tokens, int mbps, int* __restrict__ status) {
   pdl_wait();
   pdl_trigger();
   int per_row = kv_heads * hd / 8;
@@ -488,6 +489,10 @@ __global__ void __launch_bounds__(256) paged_kv_append_kernel(const float* __res
     int row = (int)(idx / per_row), c = (int)(idx % per_row);
     int pos = row_pos[row];
     if (pos < 0) continue;
+    if (pos / page_tokens >= mbps) {   // beyond the block-table row: skip the row, report it
+      if (c == 0 && status) atomicExch(status, WKB_STATUS_KV_POS_RANGE);
+      continue;
+    }
     int head = (c * 8) / hd, d0 = (c * 8) % hd;
     uint32_t page = block_table[(i64)row_slot[row] * mbps + pos / page_tokens];
     i64 dst = (((i64)page * kv_heads + head) * page_tokens + pos % page_tokens) * hd + d0;
@@ -516,7 +521,7 @@ static int launch_decode_mma(const float* q, const void* kc, const void* vc, con
   if (e != cudaSuccess) return (int)e;
   i64 total = (i64)g.rows * g.q_heads * (128 / 4);
   return (int)launch_pdl(paged_attn_merge_kernel<128>, (unsigned)((total + 127) / 128), 128, 0, st, (const float*)scratch, out, out_dtype,
-                         out_row_stride, row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens);
+                         out_row_stride, row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens, g.mbps * g.page_tokens);
 }
 
 template <int HD, int G>
@@ -534,7 +539,7 @@ static int launch_decode(const float* q, const void* kc, const void* vc, const u
   if (e != cudaSuccess || direct) return (int)e;
   i64 total = (i64)g.rows * g.q_heads * (HD / 4);
   return (int)launch_pdl(paged_attn_merge_kernel<HD>, (unsigned)((total + 127) / 128), 128, 0, st, (const float*)scratch, out, out_dtype,
-                         out_row_stride, row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens);
+                         out_row_stride, row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens, g.mbps * g.page_tokens);
 }
 
 }  // namespace wkb
@@ -623,7 +628,7 @@ int wkb_paged_kv_append(const float* ksrc, const float* vsrc, i64 src_row_stride
   if (blocks > (i64)WKB_SM_COUNT * 16) blocks = (i64)WKB_SM_COUNT * 16;
   return (int)launch_pdl(paged_kv_append_kernel, (int)blocks, 256, 0, as_stream(stream), ksrc, vsrc, src_row_stride, (u16*)kcache,
                          (u16*)vcache, block_table, row_slot, row_pos, (int)rows, (int)kv_heads, (int)head_dim, (int)page_tokens,
-                         (int)max_blocks_per_seq);
+                         (int)max_blocks_per_seq, gemm_status_word());
 }
 }
 

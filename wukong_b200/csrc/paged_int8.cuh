@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(256) paged_kv_append_i8_kernel(const float* __
                                                                  float* __restrict__ kscale, float* __restrict__ vscale,
                                                                  const uint32_t* __restrict__ block_table, const int* __restrict__ row_slot,
                                                                  const int* __restrict__ row_pos, int rows, int kv_heads, int page_tokens,
-                                                                 int page_shift, int mbps) {
+                                                                 int page_shift, int mbps, int* __restrict__ status) {
   constexpr int EPL = HD / 32;     // elements per lane: 2 or 4
   const int lane = threadIdx.x & 31;
   const i64 unit = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -26,6 +26,10 @@ __global__ void __launch_bounds__(256) paged_kv_append_i8_kernel(const float* __
   const int row = (int)(unit / kv_heads), h = (int)(unit % kv_heads);
   const int pos = row_pos[row];
   if (pos < 0) return;
+  if ((pos >> page_shift) >= mbps) {   // beyond the block-table row: skip the row, report it
+    if (lane == 0 && h == 0 && status) atomicExch(status, WKB_STATUS_KV_POS_RANGE);
+    return;
+  }
   const uint32_t page = block_table[(i64)row_slot[row] * mbps + (pos >> page_shift)];
   const i64 tok = ((i64)page * kv_heads + h) * page_tokens + (pos & (page_tokens - 1));
 #pragma unroll
@@ -75,7 +79,7 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_i8_kernel(
   const int chunk = (int)(unit / ((i64)g.rows * g.kv_heads));
   const int kvh = (int)(unit % g.kv_heads);
   const int row = (int)((unit / g.kv_heads) % g.rows);
-  const int ctx = row_ctx[row];
+  const int ctx = min(row_ctx[row], g.mbps * g.page_tokens);
   const int t0 = chunk * g.chunk_tokens;
   float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
   const i64 head_stride = (i64)g.max_chunks * (HD + 4);
@@ -192,7 +196,7 @@ static int launch_decode_i8(const float* q, const void* kq, const void* vq, cons
   if (e != cudaSuccess) return (int)e;
   const i64 total = (i64)g.rows * g.q_heads * (HD / 4);
   paged_attn_merge_kernel<HD><<<(unsigned)((total + 127) / 128), 128, 0, st>>>(scratch, out, out_dtype, out_row_stride, row_ctx, g.rows,
-                                                                                g.q_heads, g.max_chunks, g.chunk_tokens);
+                                                                                g.q_heads, g.max_chunks, g.chunk_tokens, g.mbps * g.page_tokens);
   return (int)cudaGetLastError();
 }
 
@@ -216,11 +220,11 @@ int wkb_paged_kv_append_int8(const float* ksrc, const float* vsrc, i64 src_row_s
   if (head_dim == 64)
     paged_kv_append_i8_kernel<64><<<blocks, 256, 0, st>>>(ksrc, vsrc, src_row_stride, (int8_t*)kq, (int8_t*)vq, kscale, vscale, block_table,
                                                           row_slot, row_pos, (int)rows, (int)kv_heads, (int)page_tokens, page_shift,
-                                                          (int)max_blocks_per_seq);
+                                                          (int)max_blocks_per_seq, gemm_status_word());
   else
     paged_kv_append_i8_kernel<128><<<blocks, 256, 0, st>>>(ksrc, vsrc, src_row_stride, (int8_t*)kq, (int8_t*)vq, kscale, vscale, block_table,
                                                            row_slot, row_pos, (int)rows, (int)kv_heads, (int)page_tokens, page_shift,
-                                                           (int)max_blocks_per_seq);
+                                                           (int)max_blocks_per_seq, gemm_status_word());
   return (int)cudaGetLastError();
 }
 

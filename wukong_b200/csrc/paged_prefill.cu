@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD == 64 ? 3 : 1) paged_attn_pr
     const int a = gi + 8 * rr;
     tok[rr] = a / G;
     hd[rr] = kvh * G + a % G;
-    ctx[rr] = tok[rr] < nrows ? row_ctx[row0 + tok[rr]] : 0;
+    ctx[rr] = tok[rr] < nrows ? min(row_ctx[row0 + tok[rr]], g.mbps * g.page_tokens) : 0;
   }
   int kmax = max(ctx[0], ctx[1]);
   kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, 4));

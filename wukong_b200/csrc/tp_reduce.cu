@@ -16,7 +16,10 @@
 // rewritten while a peer may still read it.  Sequence numbers come from a per-rank device step counter plus the
 // phase index baked into the launch, so the launches can live in a CUDA graph.
 // Peer memory is mapped with CUDA IPC (no multicast objects); loads are plain ld.global, never TMA.
-// Waits are bounded (about a second): on expiry the block records it in `status`, skips the sum and returns.
+// Waits are bounded (one second unless wkb_tp_set_wait_limit_ms says otherwise): on expiry the block records 21 in
+// `status`, skips the sum (x and out are left untouched) and returns.  The rank that gave up also marks itself dead --
+// a poison value in its own flag row and in its slot of every peer's -- so every later phase on every rank ends at once
+// with code 22 instead of summing a buffer whose owner has moved on; the flag rows must be zeroed to start again.
 #include "common.cuh"
 #include "wkb_device.h"
 #include <cstring>
@@ -26,7 +29,8 @@ namespace wkb {
 int* gemm_status_word();
 
 constexpr int TP_MAX_WORLD = 8;
-constexpr uint32_t TP_SPIN_LIMIT = 1u << 22;   // x ~200 ns sleep: about a second
+constexpr uint32_t TP_POISON = 0xFFFFFFFFu;    // a sequence number no step reaches: "this rank gave up"
+static unsigned long long g_tp_wait_ns = 1000000000ull;   // flag-wait limit, set by wkb_tp_set_wait_limit_ms
 
 struct TpPeers {
   const float* part[TP_MAX_WORLD];   // every rank's partial buffer for this phase (own entry included), by rank
@@ -46,28 +50,45 @@ template <int NV>
 __global__ void __launch_bounds__(1024) tp_reduce_add_rmsnorm_kernel(TpPeers peers, int rank, int world, const uint32_t* __restrict__ step_ptr,
                                                                     int phase, int phases_per_step, float* __restrict__ x,
                                                                     const float* __restrict__ gamma, u16* __restrict__ out, int rows,
-                                                                    int cols, float eps, int* status) {
+                                                                    int cols, float eps, int* status, unsigned long long wait_ns) {
   __shared__ float red[32];
   __shared__ int s_ok;
   const uint32_t seq = (*step_ptr) * (uint32_t)phases_per_step + (uint32_t)phase + 1u;
+  // slot [rank] of a rank's own flag row is its "gave up" mark
+  const bool dead = ld_acquire_sys(peers.flags[rank] + rank) == TP_POISON;
   if (blockIdx.x == 0 && threadIdx.x < world && (int)threadIdx.x != rank) {
     __threadfence_system();
-    st_release_sys(peers.flags[threadIdx.x] + rank, seq);
+    st_release_sys(peers.flags[threadIdx.x] + rank, dead ? TP_POISON : seq);
   }
   if (threadIdx.x == 0) {
-    int ok = 1;
-    for (int p = 0; p < world && ok; ++p) {
+    int code = dead ? 22 : 0;
+    unsigned long long t_begin;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_begin));
+    // two limits: the clock, and a poll count in case the clock does not move
+    const unsigned long long max_polls = wait_ns / 64 + 1024;
+    for (int p = 0; p < world && !code; ++p) {
       if (p == rank) continue;
       const uint32_t* f = peers.flags[rank] + p;
-      uint32_t it = 0;
-      // sequence numbers only grow; a peer one phase ahead has already published a larger one
-      while ((int32_t)(ld_acquire_sys(f) - seq) < 0) {
-        if (++it > TP_SPIN_LIMIT) { ok = 0; break; }
+      unsigned long long it = 0;
+      for (;;) {
+        const uint32_t v = ld_acquire_sys(f);
+        if (v == TP_POISON) { code = 22; break; }        // that peer gave up earlier
+        // sequence numbers only grow; a peer one phase ahead has already published a larger one
+        if ((int32_t)(v - seq) >= 0) break;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now - t_begin > wait_ns || ++it > max_polls) { code = 21; break; }
         __nanosleep(200);
       }
     }
-    if (!ok) atomicExch(status, 21);
-    s_ok = ok;
+    if (code) atomicExch(status, code);
+    if (code == 21) {
+      // tell everyone, and remember it: this rank no longer takes part
+      st_release_sys(peers.flags[rank] + rank, TP_POISON);
+      for (int p = 0; p < world; ++p)
+        if (p != rank) st_release_sys(peers.flags[p] + rank, TP_POISON);
+    }
+    s_ok = code == 0;
   }
   __syncthreads();
   if (!s_ok) return;
@@ -170,7 +191,7 @@ int wkb_tp_reduce_add_rmsnorm(const void* const* parts, void* const* flags, i64 
   const i64 per = (nvec + threads - 1) / threads;
   cudaStream_t st = as_stream(stream);
 #define WKB_TP_LAUNCH(NV_) tp_reduce_add_rmsnorm_kernel<NV_><<<grid, threads, 0, st>>>(peers, (int)rank, (int)world, (const uint32_t*)step_ptr, \
-    (int)phase, (int)phases_per_step, x, gamma_or_null, (u16*)out_bf16, (int)rows, (int)cols, eps, status)
+    (int)phase, (int)phases_per_step, x, gamma_or_null, (u16*)out_bf16, (int)rows, (int)cols, eps, status, g_tp_wait_ns)
   if (per <= 1) WKB_TP_LAUNCH(1);
   else if (per <= 2) WKB_TP_LAUNCH(2);
   else if (per <= 4) WKB_TP_LAUNCH(4);
@@ -179,6 +200,10 @@ int wkb_tp_reduce_add_rmsnorm(const void* const* parts, void* const* flags, i64 
 #undef WKB_TP_LAUNCH
   return (int)cudaGetLastError();
 }
+
+// Limit of the flag wait of wkb_tp_reduce_add_rmsnorm launches made after this call (process-wide; <= 0 restores the
+// default of one second).
+void wkb_tp_set_wait_limit_ms(i64 ms) { g_tp_wait_ns = ms > 0 ? (unsigned long long)ms * 1000000ull : 1000000000ull; }
 
 int wkb_tp_step_bump(void* step_ptr, void* stream) {
   tp_step_bump_kernel<<<1, 1, 0, as_stream(stream)>>>((uint32_t*)step_ptr);

@@ -436,7 +436,7 @@ class LlamaDecodeModel:
         """Device-side feedback between decode steps: the sampled token becomes the next input, positions and
         visible-key counts move on by one."""
         p = lambda t: t.data_ptr()
-        check(lib().wkb_decode_advance(p(self.row_token), p(self.row_pos), p(self.row_ctx), p(self.next_tok), n,
+        check(lib().wkb_decode_advance(p(self.row_token), p(self.row_pos), p(self.row_ctx), p(self.next_tok), n, self.max_ctx - 1,
                                        torch.cuda.current_stream().cuda_stream), "advance")
 
 

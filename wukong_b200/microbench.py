@@ -142,8 +142,11 @@ def case_norm(op, hbm, tf, src):
             "unit": "GB/s", "bound": "hbm", "peak": hbm, "frac": gbs / hbm, "algorithmic_bytes": alg, "peak_source": "of " + src}
 
 
-def case_paged_attn(hbm, tf, src):
-    rng = np.random.default_rng(0)
+def build_paged_attn_case(seed=0, torch_seed=None):
+    """The paged GQA decode-attention case of the micro-suite: batch 64, context lengths uniform in [128, 4096], 32 query
+    heads over 8 KV heads of dim 128, bf16 K/V ~N(0,1) in 16-token pages handed out as a seeded random permutation of
+    a shared 65 536-page pool.  Returns a dict of the device tensors and the host copies of table and contexts."""
+    rng = np.random.default_rng(seed)
     B, H, HKV, D, page, pool = 64, 32, 8, 128, 16, 65536
     ctx = rng.integers(128, 4097, B).astype(np.int32)
     mbps = 256
@@ -154,16 +157,25 @@ def case_paged_attn(hbm, tf, src):
         n = (int(ctx[b]) + page - 1) // page
         table[b, :n] = perm[nxt:nxt + n]
         nxt += n
+    gen = None
+    if torch_seed is not None:
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(torch_seed)
     kv = dev.PagedKV(1, pool, HKV, D, page)
-    kv.k.normal_()
-    kv.v.normal_()
-    q = torch.randn(B, H * D, device="cuda")
-    bt = torch.from_numpy(table.view(np.int32)).cuda()
-    row_slot = torch.arange(B, dtype=torch.int32, device="cuda")
-    row_ctx = torch.from_numpy(ctx).cuda()
+    kv.k.normal_(generator=gen)
+    kv.v.normal_(generator=gen)
+    q = torch.randn(B, H * D, device="cuda", generator=gen)
+    return dict(B=B, H=H, HKV=HKV, D=D, page=page, pool=pool, mbps=mbps, max_ctx=4096, ctx=ctx, table=table, kv=kv, q=q,
+                bt=torch.from_numpy(table.view(np.int32)).cuda(), row_slot=torch.arange(B, dtype=torch.int32, device="cuda"),
+                row_ctx=torch.from_numpy(ctx).cuda(), scale=1.0 / math.sqrt(D), pages_used=nxt)
+
+
+def case_paged_attn(hbm, tf, src):
+    c = build_paged_attn_case()
+    B, H, HKV, D, mbps, ctx, kv, q, bt, row_slot, row_ctx = (c[k] for k in ("B", "H", "HKV", "D", "mbps", "ctx", "kv", "q", "bt", "row_slot", "row_ctx"))
     out = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
     scratch = dev.paged_attn_scratch(B, H, D, 4096)
-    fn = lambda i: dev.paged_attn_decode(q, H * D, kv, 0, bt, row_slot, row_ctx, out, B, H, mbps, 4096, 1.0 / math.sqrt(D), scratch)
+    fn = lambda i: dev.paged_attn_decode(q, H * D, kv, 0, bt, row_slot, row_ctx, out, B, H, mbps, 4096, c["scale"], scratch)
     us = time_graph(fn, 10)
     alg = float(ctx.sum()) * 2 * HKV * D * 2 + B * H * D * (4 + 2) + B * mbps * 4
     gbs = alg / us / 1e3

@@ -154,13 +154,21 @@ class DecodeModel:
         return self.next_tok
 
 
+class StepTimeout(RuntimeError):
+    """A step's device work did not finish within the engine's deadline (the work is still queued)."""
+
+
 class Engine:
     """Scheduler + model: `step()` = plan rows -> upload them (and the block table when it moved) ->
-    forward (one CUDA-graph replay for a decode-only step) -> read the sampled tokens -> commit."""
+    forward (one CUDA-graph replay for a decode-only step) -> read the sampled tokens -> commit.
+    `step_timeout_ms` puts a host-side deadline on each step's device work (the reference's `sync_within`,
+    crates/wukong_codegen_gpu/src/gpu.rs:250-262): when it passes, `step()` raises StepTimeout instead of
+    blocking for ever, and the step stays uncommitted."""
 
     def __init__(self, cfg, weights, bcap, num_pages, max_blocks_per_seq, max_rows=None, prefill_chunk=256, page_tokens=16,
-                 device="cuda", use_graph=True):
+                 device="cuda", use_graph=True, step_timeout_ms=None):
         self.cfg, self.bcap = cfg, bcap
+        self.step_timeout_ms = step_timeout_ms
         self.model = DecodeModel(cfg, weights, bcap, num_pages, max_blocks_per_seq, max_rows, page_tokens, device)
         self.sched = Scheduler(bcap, num_pages, page_tokens, max_blocks_per_seq, self.model.max_rows, prefill_chunk)
         R = self.model.max_rows
@@ -180,12 +188,16 @@ class Engine:
         self.stream = torch.cuda.Stream(device=device)
         self.h2d_bytes = self.d2h_bytes = self.kernel_launches = 0
         self._planned = None
+        self._pending = None                   # a launched step whose tokens have not been committed yet
+        self._sample_rows_identity = False     # device sample_rows currently hold 0..bcap-1 (set by a decode-only step)
 
     def enqueue(self, prompt, gen_len):
         return self.sched.enqueue(prompt, gen_len)
 
     def step(self):
         s, m, R = self.sched, self.model, self.model.max_rows
+        if self._pending is not None:
+            raise RuntimeError("the previous step has not finished: call finish_step()")
         n = self._planned if self._planned is not None else s.plan_step()   # a caller may have planned already
         self._planned = None
         if n == 0:
@@ -193,16 +205,23 @@ class Engine:
         hr = self.h_rows.numpy()
         # decode-only step: every row is the one sampled row of its slot (one token per sequence)
         decode_only = n <= self.bcap and np.array_equal(s.sample_row[s.row_slot[:n]], np.arange(n, dtype=np.int32))
-        # rows past n are inactive: they write no KV (pos < 0), see no key (ctx 0) and are never sampled
-        hr[0 * R:0 * R + n] = s.row_token[:n]; hr[0 * R + n:1 * R] = 0
-        hr[1 * R:1 * R + n] = s.row_pos[:n]; hr[1 * R + n:2 * R] = -1
-        hr[2 * R:2 * R + n] = s.row_slot[:n]; hr[2 * R + n:3 * R] = 0
-        hr[3 * R:3 * R + n] = s.row_ctx[:n]; hr[3 * R + n:4 * R] = 0
+        # Only the live prefix of each row vector crosses PCIe: U = the rows this step's kernels read (the whole
+        # batch capacity on the graph path, whose launches are fixed at bcap rows), rounded up to 64.  Rows between
+        # n and U are inactive: they write no KV (pos < 0), see no key (ctx 0) and are never sampled.
+        U = min(R, (max(n, self.bcap if decode_only else 0) + 63) // 64 * 64)
+        hr[0 * R:0 * R + n] = s.row_token[:n]; hr[0 * R + n:0 * R + U] = 0
+        hr[1 * R:1 * R + n] = s.row_pos[:n]; hr[1 * R + n:1 * R + U] = -1
+        hr[2 * R:2 * R + n] = s.row_slot[:n]; hr[2 * R + n:2 * R + U] = 0
+        hr[3 * R:3 * R + n] = s.row_ctx[:n]; hr[3 * R + n:3 * R + U] = 0
         sampled_slots = np.flatnonzero(s.sample_row >= 0)
+        vectors = 4
         if decode_only:
-            hr[4 * R:4 * R + self.bcap] = np.arange(self.bcap)   # graph path: the head runs on every decode row
+            if not self._sample_rows_identity:               # graph path: the head runs on every decode row
+                hr[4 * R:4 * R + self.bcap] = np.arange(self.bcap)
+                vectors = 5
         else:
             hr[4 * R:4 * R + sampled_slots.size] = s.sample_row[sampled_slots]
+            vectors = 5
         n_tiles = 0
         if not decode_only and self.use_prefill_kernel and m.tile_rows:
             tiles = dev.prefill_tiles(s.row_slot[:n], m.tile_rows, min_run=2)
@@ -211,11 +230,17 @@ class Engine:
                 ctx_dec = s.row_ctx[:n].copy()
                 for r0, cnt in tiles:
                     ctx_dec[r0:r0 + cnt] = 0
-                hr[5 * R:5 * R + n] = ctx_dec; hr[5 * R + n:6 * R] = 0
+                hr[5 * R:5 * R + n] = ctx_dec; hr[5 * R + n:5 * R + U] = 0
                 hr[6 * R:6 * R + 2 * n_tiles] = tiles.reshape(-1)
+                vectors = 6
         with torch.cuda.stream(self.stream):
-            self.d_rows.copy_(self.h_rows, non_blocking=True)
-            self.h2d_bytes += self.h_rows.numel() * 4
+            for v in range(vectors):
+                self.d_rows[v * R:v * R + U].copy_(self.h_rows[v * R:v * R + U], non_blocking=True)
+            self.h2d_bytes += vectors * U * 4
+            if n_tiles:
+                self.d_rows[6 * R:6 * R + 2 * n_tiles].copy_(self.h_rows[6 * R:6 * R + 2 * n_tiles], non_blocking=True)
+                self.h2d_bytes += 2 * n_tiles * 4
+            self._sample_rows_identity = decode_only
             ep = s.manager.layout_epoch()
             if ep != self.uploaded_epoch:
                 s.manager.flat_block_table(self.h_table.numpy().view(np.uint32).reshape(self.bcap, -1))
@@ -242,7 +267,24 @@ class Engine:
             self.kernel_launches += m.launches_per_forward
             self.h_next.copy_(m.next_tok, non_blocking=True)
             self.d2h_bytes += self.bcap * 4
-        self.stream.synchronize()
+        self._pending = (decode_only, sampled_slots)
+        return self.finish_step(self.step_timeout_ms)
+
+    def finish_step(self, timeout_ms=None):
+        """Wait for the launched step (for ever, or up to timeout_ms) and commit its tokens.  After a StepTimeout the
+        step is still pending: call this again to keep waiting, or give up on the engine."""
+        if self._pending is None:
+            return 0
+        s = self.sched
+        if timeout_ms is None:
+            self.stream.synchronize()
+        else:
+            rc = lib().wkb_stream_sync_within(self.stream.cuda_stream, int(timeout_ms))
+            if rc == -1:
+                raise StepTimeout("decode step still running after %d ms" % timeout_ms)
+            check(rc, "step")
+        decode_only, sampled_slots = self._pending
+        self._pending = None
         nxt = self.h_next.numpy()
         sampled = np.zeros(self.bcap, np.int32)
         if decode_only:
@@ -259,7 +301,7 @@ class Engine:
         def body():
             m.forward(self.bcap, self.bcap)
             check(lib().wkb_decode_advance(m.row_token.data_ptr(), m.row_pos.data_ptr(), m.row_ctx.data_ptr(),
-                                           m.next_tok.data_ptr(), self.bcap, torch.cuda.current_stream().cuda_stream), "advance")
+                                           m.next_tok.data_ptr(), self.bcap, m.max_ctx - 1, torch.cuda.current_stream().cuda_stream), "advance")
         g = torch.cuda.CUDAGraph()
         with torch.cuda.stream(self.stream):
             with torch.cuda.graph(g, stream=self.stream):
