@@ -19,6 +19,8 @@ typedef uint16_t u16;
 // Codes of the library's device status word beyond the pipeline-wait codes of the tensor-core kernels (read and cleared
 // by wkb_gemm_status): a KV append met a position past its block-table row (the row was skipped, nothing written).
 #define WKB_STATUS_KV_POS_RANGE 31
+// ... or a bounded wait on an asynchronous K/V copy of the paged attention ran out (the unit's output was not written).
+#define WKB_STATUS_ATTN_WAIT 41
 
 // Fatal-error policy of the `void` entry points: the runtime ABI has no status to return there, and
 // a kernel library that silently computes nothing is worse than one that stops (the reference's own

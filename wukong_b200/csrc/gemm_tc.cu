@@ -57,6 +57,16 @@ struct GemmEpi {
   int* arg_idx;            // arg-max mode: per-(row, column tile) winning column (values go to C)
   int ksplit;              // > 1: work item = (tile, K slice); slice s writes its raw fp32 partial at c + s * slice_stride
   i64 slice_stride;        // elements between the partial outputs of consecutive K slices
+  // KVAPPEND instantiation (fused QKV projection of a decode step): columns [kv_col0, kv_col0 + 2 * kv_heads * kv_hd)
+  // are the new K then V rows; they are rounded to bf16 straight into their pages (the paged_kv_append_kernel
+  // addressing: bf16 [page][kv_head][token][dim]) instead of being stored to C.  Rows with row_pos < 0 or past the
+  // block-table row write nothing (the latter is reported in the status word).
+  u16* kcache;
+  u16* vcache;
+  const uint32_t* block_table;
+  const int* row_slot;
+  const int* row_pos;
+  int kv_col0, kv_heads, kv_hd, page_tokens, mbps;
 };
 
 // GELU for bf16 output: x * sigmoid(2u), u = sqrt(2/pi)(x + 0.044715 x^3), with the hardware exp2 and
@@ -77,7 +87,7 @@ __device__ __forceinline__ float epi_act(float y) {
 // Persistent kernel: CTA b works on tiles b, b + gridDim.x, ...; tile t is (m_tile = t % tiles_m,
 // n_tile = t / tiles_m), so CTAs running side by side share one B (weight) tile through L2.
 // ACT / OUT_BF16 / ARGMAX are compile-time so an identity epilogue carries no transcendental code.
-template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8, bool WIDE>
+template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8, bool WIDE, bool KVAPPEND = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c,
                     i64 ldc, int M, int N, int K, GemmEpi epi, int* status) {
@@ -204,6 +214,22 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int best_i = -1;
       bool pinned = false;
       (void)best_v; (void)best_i; (void)pinned;
+      // KVAPPEND: lane rr keeps where row (m0 + quarter * 32 + rr) lands in the cache: element offset of its token row
+      // for KV head 0 (-1: the row writes nothing)
+      i64 kv_dst = -1;
+      (void)kv_dst;
+      if (KVAPPEND && n0 + BN > epi.kv_col0 && row < M) {
+        const int pos = epi.row_pos[row];
+        if (pos >= 0) {
+          const int lp = pos / epi.page_tokens;
+          if (lp < epi.mbps) {
+            const uint32_t page = epi.block_table[(i64)epi.row_slot[row] * epi.mbps + lp];
+            kv_dst = ((i64)page * epi.kv_heads * epi.page_tokens + (pos % epi.page_tokens)) * epi.kv_hd;
+          } else {
+            atomicExch(status, WKB_STATUS_KV_POS_RANGE);
+          }
+        }
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -267,7 +293,18 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int e = 0; e < 32; ++e) stage[lane * 33 + e] = __uint_as_float(r[e]);
           __syncwarp();
           const float bias_v = (col_ok && epi.bias) ? epi.bias[col] : 0.0f;
-          if (col_ok) {
+          if (KVAPPEND && n0 + c0 >= epi.kv_col0) {
+            // this 32-column chunk is K or V (kv_col0 is a multiple of 32, so a chunk never straddles q | k): round into the pages
+            const int kc = col_ok ? col - epi.kv_col0 : 0, kv_dim = epi.kv_heads * epi.kv_hd;
+            u16* cache = kc < kv_dim ? epi.kcache : epi.vcache;
+            const int cc = kc < kv_dim ? kc : kc - kv_dim;
+            const i64 head_off = (i64)(cc / epi.kv_hd) * epi.page_tokens * epi.kv_hd + (cc % epi.kv_hd);
+#pragma unroll 4
+            for (int rr = 0; rr < 32; ++rr) {
+              const i64 dst = __shfl_sync(0xffffffffu, kv_dst, rr);       // every lane takes part in the exchange
+              if (col_ok && dst >= 0) cache[dst + head_off] = f32_to_bf16_bits(stage[rr * 33 + lane] + bias_v);
+            }
+          } else if (col_ok) {
             if (full) {
               float vals[32];
 #pragma unroll
@@ -549,6 +586,103 @@ int wkb_gemm_bf16_nt_ws(const void* a, i64 lda, const void* b, i64 ldb, void* c,
                         const float* bias, i64 act, const float* residual, i64 ldr, void* workspace, i64 workspace_bytes, void* stream) {
   return gemm_bf16_nt_impl(a, lda, b, ldb, c, ldc, c_bf16, m, n, k, bias, act, residual, ldr, (float*)workspace, workspace_bytes,
                            as_stream(stream));
+}
+
+// K-slice partials only (no epilogue): slice s of the product goes to workspace + s * m * n as an fp32 [m, n] plane, for a
+// consumer that adds the planes in slice order while it does its own row-wise work (wkb_add_slices_layernorm_bf16).
+// The number of slices depends on the shape only: as many as keep every SM busy, each at least three 64-element K steps
+// long, at most 8.  wkb_gemm_bf16_partial_layout reports it; the workspace must hold slices * m * n floats.
+static i64 partial_slices(i64 m, i64 n, i64 k) {
+  const i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  const i64 kiters = (k + 63) / 64;
+  i64 ks = sm_count() / (tiles > 0 ? tiles : 1);
+  if (ks > 8) ks = 8;
+  if (ks > kiters / 3) ks = kiters / 3;
+  if (ks < 1) ks = 1;
+  const i64 kper = (kiters + ks - 1) / ks;
+  return (kiters + kper - 1) / kper;
+}
+
+void wkb_gemm_bf16_partial_layout(i64 m, i64 n, i64 k, i64* slices, i64* slice_stride) {
+  *slices = (m > 0 && n > 0 && k > 0) ? partial_slices(m, n, k) : 0;
+  *slice_stride = m * n;
+}
+
+int wkb_gemm_bf16_nt_partial(const void* a, i64 lda, const void* b, i64 ldb, i64 m, i64 n, i64 k, void* workspace, i64 workspace_bytes,
+                             void* stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if (k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || n % 4 != 0) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)workspace)) & 15) return (int)cudaErrorMisalignedAddress;
+  const i64 ks = partial_slices(m, n, k);
+  if (!workspace || workspace_bytes < ks * m * n * 4) return (int)cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, m, k, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, b, n, k, ldb, BN);
+  if (rc) return rc;
+  int* status = gemm_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  auto kern = gemm_bf16_tc_kernel<0, false, false, false, false>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63] = true;
+  }
+  GemmEpi part{};
+  part.ksplit = (int)ks;
+  part.slice_stride = m * n;
+  const i64 items = ((n + BN - 1) / BN) * ((m + BM - 1) / BM) * ks;
+  return (int)launch_pdl(kern, (unsigned)(items < sm_count() ? items : sm_count()), GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb, workspace,
+                         n, (int)m, (int)n, (int)k, part, status);
+}
+
+// The fused QKV projection of a decode step: C[:, :kv_col0] = A.B^T + bias (fp32, the query heads); columns
+// [kv_col0, kv_col0 + 2 * kv_heads * head_dim) -- the new K rows, then the new V rows -- are rounded to bf16 straight
+// into their pages at row_pos through the block table and are not stored to C (the work of wkb_paged_kv_append, without
+// its launch and without the fp32 round trip).  n must be kv_col0 + 2 * kv_heads * head_dim; kv_col0 % 32 == 0.
+int wkb_gemm_bf16_nt_qkv_append(const void* a, i64 lda, const void* b, i64 ldb, float* c, i64 ldc, i64 m, i64 n, i64 k, const float* bias,
+                                i64 kv_col0, void* kcache, void* vcache, const uint32_t* block_table, const int* row_slot, const int* row_pos,
+                                i64 kv_heads, i64 head_dim, i64 page_tokens, i64 max_blocks_per_seq, void* stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if (k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (kv_col0 < 0 || kv_col0 % 32 != 0 || kv_heads <= 0 || head_dim <= 0 || page_tokens <= 0 || max_blocks_per_seq <= 0 ||
+      n != kv_col0 + 2 * kv_heads * head_dim)
+    return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)a) | ((uintptr_t)b)) & 15) return (int)cudaErrorMisalignedAddress;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, m, k, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, b, n, k, ldb, BN);
+  if (rc) return rc;
+  int* status = gemm_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  auto kern = gemm_bf16_tc_kernel<0, false, false, false, false, true>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63] = true;
+  }
+  GemmEpi epi{};
+  epi.bias = bias;
+  epi.kcache = (u16*)kcache;
+  epi.vcache = (u16*)vcache;
+  epi.block_table = block_table;
+  epi.row_slot = row_slot;
+  epi.row_pos = row_pos;
+  epi.kv_col0 = (int)kv_col0;
+  epi.kv_heads = (int)kv_heads;
+  epi.kv_hd = (int)head_dim;
+  epi.page_tokens = (int)page_tokens;
+  epi.mbps = (int)max_blocks_per_seq;
+  const i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  return (int)launch_pdl(kern, (unsigned)(tiles < sm_count() ? tiles : sm_count()), GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb, (void*)c, ldc,
+                         (int)m, (int)n, (int)k, epi, status);
 }
 
 // The same with this device's default workspace, which every stream and host thread shares: only one split-shaped

@@ -22,6 +22,7 @@
 // Both are HBM-bound: algorithmic bytes per (row, kv head, token) = 2 * head_dim * 2.
 #include "common.cuh"
 #include "wkb_device.h"
+#include "tc_common.cuh"
 
 namespace wkb {
 
@@ -224,6 +225,236 @@ __global__ void __launch_bounds__(PA_WARPS * 32) paged_attn_decode_kernel(
     }
   }
   // ---- combine the token groups (fixed xor tree over the group bits), then the lane sums of l
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+#pragma unroll
+    for (int ofs = LPT; ofs < 32; ofs <<= 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], ofs);
+    }
+    float lt = warp_sum(l[h]);
+    if (out) {
+      const float inv = lt != 0.0f ? 1.0f / lt : 0.0f;
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = acc[h][e] * inv;
+      if (grp == 0) write_row(h, v);
+      continue;
+    }
+    float* s = sbase + h * head_stride;
+    if (grp == 0) {
+      *reinterpret_cast<float4*>(s + j * 8) = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
+      *reinterpret_cast<float4*>(s + j * 8 + 4) = make_float4(acc[h][4], acc[h][5], acc[h][6], acc[h][7]);
+    }
+    if (lane == 0) { s[HD] = m[h]; s[HD + 1] = lt; }
+  }
+}
+
+// ---- the same unit of work with K / V staged in shared memory by asynchronous bulk copies ---------------------
+// The register kernel above keeps its bytes in flight in registers (two tile buffers, 185 registers, 8 warps per SM)
+// and every unit starts with a serial chain row -> block table -> first tile during which its warp streams nothing.
+// Here a (page, kv head) run -- 16 tokens x head_dim bf16, one contiguous 2 or 4 KiB piece of HBM -- is brought in by
+// ONE cp.async.bulk issued by lane 0 (global -> this CTA's shared memory, completion counted on an mbarrier; never a
+// multicast, never another GPU's memory), into a ring of NST tile slots per warp.  A tile is 32 tokens = two pages of
+// K and two of V.  Bytes in flight cost shared memory instead of registers (NST x 8 KiB per warp at head_dim 64), the
+// warp needs ~80 registers, and the arithmetic, the reduction trees and therefore the output bits are those of the
+// register kernel.  Warps are independent (own ring, own barriers, no __syncthreads), so ragged context lengths cost
+// nothing beyond the launch tail.  Every barrier wait is bounded; a wait that runs out records
+// WKB_STATUS_ATTN_WAIT, waits (bounded) for the copies still in flight and leaves the unit unwritten.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+template <int HD, int G, int NST, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) paged_attn_decode_staged_kernel(
+    const float* __restrict__ q, const uint8_t* __restrict__ kcache, const uint8_t* __restrict__ vcache,
+    const uint32_t* __restrict__ block_table, const int* __restrict__ row_slot, const int* __restrict__ row_ctx,
+    float* __restrict__ scratch, PagedGeo g, float scale_log2e, void* __restrict__ out, int out_dtype, i64 out_row_stride,
+    int* __restrict__ status) {
+  constexpr int LPT = HD / 8, TPW = 32 / LPT, STEPS = LPT, TILE = 32;
+  constexpr int ROW_BYTES = HD * 2, PAGE_BYTES = 16 * ROW_BYTES, STAGE_BYTES = 4 * PAGE_BYTES;   // K a, K b, V a, V b
+  extern __shared__ __align__(128) uint8_t pa_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grp = lane / LPT, j = lane % LPT;
+  const uint32_t ring = smem_u32(pa_smem) + (uint32_t)warp * (NST * STAGE_BYTES);
+  const uint32_t bars = smem_u32(pa_smem) + (uint32_t)WARPS * (NST * STAGE_BYTES) + (uint32_t)warp * (NST * 8);
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < NST; ++s) mbar_init(bars + 8u * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  pdl_wait();
+  pdl_trigger();
+  const i64 unit = (i64)blockIdx.x * WARPS + warp;
+  const i64 units = (i64)g.rows * g.kv_heads * g.max_chunks;
+  if (unit >= units) return;
+  const int chunk = (int)(unit / ((i64)g.rows * g.kv_heads));
+  const int kvh = (int)(unit % g.kv_heads);
+  const int row = (int)((unit / g.kv_heads) % g.rows);
+  const int ctx = min(row_ctx[row], g.mbps * g.page_tokens);
+  const int t0 = chunk * g.chunk_tokens;
+  float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
+  const i64 head_stride = (i64)g.max_chunks * (HD + 4);
+  auto write_row = [&](int h, const float (&v)[8]) {
+    const i64 off = (i64)row * out_row_stride + ((i64)kvh * G + h) * HD + j * 8;
+    if (out_dtype == 0) {
+      float4* d = reinterpret_cast<float4*>(static_cast<float*>(out) + off);
+      d[0] = make_float4(v[0], v[1], v[2], v[3]);
+      d[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+      uint4 pk;
+      pk.x = (uint32_t)f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
+      pk.y = (uint32_t)f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
+      pk.z = (uint32_t)f32_to_bf16_bits(v[4]) | ((uint32_t)f32_to_bf16_bits(v[5]) << 16);
+      pk.w = (uint32_t)f32_to_bf16_bits(v[6]) | ((uint32_t)f32_to_bf16_bits(v[7]) << 16);
+      *reinterpret_cast<uint4*>(static_cast<u16*>(out) + off) = pk;
+    }
+  };
+  if (t0 >= ctx) {  // nothing visible in this chunk (no copy has been issued yet)
+    if (out) {
+      const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (grp == 0)
+        for (int h = 0; h < G; ++h) write_row(h, zero);
+    } else if (lane < G) { float* s = sbase + lane * head_stride; s[HD] = -INFINITY; s[HD + 1] = 0.0f; }
+    return;
+  }
+  const int t1 = min(ctx, t0 + g.chunk_tokens);
+  const int ntiles = (t1 - t0 + TILE - 1) / TILE;
+  const uint32_t* bt = block_table + (i64)row_slot[row] * g.mbps;
+  const int first_page = t0 >> 4, last_page = (t1 - 1) >> 4;
+  // page ids of the unit, 32 at a time in the lanes (a window of 16 tiles); handed to lane 0 by shuffle
+  uint32_t my_page = bt[min(first_page + lane, last_page)];
+  const i64 page_stride = (i64)g.kv_heads * PAGE_BYTES;
+  const i64 head_off = (i64)kvh * PAGE_BYTES;
+  // issue the copies of tile i into its ring slot (all lanes take part in the shuffles, lane 0 issues)
+  auto issue = [&](int i) {
+    const int tile0 = t0 + i * TILE;
+    const int pa = (tile0 >> 4) - first_page;                 // page index inside the unit
+    const uint32_t pg_a = __shfl_sync(0xffffffffu, my_page, pa & 31);
+    const uint32_t pg_b = __shfl_sync(0xffffffffu, my_page, (pa + 1) & 31);
+    if (lane == 0) {
+      const int na = min(16, t1 - tile0), nb = min(16, max(0, t1 - tile0 - 16));   // visible tokens in the two pages
+      const uint32_t slot = ring + (uint32_t)(i % NST) * STAGE_BYTES, bar = bars + 8u * (i % NST);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the slot's last readers (generic proxy) are done
+      mbar_expect_tx(bar, (uint32_t)(na + nb) * ROW_BYTES * 2);
+      const i64 src_a = (i64)pg_a * page_stride + head_off;
+      bulk_g2s(slot, kcache + src_a, (uint32_t)na * ROW_BYTES, bar);
+      bulk_g2s(slot + 2 * PAGE_BYTES, vcache + src_a, (uint32_t)na * ROW_BYTES, bar);
+      if (nb > 0) {
+        const i64 src_b = (i64)pg_b * page_stride + head_off;
+        bulk_g2s(slot + PAGE_BYTES, kcache + src_b, (uint32_t)nb * ROW_BYTES, bar);
+        bulk_g2s(slot + 3 * PAGE_BYTES, vcache + src_b, (uint32_t)nb * ROW_BYTES, bar);
+      }
+    }
+  };
+  const int pre = min(NST, ntiles);
+  for (int i = 0; i < pre; ++i) issue(i);
+  // this lane's 8 query dims for each head of the group, pre-scaled by scale*log2(e) (these loads overlap the copies)
+  float qv[G][8];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    const float* qp = q + (i64)row * g.q_row_stride + ((i64)kvh * G + h) * HD + j * 8;
+    float4 a = *reinterpret_cast<const float4*>(qp), b = *reinterpret_cast<const float4*>(qp + 4);
+    qv[h][0] = a.x * scale_log2e; qv[h][1] = a.y * scale_log2e; qv[h][2] = a.z * scale_log2e; qv[h][3] = a.w * scale_log2e;
+    qv[h][4] = b.x * scale_log2e; qv[h][5] = b.y * scale_log2e; qv[h][6] = b.z * scale_log2e; qv[h][7] = b.w * scale_log2e;
+  }
+  float m[G], l[G], acc[G][8];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    m[h] = -INFINITY; l[h] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[h][e] = 0.0f;
+  }
+  bool ok = true;
+  int issued = pre;
+  for (int i = 0; i < ntiles; ++i) {
+    const int tile0 = t0 + i * TILE;
+    if (!mbar_wait(bars + 8u * (i % NST), (uint32_t)((i / NST) & 1))) { ok = false; break; }
+    const uint32_t slot = ring + (uint32_t)(i % NST) * STAGE_BYTES;
+    // tokens past the visible end are clamped onto the last visible token of the tile (real, finite data in the slot)
+    // and their weight is forced to zero
+    const int last_local = min(TILE, t1 - tile0) - 1;
+    // ---- scores
+    float part[G][STEPS];
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s) {
+      const int tl = min(s * TPW + grp, last_local);
+      uint4 kw;
+      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(kw.x), "=r"(kw.y), "=r"(kw.z), "=r"(kw.w)
+                   : "r"(slot + (uint32_t)tl * ROW_BYTES + (uint32_t)j * 16u));
+      float kf[8];
+      unpack8(kw, kf);
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        float d = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d = fmaf(qv[h][e], kf[e], d);
+        part[h][s] = d;
+      }
+    }
+#pragma unroll
+    for (int hh = STEPS / 2; hh >= 1; hh >>= 1) {
+      bool upper = (j & hh) != 0;
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+#pragma unroll
+        for (int ii = 0; ii < hh; ++ii) {
+          float send = upper ? part[h][ii] : part[h][ii + hh];
+          float keep = upper ? part[h][ii + hh] : part[h][ii];
+          part[h][ii] = keep + __shfl_xor_sync(0xffffffffu, send, hh);
+        }
+      }
+    }
+    const int mytok = tile0 + j * TPW + grp;
+    const bool mine = mytok < t1;
+    float p[G];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      float s = mine ? part[h][0] : -INFINITY;
+      float tm = warp_max(s);
+      float mn = fmaxf(m[h], tm);
+      float corr = exp2f(m[h] - mn);
+      p[h] = exp2f(s - mn);
+      l[h] = l[h] * corr + p[h];
+      m[h] = mn;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[h][e] *= corr;
+    }
+    // ---- values
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s) {
+      const int tl = min(s * TPW + grp, last_local);
+      uint4 vw;
+      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(vw.x), "=r"(vw.y), "=r"(vw.z), "=r"(vw.w)
+                   : "r"(slot + 2u * PAGE_BYTES + (uint32_t)tl * ROW_BYTES + (uint32_t)j * 16u));
+      float vf[8];
+      unpack8(vw, vf);
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        float pt = __shfl_sync(0xffffffffu, p[h], grp * LPT + s);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(pt, vf[e], acc[h][e]);
+      }
+    }
+    __syncwarp();                       // every lane has read the slot
+    if (i + NST < ntiles) {
+      if (((i + NST) & 15) == 0) {      // the next window of page ids (32 pages = 16 tiles)
+        const int base_page = first_page + 2 * (i + NST);
+        my_page = bt[min(base_page + lane, last_page)];
+      }
+      issue(i + NST);
+      ++issued;
+    }
+  }
+  if (!ok) {
+    if (lane == 0) atomicExch(status, WKB_STATUS_ATTN_WAIT);
+    // the copies still in flight target this CTA's shared memory: wait for them (bounded) before the warp leaves
+    for (int i2 = 0; i2 < issued; ++i2)
+      if (i2 + NST >= issued) mbar_wait(bars + 8u * (i2 % NST), (uint32_t)((i2 / NST) & 1));
+    return;
+  }
 #pragma unroll
   for (int h = 0; h < G; ++h) {
 #pragma unroll
@@ -524,6 +755,28 @@ static int launch_decode_mma(const float* q, const void* kc, const void* vc, con
                          out_row_stride, row_ctx, g.rows, g.q_heads, g.max_chunks, g.chunk_tokens, g.mbps * g.page_tokens);
 }
 
+// Launch of the staged kernel for one (NST, WARPS) shape; the dynamic shared memory limit is raised once per device.
+template <int HD, int G, int NST, int WARPS>
+static cudaError_t launch_staged_cfg(const float* q, const void* kc, const void* vc, const uint32_t* bt, const int* row_slot,
+                                     const int* row_ctx, float* scratch, void* out, int out_dtype, i64 out_row_stride, PagedGeo g,
+                                     float scale, cudaStream_t st, int* status) {
+  constexpr int SMEM = WARPS * NST * (4 * 16 * HD * 2) + WARPS * NST * 8;
+  auto kern = paged_attn_decode_staged_kernel<HD, G, NST, WARPS>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (SMEM > 48 * 1024 && !attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return e;
+    attr_set[dev & 63] = true;
+  }
+  const i64 units = (i64)g.rows * g.kv_heads * g.max_chunks;
+  const i64 blocks = (units + WARPS - 1) / WARPS;
+  if (blocks > 0x7fffffff) return cudaErrorInvalidValue;
+  return launch_pdl(kern, (unsigned)blocks, WARPS * 32, (size_t)SMEM, st, q, (const uint8_t*)kc, (const uint8_t*)vc, bt, row_slot, row_ctx,
+                    scratch, g, scale * 1.4426950408889634f, out, out_dtype, out_row_stride, status);
+}
+
 template <int HD, int G>
 static int launch_decode(const float* q, const void* kc, const void* vc, const uint32_t* bt, const int* row_slot,
                          const int* row_ctx, float* scratch, void* out, int out_dtype, i64 out_row_stride, PagedGeo g,
@@ -533,9 +786,35 @@ static int launch_decode(const float* q, const void* kc, const void* vc, const u
   if (blocks > 0x7fffffff) return (int)cudaErrorInvalidValue;
   // one unit per (row, kv head): it writes the row itself (128-bit stores: a bf16 row pitch must be a multiple of 8)
   const bool direct = g.max_chunks == 1 && (out_dtype == 0 || out_row_stride % 8 == 0);
-  cudaError_t e = launch_pdl(paged_attn_decode_kernel<HD, G>, (unsigned)blocks, PA_WARPS * 32, 0, st, q, (const uint4*)kc, (const uint4*)vc, bt,
-                             row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f, direct ? out : (void*)nullptr, out_dtype,
-                             out_row_stride);
+  cudaError_t e;
+  static const int staged_cfg = [] { const char* s = getenv("WKB_PA_STAGED"); return s ? atoi(s) : 21; }();
+  int* status = g.page_tokens == 16 && staged_cfg > 0 ? gemm_status_word() : nullptr;
+  if (status) {
+    // K / V pages staged in shared memory by bulk copies (16-token pages only)
+    void* o = direct ? out : (void*)nullptr;
+#define WKB_PA_STAGED(NST_, WARPS_) launch_staged_cfg<HD, G, NST_, WARPS_>(q, kc, vc, bt, row_slot, row_ctx, scratch, o, out_dtype, out_row_stride, g, scale, st, status)
+    if constexpr (HD == 64 && G == 1) {
+      switch (staged_cfg) {
+        case 31: e = WKB_PA_STAGED(3, 1); break;
+        case 41: e = WKB_PA_STAGED(4, 1); break;
+        case 61: e = WKB_PA_STAGED(6, 1); break;
+        case 32: e = WKB_PA_STAGED(3, 2); break;
+        case 42: e = WKB_PA_STAGED(4, 2); break;
+        case 24: e = WKB_PA_STAGED(2, 4); break;
+        case 34: e = WKB_PA_STAGED(3, 4); break;
+        default: e = WKB_PA_STAGED(2, 1); break;
+      }
+    } else if constexpr (HD == 64) {
+      e = WKB_PA_STAGED(3, 1);
+    } else {
+      e = WKB_PA_STAGED(2, 1);
+    }
+#undef WKB_PA_STAGED
+  } else {
+    e = launch_pdl(paged_attn_decode_kernel<HD, G>, (unsigned)blocks, PA_WARPS * 32, 0, st, q, (const uint4*)kc, (const uint4*)vc, bt,
+                   row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f, direct ? out : (void*)nullptr, out_dtype,
+                   out_row_stride);
+  }
   if (e != cudaSuccess || direct) return (int)e;
   i64 total = (i64)g.rows * g.q_heads * (HD / 4);
   return (int)launch_pdl(paged_attn_merge_kernel<HD>, (unsigned)((total + 127) / 128), 128, 0, st, (const float*)scratch, out, out_dtype,
