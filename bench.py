@@ -360,7 +360,7 @@ def measure_serving(args, S, D, weights, cfg, clocks, label):
     with torch.cuda.stream(eng.stream):
         def attn(li):
             s = torch.cuda.current_stream().cuda_stream
-            check(lib().wkb_paged_attn_decode(p(m.qkv), 3 * d, p(m.kv.k[li]), p(m.kv.v[li]), p(m.block_table), p(m.row_slot), p(m.row_ctx),
+            check(lib().wkb_paged_attn_decode(p(m.q), d, p(m.kv.k[li]), p(m.kv.v[li]), p(m.block_table), p(m.row_slot), p(m.row_ctx),
                                               p(m.att), 1, d, S, cfg.n_head, cfg.n_head, cfg.head_dim, PAGE, mbps, m.max_ctx, m.scale,
                                               p(m.scratch), s), "attn")
         for li in range(cfg.n_layer):

@@ -199,8 +199,7 @@ def measure(args, D, clocks, note, use_nccl, cfg, weights):
     m.block_table.copy_(torch.from_numpy(table))
     h_rows = torch.zeros(3 * BATCH, dtype=torch.int32).pin_memory()
     h_next = torch.zeros(BATCH, dtype=torch.int32).pin_memory()
-    d_rows = torch.zeros(3 * BATCH, dtype=torch.int32, device=device)
-    m.row_token, m.row_pos, m.row_ctx = (d_rows[i * BATCH:(i + 1) * BATCH] for i in range(3))
+    d_rows = m.rows[:3 * BATCH]                    # the model's row block: token | position | visible keys (| slot)
     hr = h_rows.numpy()
     hr[:BATCH] = rng.integers(0, cfg.vocab, BATCH)
     hr[BATCH:2 * BATCH] = CTX0

@@ -305,7 +305,7 @@ int wkb_paged_attn_decode_int8(const float* q, int64_t q_row_stride, const void*
 /* Prefill / chunked prefill against the same cache (causal, GQA; the reference's counterpart is the flash prefill of
  * crates/wukong_codegen_gpu/src/ptx_flash.rs under the chunked scheduler of serving.rs:1346-1595).  `tiles` is a
  * DEVICE array of n_tiles (first row, row count) int32 pairs; the rows of a tile are consecutive query tokens of ONE
- * sequence, at most wkb_paged_attn_prefill_tile_rows(q_heads, kv_heads) = 16 / (q_heads / kv_heads) of them.  Row r
+ * sequence, at most wkb_paged_attn_prefill_tile_rows(q_heads, kv_heads) = 128 / (q_heads / kv_heads) of them.  Row r
  * sees its sequence's first row_ctx[r] keys (0: the row is not written).  Keys are streamed once per tile instead of
  * once per row.  head_dim in {64, 128}; q_heads / kv_heads in {1, 2, 4, 8}; out_dtype 0 f32, 1 bf16. */
 int64_t wkb_paged_attn_prefill_tile_rows(int64_t q_heads, int64_t kv_heads);
@@ -376,9 +376,25 @@ int64_t wkb_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int wkb_gemm_bf16_nt_ws(const void* a, int64_t lda, const void* b, int64_t ldb, void* c, int64_t ldc, int c_bf16,
                         int64_t m, int64_t n, int64_t k, const float* bias, int64_t act, const float* residual,
                         int64_t ldr, void* workspace, int64_t workspace_bytes, void* stream);
+/* K-slice partial sums of the same product, no epilogue: slice s goes to workspace + s * slice_stride as an fp32 [m, n]
+ * plane, for a consumer that adds the planes in slice order while it does its own row-wise work.  The slice count
+ * depends on the shape only (wkb_gemm_bf16_partial_layout); the workspace must hold slices * m * n floats; n % 4 == 0. */
+void wkb_gemm_bf16_partial_layout(int64_t m, int64_t n, int64_t k, int64_t* slices, int64_t* slice_stride);
+int wkb_gemm_bf16_nt_partial(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k,
+                             void* workspace, int64_t workspace_bytes, void* stream);
+/* The fused QKV projection of a decode step (the reference launches the projection and the cache append separately:
+ * crates/wukong_codegen_gpu/src/serving.rs:684-937): C[:, :kv_col0] = A.B^T + bias in fp32 (the query heads); columns
+ * [kv_col0, kv_col0 + 2 * kv_heads * head_dim) -- the new K rows, then the new V rows -- are rounded to bf16 straight into
+ * their pages at row_pos through the block table (the work of wkb_paged_kv_append) and are not stored to C.
+ * n = kv_col0 + 2 * kv_heads * head_dim; kv_col0 % 32 == 0. */
+int wkb_gemm_bf16_nt_qkv_append(const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int64_t m,
+                                int64_t n, int64_t k, const float* bias, int64_t kv_col0, void* kcache, void* vcache,
+                                const uint32_t* block_table, const int* row_slot, const int* row_pos, int64_t kv_heads,
+                                int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq, void* stream);
 /* Reads and clears the library's device status word of the current device (synchronises): 0, or the code of the last
  * event -- 1-4 / 11-17 a bounded pipeline wait of the dense / W4A16 GEMM ran out, 21 the tensor-parallel reduce's flag
- * wait ran out, 31 a KV append met a position past its block-table row (the row was skipped).  The word is one per
+ * wait ran out (22: a peer had given up), 31 a KV append met a position past its block-table row (the row was skipped),
+ * 41 a bounded wait on an asynchronous K/V copy of the paged attention ran out (that unit's output was not written).  The word is one per
  * device, shared by every stream and thread: concurrent users see each other's codes and the read clears them all. */
 int wkb_gemm_status(void);
 
@@ -412,6 +428,66 @@ int wkb_gemm_e4m3_nt(const void* a, int64_t lda, const void* b, int64_t ldb, voi
 int64_t wkb_gemm_argmax_tiles(int64_t n);
 int wkb_gemm_bf16_nt_argmax(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k,
                             const float* bias, float* part_val, int* part_idx, int* out, void* stream);
+
+/* ---- the GPT-2-shape decode model step behind one call --------------------------------------------------------------
+ * The per-step launch sequence of the resident serving loop (reference: `DecodeLayer::forward_step_on`,
+ * crates/wukong_codegen_gpu/src/serving.rs:684-937, and the body `Scheduler::step_graphed` replays, :1536-1575), issued
+ * by the library so that any host calls one entry per step and may capture it into a CUDA graph.  The object owns no
+ * device memory.  dims = {n_layer, d_model, n_head, d_ff, vocab, n_pos, bcap, max_rows, num_pages, max_blocks_per_seq,
+ * page_tokens, eps bits}.  weights = HOST array of 4 + 12 * n_layer device pointers: wte, wpe (bf16), lnf_g, lnf_b, then
+ * per layer ln1_g, ln1_b, w_qkv (bf16 [3d, d]), b_qkv, w_o (bf16 [d, d]), b_o, ln2_g, ln2_b, w_fc (bf16 [ff, d]), b_fc,
+ * w_proj (bf16 [d, ff]), b_proj (vectors f32).  kcache / vcache: bf16 [n_layer][num_pages][n_head][page_tokens][head_dim].
+ * rows: int32 [8 * max_rows] = token | position | slot | visible keys | sampled rows | visible keys for the row-per-token
+ * kernel | prefill tiles (2 vectors).  next_tok: int32 [bcap].  workspace: wkb_gpt2_workspace_bytes(dims) bytes, 256-byte
+ * aligned.  logits_or_null: f32 [bcap, ldl] when steps with keep_logits are wanted.
+ * wkb_gpt2_step runs the first n_rows rows; the n_sample rows named in the sampled-rows vector reach the LM head and
+ * their greedy tokens land in next_tok[0 .. n_sample).  n_tiles > 0: the step carries prompt chunks (tile list in the rows
+ * block, see wkb_paged_attn_prefill).  It only launches (no synchronisation, no allocation).  wkb_gpt2_advance is the
+ * device-side token feedback between two decode steps (wkb_decode_advance on the model's own vectors). */
+int64_t wkb_gpt2_workspace_bytes(const int64_t* dims);
+void* wkb_gpt2_new(const int64_t* dims, const void* const* weights, void* kcache, void* vcache, void* block_table, void* rows,
+                   void* next_tok, void* workspace, void* logits_or_null, int64_t ldl);
+void wkb_gpt2_delete(void* h);
+int wkb_gpt2_step(void* h, int64_t n_rows, int64_t n_sample, int64_t n_tiles, int keep_logits, void* stream);
+int wkb_gpt2_advance(void* h, int64_t n, void* stream);
+int64_t wkb_gpt2_launches(void* h);
+/* Optional two-lane execution of decode-only steps of at least 256 rows: the rows are cut in two halves that walk the
+ * layers on two streams (the caller's and one the model created), forked and joined by events, so one half's HBM-bound
+ * attention can overlap the other half's latency-bound GEMMs; capturable into a CUDA graph as two parallel branches.
+ * Off by default (it measured slower on the 512-sequence serving step); on = 1 or environment WKB_TWO_LANES=1 at creation
+ * turns it on.  Returns the previous setting. */
+int wkb_gpt2_set_two_lanes(void* h, int on);
+/* Activation buffers inside the workspace, for tests and tools: 0 x (f32 [max_rows, d]), 1 h (bf16), 2 q (f32 [max_rows, d]),
+ * 3 att (bf16), 4 ff (bf16 [max_rows, d_ff]), 5 hs (bf16 [bcap, d]). */
+void* wkb_gpt2_buffer(void* h, int64_t which);
+
+/* ---- one tensor-parallel rank of the Llama-shape Q4_0 decode stack behind one call -----------------------------------
+ * The launch sequence of a decode step (reference: the tensor-parallel block validated in
+ * crates/wukong_codegen_gpu/src/serving.rs:4161-4240 and the decode layer of :684-937), cut into phases at the two sums
+ * over ranks of every layer so that a host can issue its collectives between calls:
+ *   0 begin | 1 + 4l attention part of layer l | 2 + 4l add + norm after the sum | 3 + 4l MLP part | 4 + 4l add + norm after
+ *   the sum | 1 + 4L LM head, local arg-max, (value, index) pair | 2 + 4L pick across ranks.
+ * dims = {n_layer, d_model, n_head, n_kv_head, d_ff, vocab, rank, world, bcap, num_pages, max_blocks_per_seq, page_tokens,
+ * eps bits}.  weights = HOST array of 4 + 6 * n_layer device pointers: embed (f32 [vocab, d]), norm_f, lm_head (this rank's
+ * vocab / world rows, wkb_q4_tile layout), inv_freq (f32 [head_dim / 2]), then per layer norm1, norm2, wqkv, wo, wgu (gate /
+ * up rows interleaved), wdown (this rank's slices, wkb_q4_tile layout).  kcache / vcache: bf16 [n_layer][num_pages]
+ * [n_kv_head / world][page_tokens][head_dim].  rows: int32 [4 * bcap] = token | position | visible keys | slot.
+ * Without wkb_llama_set_peer the host sums buffer 1 (this rank's fp32 partial) over the ranks after phases 1 + 4l and
+ * 3 + 4l; with it those sums are the library's fused peer-memory kernel (wkb_tp_reduce_add_rmsnorm) and phases
+ * 0 .. 1 + 4L are one call.  Before the last phase every rank's pairs (buffer 7) must have been gathered into buffer 8.
+ * The object owns no device memory; a step only launches. */
+int64_t wkb_llama_workspace_bytes(const int64_t* dims);
+void* wkb_llama_new(const int64_t* dims, const void* const* weights, void* kcache, void* vcache, void* block_table, void* rows,
+                    void* next_tok, void* workspace);
+void wkb_llama_delete(void* h);
+int wkb_llama_set_peer(void* h, const void* const* parts0, const void* const* parts1, void* const* flags, void* step_ptr);
+int wkb_llama_set_prefill_tiles(void* h, const int* tiles_dev, int64_t n_tiles);
+/* 0 x, 1 part, 2 xn (bf16), 3 qkv, 4 att (bf16), 5 h (bf16), 6 logits, 7 pairs, 8 all_pairs, 9 attention scratch. */
+void* wkb_llama_buffer(void* h, int64_t which);
+int64_t wkb_llama_num_phases(void* h);
+int64_t wkb_llama_launches(void* h);
+int wkb_llama_step(void* h, int64_t n, int64_t phase_begin, int64_t phase_end, void* stream);
+int wkb_llama_advance(void* h, int64_t n, void* stream);
 
 /* ---- checkpoint containers (GGUF versions 2 and 3, safetensors) ----------------------------------------------
  * Host readers with the names, arguments, check order and codes of the reference runtime entries

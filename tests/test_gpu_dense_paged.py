@@ -223,3 +223,63 @@ def test_paged_append_and_decode(dev, orc):
         dev.paged_attn_decode(torch.from_numpy(q).cuda(), q_heads * hd, kv, 0, bt, row_slot, row_ctx, outb, slots, q_heads, mbps,
                               max(ctx), scale, scratch)
         assert np.array_equal(outb.view(torch.int16).cpu().numpy().view(np.uint16), orc.to_bf16_bits(outs[1]).reshape(slots, -1))
+
+
+def test_qkv_gemm_with_fused_append_equals_gemm_then_append(dev, orc):
+    """The fused QKV projection writes the query columns like the plain GEMM and puts the K / V columns into the pages
+    exactly as the separate append kernel does (same fp32 values, same rounding, same addresses); inactive rows and rows
+    past the block-table row write nothing."""
+    import torch
+    from wukong_b200 import lib
+    L, s = lib(), torch.cuda.current_stream().cuda_stream
+    rng = np.random.default_rng(5)
+    for (rows, heads, hd, d_in) in [(70, 4, 64, 256), (512, 12, 64, 768), (33, 2, 128, 256)]:
+        d = heads * hd
+        page, mbps, slots = 16, 6, rows
+        nblk = slots * mbps
+        a = bf16_t(rng.standard_normal((rows, d_in)).astype(np.float32), orc)
+        w = bf16_t(rng.standard_normal((3 * d, d_in)).astype(np.float32) * 0.1, orc)
+        bias = torch.from_numpy(rng.standard_normal(3 * d).astype(np.float32)).cuda()
+        table = torch.from_numpy(rng.permutation(nblk).astype(np.int32).reshape(slots, mbps)).cuda()
+        pos = rng.integers(0, mbps * page, rows).astype(np.int32)
+        pos[3] = -1                      # inactive
+        pos[5] = mbps * page             # past the table: skipped and reported
+        row_pos = torch.from_numpy(pos).cuda()
+        row_slot = torch.from_numpy(rng.permutation(slots).astype(np.int32)).cuda()
+        # reference path: plain GEMM, then the append kernel
+        qkv = dev.gemm_bf16_nt(a, w, bias=bias)
+        kv_ref = dev.PagedKV(1, nblk, heads, hd, page)
+        kv_ref.k.fill_(7.0); kv_ref.v.fill_(7.0)
+        dev.paged_kv_append(kv_ref, 0, qkv[:, d:], qkv[:, 2 * d:], qkv.stride(0), table, row_slot, row_pos, rows, mbps)
+        torch.cuda.synchronize()
+        assert dev.gemm_status() == 31
+        # fused path
+        kv = dev.PagedKV(1, nblk, heads, hd, page)
+        kv.k.fill_(7.0); kv.v.fill_(7.0)
+        q = torch.full((rows, d), -3.0, device="cuda")
+        rc = L.wkb_gemm_bf16_nt_qkv_append(a.data_ptr(), d_in, w.data_ptr(), d_in, q.data_ptr(), d, rows, 3 * d, d_in, bias.data_ptr(), d,
+                                           kv.k[0].data_ptr(), kv.v[0].data_ptr(), table.data_ptr(), row_slot.data_ptr(), row_pos.data_ptr(),
+                                           heads, hd, page, mbps, s)
+        torch.cuda.synchronize()
+        assert rc == 0 and dev.gemm_status() == 31
+        assert torch.equal(q, qkv[:, :d])
+        assert torch.equal(kv.k.view(torch.int16), kv_ref.k.view(torch.int16)) and torch.equal(kv.v.view(torch.int16), kv_ref.v.view(torch.int16))
+
+
+def test_partial_gemm_slices_sum_to_the_product(dev, orc):
+    import ctypes
+    import torch
+    from wukong_b200 import lib
+    L, s = lib(), torch.cuda.current_stream().cuda_stream
+    for (m, n, k) in [(64, 768, 768), (512, 768, 3072), (100, 256, 64), (2000, 768, 768)]:
+        a = torch.randint(-3, 4, (m, k), device="cuda").to(torch.bfloat16)
+        b = torch.randint(-3, 4, (n, k), device="cuda").to(torch.bfloat16)
+        ns, st = ctypes.c_int64(), ctypes.c_int64()
+        L.wkb_gemm_bf16_partial_layout(m, n, k, ctypes.byref(ns), ctypes.byref(st))
+        assert ns.value >= 1 and st.value == m * n
+        ws = torch.full((ns.value * m * n,), float("nan"), device="cuda")
+        assert L.wkb_gemm_bf16_nt_partial(a.data_ptr(), k, b.data_ptr(), k, m, n, k, ws.data_ptr(), ws.numel() * 4, s) == 0
+        got = ws.view(ns.value, m, n).sum(0)
+        assert torch.equal(got, a.float() @ b.float().T)          # small integers: exact whatever the split
+        assert L.wkb_gemm_bf16_nt_partial(a.data_ptr(), k, b.data_ptr(), k, m, n, k, ws.data_ptr(), ws.numel() * 4 - 4, s) != 0   # short workspace refused
+    assert dev.gemm_status() == 0

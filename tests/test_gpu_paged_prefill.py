@@ -50,7 +50,7 @@ def run_case(dev, orc, q_heads, kv_heads, hd, hist, chunk, seed, ragged=False):
     q = rng.standard_normal((rows, q_heads * hd)).astype(np.float32)
     scale = 1.0 / math.sqrt(hd)
     tile_rows = int(lib().wkb_paged_attn_prefill_tile_rows(q_heads, kv_heads))
-    assert tile_rows == 16 // (q_heads // kv_heads)
+    assert tile_rows == 128 // (q_heads // kv_heads)
     tiles = dev.prefill_tiles(row_slot, tile_rows)
     assert tiles[:, 1].sum() == rows and tiles[:, 1].max() <= tile_rows
     dq, drs, drc, dt = (torch.from_numpy(a).cuda() for a in (q, row_slot, row_ctx, tiles))

@@ -660,6 +660,203 @@ __global__ void __launch_bounds__(PA_WARPS * 32, 2) paged_attn_decode_mma_kernel
   }
 }
 
+// The tensor-core unit with its K / V pages staged in shared memory by TMA.  The cache of a layer is described to the
+// TMA unit as a matrix [token row][head_dim] (token row = (page * kv_heads + head) * 16 + token); a ring slot holds one
+// 16-token page of K and of V as four boxes of 16 rows x 64 dims (2 KiB each, 128-byte swizzle, this GPU's own memory,
+// no multicast): four copies per 8 KiB, issued by lane 0 and counted on the slot's mbarrier.  With the swizzle, row r
+// keeps its 16-byte chunk c at position c ^ (r & 7).  The tokens of a tile are assigned to the MMA's column / k positions
+// through a fixed permutation (position n of an 8-token group holds token SIGMA[n]), chosen so that the two token rows a
+// quarter warp reads for a K fragment differ in bit 2 and the four it reads for a V fragment are all even or all odd:
+// every fragment load is then free of bank conflicts.  A permutation of the keys inside a tile changes neither the
+// scores nor the weighted sum; the mask and the value rows follow the same assignment.
+__device__ __forceinline__ int pa_sigma(int n) {   // 0 5 2 7 4 1 6 3
+  return (n & 1) ? ((n + 4) & 7) : n;
+}
+
+template <int G, int NST>
+__global__ void __launch_bounds__(32) paged_attn_decode_mma_staged_kernel(
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const float* __restrict__ q,
+    const uint32_t* __restrict__ block_table, const int* __restrict__ row_slot, const int* __restrict__ row_ctx,
+    float* __restrict__ scratch, PagedGeo g, float scale_log2e, int* __restrict__ status) {
+  constexpr int HD = 128, BOX = 2048, SLOT = 4 * BOX;      // K dims 0-63 | K dims 64-127 | V dims 0-63 | V dims 64-127
+  extern __shared__ uint8_t pa_smem_raw[];
+  const int lane = threadIdx.x & 31;
+  const int gi = lane >> 2, t = lane & 3;
+  const uint32_t ring = (smem_u32(pa_smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = ring + NST * SLOT;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < NST; ++s) mbar_init(bars + 8u * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
+  __syncwarp();
+  pdl_wait();
+  pdl_trigger();
+  const i64 unit = blockIdx.x;
+  const int chunk = (int)(unit / ((i64)g.rows * g.kv_heads));
+  const int kvh = (int)(unit % g.kv_heads);
+  const int row = (int)((unit / g.kv_heads) % g.rows);
+  const int ctx = min(row_ctx[row], g.mbps * g.page_tokens);
+  const int t0 = chunk * g.chunk_tokens;
+  float* sbase = scratch + (((i64)row * g.q_heads + (i64)kvh * G) * g.max_chunks + chunk) * (HD + 4);
+  const i64 head_stride = (i64)g.max_chunks * (HD + 4);
+  if (t0 >= ctx) {
+    if (lane < G) { float* s = sbase + lane * head_stride; s[HD] = -INFINITY; s[HD + 1] = 0.0f; }
+    return;
+  }
+  const int t1 = min(ctx, t0 + g.chunk_tokens);
+  const int ntiles = (t1 - t0 + 15) >> 4;
+  const uint32_t* bt = block_table + (i64)row_slot[row] * g.mbps;
+  const int first_page = t0 >> 4, last_page = (t1 - 1) >> 4;
+  uint32_t my_page = bt[min(first_page + lane, last_page)];      // page ids of the next 32 tiles, one per lane
+  auto issue = [&](int i) {
+    const uint32_t pg = __shfl_sync(0xffffffffu, my_page, i & 31);
+    if (lane == 0) {
+      const uint32_t slot = ring + (uint32_t)(i % NST) * SLOT, bar = bars + 8u * (i % NST);
+      const int y = (int)(((i64)pg * g.kv_heads + kvh) * 16);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the slot's last readers (generic proxy) are done
+      mbar_expect_tx(bar, SLOT);
+      tma_load_2d(slot, &map_k, bar, 0, y);
+      tma_load_2d(slot + BOX, &map_k, bar, 64, y);
+      tma_load_2d(slot + 2 * BOX, &map_v, bar, 0, y);
+      tma_load_2d(slot + 3 * BOX, &map_v, bar, 64, y);
+    }
+  };
+  const int pre = min(NST, ntiles);
+  for (int i = 0; i < pre; ++i) issue(i);
+  // query fragments: head gi (zero rows past the group), 8 k-steps (j, h), bf16 hi and lo of q * scale * log2(e)
+  uint32_t qh[4][2][2], ql[4][2][2];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float f[8];
+    if (gi < G) {
+      const float* qp = q + (i64)row * g.q_row_stride + ((i64)kvh * G + gi) * HD + 32 * j + 8 * t;
+      const float4 a = *reinterpret_cast<const float4*>(qp), b = *reinterpret_cast<const float4*>(qp + 4);
+      f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.0f;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float x0 = f[4 * h + 2 * c] * scale_log2e, x1 = f[4 * h + 2 * c + 1] * scale_log2e;
+        const uint32_t hi = pack2_bf16(x0, x1);
+        qh[j][h][c] = hi;
+        ql[j][h][c] = pack2_bf16(x0 - u2f(hi << 16), x1 - u2f(hi & 0xffff0000u));
+      }
+  }
+  float m = -INFINITY, l = 0.0f;
+  float acc[2][8][2];
+#pragma unroll
+  for (int sl = 0; sl < 2; ++sl)
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) { acc[sl][jj][0] = 0.0f; acc[sl][jj][1] = 0.0f; }
+  auto lds128 = [](uint32_t addr) {
+    uint4 w;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(addr));
+    return w;
+  };
+  // token (inside the 16-token tile) behind this lane's score columns 2t, 2t+1 of group u, and behind its K column gi
+  const int tokA = pa_sigma(2 * t), tokB = pa_sigma(2 * t + 1), tokK = pa_sigma(gi);
+  bool ok = true;
+  int issued = pre;
+  for (int i = 0; i < ntiles; ++i) {
+    const int tile0 = t0 + 16 * i;
+    if (!mbar_wait(bars + 8u * (i % NST), (uint32_t)((i / NST) & 1))) { ok = false; break; }
+    const uint32_t kslot = ring + (uint32_t)(i % NST) * SLOT, vslot = kslot + 2 * BOX;
+    const int last_local = min(16, t1 - tile0) - 1;     // rows past it may never have been written: clamp onto it (weight forced to zero)
+    // ---- scores of 16 tokens for the group's heads
+    float sc[2][2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      sc[u][0] = 0.0f; sc[u][1] = 0.0f;
+      const int r = min(8 * u + tokK, last_local);
+      const uint32_t rowaddr = kslot + (uint32_t)r * 128u;
+      const uint32_t sw = (uint32_t)(r & 7);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // 16-byte chunk 4j + t of the 256-byte row: half j >> 1, position ((4 (j & 1) + t) ^ (r & 7)) inside it
+        const uint4 kw = lds128(rowaddr + (uint32_t)(j >> 1) * BOX + ((((uint32_t)(4 * (j & 1) + t)) ^ sw) << 4));
+        const uint32_t kr[4] = {kw.x, kw.y, kw.z, kw.w};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mma_bf16_16816(sc[u], qh[j][h][0], qh[j][h][1], kr[2 * h], kr[2 * h + 1]);
+          mma_bf16_16816(sc[u], ql[j][h][0], ql[j][h][1], kr[2 * h], kr[2 * h + 1]);
+        }
+      }
+    }
+    float s4[4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      s4[2 * u] = (tile0 + 8 * u + tokA < t1) ? sc[u][0] : -INFINITY;
+      s4[2 * u + 1] = (tile0 + 8 * u + tokB < t1) ? sc[u][1] : -INFINITY;
+    }
+    float tm = fmaxf(fmaxf(s4[0], s4[1]), fmaxf(s4[2], s4[3]));
+    tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+    tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+    const float mn = fmaxf(m, tm);           // finite: every tile has a visible token
+    const float corr = exp2f(m - mn);
+    m = mn;
+    const uint32_t p01 = pack2_bf16(exp2f(s4[0] - mn), exp2f(s4[1] - mn));
+    const uint32_t p23 = pack2_bf16(exp2f(s4[2] - mn), exp2f(s4[3] - mn));
+    l = l * corr + ((u2f(p01 << 16) + u2f(p01 & 0xffff0000u)) + (u2f(p23 << 16) + u2f(p23 & 0xffff0000u)));
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl)
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) { acc[sl][jj][0] *= corr; acc[sl][jj][1] *= corr; }
+    // ---- values: k positions 2t, 2t+1, 2t+8, 2t+9 hold tokens tokA, tokB, 8 + tokA, 8 + tokB; dims 64 * sl + 8 * gi .. +8
+    uint32_t vrow[4], vsw[4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int r = min(((a & 1) ? tokB : tokA) + 8 * (a >> 1), last_local);
+      vrow[a] = vslot + (uint32_t)r * 128u;
+      vsw[a] = (((uint32_t)gi) ^ (uint32_t)(r & 7)) << 4;
+    }
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl) {
+      const uint4 v0 = lds128(vrow[0] + sl * BOX + vsw[0]), v1 = lds128(vrow[1] + sl * BOX + vsw[1]);
+      const uint4 v2 = lds128(vrow[2] + sl * BOX + vsw[2]), v3 = lds128(vrow[3] + sl * BOX + vsw[3]);
+      const uint32_t x0[4] = {v0.x, v0.y, v0.z, v0.w}, x1[4] = {v1.x, v1.y, v1.z, v1.w};
+      const uint32_t y0[4] = {v2.x, v2.y, v2.z, v2.w}, y1[4] = {v3.x, v3.y, v3.z, v3.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        mma_bf16_16816(acc[sl][2 * e], p01, p23, byte_perm(x0[e], x1[e], 0x5410u), byte_perm(y0[e], y1[e], 0x5410u));
+        mma_bf16_16816(acc[sl][2 * e + 1], p01, p23, byte_perm(x0[e], x1[e], 0x7632u), byte_perm(y0[e], y1[e], 0x7632u));
+      }
+    }
+    __syncwarp();                       // every lane has read the slot
+    if (i + NST < ntiles) {
+      if (((i + NST) & 31) == 0) my_page = bt[min(first_page + i + NST + lane, last_page)];
+      issue(i + NST);
+      ++issued;
+    }
+  }
+  if (!ok) {
+    if (lane == 0) atomicExch(status, WKB_STATUS_ATTN_WAIT);
+    for (int i2 = 0; i2 < issued; ++i2)
+      if (i2 + NST >= issued) mbar_wait(bars + 8u * (i2 % NST), (uint32_t)((i2 / NST) & 1));
+    return;
+  }
+  float lt = l + __shfl_xor_sync(0xffffffffu, l, 1);
+  lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+  if (gi < G) {
+    float* s = sbase + gi * head_stride;
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl) {
+      float* d = s + 64 * sl + 16 * t;
+      *reinterpret_cast<float4*>(d) = make_float4(acc[sl][0][0], acc[sl][1][0], acc[sl][2][0], acc[sl][3][0]);
+      *reinterpret_cast<float4*>(d + 4) = make_float4(acc[sl][4][0], acc[sl][5][0], acc[sl][6][0], acc[sl][7][0]);
+      *reinterpret_cast<float4*>(d + 8) = make_float4(acc[sl][0][1], acc[sl][1][1], acc[sl][2][1], acc[sl][3][1]);
+      *reinterpret_cast<float4*>(d + 12) = make_float4(acc[sl][4][1], acc[sl][5][1], acc[sl][6][1], acc[sl][7][1]);
+    }
+    if (t == 0) { s[HD] = m; s[HD + 1] = lt; }
+  }
+}
+
 // Merge a row-head's chunks in ascending order; out_dtype 0 = f32, 1 = bf16.
 template <int HD>
 __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const float* __restrict__ scratch, void* __restrict__ out,
@@ -740,15 +937,50 @@ __global__ void __launch_bounds__(256) paged_kv_append_kernel(const float* __res
   }
 }
 
+// One layer's cache as a matrix [token rows][head_dim] of bf16 for the TMA unit; box = one page of one head (16 rows) x 64
+// dims, 128-byte swizzle.  The row extent is left open: the kernels only address pages named by the block table.
+static int make_kv_page_map(CUtensorMap* map, const void* cache, i64 head_dim) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return (int)cudaErrorNotSupported;
+  cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)1 << 31};
+  cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+  cuuint32_t box[2] = {64, 16};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
 template <int G>
 static int launch_decode_mma(const float* q, const void* kc, const void* vc, const uint32_t* bt, const int* row_slot,
                              const int* row_ctx, float* scratch, void* out, int out_dtype, i64 out_row_stride, PagedGeo g,
                              float scale, cudaStream_t st) {
   i64 units = (i64)g.rows * g.kv_heads * g.max_chunks;
   i64 blocks = (units + PA_WARPS - 1) / PA_WARPS;
-  if (blocks > 0x7fffffff) return (int)cudaErrorInvalidValue;
-  cudaError_t e = launch_pdl(paged_attn_decode_mma_kernel<G>, (unsigned)blocks, PA_WARPS * 32, 0, st, q, (const uint4*)kc, (const uint4*)vc, bt,
-                             row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f);
+  if (blocks > 0x7fffffff || units > 0x7fffffff) return (int)cudaErrorInvalidValue;
+  cudaError_t e;
+  static const int staged_cfg = [] { const char* s = getenv("WKB_PA_MMA_STAGED"); return s ? atoi(s) : 31; }();
+  int* status = g.page_tokens == 16 && staged_cfg > 0 ? gemm_status_word() : nullptr;
+  if (status) {
+    // one warp per CTA, K / V pages staged in shared memory by TMA (16-token pages only)
+    CUtensorMap mk, mv;
+    int rc = make_kv_page_map(&mk, kc, 128);
+    if (rc) return rc;
+    rc = make_kv_page_map(&mv, vc, 128);
+    if (rc) return rc;
+    constexpr int SLOT = 4 * 2048;
+#define WKB_PA_MMA_STAGED(NST_) launch_pdl(paged_attn_decode_mma_staged_kernel<G, NST_>, (unsigned)units, 32, (size_t)(NST_ * SLOT + NST_ * 8 + 1024), st, mk, mv, q, \
+    bt, row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f, status)
+    switch (staged_cfg / 10) {
+      case 3: e = WKB_PA_MMA_STAGED(3); break;
+      case 4: e = WKB_PA_MMA_STAGED(4); break;
+      default: e = WKB_PA_MMA_STAGED(2); break;
+    }
+#undef WKB_PA_MMA_STAGED
+  } else {
+    e = launch_pdl(paged_attn_decode_mma_kernel<G>, (unsigned)blocks, PA_WARPS * 32, 0, st, q, (const uint4*)kc, (const uint4*)vc, bt,
+                   row_slot, row_ctx, scratch, g, scale * 1.4426950408889634f);
+  }
   if (e != cudaSuccess) return (int)e;
   i64 total = (i64)g.rows * g.q_heads * (128 / 4);
   return (int)launch_pdl(paged_attn_merge_kernel<128>, (unsigned)((total + 127) / 128), 128, 0, st, (const float*)scratch, out, out_dtype,
@@ -838,7 +1070,15 @@ static void pa_plan(i64 rows, i64 kv_heads, i64 head_dim, int G, i64 max_ctx, in
   // the SIMT kernels then write the rows themselves and the merge launch disappears (same time per launch measured
   // on 512 rows x 12 heads with contexts up to 896).
   const bool simt = head_dim == 64 || G == 1;
-  if (simt && chunk_tokens == 512 && max_ctx > 512 && max_ctx <= 1024) chunk_tokens = 1024;
+  if (simt) {
+    // The SIMT kernels stage K / V in shared memory and keep about 2000 single-warp CTAs resident: they want the fewest
+    // chunks that still give some 3000 units (measured on 12 heads of 64, contexts up to 640: 512 rows -- one
+    // 1024-token chunk, no merge launch, 96.7 us; 64 rows -- 256-token chunks 19.4 us against 23.4 us unsplit).
+    const i64 pairs = rows * kv_heads > 0 ? rows * kv_heads : 1;
+    const i64 chunks_wanted = (3000 + pairs - 1) / pairs;
+    chunk_tokens = 1024;
+    while (chunk_tokens > 256 && (max_ctx + chunk_tokens - 1) / chunk_tokens < chunks_wanted) chunk_tokens /= 2;
+  }
   i64 chunks = (max_ctx + chunk_tokens - 1) / chunk_tokens;
   if (chunks < 1) chunks = 1;
   *chunk_tokens_out = chunk_tokens;

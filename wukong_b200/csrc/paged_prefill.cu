@@ -20,6 +20,9 @@
 
 namespace wkb {
 
+int paged_attn_prefill_tc(const float*, i64, const void*, const void*, const uint32_t*, const int*, const int*, const int*, i64, void*, int, i64, i64,
+                          i64, i64, i64, float, cudaStream_t);
+
 struct PrefillGeo {
   int n_tiles, q_heads, kv_heads, page_tokens, page_shift, mbps;
   i64 q_row_stride, out_row_stride;
@@ -41,6 +44,7 @@ __device__ __forceinline__ uint32_t pf_perm(uint32_t a, uint32_t b, uint32_t sel
 }
 
 constexpr int PF_WARPS = 4;
+constexpr int PF_SUBS = 8;   // 16-row sub-tiles of a 128-row tile
 
 template <int HD, int G>
 __global__ void __launch_bounds__(PF_WARPS * 32, HD == 64 ? 3 : 1) paged_attn_prefill_kernel(
@@ -52,11 +56,15 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD == 64 ? 3 : 1) paged_attn_pr
   constexpr int NSL = HD / 64;     // 64-dim slabs of the output
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gi = lane >> 2, t = lane & 3;
+  // a caller's tile holds up to 128 / G rows; a warp takes one of its PF_SUBS sub-tiles of 16 / G rows
   const i64 unit = (i64)blockIdx.x * PF_WARPS + warp;
-  if (unit >= (i64)g.n_tiles * g.kv_heads) return;
+  if (unit >= (i64)g.n_tiles * PF_SUBS * g.kv_heads) return;
   const int kvh = (int)(unit % g.kv_heads);
-  const int2 tile = tiles[unit / g.kv_heads];
-  const int row0 = tile.x, nrows = min(tile.y, 16 / G);
+  const i64 ts = unit / g.kv_heads;
+  const int2 tile = tiles[ts / PF_SUBS];
+  const int sub = (int)(ts % PF_SUBS);
+  const int row0 = tile.x + sub * (16 / G), nrows = min(min(tile.y, 128 / G) - sub * (16 / G), 16 / G);
+  if (nrows <= 0) return;
   // this lane's two A rows: (token, head-of-group) = (a / G, a % G) for a = gi and gi + 8
   int tok[2], hd[2], ctx[2];
 #pragma unroll
@@ -220,7 +228,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD == 64 ? 3 : 1) paged_attn_pr
 template <int HD, int G>
 static int launch_prefill(const float* q, const void* kc, const void* vc, const uint32_t* bt, const int* row_slot, const int* row_ctx,
                           const int* tiles, void* out, int out_dtype, PrefillGeo g, float scale, cudaStream_t st) {
-  const i64 units = (i64)g.n_tiles * g.kv_heads;
+  const i64 units = (i64)g.n_tiles * PF_SUBS * g.kv_heads;
   const i64 blocks = (units + PF_WARPS - 1) / PF_WARPS;
   if (blocks > 0x7fffffff) return (int)cudaErrorInvalidValue;
   paged_attn_prefill_kernel<HD, G><<<(unsigned)blocks, PF_WARPS * 32, 0, st>>>(
@@ -234,11 +242,11 @@ using namespace wkb;
 
 extern "C" {
 
-// Query tokens per tile: the 16 rows of the tensor-core operand hold (token, head-of-group) pairs.
+// Query tokens per tile: the 128 rows of the tensor-core operand hold (token, head-of-group) pairs.
 i64 wkb_paged_attn_prefill_tile_rows(i64 q_heads, i64 kv_heads) {
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return 0;
   const i64 G = q_heads / kv_heads;
-  return (G == 1 || G == 2 || G == 4 || G == 8) ? 16 / G : 0;
+  return (G == 1 || G == 2 || G == 4 || G == 8) ? 128 / G : 0;
 }
 
 int wkb_paged_attn_prefill(const float* q, i64 q_row_stride, const void* kcache, const void* vcache, const uint32_t* block_table,
@@ -256,6 +264,11 @@ int wkb_paged_attn_prefill(const float* q, i64 q_row_stride, const void* kcache,
   PrefillGeo g{(int)n_tiles, (int)q_heads, (int)kv_heads, (int)page_tokens, page_shift, (int)max_blocks_per_seq, q_row_stride, out_row_stride};
   const int G = (int)(q_heads / kv_heads);
   cudaStream_t st = as_stream(stream);
+  // 16-token pages: both contractions on tcgen05, K / V pages landed by TMA; other page sizes: the mma.sync kernel
+  static const bool use_tc = [] { const char* e = getenv("WKB_PREFILL_TC"); return !(e && e[0] == '0'); }();
+  if (page_tokens == 16 && use_tc && (head_dim == 64 || head_dim == 128))
+    return paged_attn_prefill_tc(q, q_row_stride, kcache, vcache, block_table, row_slot, row_ctx, tiles, n_tiles, out, out_dtype, out_row_stride,
+                                 q_heads, kv_heads, head_dim, max_blocks_per_seq, scale, st);
 #define WKB_PF_CASE(HD_, G_) \
   if (head_dim == HD_ && G == G_) return launch_prefill<HD_, G_>(q, kcache, vcache, block_table, row_slot, row_ctx, tiles, out, out_dtype, g, scale, st);
   WKB_PF_CASE(64, 1) WKB_PF_CASE(64, 2) WKB_PF_CASE(64, 4) WKB_PF_CASE(64, 8)

@@ -267,12 +267,15 @@ class PeerReduce:
 
 
 class LlamaDecodeModel:
-    """One rank of the tensor-parallel decode model.  `forward(n)` runs rows 0..n-1 of the row buffers
-    (token, position, slot, visible keys); `reduce(t)` must sum `t` over the ranks in place (None: one rank);
-    `gather(pairs, all_pairs)` must gather the ranks' arg-max candidates (None: one rank)."""
+    """One rank of the tensor-parallel decode model.  The launch sequence lives behind the C ABI (`wkb_llama_step`, cut
+    into phases at the sums over ranks); this class owns the device memory and drives the phases.  `forward(n)` runs rows
+    0..n-1 of the row vectors (token, position, visible keys, slot); `reduce(t)` must sum `t` over the ranks in place
+    (None: one rank); `gather(pairs, all_pairs)` must gather the ranks' arg-max candidates (None: one rank); `peer`
+    (a PeerReduce) selects the library's fused peer-memory reduce instead of `reduce`."""
 
     def __init__(self, cfg, weights, rank, world, bcap, num_pages, max_blocks_per_seq, page_tokens=16, device="cuda",
                  reduce=None, gather=None, peer=None):
+        import ctypes
         cfg.check_world(world)
         self.cfg, self.w, self.rank, self.world, self.bcap, self.device = cfg, weights, rank, world, bcap, device
         self.reduce, self.gather, self.peer = reduce, gather, peer
@@ -283,161 +286,127 @@ class LlamaDecodeModel:
         self.qkv_w = (self.hq + 2 * self.hkv) * hd
         self.kv = dev.PagedKV(cfg.n_layer, num_pages, self.hkv, hd, page_tokens, device)
         i32 = dict(dtype=torch.int32, device=device)
-        self.row_token, self.row_pos = torch.zeros(R, **i32), torch.full((R,), -1, **i32)
-        self.row_slot, self.row_ctx = torch.arange(R, **i32), torch.zeros(R, **i32)
+        self.rows = torch.zeros(4 * R, **i32)            # token | position | visible keys | slot
+        self.rows[R:2 * R] = -1
+        self.rows[3 * R:] = torch.arange(R, **i32)
+        self.row_token, self.row_pos, self.row_ctx, self.row_slot = (self.rows[i * R:(i + 1) * R] for i in range(4))
         self.block_table = torch.zeros((bcap, max_blocks_per_seq), **i32)
-        f32 = dict(dtype=torch.float32, device=device)
-        bf = dict(dtype=torch.bfloat16, device=device)
-        self.x, self.part = torch.zeros((R, d), **f32), torch.zeros((R, d), **f32)
-        # with the peer-memory reduce the two projections write straight into the buffers the peers read
-        self.part_attn, self.part_mlp = (peer.part[0], peer.part[1]) if peer is not None else (self.part, self.part)
-        self.xn = torch.zeros((R, d), **bf)
-        self.qkv = torch.zeros((R, self.qkv_w), **f32)
-        self.att = torch.zeros((R, self.hq * hd), **bf)
-        self.h = torch.zeros((R, self.f), **bf)
-        self.logits = torch.zeros((R, self.vloc), **f32)
-        self.idx_local, self.next_tok = torch.zeros(R, **i32), torch.zeros(R, **i32)
-        self.pairs, self.all_pairs = torch.zeros((R, 2), **i32), torch.zeros((world, R, 2), **i32)
+        self.next_tok = torch.zeros(R, **i32)
         half = hd // 2
         inv = 1.0 / (np.float32(cfg.rope_base) ** (np.arange(half, dtype=np.float32) * np.float32(2.0 / hd)))
         self.inv_freq = torch.from_numpy(inv.astype(np.float32)).to(device)
+        dims = [cfg.n_layer, d, cfg.n_head, cfg.n_kv_head, cfg.d_ff, cfg.vocab, rank, world, bcap, num_pages, max_blocks_per_seq, page_tokens,
+                int(np.float32(cfg.eps).view(np.uint32))]
+        self._dims = (ctypes.c_int64 * len(dims))(*dims)
+        self.workspace = torch.zeros(int(lib().wkb_llama_workspace_bytes(self._dims)) + 256, dtype=torch.uint8, device=device)
+        pad = (-self.workspace.data_ptr()) % 256
+        ptrs = [weights.embed, weights.norm_f, weights.lm_head.tiled, self.inv_freq]
+        for lw in weights.layers:
+            ptrs += [lw["norm1"], lw["norm2"], lw["wqkv"].tiled, lw["wo"].tiled, lw["wgu"].tiled, lw["wdown"].tiled]
+        self._wptrs = (ctypes.c_void_p * len(ptrs))(*[t.data_ptr() for t in ptrs])
+        self._h = lib().wkb_llama_new(self._dims, self._wptrs, self.kv.k.data_ptr(), self.kv.v.data_ptr(), self.block_table.data_ptr(),
+                                      self.rows.data_ptr(), self.next_tok.data_ptr(), self.workspace[pad:].data_ptr())
+        if not self._h:
+            raise ValueError("LlamaDecodeModel: geometry refused by wkb_llama_new")
+        self.n_phases = int(lib().wkb_llama_num_phases(self._h))
+
+        def view(which, dtype, *shape):
+            off = lib().wkb_llama_buffer(self._h, which) - self.workspace.data_ptr()
+            n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+            return self.workspace[off:off + n].view(dtype).view(*shape)
+        f32, bf = torch.float32, torch.bfloat16
+        self.x, self.part, self.xn = view(0, f32, R, d), view(1, f32, R, d), view(2, bf, R, d)
+        self.qkv, self.att, self.h = view(3, f32, R, self.qkv_w), view(4, bf, R, self.hq * hd), view(5, bf, R, self.f)
+        self.logits = view(6, f32, R, self.vloc)
+        self.pairs, self.all_pairs = view(7, torch.int32, R, 2), view(8, torch.int32, world, R, 2)
+        off = lib().wkb_llama_buffer(self._h, 9) - self.workspace.data_ptr()
+        self.scratch = self.workspace[off:off + int(lib().wkb_paged_attn_scratch_bytes(R, self.hq, hd, self.max_ctx))].view(f32)
+        # a GEMM workspace of the model's own for callers that time the linears alone (the step uses the arena's)
         ws_bytes = max(int(lib().wkb_gemm_q4_0_workspace_bytes(w.n, w.k))
                        for w in [weights.lm_head] + [lw[k] for lw in weights.layers for k in ("wqkv", "wo", "wgu", "wdown")])
-        self.workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=device)
-        self.scratch = dev.paged_attn_scratch(R, self.hq, hd, self.max_ctx, device)
+        self.gemm_workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device=device)
         self.scale = 1.0 / math.sqrt(hd)
         self.launches_per_forward = 0
-        self.prefill_tiles = None       # set by set_prefill_rows for a step whose rows are prompt chunks
+        self._tiles = None
+        if peer is not None:
+            check(lib().wkb_llama_set_peer(self._h, peer.part_ptrs[0], peer.part_ptrs[1], peer.flag_ptrs, peer.step.data_ptr()), "wkb_llama_set_peer")
         # one rank, at most 64 rows: the split-K second passes are folded into the kernels that consume the results
-        self.fold_slices = world == 1 and reduce is None and peer is None and bcap <= 64
+        self.fold_slices = world == 1 and peer is None and bcap <= 64
 
-    def _partial_layout(self, w):
-        import ctypes
-        a, b, c = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
-        lib().wkb_gemm_q4_0_partial_layout(w.n, w.k, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
-        return int(a.value), int(b.value), int(c.value)
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().wkb_llama_delete(self._h)
+            self._h = None
 
     def _gemm(self, w, x, ldx, out, ldo, mode, n, what):
         p = lambda t: t.data_ptr()
-        check(lib().wkb_gemm_q4_0_bf16_nt(p(w.tiled), p(x), ldx, p(out), ldo, mode, n, w.n, w.k, p(self.workspace),
-                                          self.workspace.numel(), torch.cuda.current_stream().cuda_stream), what)
+        check(lib().wkb_gemm_q4_0_bf16_nt(p(w.tiled), p(x), ldx, p(out), ldo, mode, n, w.n, w.k, p(self.gemm_workspace),
+                                          self.gemm_workspace.numel(), torch.cuda.current_stream().cuda_stream), what)
 
     def set_prefill_rows(self, row_slot_host):
         """Chunked prefill: the step's rows are laid out sequence by sequence (several consecutive positions of a
         sequence per step, at most `bcap` rows in all); `row_slot_host` is the host copy of row_slot for the live rows.
         Attention then runs on the tiled prefill kernel.  Pass None to go back to one row per sequence."""
         if row_slot_host is None:
-            self.prefill_tiles = None
+            self._tiles = None
+            check(lib().wkb_llama_set_prefill_tiles(self._h, None, 0), "wkb_llama_set_prefill_tiles")
             return
         tile_rows = int(lib().wkb_paged_attn_prefill_tile_rows(self.hq, self.hkv))
         tiles = dev.prefill_tiles(np.asarray(row_slot_host, np.int32), tile_rows)
-        self.prefill_tiles = torch.from_numpy(tiles).to(self.block_table.device)
+        self._tiles = torch.from_numpy(tiles).to(self.block_table.device)
+        check(lib().wkb_llama_set_prefill_tiles(self._h, self._tiles.data_ptr(), self._tiles.shape[0]), "wkb_llama_set_prefill_tiles")
+
+    def _phases(self, n, a, b):
+        check(lib().wkb_llama_step(self._h, n, a, b, torch.cuda.current_stream().cuda_stream), "wkb_llama_step")
 
     # ---- phases (a caller that emulates several ranks on one device runs them in lockstep) ----
     def begin(self, n):
-        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
-        cfg = self.cfg
-        check(L.wkb_embedding_f32(p(self.x), p(self.w.embed), p(self.row_token), n, cfg.d_model, cfg.vocab, s), "embedding")
-        check(L.wkb_add_rmsnorm_bf16(p(self.x), None, p(self.w.layers[0]["norm1"]), p(self.xn), n, cfg.d_model, cfg.eps, s), "norm1")
+        self._phases(n, 0, 1)
 
     def attn_part(self, li, n):
-        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
-        cfg, lw, hd = self.cfg, self.w.layers[li], self.cfg.head_dim
-        if self.fold_slices:
-            nsl, sst, sld = self._partial_layout(lw["wqkv"])
-            self._gemm(lw["wqkv"], self.xn, cfg.d_model, self.qkv, self.qkv_w, 3, n, "qkv")
-            check(L.wkb_rope_qk_paged_append_slices(p(self.qkv), self.qkv_w, p(self.workspace), nsl, sst, sld, p(self.inv_freq),
-                                                    p(self.block_table), p(self.row_slot), p(self.row_pos), p(self.kv.k[li]), p(self.kv.v[li]),
-                                                    n, self.hq, self.hkv, hd // 2, self.page_tokens, self.mbps, s), "rope_append")
-        else:
-            self._gemm(lw["wqkv"], self.xn, cfg.d_model, self.qkv, self.qkv_w, 0, n, "qkv")
-            check(L.wkb_rope_qk_paged_append(p(self.qkv), self.qkv_w, p(self.inv_freq), p(self.block_table), p(self.row_slot), p(self.row_pos),
-                                             p(self.kv.k[li]), p(self.kv.v[li]), n, self.hq, self.hkv, hd // 2, self.page_tokens, self.mbps, s),
-                  "rope_append")
-        if self.prefill_tiles is not None:
-            # prompt chunks: several rows per sequence, keys streamed once per tile (the tiles must cover every live row)
-            check(L.wkb_paged_attn_prefill(p(self.qkv), self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table),
-                                           p(self.row_slot), p(self.row_ctx), p(self.prefill_tiles), self.prefill_tiles.shape[0],
-                                           p(self.att), 1, self.hq * hd, self.hq, self.hkv, hd, self.page_tokens, self.mbps,
-                                           self.scale, s), "prefill attention")
-        else:
-            check(L.wkb_paged_attn_decode(p(self.qkv), self.qkv_w, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
-                                          p(self.row_ctx), p(self.att), 1, self.hq * hd, n, self.hq, self.hkv, hd, self.page_tokens, self.mbps,
-                                          self.max_ctx, self.scale, p(self.scratch), s), "attention")
-        self._gemm(lw["wo"], self.att, self.hq * hd, self.part_attn, cfg.d_model, 3 if self.fold_slices else 0, n, "o_proj")
-
-    def _peer_reduce(self, which, phase, gain, n, what):
-        pr, s, p = self.peer, torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
-        check(lib().wkb_tp_reduce_add_rmsnorm(pr.part_ptrs[which], pr.flag_ptrs, self.rank, self.world, p(pr.step), phase,
-                                              2 * self.cfg.n_layer, p(self.x), p(gain), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), what)
-
-    def _add_slices_norm(self, w, gain, n, what):
-        nsl, sst, sld = self._partial_layout(w)
-        p = lambda t: t.data_ptr()
-        check(lib().wkb_add_slices_rmsnorm_bf16(p(self.x), p(self.workspace), nsl, sst, sld, p(gain), p(self.xn), n, self.cfg.d_model,
-                                                self.cfg.eps, torch.cuda.current_stream().cuda_stream), what)
+        self._phases(n, 1 + 4 * li, 2 + 4 * li)
 
     def after_attn(self, li, n):
-        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
-        if self.peer is not None:
-            return self._peer_reduce(0, 2 * li, self.w.layers[li]["norm2"], n, "reduce_norm2")
-        if self.fold_slices:
-            return self._add_slices_norm(self.w.layers[li]["wo"], self.w.layers[li]["norm2"], n, "norm2")
-        check(L.wkb_add_rmsnorm_bf16(p(self.x), p(self.part), p(self.w.layers[li]["norm2"]), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), "norm2")
+        self._phases(n, 2 + 4 * li, 3 + 4 * li)
 
     def mlp_part(self, li, n):
-        lw = self.w.layers[li]
-        self._gemm(lw["wgu"], self.xn, self.cfg.d_model, self.h, self.f, 2, n, "gate_up")
-        self._gemm(lw["wdown"], self.h, self.f, self.part_mlp, self.cfg.d_model, 3 if self.fold_slices else 0, n, "down")
+        self._phases(n, 3 + 4 * li, 4 + 4 * li)
 
     def after_mlp(self, li, n):
-        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
-        gain = self.w.layers[li + 1]["norm1"] if li + 1 < self.cfg.n_layer else self.w.norm_f
-        if self.peer is not None:
-            return self._peer_reduce(1, 2 * li + 1, gain, n, "reduce_norm_next")
-        if self.fold_slices:
-            return self._add_slices_norm(self.w.layers[li]["wdown"], gain, n, "norm_next")
-        check(L.wkb_add_rmsnorm_bf16(p(self.x), p(self.part), p(gain), p(self.xn), n, self.cfg.d_model, self.cfg.eps, s), "norm_next")
+        self._phases(n, 4 + 4 * li, 5 + 4 * li)
 
     def head_local(self, n):
-        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
-        self._gemm(self.w.lm_head, self.xn, self.cfg.d_model, self.logits, self.vloc, 0, n, "lm_head")
-        check(L.wkb_rowargmax_strided_i32(p(self.logits), p(self.idx_local), n, self.vloc, self.vloc, s), "argmax")
-        check(L.wkb_argmax_pack(p(self.logits), self.vloc, p(self.idx_local), self.rank * self.vloc, n, p(self.pairs), s), "argmax_pack")
+        self._phases(n, self.n_phases - 2, self.n_phases - 1)
 
     def head_pick(self, n):
-        L, s, p = lib(), torch.cuda.current_stream().cuda_stream, (lambda t: t.data_ptr())
-        check(L.wkb_argmax_pick(p(self.all_pairs), self.world, self.bcap, p(self.next_tok), s), "argmax_pick")
-        if self.peer is not None:
-            check(L.wkb_tp_step_bump(p(self.peer.step), s), "step_bump")
+        self._phases(n, self.n_phases - 1, self.n_phases)
 
     def forward(self, n):
-        self.begin(n)
-        for li in range(self.cfg.n_layer):
-            self.attn_part(li, n)
-            if self.reduce is not None and self.peer is None:
+        P = self.n_phases
+        if self.reduce is None or self.peer is not None:
+            self._phases(n, 0, P - 1)                  # no host-side sum: everything up to the pairs in one call
+        else:
+            self.begin(n)
+            for li in range(self.cfg.n_layer):
+                self.attn_part(li, n)
                 self.reduce(self.part)
-            self.after_attn(li, n)
-            self.mlp_part(li, n)
-            if self.reduce is not None and self.peer is None:
+                self.after_attn(li, n)
+                self.mlp_part(li, n)
                 self.reduce(self.part)
-            self.after_mlp(li, n)
-        self.head_local(n)
+                self.after_mlp(li, n)
+            self.head_local(n)
         if self.gather is not None:
             self.gather(self.pairs, self.all_pairs)
         else:
             self.all_pairs[0].copy_(self.pairs)
         self.head_pick(n)
-        # per layer: 2 norms, 4 GEMMs (+ their split-K second passes, not counted), rope + append, attention (2 kernels); embedding + first norm; head: GEMM, arg-max, pack, pick
-        self.launches_per_forward = self.cfg.n_layer * 9 + 2 + 4
+        self.launches_per_forward = int(lib().wkb_llama_launches(self._h)) + (0 if self.gather is not None else 1)
         return self.next_tok
 
     def advance(self, n):
         """Device-side feedback between decode steps: the sampled token becomes the next input, positions and
         visible-key counts move on by one."""
-        p = lambda t: t.data_ptr()
-        check(lib().wkb_decode_advance(p(self.row_token), p(self.row_pos), p(self.row_ctx), p(self.next_tok), n, self.max_ctx - 1,
-                                       torch.cuda.current_stream().cuda_stream), "advance")
+        check(lib().wkb_llama_advance(self._h, n, torch.cuda.current_stream().cuda_stream), "wkb_llama_advance")
 
 
 class LocalTensorParallel:
@@ -506,13 +475,7 @@ class DecodeStepRunner:
 
         if m.peer is not None:
             def body():
-                m.begin(n)
-                for li in range(L):
-                    m.attn_part(li, n)
-                    m.after_attn(li, n)
-                    m.mlp_part(li, n)
-                    m.after_mlp(li, n)
-                m.head_local(n)
+                m._phases(n, 0, m.n_phases - 1)
             self.segments.append(self._capture(body))
 
             def tail():

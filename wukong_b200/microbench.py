@@ -235,7 +235,7 @@ def case_paged_prefill(H, HKV, D, seqs, hist, chunk, hbm, tf, src):
     bt = torch.from_numpy(table.view(np.int32)).cuda()
     rs = np.repeat(np.arange(seqs, dtype=np.int32), chunk)
     rc = np.tile(np.arange(hist + 1, total + 1, dtype=np.int32), seqs)
-    tile_rows = 16 // (H // HKV)
+    tile_rows = int(lib().wkb_paged_attn_prefill_tile_rows(H, HKV))
     tiles = dev.prefill_tiles(rs, tile_rows)
     row_slot, row_ctx, d_tiles = torch.from_numpy(rs).cuda(), torch.from_numpy(rc).cuda(), torch.from_numpy(tiles).cuda()
     out = torch.empty(rows, H * D, dtype=torch.bfloat16, device="cuda")
@@ -250,7 +250,8 @@ def case_paged_prefill(H, HKV, D, seqs, hist, chunk, hbm, tf, src):
             "us": us, "achieved": flops / us / 1e6, "unit": "TFLOP/s", "bound": "tensor", "peak": tf, "frac": flops / us / 1e6 / tf,
             "useful_flops": flops, "key_bytes_streamed": key_bytes, "key_stream_gbs": key_bytes / us / 1e3, "prompt_tok_per_s": rows / us * 1e6,
             "row_per_token_us": us_rows, "speedup_vs_row_per_token": us_rows / us,
-            "note": "mma.sync (legacy tensor path) with q as bf16 hi + lo: 1.5x the useful flops are issued", "peak_source": "of " + src}
+            "note": "tcgen05 (S = Q.K^T with q as bf16 hi + lo, P.V with P in tensor memory): 1.5x the useful flops are issued, "
+                    "plus the masked part of the diagonal blocks", "peak_source": "of " + src}
 
 
 def run(out=sys.stdout, only=None, reps_scale=1.0):

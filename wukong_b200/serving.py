@@ -70,10 +70,13 @@ def _to_dev(a, device):
 
 
 class DecodeModel:
-    """Device-resident GPT-2-shape model over a paged KV cache; `forward(n)` runs the first n rows of
-    the row buffers (token, position, slot, visible keys) and leaves arg-max tokens in `next_tok`."""
+    """Device-resident GPT-2-shape model over a paged KV cache; `forward(n, n_sample)` runs the first n rows of
+    the row vectors (token, position, slot, visible keys) and leaves arg-max tokens in `next_tok`.  The launch sequence
+    itself lives behind the C ABI (`wkb_gpt2_step`); this class owns the device memory (torch tensors) and hands the
+    library their addresses."""
 
     def __init__(self, cfg, weights, bcap, num_pages, max_blocks_per_seq, max_rows=None, page_tokens=16, device="cuda"):
+        import ctypes
         self.cfg, self.bcap, self.device = cfg, bcap, device
         self.max_rows = max_rows or bcap
         self.page_tokens, self.mbps = page_tokens, max_blocks_per_seq
@@ -83,75 +86,59 @@ class DecodeModel:
         self.layers = [{k: _to_dev(v, device) for k, v in lw.items()} for lw in weights["layers"]]
         self.kv = dev.PagedKV(cfg.n_layer, num_pages, cfg.n_head, cfg.head_dim, page_tokens, device)
         i32 = dict(dtype=torch.int32, device=device)
-        self.row_token, self.row_pos = torch.zeros(R, **i32), torch.full((R,), -1, **i32)
-        self.row_slot, self.row_ctx = torch.zeros(R, **i32), torch.zeros(R, **i32)
-        self.sample_rows = torch.zeros(R, **i32)
-        # prompt chunks: rows of runs of one sequence go through the tiled prefill kernel (keys streamed once per
-        # tile); row_ctx_dec is row_ctx with those rows zeroed, for the row-per-token kernel that takes the rest
-        self.row_ctx_dec, self.tiles = torch.zeros(R, **i32), torch.zeros(2 * R, **i32)
+        self.rows = torch.zeros(8 * R, **i32)
+        self.rows[R:2 * R] = -1                                   # every row starts inactive
+        self._carve_rows()
         self.tile_rows = int(lib().wkb_paged_attn_prefill_tile_rows(cfg.n_head, cfg.n_head))
         self.block_table = torch.zeros((bcap, max_blocks_per_seq), **i32)
-        self.x = torch.zeros((R, d), dtype=torch.float32, device=device)
-        self.h = torch.zeros((R, d), dtype=torch.bfloat16, device=device)
-        self.qkv = torch.zeros((R, 3 * d), dtype=torch.float32, device=device)
-        self.att = torch.zeros((R, d), dtype=torch.bfloat16, device=device)
-        self.ff = torch.zeros((R, f), dtype=torch.bfloat16, device=device)
-        self.xs = torch.zeros((bcap, d), dtype=torch.float32, device=device)
-        self.hs = torch.zeros((bcap, d), dtype=torch.bfloat16, device=device)
         self.ldl = (cfg.vocab + 7) // 8 * 8                      # logits pitch, 16-byte aligned rows
         self.logits = torch.zeros((bcap, self.ldl), dtype=torch.float32, device=device)
         self.next_tok = torch.zeros(bcap, **i32)
-        tiles = lib().wkb_gemm_argmax_tiles(cfg.vocab)
-        self.part_val = torch.zeros(bcap * tiles, dtype=torch.float32, device=device)
-        self.part_idx = torch.zeros(bcap * tiles, **i32)
         self.keep_logits = False      # True: materialise fp32 logits (tests); False: arg-max fused into the LM head
-        self.scratch = dev.paged_attn_scratch(R, cfg.n_head, cfg.head_dim, self.max_ctx, device)
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        dims = [cfg.n_layer, d, cfg.n_head, f, cfg.vocab, cfg.n_pos, bcap, R, num_pages, max_blocks_per_seq, page_tokens,
+                int(np.float32(cfg.eps).view(np.uint32))]
+        self._dims = (ctypes.c_int64 * len(dims))(*dims)
+        self.workspace = torch.zeros(int(lib().wkb_gpt2_workspace_bytes(self._dims)) + 256, dtype=torch.uint8, device=device)
+        pad = (-self.workspace.data_ptr()) % 256
+        ws = self.workspace[pad:]
+        ptrs = [self.w["wte"], self.w["wpe"], self.w["lnf_g"], self.w["lnf_b"]]
+        for lw in self.layers:
+            ptrs += [lw[k] for k in ("ln1_g", "ln1_b", "w_qkv", "b_qkv", "w_o", "b_o", "ln2_g", "ln2_b", "w_fc", "b_fc", "w_proj", "b_proj")]
+        self._wptrs = (ctypes.c_void_p * len(ptrs))(*[t.data_ptr() for t in ptrs])
+        self._h = lib().wkb_gpt2_new(self._dims, self._wptrs, self.kv.k.data_ptr(), self.kv.v.data_ptr(), self.block_table.data_ptr(),
+                                     self.rows.data_ptr(), self.next_tok.data_ptr(), ws.data_ptr(), self.logits.data_ptr(), self.ldl)
+        if not self._h:
+            raise ValueError("DecodeModel: geometry refused by wkb_gpt2_new")
+        # typed views of the activation buffers inside the workspace (tests, the benchmark's kernel timings)
+        def view(which, dtype, rows, cols):
+            off = lib().wkb_gpt2_buffer(self._h, which) - self.workspace.data_ptr()
+            n = rows * cols * torch.empty((), dtype=dtype).element_size()
+            return self.workspace[off:off + n].view(dtype).view(rows, cols)
+        self.x, self.h = view(0, torch.float32, R, d), view(1, torch.bfloat16, R, d)
+        self.q, self.att = view(2, torch.float32, R, d), view(3, torch.bfloat16, R, d)
+        self.ff, self.hs = view(4, torch.bfloat16, R, f), view(5, torch.bfloat16, bcap, d)
+        self.scratch = dev.paged_attn_scratch(R, cfg.n_head, cfg.head_dim, self.max_ctx, device)   # for callers that time the attention alone
         self.launches_per_forward = 0
+
+    def _carve_rows(self):
+        R = self.max_rows
+        self.row_token, self.row_pos, self.row_slot, self.row_ctx, self.sample_rows, self.row_ctx_dec = (self.rows[i * R:(i + 1) * R] for i in range(6))
+        self.tiles = self.rows[6 * R:8 * R]
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().wkb_gpt2_delete(self._h)
+            self._h = None
 
     # -- one forward over the first n rows; n_sample rows (indices in sample_rows) reach the LM head
     def forward(self, n, n_sample, n_tiles=0):
-        cfg, L, s = self.cfg, lib(), torch.cuda.current_stream().cuda_stream
-        ctx_dec = self.row_ctx_dec if n_tiles else self.row_ctx
-        d, f, p = cfg.d_model, cfg.d_ff, (lambda t: t.data_ptr())
-        launches = 0
-        check(L.wkb_embed_tok_pos_bf16(p(self.x), p(self.w["wte"]), p(self.w["wpe"]), p(self.row_token), p(self.row_pos), n, d,
-                                       cfg.vocab, cfg.n_pos, s), "embed")
-        launches += 1
-        for li, lw in enumerate(self.layers):
-            check(L.wkb_norm_fast(p(self.x), 0, p(self.h), 1, p(lw["ln1_g"]), p(lw["ln1_b"]), n, d, cfg.eps, 1, s), "ln1")
-            check(L.wkb_gemm_bf16_nt(p(self.h), d, p(lw["w_qkv"]), d, p(self.qkv), 3 * d, 0, n, 3 * d, d, p(lw["b_qkv"]), 0, None, 0, s), "qkv")
-            check(L.wkb_paged_kv_append(p(self.qkv) + 4 * d, p(self.qkv) + 8 * d, 3 * d, p(self.kv.k[li]), p(self.kv.v[li]),
-                                        p(self.block_table), p(self.row_slot), p(self.row_pos), n, cfg.n_head, cfg.head_dim,
-                                        self.page_tokens, self.mbps, s), "kv_append")
-            check(L.wkb_paged_attn_decode(p(self.qkv), 3 * d, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
-                                          p(ctx_dec), p(self.att), 1, d, n, cfg.n_head, cfg.n_head, cfg.head_dim, self.page_tokens,
-                                          self.mbps, self.max_ctx, self.scale, p(self.scratch), s), "attn")
-            if n_tiles:
-                check(L.wkb_paged_attn_prefill(p(self.qkv), 3 * d, p(self.kv.k[li]), p(self.kv.v[li]), p(self.block_table), p(self.row_slot),
-                                               p(self.row_ctx), p(self.tiles), n_tiles, p(self.att), 1, d, cfg.n_head, cfg.n_head,
-                                               cfg.head_dim, self.page_tokens, self.mbps, self.scale, s), "attn_prefill")
-            check(L.wkb_gemm_bf16_nt(p(self.att), d, p(lw["w_o"]), d, p(self.x), d, 0, n, d, d, p(lw["b_o"]), 0, p(self.x), d, s), "o_proj")
-            check(L.wkb_norm_fast(p(self.x), 0, p(self.h), 1, p(lw["ln2_g"]), p(lw["ln2_b"]), n, d, cfg.eps, 1, s), "ln2")
-            check(L.wkb_gemm_bf16_nt(p(self.h), d, p(lw["w_fc"]), d, p(self.ff), f, 1, n, f, d, p(lw["b_fc"]), 2, None, 0, s), "fc")
-            check(L.wkb_gemm_bf16_nt(p(self.ff), f, p(lw["w_proj"]), f, p(self.x), d, 0, n, d, f, p(lw["b_proj"]), 0, p(self.x), d, s), "proj")
-            launches += 9
-        # LM head on the sampled rows only: gather -> final norm -> tied head -> arg-max
-        check(L.wkb_embedding_f32(p(self.xs), p(self.x), p(self.sample_rows), n_sample, d, n, s), "gather")
-        check(L.wkb_norm_fast(p(self.xs), 0, p(self.hs), 1, p(self.w["lnf_g"]), p(self.w["lnf_b"]), n_sample, d, cfg.eps, 1, s), "lnf")
-        if self.keep_logits:
-            check(L.wkb_gemm_bf16_nt(p(self.hs), d, p(self.w["wte"]), d, p(self.logits), self.ldl, 0, n_sample, cfg.vocab, d, None, 0, None, 0, s), "lm_head")
-            check(L.wkb_rowargmax_strided_i32(p(self.logits), p(self.next_tok), n_sample, cfg.vocab, self.ldl, s), "argmax")
-        else:
-            check(L.wkb_gemm_bf16_nt_argmax(p(self.hs), d, p(self.w["wte"]), d, n_sample, cfg.vocab, d, None, p(self.part_val),
-                                            p(self.part_idx), p(self.next_tok), s), "lm_head_argmax")
-        # the attention call is two kernels; a GEMM with few tiles and K >= 2048 (the down projection) adds its
-        # split-K finishing pass
-        tiles = lambda m, nn: ((m + 127) // 128) * ((nn + 127) // 128)
-        split = 1 if (2 * tiles(n, d) <= 148 and f >= 2048) else 0
-        attn = int(L.wkb_paged_attn_decode_launches(n, cfg.n_head, cfg.n_head, cfg.head_dim, self.max_ctx, 1, d)) - 1   # beyond the one counted above
-        self.launches_per_forward = launches + len(self.layers) * (attn + split + (1 if n_tiles else 0)) + 4
+        check(lib().wkb_gpt2_step(self._h, n, n_sample, n_tiles, int(self.keep_logits), torch.cuda.current_stream().cuda_stream), "wkb_gpt2_step")
+        self.launches_per_forward = int(lib().wkb_gpt2_launches(self._h))
         return self.next_tok
+
+    def advance(self, n):
+        check(lib().wkb_gpt2_advance(self._h, n, torch.cuda.current_stream().cuda_stream), "wkb_gpt2_advance")
 
 
 class StepTimeout(RuntimeError):
@@ -175,10 +162,8 @@ class Engine:
         pin = lambda n, dt=torch.int32: torch.zeros(n, dtype=dt).pin_memory()
         # one pinned staging block: token | pos | slot | ctx | sample_rows | ctx of the row-per-token kernel | prefill tiles
         self.h_rows = pin(8 * R)
-        self.d_rows = torch.zeros(8 * R, dtype=torch.int32, device=device)
         m = self.model
-        m.row_token, m.row_pos, m.row_slot, m.row_ctx, m.sample_rows, m.row_ctx_dec = (self.d_rows[i * R:(i + 1) * R] for i in range(6))
-        m.tiles = self.d_rows[6 * R:8 * R]
+        self.d_rows = m.rows                   # the model's own row block (the library reads the step's rows from it)
         self.use_prefill_kernel = True
         self.h_table = pin(bcap * max_blocks_per_seq)
         self.h_next = pin(bcap)
@@ -300,8 +285,7 @@ class Engine:
         m = self.model
         def body():
             m.forward(self.bcap, self.bcap)
-            check(lib().wkb_decode_advance(m.row_token.data_ptr(), m.row_pos.data_ptr(), m.row_ctx.data_ptr(),
-                                           m.next_tok.data_ptr(), self.bcap, m.max_ctx - 1, torch.cuda.current_stream().cuda_stream), "advance")
+            m.advance(self.bcap)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.stream(self.stream):
             with torch.cuda.graph(g, stream=self.stream):
