@@ -139,7 +139,8 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
       ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// 32 registers -> 32 consecutive columns of this thread's TMEM lane; returns once the store has landed
+// 32 registers -> 32 consecutive columns of this thread's TMEM lane; the caller waits for the store (tcgen05.wait::st)
+// before it tells anyone about it
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -150,7 +151,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
         "r"(r[30]), "r"(r[31])
       : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -311,6 +311,18 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     const uint32_t swz = (uint32_t)(r & 7);
     int it = 0;
     bool ok = true;
+    int pending = -1;     // operand buffer whose tcgen05.st has been issued but not yet announced
+    // The store of a stage is announced to the MMA lane one iteration later, after the next stage's raw bytes have been
+    // requested from shared memory: the thread then never sits in tcgen05.wait::st right behind its own store.
+    auto publish = [&]() {
+      if (pending >= 0) {
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_full(pending));
+        pending = -1;
+      }
+    };
     for (int t = group; t < plan.n_tiles && ok; t += plan.groups) {
       for (int s = 0; s < nstages && ok; ++s, ++it) {
         const int slot = it % RAW_STAGES;
@@ -319,6 +331,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         const uint4 q0 = lds128(rawp + r * 128 + (((uint32_t)(2 * part) ^ swz) << 4));
         const uint4 q1 = lds128(rawp + r * 128 + (((uint32_t)(2 * part + 1) ^ swz) << 4));
         const uint32_t sw = lds32(rawp + RAW_BYTES + r * 16 + part * 4);   // f16 scales of blocks 2*part, 2*part+1
+        publish();                                                          // the previous stage's store has had time to land
         __syncwarp();
         if (lane == 0) mbar_arrive(raw_empty(slot));                        // the stage now lives in registers
         uint32_t v[32];
@@ -329,11 +342,10 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(A_COL0 + buf * A_STAGE_COLS + part * 32);
         tmem_st32(ta, v);
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(a_full(buf));
+        pending = buf;
       }
     }
+    publish();
   } else {
     // ---------------- epilogue warps: TMEM lane quarter (warp % 4), thread = weight row ----------------
     const int quarter = warp & 3;

@@ -82,7 +82,8 @@ struct LlamaModel {
   // prompt chunks (optional)
   const int* tiles;
   i64 n_tiles;
-  bool fold_slices;
+  bool fold_slices;   // one rank, <= 64 rows: the O / down split-K second passes are folded into the add + norm that follows
+  bool fold_qkv;      // <= 64 rows (any rank count): the QKV projection's second pass is folded into RoPE + append
   i64 launches;
 };
 
@@ -169,7 +170,7 @@ static int ll_phase(LlamaModel* m, i64 ph, i64 n, void* stream) {
   float* part_mlp = m->peer ? (float*)m->part_ptrs[1][m->rank] : m->part;
   switch (sub) {
     case 0: {   // attention part
-      if (m->fold_slices) {
+      if (m->fold_qkv) {
         i64 nsl, sst, sld;
         wkb_gemm_q4_0_partial_layout(m->qkv_w, d, &nsl, &sst, &sld);
         WKB_TRY(ll_gemm(m, lw.wqkv, m->qkv_w, d, m->xn, d, m->qkv, m->qkv_w, 3, n, stream));
@@ -262,6 +263,7 @@ void* wkb_llama_new(const i64* dims, const void* const* weights, void* kcache, v
   m->gemm_ws = b + Lo.off[11]; m->gemm_ws_bytes = Lo.gemm_ws_bytes;
   m->peer = false; m->step_ptr = nullptr; m->tiles = nullptr; m->n_tiles = 0;
   m->fold_slices = world == 1 && m->bcap <= 64;
+  m->fold_qkv = m->bcap <= 64;
   m->launches = 0;
   wkb_gemm_init();
   return m;

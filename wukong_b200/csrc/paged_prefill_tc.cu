@@ -8,14 +8,14 @@
 //                 B = a block of 128 keys = 8 pages, each page landed by TMA (cp.async.bulk.tensor.2d over the cache seen
 //                 as a [token row, head_dim] matrix; 128-byte swizzle; this GPU's memory; no multicast) exactly as the
 //                 K-major operand wants it; accumulator: 128 lanes x 128 columns of tensor memory.
-//   softmax       four warps, thread = query row = TMEM lane: tcgen05.ld the row's 128 scores, mask by the row's own
+//   softmax       eight warps, two threads per query row (= TMEM lane): tcgen05.ld the row's 128 scores, mask by the row's own
 //                 visible-key count, online max / sum in base 2, probabilities rounded to bf16 (the normaliser sums the
 //                 rounded values) and written back to tensor memory with tcgen05.st.
 //   O += P . V    A = P from TENSOR MEMORY; B = the V pages as they lie in the cache ([key][dim], i.e. the MN-major form
 //                 of the operand: no transpose pass), fp32 accumulator in tensor memory, rescaled in place when a
 //                 row's running maximum moves.
-// One CTA = (tile, KV head): 192 threads = TMA producer warp, MMA-issuing warp, four softmax / epilogue warps; K / V
-// blocks go through a 2-deep ring.  Keys are streamed once per 128 / G query tokens.  Every index depends on the
+// One CTA = (tile, KV head): 320 threads = TMA producer warp, MMA-issuing warp, eight softmax / epilogue warps (two
+// threads per query row); K / V blocks go through a 2-deep ring.  Keys are streamed once per 128 / G query tokens.  Every index depends on the
 // logical key position only.  Every mbarrier wait is bounded (status code WKB_STATUS_ATTN_WAIT, rows left unwritten).
 #include "common.cuh"
 #include "wkb_device.h"
@@ -26,7 +26,7 @@ int* gemm_status_word();
 
 namespace pftc {
 
-constexpr int QROWS = 128, KBLK = 128, THREADS = 192, STAGES = 2;
+constexpr int QROWS = 128, KBLK = 128, THREADS = 320, STAGES = 2;   // warps: TMA producer, MMA issuer, 8 x softmax
 constexpr int SUB_BYTES = 128 * 128;          // one 64-dim half of a 128-row operand tile: 128 rows x 128 B
 
 struct Geo {
@@ -69,6 +69,18 @@ __device__ __forceinline__ void tld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tst32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -86,16 +98,21 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return r;
 }
 
-// Shared memory: Q tile | STAGES x (K block, V block) | barriers | tmem slot | tile-wide max of the visible-key counts
+// Shared memory: Q tile | STAGES x (K block, V block) | barriers (nine, 72 bytes) | tmem slot (+128) | tile-wide max of the visible-key counts
 template <int HD>
 struct Smem {
   static constexpr int NSUB = HD / 64;
   static constexpr int OP_BYTES = NSUB * SUB_BYTES;                 // one 128-row operand (Q, a K block or a V block)
   static constexpr int STAGE_BYTES = 2 * OP_BYTES;
   static constexpr int Q_BYTES = 2 * OP_BYTES;                      // the query tile twice: bf16 hi part and bf16 lo part
-  static constexpr int BYTES = Q_BYTES + STAGES * STAGE_BYTES + 1024 /*align*/ + 256;
-  static constexpr uint32_t TMEM_COLS = HD == 64 ? 256 : 512;
-  static constexpr int S_COL = 0, P_COL = 128, O_COL = HD == 64 ? 192 : 256;
+  static constexpr int XCH_BYTES = 2 * (2 * 2 * 128 * 4);           // values + sequence numbers traded by the two threads of a row
+  static constexpr int BYTES = Q_BYTES + STAGES * STAGE_BYTES + 1024 /*align*/ + 256 + XCH_BYTES;
+  // head_dim 128 runs one CTA per SM and double-buffers the scores and the probabilities in tensor memory, so the next
+  // block's Q . K^T runs while this block's softmax does; head_dim 64 fits two CTAs per SM (256 columns each), which
+  // overlap each other instead
+  static constexpr bool DB = HD == 128;
+  static constexpr uint32_t TMEM_COLS = DB ? 512 : 256;
+  static constexpr int S_COL0 = 0, S_COL1 = DB ? 128 : 0, P_COL0 = DB ? 256 : 128, P_COL1 = DB ? 320 : 128, O_COL = DB ? 384 : 192;
 };
 
 template <int HD, int G>
@@ -112,11 +129,18 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
   uint8_t* gen = smem_raw + (base - raw);
   const uint32_t q_base = base, ring = base + SM::Q_BYTES;
   const uint32_t bars = ring + STAGES * SM::STAGE_BYTES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + SM::Q_BYTES + STAGES * SM::STAGE_BYTES + 64);
-  int* kmax_slot = reinterpret_cast<int*>(gen + SM::Q_BYTES + STAGES * SM::STAGE_BYTES + 72);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + SM::Q_BYTES + STAGES * SM::STAGE_BYTES + 128);
+  int* kmax_slot = reinterpret_cast<int*>(gen + SM::Q_BYTES + STAGES * SM::STAGE_BYTES + 136);
+  float* xmax = reinterpret_cast<float*>(gen + SM::Q_BYTES + STAGES * SM::STAGE_BYTES + 256);
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  const uint32_t s_full = bars + 8u * (2 * STAGES), p_full = bars + 8u * (2 * STAGES + 1), o_full = bars + 8u * (2 * STAGES + 2);
+  const uint32_t s_full0 = bars + 8u * (2 * STAGES), p_full = bars + 8u * (2 * STAGES + 1), o_full = bars + 8u * (2 * STAGES + 2);
+  const uint32_t s_full1 = bars + 8u * (2 * STAGES + 3), o_done = bars + 8u * (2 * STAGES + 4);
+  // score / probability buffer and barrier phase of key block kb
+  auto s_bar = [&](int kb) { return (SM::DB && (kb & 1)) ? s_full1 : s_full0; };
+  auto s_par = [&](int kb) { return (uint32_t)(SM::DB ? (kb >> 1) & 1 : kb & 1); };
+  auto s_col = [&](int kb) { return (uint32_t)((kb & 1) ? SM::S_COL1 : SM::S_COL0); };
+  auto p_col = [&](int kb) { return (uint32_t)((kb & 1) ? SM::P_COL1 : SM::P_COL0); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.x % g.kv_heads;
@@ -126,7 +150,7 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(o_full, 1);
+    mbar_init(s_full0, 1); mbar_init(s_full1, 1); mbar_init(p_full, 8); mbar_init(o_full, 1); mbar_init(o_done, 1);
     *kmax_slot = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
@@ -136,11 +160,25 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(SM::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  // ---- the query tile: fp32 rows -> bf16, pre-scaled, into the swizzled K-major operand image; rows past `live` are zero
-  {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  // the tile-wide largest visible-key count decides how many key blocks every role walks
+  if (threadIdx.x < QROWS) {
+    const int a = threadIdx.x;
+    const int c = a < live ? min(row_ctx[row0 + a / G], g.mbps * 16) : 0;
+    if (c > 0) atomicMax(kmax_slot, c);
+  }
+  for (int i = threadIdx.x; i < 2 * 2 * QROWS; i += THREADS) reinterpret_cast<int*>(xmax + 2 * 2 * QROWS)[i] = 0;
+  __syncthreads();
+  const uint32_t tmem = *tmem_slot;
+  const int kmax = *kmax_slot;
+  const int nkb = (kmax + KBLK - 1) / KBLK;
+  // ---- the query tile: fp32 rows -> bf16 hi + lo, pre-scaled, into the swizzled K-major operand image; rows past `live`
+  // are zero.  Warps 1-9 do this while the producer warp already has the first key blocks under way.
+  if (warp != 0) {
     constexpr int CH = HD / 8;                     // 16-byte chunks per operand row
-    for (int idx = threadIdx.x; idx < QROWS * CH; idx += THREADS) {
+    for (int idx = threadIdx.x - 32; idx < QROWS * CH; idx += THREADS - 32) {
       const int a = idx / CH, c = idx % CH;
       uint32_t hi[4] = {0u, 0u, 0u, 0u}, lo[4] = {0u, 0u, 0u, 0u};
       if (a < live) {
@@ -159,20 +197,9 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
       asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
       asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + SM::OP_BYTES), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
     }
-    // the tile-wide largest visible-key count decides how many key blocks every role walks
-    if (threadIdx.x < QROWS) {
-      const int a = threadIdx.x;
-      const int c = a < live ? min(row_ctx[row0 + a / G], g.mbps * 16) : 0;
-      if (c > 0) atomicMax(kmax_slot, c);
-    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the MMA reads the query image through the async proxy
+    asm volatile("bar.sync 1, %0;" ::"n"(THREADS - 32) : "memory");    // every thread of warps 1-9 gets here unconditionally
   }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the MMA reads the query image through the async proxy
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = *tmem_slot;
-  const int kmax = *kmax_slot;
-  const int nkb = (kmax + KBLK - 1) / KBLK;
   const uint32_t* bt = block_table + (i64)row_slot[row0] * g.mbps;
 
   if (warp == 0) {
@@ -216,100 +243,147 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
     if (lane == 0) {
       constexpr uint32_t ID_S = idesc(KBLK, false), ID_O = idesc(HD, true);
       bool ok = true;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
+      // S(kb) = Q . K(kb)^T over head_dim in steps of 16, query hi part then lo part
+      auto issue_scores = [&](int kb) {
         const int s = kb % STAGES;
-        if (!mbar_wait(full_bar(s), (kb / STAGES) & 1)) { atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; break; }
+        if (!mbar_wait(full_bar(s), (kb / STAGES) & 1)) { atomicExch(status, WKB_STATUS_ATTN_WAIT); return false; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t kaddr = ring + s * SM::STAGE_BYTES, vaddr = kaddr + SM::OP_BYTES;
-        // S = Q . K^T over head_dim in steps of 16 (the previous block's P . V, issued earlier, retires first)
+        const uint32_t kaddr = ring + s * SM::STAGE_BYTES;
 #pragma unroll
         for (int part = 0; part < 2; ++part)
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k) {
             const uint32_t off = (uint32_t)(k >> 2) * SUB_BYTES + (uint32_t)(k & 3) * 32u;
-            umma_bf16(tmem + SM::S_COL, make_sdesc(q_base + part * SM::OP_BYTES + off), make_sdesc(kaddr + off), ID_S, (part > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem + s_col(kb), make_sdesc(q_base + part * SM::OP_BYTES + off), make_sdesc(kaddr + off), ID_S, (part > 0 || k > 0) ? 1u : 0u);
           }
-        umma_commit(s_full);
+        umma_commit(s_bar(kb));
+        return true;
+      };
+      if (SM::DB && nkb > 0) ok = issue_scores(0);
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        // double-buffered: the next block's scores are issued before this block's P . V, so they are computed while the
+        // softmax warps work on this block (the buffer they go to was released with the block before this one)
+        if (SM::DB) { if (kb + 1 < nkb) ok = issue_scores(kb + 1); }
+        else ok = issue_scores(kb);
+        if (!ok) break;
         // O += P . V once the softmax warps have written P (and rescaled O, and zeroed the V rows past the last key)
         if (!mbar_wait(p_full, kb & 1)) { atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t vaddr = ring + (kb % STAGES) * SM::STAGE_BYTES + SM::OP_BYTES;
 #pragma unroll
         for (int k = 0; k < KBLK / 16; ++k)
-          umma_ts(tmem + SM::O_COL, tmem + SM::P_COL + (uint32_t)(k * 8), make_sdesc_mn(vaddr + (uint32_t)k * 2048u, SUB_BYTES), ID_O,
+          umma_ts(tmem + SM::O_COL, tmem + p_col(kb) + (uint32_t)(k * 8), make_sdesc_mn(vaddr + (uint32_t)k * 2048u, SUB_BYTES), ID_O,
                   (kb > 0 || k > 0) ? 1u : 0u);
-        umma_commit(empty_bar(s));
+        umma_commit(empty_bar(kb % STAGES));
+        umma_commit(o_done);
         if (kb + 1 == nkb) umma_commit(o_full);
       }
     }
   } else {
-    // ---------------- softmax and epilogue: thread = operand row a = TMEM lane ----------------
-    const int quarter = warp & 3;
+    // ---------------- softmax and epilogue: eight warps, two threads per operand row ----------------
+    // A warp reaches the 32 TMEM lanes of its quarter (warp % 4); warps w and w + 4 share a quarter and split a row's
+    // 128 keys (and the output's columns) in two halves.  With one warp per scheduler the exponentials and the
+    // dependent max / sum chains were the slowest part of a key block, so the halves double the warps in flight, the
+    // scores of a half stay in registers (one pass, two loads in flight), the chains are split four ways and the
+    // unmasked interior blocks skip the mask.
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int a = quarter * 32 + lane;
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
     const int ctx = a < live ? min(row_ctx[row0 + a / G], g.mbps * 16) : 0;
-    float m_run = -INFINITY, l_run = 0.0f;
+    const int sm_tid = (warp - 2) * 32 + lane;               // 0 .. 255 over the softmax warps
+    float m_run = -INFINITY, l_run = 0.0f;                   // l_run: this thread's half of the row's normaliser
     bool ok = true;
+    auto ex2 = [](float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; };
+    // The two threads of a row trade one float per key block through shared memory: value, then a sequence number; the
+    // reader polls the partner's sequence number a bounded number of times (no barrier instruction: a barrier that one
+    // side never reaches cannot be bounded).  Slots alternate by block parity, so a writer two blocks ahead is the
+    // earliest that could touch a slot again, and it cannot be two ahead before its partner has read this one.
+    volatile float* xval = xmax;
+    volatile int* xseq = reinterpret_cast<volatile int*>(xmax + 2 * 2 * QROWS);
+    auto exchange = [&](int seq, float mine, float& theirs) {
+      const int me = ((seq & 1) * 2 + half) * QROWS + a, them = ((seq & 1) * 2 + (half ^ 1)) * QROWS + a;
+      xval[me] = mine;
+      __threadfence_block();
+      xseq[me] = seq + 1;
+      for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        if (xseq[them] == seq + 1) { __threadfence_block(); theirs = xval[them]; return true; }
+      }
+      return false;
+    };
     for (int kb = 0; kb < nkb; ++kb) {
       int good = 1;
-      if (lane == 0) good = mbar_wait(s_full, kb & 1) ? 1 : 0;
+      if (lane == 0) good = mbar_wait(s_bar(kb), s_par(kb)) ? 1 : 0;
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) { if (lane == 0) atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int key0 = kb * KBLK;
-      const int vis = min(max(ctx - key0, 0), KBLK);          // visible keys of this row inside the block
-      // pass 1: the row's maximum over its visible scores
-      float bm = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < KBLK; c0 += 32) {
-        uint32_t r[32];
-        tld32(lane_base + SM::S_COL + c0, r);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) bm = (c0 + e < vis) ? fmaxf(bm, __uint_as_float(r[e])) : bm;
+      const int key0 = kb * KBLK + 64 * half;
+      const int vis = min(max(ctx - key0, 0), 64);            // visible keys of this row inside this thread's half block
+      uint32_t r[64];
+      {
+        uint32_t (&r0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
+        uint32_t (&r1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
+        tld32_nowait(lane_base + s_col(kb) + 64 * half, r0);
+        tld32_nowait(lane_base + s_col(kb) + 64 * half + 32, r1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
-      const float m_new = fmaxf(m_run, bm);
+      const bool interior = __all_sync(0xffffffffu, vis == 64);
+      if (!interior) {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) r[e] = e < vis ? r[e] : 0xff800000u;      // -inf
+      }
+      float b4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int e = 0; e < 64; e += 4) {
+        b4[0] = fmaxf(b4[0], __uint_as_float(r[e])); b4[1] = fmaxf(b4[1], __uint_as_float(r[e + 1]));
+        b4[2] = fmaxf(b4[2], __uint_as_float(r[e + 2])); b4[3] = fmaxf(b4[3], __uint_as_float(r[e + 3]));
+      }
+      const float bm = fmaxf(fmaxf(b4[0], b4[1]), fmaxf(b4[2], b4[3]));
+      // the other half's maximum
+      float other;
+      if (!exchange(kb, bm, other)) { if (lane == 0) atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; break; }
+      const float m_new = fmaxf(m_run, fmaxf(bm, other));
       const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-      const float corr = exp2f(m_run - m_use);                 // 0 for a row that had seen nothing yet
-      // pass 2: probabilities, rounded to bf16, into tensor memory as the A operand of P . V (a column = two keys)
-      float rs = 0.0f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < KBLK; c0 += 64) {
-        uint32_t pk[32];
+      const float corr = ex2(m_run - m_use);                   // 0 for a row that had seen nothing yet
+      // probabilities, rounded to bf16, into tensor memory as the A operand of P . V (a column = two keys); the
+      // normaliser sums the rounded values
+      uint32_t pk[32];
+      float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t r[32];
-          tld32(lane_base + SM::S_COL + c0 + 32 * hh, r);
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const int c = c0 + 32 * hh + e;
-            const float p0 = c < vis ? exp2f(__uint_as_float(r[e]) - m_use) : 0.0f;
-            const float p1 = c + 1 < vis ? exp2f(__uint_as_float(r[e + 1]) - m_use) : 0.0f;
-            const uint32_t w = pack2(p0, p1);
-            rs += u2f(w << 16) + u2f(w & 0xffff0000u);
-            pk[16 * hh + (e >> 1)] = w;
-          }
-        }
-        tst32(lane_base + SM::P_COL + (c0 >> 1), pk);
+      for (int e = 0; e < 64; e += 2) {
+        const uint32_t w = pack2(ex2(__uint_as_float(r[e]) - m_use), ex2(__uint_as_float(r[e + 1]) - m_use));   // ex2(-inf) = 0
+        pk[e >> 1] = w;
+        s4[(e >> 1) & 1] += u2f(w << 16);
+        s4[2 + ((e >> 1) & 1)] += u2f(w & 0xffff0000u);
       }
-      l_run = l_run * corr + rs;
+      tst32(lane_base + p_col(kb) + 32 * half, pk);
+      l_run = l_run * corr + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
       m_run = m_new;
-      // rescale the output accumulator when any row of this warp moved its maximum (the accumulator holds the blocks
-      // before this one: their P . V retired before this block's scores did)
+      // rescale this thread's half of the output accumulator when a row of the warp moved its maximum; the accumulator
+      // holds the blocks before this one, whose last P . V must have retired (with single-buffered scores it retired
+      // before this block's scores did)
+      if (SM::DB && kb > 0) {
+        int od = 1;
+        if (lane == 0) od = mbar_wait(o_done, (kb - 1) & 1) ? 1 : 0;
+        od = __shfl_sync(0xffffffffu, od, 0);
+        if (!od) { if (lane == 0) atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
       if (kb > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t r[32];
-          tld32(lane_base + SM::O_COL + c0, r);
+        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+          uint32_t o[32];
+          tld32(lane_base + SM::O_COL + half * (HD / 2) + c0, o);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * corr);
-          tst32(lane_base + SM::O_COL + c0, r);
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+          tst32(lane_base + SM::O_COL + half * (HD / 2) + c0, o);
         }
       }
       // the last block may hold key rows that were never written (a partly filled page): their probabilities are zero,
       // but 0 x NaN would still poison the product, so those V rows are zeroed in shared memory first
-      if (kb + 1 == nkb && (kmax - key0) < KBLK) {
+      if (kb + 1 == nkb && (kmax - kb * KBLK) < KBLK) {
         const uint32_t vaddr = ring + (kb % STAGES) * SM::STAGE_BYTES + SM::OP_BYTES;
-        const int first_bad = kmax - key0;
-        for (int idx = (warp - 2) * 32 + lane; idx < (KBLK - first_bad) * NSUB * 8; idx += 128) {
+        const int first_bad = kmax - kb * KBLK;
+        for (int idx = sm_tid; idx < (KBLK - first_bad) * NSUB * 8; idx += 256) {
           const int rrow = first_bad + idx / (NSUB * 8), rem = idx % (NSUB * 8);
           asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(vaddr + (uint32_t)(rem >> 3) * SUB_BYTES + (uint32_t)rrow * 128u + (uint32_t)((rem & 7) << 4)),
                        "r"(0u) : "memory");
@@ -321,36 +395,40 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    // ---- epilogue: normalise and write the rows
+    // ---- epilogue: normalise and write this thread's half of the row
     if (ok && nkb > 0) {
       int good = 1;
       if (lane == 0) good = mbar_wait(o_full, 0) ? 1 : 0;
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) { if (lane == 0) atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; }
     }
+    // the two halves of the normaliser meet the same way
+    float l_other = 0.0f;
+    if (ok && nkb > 0 && !exchange(nkb, l_run, l_other)) { if (lane == 0) atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; }
+    const float l_tot = l_run + l_other;
     if (ok && nkb > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float inv = l_run != 0.0f ? 1.0f / l_run : 0.0f;
-      const i64 o = (i64)(row0 + a / G) * g.out_row_stride + ((i64)kvh * G + a % G) * HD;
+      const float inv = l_tot != 0.0f ? 1.0f / l_tot : 0.0f;
+      const i64 o = (i64)(row0 + a / G) * g.out_row_stride + ((i64)kvh * G + a % G) * HD + half * (HD / 2);
 #pragma unroll 1
-      for (int c0 = 0; c0 < HD; c0 += 32) {
-        uint32_t r[32];
-        tld32(lane_base + SM::O_COL + c0, r);       // every lane of the warp takes part in the load
+      for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+        uint32_t rr[32];
+        tld32(lane_base + SM::O_COL + half * (HD / 2) + c0, rr);       // every lane of the warp takes part in the load
         if (ctx > 0) {
           if (out_dtype == 0) {
             float4* d = reinterpret_cast<float4*>(static_cast<float*>(out) + o + c0);
 #pragma unroll
             for (int e = 0; e < 8; ++e)
-              d[e] = make_float4(__uint_as_float(r[4 * e]) * inv, __uint_as_float(r[4 * e + 1]) * inv, __uint_as_float(r[4 * e + 2]) * inv,
-                                 __uint_as_float(r[4 * e + 3]) * inv);
+              d[e] = make_float4(__uint_as_float(rr[4 * e]) * inv, __uint_as_float(rr[4 * e + 1]) * inv, __uint_as_float(rr[4 * e + 2]) * inv,
+                                 __uint_as_float(rr[4 * e + 3]) * inv);
           } else {
             uint4* d = reinterpret_cast<uint4*>(static_cast<u16*>(out) + o + c0);
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              d[e] = make_uint4(pack2(__uint_as_float(r[8 * e]) * inv, __uint_as_float(r[8 * e + 1]) * inv),
-                                pack2(__uint_as_float(r[8 * e + 2]) * inv, __uint_as_float(r[8 * e + 3]) * inv),
-                                pack2(__uint_as_float(r[8 * e + 4]) * inv, __uint_as_float(r[8 * e + 5]) * inv),
-                                pack2(__uint_as_float(r[8 * e + 6]) * inv, __uint_as_float(r[8 * e + 7]) * inv));
+              d[e] = make_uint4(pack2(__uint_as_float(rr[8 * e]) * inv, __uint_as_float(rr[8 * e + 1]) * inv),
+                                pack2(__uint_as_float(rr[8 * e + 2]) * inv, __uint_as_float(rr[8 * e + 3]) * inv),
+                                pack2(__uint_as_float(rr[8 * e + 4]) * inv, __uint_as_float(rr[8 * e + 5]) * inv),
+                                pack2(__uint_as_float(rr[8 * e + 6]) * inv, __uint_as_float(rr[8 * e + 7]) * inv));
           }
         }
       }

@@ -68,80 +68,92 @@ __global__ void __launch_bounds__(128) quantize_act_kernel(const float* __restri
 }
 
 // ---- the contract GEMV ---------------------------------------------------------------------------
-// A warp owns RB consecutive rows at a time; lane l owns blocks l, l+32, ...  Per block: the exact
-// integer dot by dp4a, the term (dw*dx)*f32(isum) with each product rounded once, parked in shared
-// memory; then lane r < RB adds row r's terms in block order.
-constexpr int GQ_RB = 4;
+// A CTA of 8 warps owns 32 consecutive rows at a time, 4 per warp; lane l owns blocks l, l+32, ...  Per block: the
+// exact integer dot by dp4a, the term (dw*dx)*f32(isum) with each product rounded once, parked in shared memory.
+// Then ONE warp adds the 32 rows' terms in block order, a lane per row -- the part of the contract that cannot be
+// re-associated: nb dependent adds, paid once per 32 rows with all 32 lanes busy and the loads issued eight ahead
+// of the adds (it used to be paid per 4 rows by 4 lanes of every warp).
+constexpr int GQ_RB = 4, GQ_WARPS = 8, GQ_ROWS = GQ_RB * GQ_WARPS;
 
 template <bool Q4>
-__global__ void __launch_bounds__(128) gemv_q_contract_kernel(const uint4* __restrict__ qs, const u16* __restrict__ d,
-                                                              const int8_t* __restrict__ xq, const float* __restrict__ dx,
-                                                              const int* __restrict__ sx, float* __restrict__ y, i64 n,
-                                                              int nb) {
+__global__ void __launch_bounds__(GQ_WARPS * 32) gemv_q_contract_kernel(const uint4* __restrict__ qs, const u16* __restrict__ d,
+                                                                        const int8_t* __restrict__ xq, const float* __restrict__ dx,
+                                                                        const int* __restrict__ sx, float* __restrict__ y, i64 n,
+                                                                        int nb) {
   extern __shared__ __align__(16) unsigned char smem[];
   // x words transposed: xs[w][b], w = 0..7 (32-bit word of the block's 32 quants)
   int* xs = reinterpret_cast<int*>(smem);
   float* dxs = reinterpret_cast<float*>(xs + 8 * nb);
   int* sxs = reinterpret_cast<int*>(dxs + nb);
-  float* terms = reinterpret_cast<float*>(sxs + nb);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float* terms = reinterpret_cast<float*>(sxs + nb);      // [32 rows][nb]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < nb * 8; i += blockDim.x) {
     int b = i >> 3, w = i & 7;
     xs[w * nb + b] = reinterpret_cast<const int*>(xq)[i];
   }
   for (int i = threadIdx.x; i < nb; i += blockDim.x) { dxs[i] = dx[i]; sxs[i] = sx[i]; }
   __syncthreads();
-  float* myterms = terms + (size_t)warp * GQ_RB * nb;
   constexpr int QW = Q4 ? 1 : 2;  // uint4 words per block
-  i64 nbatches = (n + GQ_RB - 1) / GQ_RB;
-  for (i64 batch = (i64)blockIdx.x * nwarps + warp; batch < nbatches; batch += (i64)gridDim.x * nwarps) {
-    i64 r0 = batch * GQ_RB;
-    for (int b = lane; b < nb; b += 32) {
-      int xw[8];
+  const i64 nbatches = (n + GQ_ROWS - 1) / GQ_ROWS;
+  for (i64 batch = blockIdx.x; batch < nbatches; batch += gridDim.x) {
+    const i64 rbase = batch * GQ_ROWS;
+    const i64 r0 = rbase + warp * GQ_RB;
+    if (r0 < n) {
+      for (int b = lane; b < nb; b += 32) {
+        int xw[8];
 #pragma unroll
-      for (int w = 0; w < 8; ++w) xw[w] = xs[w * nb + b];
-      float dxb = dxs[b];
-      int sxb = sxs[b];
-      uint4 wq[GQ_RB][QW];
-      u16 dw[GQ_RB];
+        for (int w = 0; w < 8; ++w) xw[w] = xs[w * nb + b];
+        float dxb = dxs[b];
+        int sxb = sxs[b];
+        uint4 wq[GQ_RB][QW];
+        u16 dw[GQ_RB];
 #pragma unroll
-      for (int r = 0; r < GQ_RB; ++r) {
-        i64 row = r0 + r < n ? r0 + r : n - 1;
-        const uint4* p = qs + (row * nb + b) * QW;
+        for (int r = 0; r < GQ_RB; ++r) {
+          i64 row = r0 + r < n ? r0 + r : n - 1;
+          const uint4* p = qs + (row * nb + b) * QW;
 #pragma unroll
-        for (int h = 0; h < QW; ++h) wq[r][h] = p[h];
-        dw[r] = d[row * nb + b];
-      }
-#pragma unroll
-      for (int r = 0; r < GQ_RB; ++r) {
-        int isum = 0;
-        if (Q4) {
-          uint32_t ws[4] = {wq[r][0].x, wq[r][0].y, wq[r][0].z, wq[r][0].w};
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            int lo = (int)(ws[w] & 0x0f0f0f0fu), hi = (int)((ws[w] >> 4) & 0x0f0f0f0fu);
-            isum = __dp4a(lo, xw[w], isum);       // elements 4w..4w+3
-            isum = __dp4a(hi, xw[w + 4], isum);   // elements 16+4w..16+4w+3
-          }
-          isum -= 8 * sxb;  // sum (nib-8)*x = sum nib*x - 8*sum x, all exact integers
-        } else {
-          uint32_t ws[8] = {wq[r][0].x, wq[r][0].y, wq[r][0].z, wq[r][0].w,
-                            wq[r][QW - 1].x, wq[r][QW - 1].y, wq[r][QW - 1].z, wq[r][QW - 1].w};
-#pragma unroll
-          for (int w = 0; w < 8; ++w) isum = __dp4a((int)ws[w], xw[w], isum);
+          for (int h = 0; h < QW; ++h) wq[r][h] = p[h];
+          dw[r] = d[row * nb + b];
         }
-        float term = fmul(fmul(f16_bits_to_f32(dw[r]), dxb), (float)isum);
-        myterms[r * nb + b] = term;
+#pragma unroll
+        for (int r = 0; r < GQ_RB; ++r) {
+          int isum = 0;
+          if (Q4) {
+            uint32_t ws[4] = {wq[r][0].x, wq[r][0].y, wq[r][0].z, wq[r][0].w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              int lo = (int)(ws[w] & 0x0f0f0f0fu), hi = (int)((ws[w] >> 4) & 0x0f0f0f0fu);
+              isum = __dp4a(lo, xw[w], isum);       // elements 4w..4w+3
+              isum = __dp4a(hi, xw[w + 4], isum);   // elements 16+4w..16+4w+3
+            }
+            isum -= 8 * sxb;  // sum (nib-8)*x = sum nib*x - 8*sum x, all exact integers
+          } else {
+            uint32_t ws[8] = {wq[r][0].x, wq[r][0].y, wq[r][0].z, wq[r][0].w,
+                              wq[r][QW - 1].x, wq[r][QW - 1].y, wq[r][QW - 1].z, wq[r][QW - 1].w};
+#pragma unroll
+            for (int w = 0; w < 8; ++w) isum = __dp4a((int)ws[w], xw[w], isum);
+          }
+          float term = fmul(fmul(f16_bits_to_f32(dw[r]), dxb), (float)isum);
+          terms[(warp * GQ_RB + r) * nb + b] = term;
+        }
       }
     }
-    __syncwarp();
-    if (lane < GQ_RB && r0 + lane < n) {
-      const float* t = myterms + lane * nb;
+    __syncthreads();
+    if (warp == 0 && rbase + lane < n) {
+      const float* t = terms + lane * nb;
       float acc = 0.0f;
-      for (int b = 0; b < nb; ++b) acc = fadd(acc, t[b]);
-      y[r0 + lane] = acc;
+      int b = 0;
+      for (; b + 8 <= nb; b += 8) {
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = t[b + e];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc = fadd(acc, v[e]);
+      }
+      for (; b < nb; ++b) acc = fadd(acc, t[b]);
+      y[rbase + lane] = acc;
     }
-    __syncwarp();
+    __syncthreads();
   }
 }
 
@@ -235,7 +247,7 @@ constexpr i64 NOALLOC_DX_OFF = NOALLOC_XQ_BYTES;               // f32 scales
 constexpr i64 NOALLOC_SX_OFF = NOALLOC_DX_OFF + NOALLOC_MAX_NB * 4;  // i32 sums
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SX_OFF + NOALLOC_MAX_NB * 4];
 
-static size_t contract_smem(int nb, int warps) { return (size_t)nb * (32 + 4 + 4) + (size_t)warps * GQ_RB * nb * 4; }
+static size_t contract_smem(int nb) { return (size_t)nb * (32 + 4 + 4) + (size_t)GQ_ROWS * nb * 4; }
 
 // ---- y = W x, bf16 activation, every load issued before any arithmetic -----------------------------------------
 // A GEMV of these sizes (9-25 MB of weights) lasts a few microseconds at HBM speed, so what matters is that the
@@ -356,17 +368,14 @@ int wkb_gemv_q_contract(const void* qs, const void* d, const void* xq, const flo
                         i64 n, i64 k, int q4, void* stream) {
   if (n <= 0 || k <= 0) return 0;
   int nb = (int)((k + 31) / 32);
-  int warps = 4;
-  while (warps > 1 && contract_smem(nb, warps) > 200 * 1024) warps >>= 1;
-  size_t sm = contract_smem(nb, warps);
+  size_t sm = contract_smem(nb);
   if (sm > 200 * 1024) return (int)cudaErrorInvalidValue;
-  i64 nbatches = (n + GQ_RB - 1) / GQ_RB;
-  i64 blocks = (nbatches + warps - 1) / warps;
+  i64 blocks = (n + GQ_ROWS - 1) / GQ_ROWS;
   if (blocks > (i64)WKB_SM_COUNT * 8) blocks = (i64)WKB_SM_COUNT * 8;
   auto kern = q4 ? gemv_q_contract_kernel<true> : gemv_q_contract_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   if (e != cudaSuccess) return (int)e;
-  kern<<<(int)blocks, warps * 32, sm, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const int8_t*)xq, dx, sx, y, n, nb);
+  kern<<<(int)blocks, GQ_WARPS * 32, sm, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const int8_t*)xq, dx, sx, y, n, nb);
   return (int)cudaGetLastError();
 }
 
