@@ -9,17 +9,22 @@
 //     in shared memory; a CTA owns one K slice and walks over weight-row tiles of 128 rows;
 //   * warp 0 streams raw tiles (128 rows x 256 K: 16 KB of nibbles + 2 KB of f16 scales) through a
 //     5-stage TMA ring (128-byte swizzle, no multicast);
-//   * warps 2-17 dequantise: thread = weight row, two 32-value blocks of each stage; nibble -> bf16 with
+//   * warps 4-19 dequantise: thread = weight row, two 32-value blocks of each stage; nibble -> bf16 with
 //     one byte permute (0x4300 | nib = 128 + nib exactly), subtract 136, multiply by the block scale rounded
 //     to bf16, all in bf16x2 (the reference's kernel does the same two operations per pair in f16x2, its
 //     activations being f16).  The result is written with tcgen05.st straight into TENSOR MEMORY, where
 //     lane = weight row and a column holds two consecutive K values: the MMA's A operand never touches
-//     shared memory, so there is no swizzled store, no proxy fence, and the 256 KB of TMEM give three
-//     whole 256-K stages of operand buffering on top of the two accumulators;
-//   * warp 1 issues tcgen05.mma with A in tensor memory and B (activations) from shared memory
-//     (M = 128 weight rows, N = 64 activation rows, K = 16) x 16 per stage into one of two TMEM
-//     accumulators; tcgen05.commit recycles the operand stage;
-//   * warps 18-21 read the accumulator (thread = weight row, 64 activation rows in registers).
+//     shared memory, so there is no swizzled store and no proxy fence; two 256-K stages of operand
+//     buffering sit beside the four accumulators in the 512 TMEM columns;
+//   * warps 1 and 2 issue tcgen05.mma with A in tensor memory and B (activations) from shared memory
+//     (M = 128 weight rows, N = 64 activation rows, K = 16) x 16 per stage; tcgen05.commit recycles the
+//     operand stage.  One thread issues such an MMA about every 27-36 ns, the tensor pipe retires one every
+//     19-20 ns (measured with two issuing warps), so the CTA walks over its weight-row tiles two at a time:
+//     the stages of the two tiles alternate in the stream, warp 1 accumulates the even tile and warp 2 the
+//     odd one, each into its own accumulator and in K order (the sum of a tile is the same whichever warp
+//     issues it);
+//   * warps 20-23 read the accumulators (four of them, so a pair of tiles is finished while the next pair
+//     is multiplied; thread = weight row, 64 activation rows in registers).
 //     With one K slice they finish the tile directly.  With several, they write the partial tile to
 //     the workspace and count arrivals per (tile, lane quarter); the last arriving warp adds the
 //     slices in slice order (so the result does not depend on arrival order) and finishes.
@@ -27,6 +32,9 @@
 //   bf16 if asked, and a store that is coalesced across lanes (consecutive n for one m).
 // The weight value the tensor core sees is exactly bf16_rn(bf16_rn(d) * (nib - 8)); accumulation is
 // fp32 in the tensor core's own order.
+// The kernel is launched as a programmatic dependent: the weight stream does not depend on the kernel before it, so the
+// first ring of raw stages is requested (and dequantised) while that kernel is still draining; only the activation load
+// and the stores wait for it.
 // Every mbarrier wait is bounded; on expiry a code is recorded in the status word, the role stops
 // issuing, and the CTA drains and frees its TMEM.
 #include "common.cuh"
@@ -47,13 +55,14 @@ constexpr int RAW_STAGES = 5;
 constexpr int RAW_BYTES = TN * 128, SCALE_BYTES = TN * 16, RAW_STAGE_BYTES = RAW_BYTES + SCALE_BYTES;
 constexpr int X_SUB_BYTES = TM * 128;
 constexpr int X_BYTES = (KS_MAX / 64) * X_SUB_BYTES;
-// tensor memory: columns 0-127 two fp32 accumulators (64 activation rows each), 128-511 three stage buffers of
+// tensor memory: columns 0-255 four fp32 accumulators (64 activation rows each), 256-511 two stage buffers of
 // dequantised weights (256 K as 128 columns of bf16 pairs; lane = weight row)
-constexpr int A_STAGES = 3, A_STAGE_COLS = STAGE_K / 2, A_COL0 = 2 * TM;
+constexpr int A_STAGES = 2, A_STAGE_COLS = STAGE_K / 2, NUM_ACC = 4, A_COL0 = NUM_ACC * TM;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int NUM_BARS = 1 + 2 * RAW_STAGES + 2 * A_STAGES + 4;
+constexpr int NUM_BARS = 1 + 2 * RAW_STAGES + 2 * A_STAGES + 2 * NUM_ACC;
 constexpr int SMEM = X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + 1024 + 256;
-constexpr int DEQ_WARPS = 16, THREADS = 32 * (2 + DEQ_WARPS + 4);
+// warps: 0 TMA producer, 1-2 MMA issuers, 3 TMEM allocation, 4-19 dequantisers, 20-23 epilogue
+constexpr int DEQ_WARP0 = 4, DEQ_WARPS = 16, EPI_WARP0 = DEQ_WARP0 + DEQ_WARPS, THREADS = 32 * (EPI_WARP0 + 4);
 // instruction descriptor, kind::f16: D = f32, A = B = bf16 (the two operand formats must agree: an f16 A with a
 // bf16 B is rejected by the hardware as an illegal instruction)
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
@@ -223,23 +232,32 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   auto a_full = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + b); };
   auto a_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + A_STAGES + b); };
   auto t_full = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_STAGES + b); };
-  auto t_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_STAGES + 2 + b); };
+  auto t_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_STAGES + NUM_ACC + b); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ks = blockIdx.x % plan.ksplit, group = blockIdx.x / plan.ksplit;
   const int stage0 = ks * plan.stages_per_slice;
   const int nstages = min(plan.stages_per_slice, plan.kstages - stage0);  // >= 1 by construction
   const int nsub = nstages * (STAGE_K / 64);
+  // This CTA's tiles are group, group + groups, ...; they are taken two at a time and the stages of a pair alternate in
+  // the stream that the producer, the dequantisers and the two MMA warps all follow: stream position -> (local tile, stage)
+  const int ntl = group < plan.n_tiles ? (plan.n_tiles - group + plan.groups - 1) / plan.groups : 0;
+  const int pair_its = 2 * nstages, full_pairs = ntl >> 1, total_its = ntl * nstages;
+  auto locate = [&](int it, int& j, int& s) {
+    const int p = it / pair_its;
+    if (p < full_pairs) { const int q = it - p * pair_its; s = q >> 1; j = 2 * p + (q & 1); }
+    else { s = it - full_pairs * pair_its; j = 2 * full_pairs; }
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(x_full, 1);
     for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DEQ_WARPS); }
     for (int b = 0; b < A_STAGES; ++b) { mbar_init(a_full(b), DEQ_WARPS); mbar_init(a_empty(b), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(t_full(b), 1); mbar_init(t_empty(b), 4); }
+    for (int b = 0; b < NUM_ACC; ++b) { mbar_init(t_full(b), 1); mbar_init(t_empty(b), 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
   }
-  if (warp == 1) {
+  if (warp == 3) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -247,43 +265,54 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      mbar_expect_tx(x_full, (uint32_t)nsub * X_SUB_BYTES);
-      for (int j = 0; j < nsub; ++j) tma_load_2d(x_base + j * X_SUB_BYTES, &map_x, x_full, stage0 * STAGE_K + j * 64, 0);
       int it = 0;
       bool ok = true;
-      for (int t = group; t < plan.n_tiles && ok; t += plan.groups) {
-        for (int s = 0; s < nstages; ++s, ++it) {
+      auto issue_raw = [&](int upto) {
+        for (; it < upto && ok; ++it) {
+          int j, st;
+          locate(it, j, st);
           const int slot = it % RAW_STAGES;
           if (!mbar_wait_parked(raw_empty(slot), ((it / RAW_STAGES) & 1) ^ 1)) { atomicExch(status, 11); ok = false; break; }
           mbar_expect_tx(raw_full(slot), RAW_STAGE_BYTES);
           // one contiguous 18 KB stage image: (tile, stage) -> nibble rows already in their swizzled places, then scales
-          bulk_load(raw_base + slot * RAW_STAGE_BYTES, wt + ((i64)t * plan.kstages_pitch + stage0 + s) * RAW_STAGE_BYTES,
-                    RAW_STAGE_BYTES, raw_full(slot));
+          bulk_load(raw_base + slot * RAW_STAGE_BYTES,
+                    wt + ((i64)(group + j * plan.groups) * plan.kstages_pitch + stage0 + st) * RAW_STAGE_BYTES, RAW_STAGE_BYTES, raw_full(slot));
         }
-      }
+      };
+      // the resident weights do not depend on the kernel before this one: fill the ring first, then wait for that kernel
+      // and fetch its output, the activation slice
+      issue_raw(min(RAW_STAGES, total_its));
+      pdl_wait();
+      mbar_expect_tx(x_full, (uint32_t)nsub * X_SUB_BYTES);
+      for (int j = 0; j < nsub; ++j) tma_load_2d(x_base + j * X_SUB_BYTES, &map_x, x_full, stage0 * STAGE_K + j * 64, 0);
+      issue_raw(total_its);
       if (!ok) {
         // wait (bounded) for the copies already started before the CTA may exit
         mbar_wait(x_full, 0);
         for (int j = it > RAW_STAGES ? it - RAW_STAGES : 0; j < it; ++j) mbar_wait(raw_full(j % RAW_STAGES), (j / RAW_STAGES) & 1);
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer: A (dequantised weights) from tensor memory, B (activations) from shared memory ----------------
+  } else if (warp <= 2) {
+    // ---------------- MMA issuers: A (dequantised weights) from tensor memory, B (activations) from shared memory ----------------
+    // warp 1 takes the even local tiles, warp 2 the odd ones
     if (lane == 0) {
+      const int e = warp - 1;
       bool ok = mbar_wait_parked(x_full, 0);
       if (!ok) atomicExch(status, 12);
-      int as = 0, local = 0;
       const uint64_t bdesc0 = make_sdesc(x_base);   // the start-address field counts 16-byte units: later operands are plain adds
-      for (int t = group; t < plan.n_tiles && ok; t += plan.groups, ++local) {
-        const int acc = local & 1;
-        if (!mbar_wait_parked(t_empty(acc), ((local >> 1) & 1) ^ 1)) { atomicExch(status, 13); ok = false; break; }
+      for (int j = e; j < ntl && ok; j += 2) {
+        const int acc = j & (NUM_ACC - 1);
+        if (!mbar_wait_parked(t_empty(acc), ((j / NUM_ACC) & 1) ^ 1)) { atomicExch(status, 13); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TM);
-        for (int s = 0; s < nstages; ++s, ++as) {
+        const int p = j >> 1;
+        for (int s = 0; s < nstages; ++s) {
+          const int as = p < full_pairs ? p * pair_its + 2 * s + e : full_pairs * pair_its + s;   // position in the stream
           const int buf = as % A_STAGES;
           if (!mbar_wait_parked(a_full(buf), (as / A_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -292,21 +321,23 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
           if (s == 0) {
             umma_bf16_ts(tmem_d, ta, bd, IDESC, 0u);   // first K step of the tile overwrites the accumulator
 #pragma unroll
-            for (int j = 1; j < 16; ++j)
-              umma_bf16_ts(tmem_d, ta + (uint32_t)(j * 8), bd + (uint64_t)(((j >> 2) * X_SUB_BYTES + (j & 3) * 32) >> 4), IDESC, 1u);
+            for (int k = 1; k < 16; ++k)
+              umma_bf16_ts(tmem_d, ta + (uint32_t)(k * 8), bd + (uint64_t)(((k >> 2) * X_SUB_BYTES + (k & 3) * 32) >> 4), IDESC, 1u);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              umma_bf16_ts(tmem_d, ta + (uint32_t)(j * 8), bd + (uint64_t)(((j >> 2) * X_SUB_BYTES + (j & 3) * 32) >> 4), IDESC, 1u);
+            for (int k = 0; k < 16; ++k)
+              umma_bf16_ts(tmem_d, ta + (uint32_t)(k * 8), bd + (uint64_t)(((k >> 2) * X_SUB_BYTES + (k & 3) * 32) >> 4), IDESC, 1u);
           }
           umma_commit(a_empty(buf));
         }
         if (ok) umma_commit(t_full(acc));
       }
     }
-  } else if (warp < 2 + DEQ_WARPS) {
+  } else if (warp == 3) {
+    // nothing more: this warp owns the tensor-memory allocation
+  } else if (warp < EPI_WARP0) {
     // ---------------- dequantisers: thread = weight row (its TMEM lane), two 32-value blocks of every 256-K stage ----------------
-    const int quarter = warp & 3, part = (warp - 2) >> 2;   // a warp reaches only the TMEM lanes of its quarter
+    const int quarter = warp & 3, part = (warp - DEQ_WARP0) >> 2;   // a warp reaches only the TMEM lanes of its quarter
     const int r = quarter * 32 + lane;
     const uint32_t swz = (uint32_t)(r & 7);
     int it = 0;
@@ -323,8 +354,8 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         pending = -1;
       }
     };
-    for (int t = group; t < plan.n_tiles && ok; t += plan.groups) {
-      for (int s = 0; s < nstages && ok; ++s, ++it) {
+    {
+      for (; it < total_its && ok; ++it) {
         const int slot = it % RAW_STAGES;
         if (!mbar_wait_parked(raw_full(slot), (it / RAW_STAGES) & 1)) { if (lane == 0) atomicExch(status, 15); ok = false; break; }
         const uint32_t rawp = raw_base + slot * RAW_STAGE_BYTES;
@@ -352,10 +383,11 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     const i64 n_pad = (i64)plan.n_tiles * TN;
     int local = 0;
     bool ok = true;
+    pdl_wait();
     for (int t = group; t < plan.n_tiles && ok; t += plan.groups, ++local) {
-      const int acc = local & 1;
+      const int acc = local & (NUM_ACC - 1);
       const int n = t * TN + quarter * 32 + lane;
-      if (!mbar_wait_parked(t_full(acc), (local >> 1) & 1)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
+      if (!mbar_wait_parked(t_full(acc), (local / NUM_ACC) & 1)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TM);
       if (plan.ksplit == 1 && MODE != 3) {
@@ -396,7 +428,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 3) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
@@ -410,6 +442,8 @@ __global__ void __launch_bounds__(256) q4_splitk_reduce_kernel(const float* __re
                                                                void* out, i64 ldo) {
   const i64 quads = n_pad >> 2;
   const i64 total = (i64)M * quads;
+  pdl_wait();
+  pdl_trigger();
   for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
     const int m = (int)(idx / quads);
     const i64 n0 = (idx % quads) << 2;
@@ -548,18 +582,17 @@ int wkb_gemm_q4_0_bf16_nt(const void* w_tiled, const void* x_bf16, int64_t ldx, 
     int rc = q4tc::encode_x(&mx, (const u16*)x_bf16 + m0 * ldx, k, mc, ldx);
     if (rc) return rc;
     void* o = reinterpret_cast<uint8_t*>(out) + m0 * ldo * esz;
-    table[out_mode]<<<plan.ksplit * plan.groups, q4tc::THREADS, q4tc::SMEM, as_stream(stream)>>>(
-        mx, (const uint8_t*)w_tiled, o, ldo, (int)mc, (int)n, plan, ws, status);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(table[out_mode], plan.ksplit * plan.groups, q4tc::THREADS, (size_t)q4tc::SMEM, as_stream(stream), mx,
+                               (const uint8_t*)w_tiled, o, ldo, (int)mc, (int)n, plan, ws, status);
     if (e != cudaSuccess) return (int)e;
     if (plan.ksplit > 1 && out_mode != 3) {
       const i64 total = mc * (n_pad >> 2);
       i64 grid = (total + 255) / 256;
       if (grid > gemm_sm_count() * 8) grid = gemm_sm_count() * 8;
-      if (out_mode == 0) q4tc::q4_splitk_reduce_kernel<0><<<(int)grid, 256, 0, as_stream(stream)>>>(ws, plan.ksplit, (int)mc, (int)n, n_pad, o, ldo);
-      else if (out_mode == 1) q4tc::q4_splitk_reduce_kernel<1><<<(int)grid, 256, 0, as_stream(stream)>>>(ws, plan.ksplit, (int)mc, (int)n, n_pad, o, ldo);
-      else q4tc::q4_splitk_reduce_kernel<2><<<(int)grid, 256, 0, as_stream(stream)>>>(ws, plan.ksplit, (int)mc, (int)n, n_pad, o, ldo);
-      e = cudaGetLastError();
+      const float* cws = ws;
+      if (out_mode == 0) e = launch_pdl(q4tc::q4_splitk_reduce_kernel<0>, (int)grid, 256, 0, as_stream(stream), cws, plan.ksplit, (int)mc, (int)n, n_pad, o, ldo);
+      else if (out_mode == 1) e = launch_pdl(q4tc::q4_splitk_reduce_kernel<1>, (int)grid, 256, 0, as_stream(stream), cws, plan.ksplit, (int)mc, (int)n, n_pad, o, ldo);
+      else e = launch_pdl(q4tc::q4_splitk_reduce_kernel<2>, (int)grid, 256, 0, as_stream(stream), cws, plan.ksplit, (int)mc, (int)n, n_pad, o, ldo);
       if (e != cudaSuccess) return (int)e;
     }
   }
