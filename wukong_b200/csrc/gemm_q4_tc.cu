@@ -5,17 +5,21 @@
 //
 // The kernel is bound by the weight stream (0.5625 B per weight) and, on this part, by the instructions it
 // takes to turn nibbles into tensor-core operands, so it is built to keep both busy on every SM:
-//   * the activation slice x[:, k-slice] (<= 1024 columns, 128 KB) is loaded once per CTA and stays
-//     in shared memory; a CTA owns one K slice and walks over weight-row tiles of 128 rows;
+//   * the activation slice x[:, k-slice] (<= 1024 columns, 128 KB) is loaded once per CTA (one barrier per
+//     256-K stage, so the first MMAs start when a quarter of it has landed) and stays in shared memory; a CTA owns one K slice and walks over weight-row tiles of 128 rows;
 //   * warp 0 streams raw tiles (128 rows x 256 K: 16 KB of nibbles + 2 KB of f16 scales) through a
 //     5-stage TMA ring (128-byte swizzle, no multicast);
-//   * warps 4-19 dequantise: thread = weight row, two 32-value blocks of each stage; nibble -> bf16 with
+//   * warps 4-19 dequantise, in two teams of eight (one team per tile of the pair, each feeding its own MMA warp,
+//     so a stage is handed over between 8 warps and one lane, not 16): thread = weight row, four 32-value
+//     blocks of each stage, written as two half-stage buffers so that the MMAs of one half run while the
+//     other half is converted; nibble -> bf16 with
 //     one byte permute (0x4300 | nib = 128 + nib exactly), subtract 136, multiply by the block scale rounded
 //     to bf16, all in bf16x2 (the reference's kernel does the same two operations per pair in f16x2, its
 //     activations being f16).  The result is written with tcgen05.st straight into TENSOR MEMORY, where
 //     lane = weight row and a column holds two consecutive K values: the MMA's A operand never touches
-//     shared memory, so there is no swizzled store and no proxy fence; two 256-K stages of operand
-//     buffering sit beside the four accumulators in the 512 TMEM columns;
+//     shared memory, so there is no swizzled store and no proxy fence; one 256-K stage of operand
+//     buffering per team (two halves, recycled independently) sits beside the four accumulators in the 512
+//     TMEM columns;
 //   * warps 1 and 2 issue tcgen05.mma with A in tensor memory and B (activations) from shared memory
 //     (M = 128 weight rows, N = 64 activation rows, K = 16) x 16 per stage; tcgen05.commit recycles the
 //     operand stage.  One thread issues such an MMA about every 27-36 ns, the tensor pipe retires one every
@@ -23,8 +27,9 @@
 //     the stages of the two tiles alternate in the stream, warp 1 accumulates the even tile and warp 2 the
 //     odd one, each into its own accumulator and in K order (the sum of a tile is the same whichever warp
 //     issues it);
-//   * warps 20-23 read the accumulators (four of them, so a pair of tiles is finished while the next pair
-//     is multiplied; thread = weight row, 64 activation rows in registers).
+//   * warps 20-27 read the accumulators (four of them, so a pair of tiles is finished while the next pair
+//     is multiplied; one set of four warps per tile of the pair; thread = weight row, 64 activation rows in
+//     registers).
 //     With one K slice they finish the tile directly.  With several, they write the partial tile to
 //     the workspace and count arrivals per (tile, lane quarter); the last arriving warp adds the
 //     slices in slice order (so the result does not depend on arrival order) and finishes.
@@ -55,14 +60,16 @@ constexpr int RAW_STAGES = 5;
 constexpr int RAW_BYTES = TN * 128, SCALE_BYTES = TN * 16, RAW_STAGE_BYTES = RAW_BYTES + SCALE_BYTES;
 constexpr int X_SUB_BYTES = TM * 128;
 constexpr int X_BYTES = (KS_MAX / 64) * X_SUB_BYTES;
-// tensor memory: columns 0-255 four fp32 accumulators (64 activation rows each), 256-511 two stage buffers of
-// dequantised weights (256 K as 128 columns of bf16 pairs; lane = weight row)
-constexpr int A_STAGES = 2, A_STAGE_COLS = STAGE_K / 2, NUM_ACC = 4, A_COL0 = NUM_ACC * TM;
+// tensor memory: columns 0-255 four fp32 accumulators (64 activation rows each), 256-511 one stage buffer of
+// dequantised weights per team (256 K as 128 columns of bf16 pairs, two halves of 64 columns; lane = weight row)
+constexpr int A_STAGE_COLS = STAGE_K / 2, A_HALF_COLS = A_STAGE_COLS / 2, NUM_ACC = 4, A_COL0 = NUM_ACC * TM;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int NUM_BARS = 1 + 2 * RAW_STAGES + 2 * A_STAGES + 2 * NUM_ACC;
+constexpr int X_STAGES = KS_MAX / STAGE_K;
+constexpr int NUM_BARS = X_STAGES + 2 * RAW_STAGES + 8 + 2 * NUM_ACC;
 constexpr int SMEM = X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + 1024 + 256;
-// warps: 0 TMA producer, 1-2 MMA issuers, 3 TMEM allocation, 4-19 dequantisers, 20-23 epilogue
-constexpr int DEQ_WARP0 = 4, DEQ_WARPS = 16, EPI_WARP0 = DEQ_WARP0 + DEQ_WARPS, THREADS = 32 * (EPI_WARP0 + 4);
+static_assert(8 * NUM_BARS + 8 <= 256, "barriers and the TMEM slot share 256 bytes");
+// warps: 0 TMA producer, 1-2 MMA issuers, 3 TMEM allocation, 4-19 dequantisers (two teams of 8), 20-27 epilogue (two sets of 4)
+constexpr int DEQ_WARP0 = 4, TEAM_WARPS = 8, EPI_WARP0 = DEQ_WARP0 + 2 * TEAM_WARPS, THREADS = 32 * (EPI_WARP0 + 8);
 // instruction descriptor, kind::f16: D = f32, A = B = bf16 (the two operand formats must agree: an f16 A with a
 // bf16 B is rejected by the hardware as an illegal instruction)
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TM >> 3) << 17) | ((uint32_t)(TN >> 4) << 24);
@@ -226,21 +233,21 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   const uint32_t x_base = base, raw_base = base + X_BYTES;
   const uint32_t bars = raw_base + RAW_STAGES * RAW_STAGE_BYTES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + X_BYTES + RAW_STAGES * RAW_STAGE_BYTES + 8 * NUM_BARS);
-  const uint32_t x_full = bars;
-  auto raw_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto raw_empty = [&](int s) { return bars + 8u * (1 + RAW_STAGES + s); };
-  auto a_full = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + b); };
-  auto a_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + A_STAGES + b); };
-  auto t_full = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_STAGES + b); };
-  auto t_empty = [&](int b) { return bars + 8u * (1 + 2 * RAW_STAGES + 2 * A_STAGES + NUM_ACC + b); };
+  auto x_full = [&](int s) { return bars + 8u * s; };                                  // one per 256-K stage of the slice
+  auto raw_full = [&](int s) { return bars + 8u * (X_STAGES + s); };
+  auto raw_empty = [&](int s) { return bars + 8u * (X_STAGES + RAW_STAGES + s); };
+  auto a_full = [&](int team, int half) { return bars + 8u * (X_STAGES + 2 * RAW_STAGES + team * 2 + half); };
+  auto a_empty = [&](int team, int half) { return bars + 8u * (X_STAGES + 2 * RAW_STAGES + 4 + team * 2 + half); };
+  auto t_full = [&](int b) { return bars + 8u * (X_STAGES + 2 * RAW_STAGES + 8 + b); };
+  auto t_empty = [&](int b) { return bars + 8u * (X_STAGES + 2 * RAW_STAGES + 8 + NUM_ACC + b); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ks = blockIdx.x % plan.ksplit, group = blockIdx.x / plan.ksplit;
   const int stage0 = ks * plan.stages_per_slice;
   const int nstages = min(plan.stages_per_slice, plan.kstages - stage0);  // >= 1 by construction
-  const int nsub = nstages * (STAGE_K / 64);
   // This CTA's tiles are group, group + groups, ...; they are taken two at a time and the stages of a pair alternate in
-  // the stream that the producer, the dequantisers and the two MMA warps all follow: stream position -> (local tile, stage)
+  // the stream the producer follows: stream position -> (local tile, stage).  Even local tiles belong to team 0 (dequantiser
+  // warps 4-11, MMA warp 1, epilogue warps 20-23), odd ones to team 1.
   const int ntl = group < plan.n_tiles ? (plan.n_tiles - group + plan.groups - 1) / plan.groups : 0;
   const int pair_its = 2 * nstages, full_pairs = ntl >> 1, total_its = ntl * nstages;
   auto locate = [&](int it, int& j, int& s) {
@@ -248,11 +255,13 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     if (p < full_pairs) { const int q = it - p * pair_its; s = q >> 1; j = 2 * p + (q & 1); }
     else { s = it - full_pairs * pair_its; j = 2 * full_pairs; }
   };
+  // the inverse for a team: position of stage s of local tile j
+  auto position = [&](int j, int s) { return (j >> 1) < full_pairs ? (j >> 1) * pair_its + 2 * s + (j & 1) : full_pairs * pair_its + s; };
 
   if (threadIdx.x == 0) {
-    mbar_init(x_full, 1);
-    for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), DEQ_WARPS); }
-    for (int b = 0; b < A_STAGES; ++b) { mbar_init(a_full(b), DEQ_WARPS); mbar_init(a_empty(b), 1); }
+    for (int s = 0; s < X_STAGES; ++s) mbar_init(x_full(s), 1);
+    for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), TEAM_WARPS); }
+    for (int b = 0; b < 4; ++b) { mbar_init(a_full(b >> 1, b & 1), TEAM_WARPS); mbar_init(a_empty(b >> 1, b & 1), 1); }
     for (int b = 0; b < NUM_ACC; ++b) { mbar_init(t_full(b), 1); mbar_init(t_empty(b), 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
@@ -288,12 +297,14 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
       // and fetch its output, the activation slice
       issue_raw(min(RAW_STAGES, total_its));
       pdl_wait();
-      mbar_expect_tx(x_full, (uint32_t)nsub * X_SUB_BYTES);
-      for (int j = 0; j < nsub; ++j) tma_load_2d(x_base + j * X_SUB_BYTES, &map_x, x_full, stage0 * STAGE_K + j * 64, 0);
+      for (int xs = 0; xs < nstages; ++xs) {
+        mbar_expect_tx(x_full(xs), 4u * X_SUB_BYTES);
+        for (int j = 4 * xs; j < 4 * xs + 4; ++j) tma_load_2d(x_base + j * X_SUB_BYTES, &map_x, x_full(xs), stage0 * STAGE_K + j * 64, 0);
+      }
       issue_raw(total_its);
       if (!ok) {
         // wait (bounded) for the copies already started before the CTA may exit
-        mbar_wait(x_full, 0);
+        for (int xs = 0; xs < nstages; ++xs) mbar_wait(x_full(xs), 0);
         for (int j = it > RAW_STAGES ? it - RAW_STAGES : 0; j < it; ++j) mbar_wait(raw_full(j % RAW_STAGES), (j / RAW_STAGES) & 1);
       }
     }
@@ -301,34 +312,29 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     // ---------------- MMA issuers: A (dequantised weights) from tensor memory, B (activations) from shared memory ----------------
     // warp 1 takes the even local tiles, warp 2 the odd ones
     if (lane == 0) {
-      const int e = warp - 1;
-      bool ok = mbar_wait_parked(x_full, 0);
-      if (!ok) atomicExch(status, 12);
+      const int team = warp - 1;
+      bool ok = true;
+      int n = 0;                                    // stages this team has multiplied so far
       const uint64_t bdesc0 = make_sdesc(x_base);   // the start-address field counts 16-byte units: later operands are plain adds
-      for (int j = e; j < ntl && ok; j += 2) {
+      const uint32_t ta0 = tmem_base + (uint32_t)(A_COL0 + team * A_STAGE_COLS);
+      for (int j = team; j < ntl && ok; j += 2) {
         const int acc = j & (NUM_ACC - 1);
         if (!mbar_wait_parked(t_empty(acc), ((j / NUM_ACC) & 1) ^ 1)) { atomicExch(status, 13); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TM);
-        const int p = j >> 1;
-        for (int s = 0; s < nstages; ++s) {
-          const int as = p < full_pairs ? p * pair_its + 2 * s + e : full_pairs * pair_its + s;   // position in the stream
-          const int buf = as % A_STAGES;
-          if (!mbar_wait_parked(a_full(buf), (as / A_STAGES) & 1)) { atomicExch(status, 14); ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t ta = tmem_base + (uint32_t)(A_COL0 + buf * A_STAGE_COLS);
+        for (int s = 0; s < nstages && ok; ++s, ++n) {
+          if (!mbar_wait_parked(x_full(s), 0)) { atomicExch(status, 12); ok = false; break; }   // completes once; later tiles pass at once
           const uint64_t bd = bdesc0 + (uint64_t)((s * 4 * X_SUB_BYTES) >> 4);
-          if (s == 0) {
-            umma_bf16_ts(tmem_d, ta, bd, IDESC, 0u);   // first K step of the tile overwrites the accumulator
 #pragma unroll
-            for (int k = 1; k < 16; ++k)
-              umma_bf16_ts(tmem_d, ta + (uint32_t)(k * 8), bd + (uint64_t)(((k >> 2) * X_SUB_BYTES + (k & 3) * 32) >> 4), IDESC, 1u);
-          } else {
+          for (int half = 0; half < 2; ++half) {
+            if (!mbar_wait_parked(a_full(team, half), n & 1)) { atomicExch(status, 14); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int k = 0; k < 16; ++k)
-              umma_bf16_ts(tmem_d, ta + (uint32_t)(k * 8), bd + (uint64_t)(((k >> 2) * X_SUB_BYTES + (k & 3) * 32) >> 4), IDESC, 1u);
+            for (int k = 8 * half; k < 8 * half + 8; ++k)
+              umma_bf16_ts(tmem_d, ta0 + (uint32_t)(k * 8), bd + (uint64_t)(((k >> 2) * X_SUB_BYTES + (k & 3) * 32) >> 4), IDESC,
+                           (s == 0 && k == 0) ? 0u : 1u);   // the first K step of a tile overwrites the accumulator
+            umma_commit(a_empty(team, half));
           }
-          umma_commit(a_empty(buf));
         }
         if (ok) umma_commit(t_full(acc));
       }
@@ -336,44 +342,56 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   } else if (warp == 3) {
     // nothing more: this warp owns the tensor-memory allocation
   } else if (warp < EPI_WARP0) {
-    // ---------------- dequantisers: thread = weight row (its TMEM lane), two 32-value blocks of every 256-K stage ----------------
-    const int quarter = warp & 3, part = (warp - DEQ_WARP0) >> 2;   // a warp reaches only the TMEM lanes of its quarter
+    // ---------------- dequantisers: thread = weight row (its TMEM lane), four 32-value blocks of every 256-K stage of its team ----------------
+    const int team = (warp - DEQ_WARP0) >> 3, quarter = warp & 3, part = ((warp - DEQ_WARP0) >> 2) & 1;   // a warp reaches only the TMEM lanes of its quarter
     const int r = quarter * 32 + lane;
     const uint32_t swz = (uint32_t)(r & 7);
-    int it = 0;
+    const uint32_t ta0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(A_COL0 + team * A_STAGE_COLS + part * 32);
     bool ok = true;
-    int pending = -1;     // operand buffer whose tcgen05.st has been issued but not yet announced
-    // The store of a stage is announced to the MMA lane one iteration later, after the next stage's raw bytes have been
-    // requested from shared memory: the thread then never sits in tcgen05.wait::st right behind its own store.
+    int n = 0;            // stages this team has converted so far
+    int pending = -1;     // half whose tcgen05.st has been issued but not yet announced
+    // A store is announced to the MMA lane only after the next piece of work has been started: the thread then never sits in
+    // tcgen05.wait::st right behind its own store.
     auto publish = [&]() {
       if (pending >= 0) {
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(a_full(pending));
+        if (lane == 0) mbar_arrive(a_full(team, pending));
         pending = -1;
       }
     };
-    {
-      for (; it < total_its && ok; ++it) {
+    for (int j = team; j < ntl && ok; j += 2) {
+      for (int s = 0; s < nstages && ok; ++s, ++n) {
+        const int it = position(j, s);
         const int slot = it % RAW_STAGES;
         if (!mbar_wait_parked(raw_full(slot), (it / RAW_STAGES) & 1)) { if (lane == 0) atomicExch(status, 15); ok = false; break; }
         const uint32_t rawp = raw_base + slot * RAW_STAGE_BYTES;
+        // blocks 2*part, 2*part+1 (first half of the stage) and 4+2*part, 5+2*part (second half), with their f16 scales
         const uint4 q0 = lds128(rawp + r * 128 + (((uint32_t)(2 * part) ^ swz) << 4));
         const uint4 q1 = lds128(rawp + r * 128 + (((uint32_t)(2 * part + 1) ^ swz) << 4));
-        const uint32_t sw = lds32(rawp + RAW_BYTES + r * 16 + part * 4);   // f16 scales of blocks 2*part, 2*part+1
-        publish();                                                          // the previous stage's store has had time to land
+        const uint4 q2 = lds128(rawp + r * 128 + (((uint32_t)(4 + 2 * part) ^ swz) << 4));
+        const uint4 q3 = lds128(rawp + r * 128 + (((uint32_t)(5 + 2 * part) ^ swz) << 4));
+        const uint32_t sw0 = lds32(rawp + RAW_BYTES + r * 16 + part * 4);
+        const uint32_t sw1 = lds32(rawp + RAW_BYTES + r * 16 + (2 + part) * 4);
+        publish();                                                          // the previous stage's second half
         __syncwarp();
         if (lane == 0) mbar_arrive(raw_empty(slot));                        // the stage now lives in registers
         uint32_t v[32];
-        deq_block(q0, bf16x2_of_f16(sw & 0xFFFFu), v);
-        deq_block(q1, bf16x2_of_f16(sw >> 16), v + 16);
-        const int buf = it % A_STAGES;
-        if (!mbar_wait_parked(a_empty(buf), ((it / A_STAGES) & 1) ^ 1)) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
+        deq_block(q0, bf16x2_of_f16(sw0 & 0xFFFFu), v);
+        deq_block(q1, bf16x2_of_f16(sw0 >> 16), v + 16);
+        if (!mbar_wait_parked(a_empty(team, 0), (n & 1) ^ 1)) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(A_COL0 + buf * A_STAGE_COLS + part * 32);
-        tmem_st32(ta, v);
-        pending = buf;
+        tmem_st32(ta0, v);
+        pending = 0;
+        uint32_t w[32];
+        deq_block(q2, bf16x2_of_f16(sw1 & 0xFFFFu), w);
+        deq_block(q3, bf16x2_of_f16(sw1 >> 16), w + 16);
+        publish();                                                          // the first half, while its store had the second half's arithmetic to land behind
+        if (!mbar_wait_parked(a_empty(team, 1), (n & 1) ^ 1)) { if (lane == 0) atomicExch(status, 16); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tmem_st32(ta0 + (uint32_t)A_HALF_COLS, w);
+        pending = 1;
       }
     }
     publish();
@@ -381,10 +399,10 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     // ---------------- epilogue warps: TMEM lane quarter (warp % 4), thread = weight row ----------------
     const int quarter = warp & 3;
     const i64 n_pad = (i64)plan.n_tiles * TN;
-    int local = 0;
     bool ok = true;
     pdl_wait();
-    for (int t = group; t < plan.n_tiles && ok; t += plan.groups, ++local) {
+    for (int local = (warp - EPI_WARP0) >> 2; local < ntl && ok; local += 2) {   // set 0: even local tiles, set 1: odd ones
+      const int t = group + local * plan.groups;
       const int acc = local & (NUM_ACC - 1);
       const int n = t * TN + quarter * 32 + lane;
       if (!mbar_wait_parked(t_full(acc), (local / NUM_ACC) & 1)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
