@@ -98,7 +98,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return r;
 }
 
-// Shared memory: Q tile | STAGES x (K block, V block) | barriers (nine, 72 bytes) | tmem slot (+128) | tile-wide max of the visible-key counts
+// Shared memory: Q tile | STAGES x (K block, V block) | barriers (thirteen, 104 bytes) | tmem slot (+128) | tile-wide max of the visible-key counts
 template <int HD>
 struct Smem {
   static constexpr int NSUB = HD / 64;
@@ -132,10 +132,14 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + SM::Q_BYTES + STAGES * SM::STAGE_BYTES + 128);
   int* kmax_slot = reinterpret_cast<int*>(gen + SM::Q_BYTES + STAGES * SM::STAGE_BYTES + 136);
   float* xmax = reinterpret_cast<float*>(gen + SM::Q_BYTES + STAGES * SM::STAGE_BYTES + 256);
-  auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  const uint32_t s_full0 = bars + 8u * (2 * STAGES), p_full = bars + 8u * (2 * STAGES + 1), o_full = bars + 8u * (2 * STAGES + 2);
-  const uint32_t s_full1 = bars + 8u * (2 * STAGES + 3), o_done = bars + 8u * (2 * STAGES + 4);
+  // K and V of a key block travel separately: a K slot is free again once the block's Q . K^T has retired, a V slot once its
+  // P . V has, so the load of the K block two ahead starts a whole block earlier than if the two shared a barrier
+  auto kfull = [&](int s) { return bars + 8u * s; };
+  auto kempty = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto vfull = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+  auto vempty = [&](int s) { return bars + 8u * (3 * STAGES + s); };
+  const uint32_t s_full0 = bars + 8u * (4 * STAGES), p_full = bars + 8u * (4 * STAGES + 1), o_full = bars + 8u * (4 * STAGES + 2);
+  const uint32_t s_full1 = bars + 8u * (4 * STAGES + 3), o_done = bars + 8u * (4 * STAGES + 4);
   // score / probability buffer and barrier phase of key block kb
   auto s_bar = [&](int kb) { return (SM::DB && (kb & 1)) ? s_full1 : s_full0; };
   auto s_par = [&](int kb) { return (uint32_t)(SM::DB ? (kb >> 1) & 1 : kb & 1); };
@@ -149,7 +153,7 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
   const int live = nrows * G;                      // operand rows in use: a = token * G + head-of-group
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(kfull(s), 1); mbar_init(kempty(s), 1); mbar_init(vfull(s), 1); mbar_init(vempty(s), 1); }
     mbar_init(s_full0, 1); mbar_init(s_full1, 1); mbar_init(p_full, 8); mbar_init(o_full, 1); mbar_init(o_done, 1);
     *kmax_slot = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -210,33 +214,64 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
       const int last_page = (kmax - 1) >> 4;
       const int p = lane & 7;
       bool ok = true;
-      int kb = 0;
-      // pages past the last visible key do not exist: the last real page stands in (its rows are masked / zeroed)
-      uint32_t page = bt[min(p, last_page)];
-      for (; kb < nkb && ok; ++kb) {
+      // one operand (K or V) of key block kb: lane 0 waits for the slot and arms the barrier, lanes 0-7 issue their page
+      auto load = [&](int kb, bool is_v, uint32_t page) {
         const int s = kb % STAGES;
-        const uint32_t page_next = kb + 1 < nkb ? bt[min(8 * (kb + 1) + p, last_page)] : 0u;
+        const uint32_t fb = is_v ? vfull(s) : kfull(s), eb = is_v ? vempty(s) : kempty(s);
         int good = 1;
         if (lane == 0) {
-          good = mbar_wait(empty_bar(s), ((kb / STAGES) & 1) ^ 1) ? 1 : 0;
-          if (good) mbar_expect_tx(full_bar(s), SM::STAGE_BYTES);
+          good = mbar_wait(eb, ((kb / STAGES) & 1) ^ 1) ? 1 : 0;
+          if (good) mbar_expect_tx(fb, SM::OP_BYTES);
           else atomicExch(status, WKB_STATUS_ATTN_WAIT);
         }
         good = __shfl_sync(0xffffffffu, good, 0);
-        if (!good) { ok = false; break; }
+        if (!good) return false;
         if (lane < 8) {
-          const uint32_t kdst = ring + s * SM::STAGE_BYTES, vdst = kdst + SM::OP_BYTES;
+          const uint32_t dst = ring + s * SM::STAGE_BYTES + (is_v ? SM::OP_BYTES : 0);
           const int y = (int)(((i64)page * g.kv_heads + kvh) * 16);
 #pragma unroll
-          for (int h = 0; h < NSUB; ++h) {
-            tma_load_2d(kdst + h * SUB_BYTES + p * 2048, &map_k, full_bar(s), 64 * h, y);
-            tma_load_2d(vdst + h * SUB_BYTES + p * 2048, &map_v, full_bar(s), 64 * h, y);
-          }
+          for (int h = 0; h < NSUB; ++h) tma_load_2d(dst + h * SUB_BYTES + p * 2048, is_v ? &map_v : &map_k, fb, 64 * h, y);
         }
-        page = page_next;
+        return true;
+      };
+      // pages past the last visible key do not exist: the last real page stands in (its rows are masked / zeroed)
+      uint32_t page = bt[min(p, last_page)];
+      int k_issued = 0, v_issued = 0;       // blocks whose K / V loads have been started
+      if (SM::DB) {
+        // K runs one block ahead of V, the order in which the MMA warp (which issues the next block's Q . K^T before this
+        // block's P . V) frees the slots: K(0) K(1) V(0) K(2) V(1) ...
+        ok = load(0, false, page);
+        if (ok) k_issued = 1;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          const uint32_t page_next = kb + 1 < nkb ? bt[min(8 * (kb + 1) + p, last_page)] : 0u;
+          if (kb + 1 < nkb) {
+            ok = load(kb + 1, false, page_next);
+            if (!ok) break;
+            k_issued = kb + 2;
+          }
+          ok = load(kb, true, page);
+          if (!ok) break;
+          v_issued = kb + 1;
+          page = page_next;
+        }
+      } else {
+        // K(0) V(0) K(1) V(1) ...; the next block's table entry is fetched while this block's slots are awaited
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          const uint32_t page_next = kb + 1 < nkb ? bt[min(8 * (kb + 1) + p, last_page)] : 0u;
+          ok = load(kb, false, page);
+          if (!ok) break;
+          k_issued = kb + 1;
+          ok = load(kb, true, page);
+          if (!ok) break;
+          v_issued = kb + 1;
+          page = page_next;
+        }
       }
-      if (!ok && lane == 0)
-        for (int j = kb > STAGES ? kb - STAGES : 0; j < kb; ++j) mbar_wait(full_bar(j % STAGES), (j / STAGES) & 1);
+      if (!ok && lane == 0) {
+        // wait (bounded) for the copies already started before the CTA may exit
+        for (int j = k_issued > STAGES ? k_issued - STAGES : 0; j < k_issued; ++j) mbar_wait(kfull(j % STAGES), (j / STAGES) & 1);
+        for (int j = v_issued > STAGES ? v_issued - STAGES : 0; j < v_issued; ++j) mbar_wait(vfull(j % STAGES), (j / STAGES) & 1);
+      }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -246,7 +281,14 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
       // S(kb) = Q . K(kb)^T over head_dim in steps of 16, query hi part then lo part
       auto issue_scores = [&](int kb) {
         const int s = kb % STAGES;
-        if (!mbar_wait(full_bar(s), (kb / STAGES) & 1)) { atomicExch(status, WKB_STATUS_ATTN_WAIT); return false; }
+        if (!mbar_wait(kfull(s), (kb / STAGES) & 1)) { atomicExch(status, WKB_STATUS_ATTN_WAIT); return false; }
+        // Single-buffered scores: K and V of a block are requested together, so waiting for both here costs nothing and
+        // tells the softmax warps (which zero the unwritten V rows of a ragged last block) that V has landed when the
+        // scores arrive.  With double-buffered scores they wait for V themselves.
+        if (!SM::DB && !mbar_wait(vfull(s), (kb / STAGES) & 1)) {
+          atomicExch(status, WKB_STATUS_ATTN_WAIT);
+          return false;
+        }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t kaddr = ring + s * SM::STAGE_BYTES;
 #pragma unroll
@@ -257,6 +299,7 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
             umma_bf16(tmem + s_col(kb), make_sdesc(q_base + part * SM::OP_BYTES + off), make_sdesc(kaddr + off), ID_S, (part > 0 || k > 0) ? 1u : 0u);
           }
         umma_commit(s_bar(kb));
+        umma_commit(kempty(s));
         return true;
       };
       if (SM::DB && nkb > 0) ok = issue_scores(0);
@@ -267,14 +310,14 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
         else ok = issue_scores(kb);
         if (!ok) break;
         // O += P . V once the softmax warps have written P (and rescaled O, and zeroed the V rows past the last key)
-        if (!mbar_wait(p_full, kb & 1)) { atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; break; }
+        if (!mbar_wait(p_full, kb & 1) || !mbar_wait(vfull(kb % STAGES), (kb / STAGES) & 1)) { atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t vaddr = ring + (kb % STAGES) * SM::STAGE_BYTES + SM::OP_BYTES;
 #pragma unroll
         for (int k = 0; k < KBLK / 16; ++k)
           umma_ts(tmem + SM::O_COL, tmem + p_col(kb) + (uint32_t)(k * 8), make_sdesc_mn(vaddr + (uint32_t)k * 2048u, SUB_BYTES), ID_O,
                   (kb > 0 || k > 0) ? 1u : 0u);
-        umma_commit(empty_bar(kb % STAGES));
+        umma_commit(vempty(kb % STAGES));
         umma_commit(o_done);
         if (kb + 1 == nkb) umma_commit(o_full);
       }
@@ -381,6 +424,12 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __
       // the last block may hold key rows that were never written (a partly filled page): their probabilities are zero,
       // but 0 x NaN would still poison the product, so those V rows are zeroed in shared memory first
       if (kb + 1 == nkb && (kmax - kb * KBLK) < KBLK) {
+        if constexpr (SM::DB) {
+          int vok = 1;
+          if (lane == 0) vok = mbar_wait(vfull(kb % STAGES), (kb / STAGES) & 1) ? 1 : 0;     // the V block must have landed
+          vok = __shfl_sync(0xffffffffu, vok, 0);
+          if (!vok) { if (lane == 0) atomicExch(status, WKB_STATUS_ATTN_WAIT); ok = false; break; }
+        }
         const uint32_t vaddr = ring + (kb % STAGES) * SM::STAGE_BYTES + SM::OP_BYTES;
         const int first_bad = kmax - kb * KBLK;
         for (int idx = sm_tid; idx < (KBLK - first_bad) * NSUB * 8; idx += 256) {
