@@ -307,16 +307,27 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-template <typename TOut, int VPL>
-__global__ void __launch_bounds__(256, 2) norm_row_warp_kernel(const __nv_bfloat16* __restrict__ x, TOut* __restrict__ out,
+// gamma / beta are the same for every row; read where they are used (from L1), not hoisted out of the row loop into
+// registers the row itself needs
+__device__ __forceinline__ float4 ld_f4_here(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+template <typename TOut, int VPL, int OP, bool HAS_GAMMA, bool HAS_BETA>
+__global__ void __launch_bounds__(128, VPL >= 16 ? 3 : 4) norm_row_warp_kernel(const __nv_bfloat16* __restrict__ x, TOut* __restrict__ out,
                                                             const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                            i64 rows, int cols, float eps, int op, int rows_per_warp) {
+                                                            i64 rows, int cols, float eps, i64 warps) {
+  // the operation and the presence of gamma / beta are compile-time: as run-time branches inside the unrolled row loops
+  // they were hoisted out of them, and the row spilled to local memory (0.41 of the HBM peak instead of 0.9)
+  constexpr int op = OP;
   const int lane = threadIdx.x & 31;
   const i64 warp = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const float inv_n = 1.0f / (float)cols;
-  for (int it = 0; it < rows_per_warp; ++it) {
-    const i64 r = warp * rows_per_warp + it;
-    if (r >= rows) return;
+  // rows are dealt out round-robin over the warps of the grid: every SM then carries the same number of rows to within
+  // one (consecutive rows per warp left the SMs that hold two CTAs with twice the rows of those that hold one)
+  for (i64 r = warp; r < rows; r += warps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + r * (i64)cols);
     uint4 w[VPL];
 #pragma unroll
@@ -365,6 +376,7 @@ __global__ void __launch_bounds__(256, 2) norm_row_warp_kernel(const __nv_bfloat
         // layernorm: mean first, then the centred second moment from the registers
         const float mean = warp_sum(s1) * inv_n;
         float q = 0.0f;
+
 #pragma unroll
         for (int k = 0; k < VPL; ++k) {
           const uint32_t s4[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
@@ -396,15 +408,15 @@ __global__ void __launch_bounds__(256, 2) norm_row_warp_kernel(const __nv_bfloat
         for (int e = 0; e < 8; ++e) o[e] *= scale;
       } else {
         float g[8], b[8];
-        if (gamma) {
-          const float4 g0 = reinterpret_cast<const float4*>(gamma)[2 * vi], g1 = reinterpret_cast<const float4*>(gamma)[2 * vi + 1];
+        if (HAS_GAMMA) {
+          const float4 g0 = ld_f4_here(gamma + 8 * vi), g1 = ld_f4_here(gamma + 8 * vi + 4);
           g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
         } else {
 #pragma unroll
           for (int e = 0; e < 8; ++e) g[e] = 1.0f;
         }
-        if (beta) {
-          const float4 b0 = reinterpret_cast<const float4*>(beta)[2 * vi], b1 = reinterpret_cast<const float4*>(beta)[2 * vi + 1];
+        if (HAS_BETA) {
+          const float4 b0 = ld_f4_here(beta + 8 * vi), b1 = ld_f4_here(beta + 8 * vi + 4);
           b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
         } else {
 #pragma unroll
@@ -428,12 +440,21 @@ __global__ void __launch_bounds__(256, 2) norm_row_warp_kernel(const __nv_bfloat
 template <typename TOut, int VPL>
 static int launch_row_warp(const void* x, void* out, const float* g, const float* b, i64 rows, i64 cols, float eps, int op,
                            cudaStream_t st) {
-  // an equal number of rows for every warp: ceil(rows / (resident warps)) rows each
-  const i64 resident = (i64)WKB_SM_COUNT * (VPL >= 16 ? 16 : 32);
-  const int rpw = (int)((rows + resident - 1) / resident);
-  const i64 warps = (rows + rpw - 1) / rpw;
-  const i64 blocks = (warps + 7) / 8;
-  norm_row_warp_kernel<TOut, VPL><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (TOut*)out, g, b, rows, (int)cols, eps, op, rpw);
+  // one grid of resident warps (whole CTAs of 8 on every SM), rows dealt out round-robin
+  // (CTAs of 4 warps; a 4096-wide row is 64 registers per lane, so 3 CTAs = 12 warps per SM leave 168 registers each;
+  // narrower rows run 4 CTAs per SM at 128 registers)
+  const i64 resident = (i64)WKB_SM_COUNT * (VPL >= 16 ? 12 : 16);
+  const i64 blocks = rows < resident ? (rows + 3) / 4 : resident / 4;
+  const i64 warps = blocks * 4;
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+#define WKB_ROW_WARP(OP_, HG_, HB_) norm_row_warp_kernel<TOut, VPL, OP_, HG_, HB_><<<(int)blocks, 128, 0, st>>>(xb, (TOut*)out, g, b, rows, (int)cols, eps, warps)
+  if (op == 0) WKB_ROW_WARP(0, false, false);
+  else if (op == 1) {
+    if (g && b) WKB_ROW_WARP(1, true, true); else if (g) WKB_ROW_WARP(1, true, false); else if (b) WKB_ROW_WARP(1, false, true); else WKB_ROW_WARP(1, false, false);
+  } else {
+    if (g && b) WKB_ROW_WARP(2, true, true); else if (g) WKB_ROW_WARP(2, true, false); else if (b) WKB_ROW_WARP(2, false, true); else WKB_ROW_WARP(2, false, false);
+  }
+#undef WKB_ROW_WARP
   return (int)cudaGetLastError();
 }
 
