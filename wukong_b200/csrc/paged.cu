@@ -499,6 +499,17 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[2], uint32_t a0, uint3
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, {%7, %8}, {%0, %1, %9, %9};"
                : "+f"(d[0]), "+f"(d[1]), "=f"(z0), "=f"(z1) : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.0f));
 }
+// The same instruction with the hi parts of the A operand in rows 0-7 (registers a0, a2) and the lo parts in rows 8-15
+// (a1, a3), which a group of at most 8 heads leaves free: one instruction multiplies both parts, rows g and g + 8 of the
+// result land in the same thread and are added there.  The legacy tensor path is what bounds these kernels once the
+// pages arrive through shared memory, so halving the score instructions is worth the two additions.
+__device__ __forceinline__ void mma_bf16_hilo(float (&d)[2], uint32_t a_hi0, uint32_t a_lo0, uint32_t a_hi8, uint32_t a_lo8, uint32_t b0, uint32_t b1) {
+  float l0, l1;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %10, %10};"
+               : "+f"(d[0]), "+f"(d[1]), "=f"(l0), "=f"(l1) : "r"(a_hi0), "r"(a_lo0), "r"(a_hi8), "r"(a_lo8), "r"(b0), "r"(b1), "f"(0.0f));
+  d[0] += l0;
+  d[1] += l1;
+}
 __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -602,8 +613,7 @@ __global__ void __launch_bounds__(PA_WARPS * 32, 2) paged_attn_decode_mma_kernel
         const uint32_t kr[4] = {kcur[u][j].x, kcur[u][j].y, kcur[u][j].z, kcur[u][j].w};
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          mma_bf16_16816(sc[u], qh[j][h][0], qh[j][h][1], kr[2 * h], kr[2 * h + 1]);
-          mma_bf16_16816(sc[u], ql[j][h][0], ql[j][h][1], kr[2 * h], kr[2 * h + 1]);
+          mma_bf16_hilo(sc[u], qh[j][h][0], ql[j][h][0], qh[j][h][1], ql[j][h][1], kr[2 * h], kr[2 * h + 1]);
         }
       }
     }
@@ -784,8 +794,7 @@ __global__ void __launch_bounds__(32) paged_attn_decode_mma_staged_kernel(
         const uint32_t kr[4] = {kw.x, kw.y, kw.z, kw.w};
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          mma_bf16_16816(sc[u], qh[j][h][0], qh[j][h][1], kr[2 * h], kr[2 * h + 1]);
-          mma_bf16_16816(sc[u], ql[j][h][0], ql[j][h][1], kr[2 * h], kr[2 * h + 1]);
+          mma_bf16_hilo(sc[u], qh[j][h][0], ql[j][h][0], qh[j][h][1], ql[j][h][1], kr[2 * h], kr[2 * h + 1]);
         }
       }
     }
