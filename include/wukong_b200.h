@@ -386,7 +386,7 @@ int wkb_gemm_bf16_nt_partial(const void* a, int64_t lda, const void* b, int64_t 
  * crates/wukong_codegen_gpu/src/serving.rs:684-937): C[:, :kv_col0] = A.B^T + bias in fp32 (the query heads); columns
  * [kv_col0, kv_col0 + 2 * kv_heads * head_dim) -- the new K rows, then the new V rows -- are rounded to bf16 straight into
  * their pages at row_pos through the block table (the work of wkb_paged_kv_append) and are not stored to C.
- * n = kv_col0 + 2 * kv_heads * head_dim; kv_col0 % 32 == 0. */
+ * n = kv_col0 + 2 * kv_heads * head_dim; kv_col0 % 32 == 0 and head_dim % 32 == 0; caches and bias 16-byte aligned. */
 int wkb_gemm_bf16_nt_qkv_append(const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc, int64_t m,
                                 int64_t n, int64_t k, const float* bias, int64_t kv_col0, void* kcache, void* vcache,
                                 const uint32_t* block_table, const int* row_slot, const int* row_pos, int64_t kv_heads,

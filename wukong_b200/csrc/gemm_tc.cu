@@ -205,17 +205,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int buf = local & 1;
       const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
       const int row = m0 + quarter * 32 + lane;
-      int good = 1;
-      if (lane == 0) good = mbar_wait(tfull_bar(buf), (local >> 1) & 1) ? 1 : 0;
-      good = __shfl_sync(0xffffffffu, good, 0);
-      if (!good) { if (lane == 0) atomicExch(status, 3); ok = false; break; }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      float best_v = -INFINITY;
-      int best_i = -1;
-      bool pinned = false;
-      (void)best_v; (void)best_i; (void)pinned;
-      // KVAPPEND: lane rr keeps where row (m0 + quarter * 32 + rr) lands in the cache: element offset of its token row
-      // for KV head 0 (-1: the row writes nothing)
+      // KVAPPEND: where this thread's row (the TMEM lane it reads) lands in the cache: element offset of its token row for
+      // KV head 0 (-1: the row writes nothing).  Looked up while the tile is still being multiplied.
       i64 kv_dst = -1;
       (void)kv_dst;
       if (KVAPPEND && n0 + BN > epi.kv_col0 && row < M) {
@@ -230,6 +221,15 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      int good = 1;
+      if (lane == 0) good = mbar_wait(tfull_bar(buf), (local >> 1) & 1) ? 1 : 0;
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { if (lane == 0) atomicExch(status, 3); ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float best_v = -INFINITY;
+      int best_i = -1;
+      bool pinned = false;
+      (void)best_v; (void)best_i; (void)pinned;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -251,7 +251,31 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_bar(buf));
         }
-        if (ARGMAX) {
+        if (KVAPPEND && n0 + c0 >= epi.kv_col0) {
+          // a K or V chunk (kv_col0 and the head size are multiples of 32, so the 32 columns are consecutive dims of one
+          // head): the thread holds them for its own row and writes them as 64 contiguous bytes of that token's cache row --
+          // no transpose, no exchange of destinations between lanes
+          if (kv_dst >= 0 && n0 + c0 + 32 <= N) {
+            const int kc = n0 + c0 - epi.kv_col0, kv_dim = epi.kv_heads * epi.kv_hd;
+            u16* cache = kc < kv_dim ? epi.kcache : epi.vcache;
+            const int cc = kc < kv_dim ? kc : kc - kv_dim;
+            uint4* dst = reinterpret_cast<uint4*>(cache + kv_dst + (i64)(cc / epi.kv_hd) * epi.page_tokens * epi.kv_hd + (cc % epi.kv_hd));
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+              if (epi.bias) {
+                const float4 b0 = *reinterpret_cast<const float4*>(epi.bias + n0 + c0 + 8 * v), b1 = *reinterpret_cast<const float4*>(epi.bias + n0 + c0 + 8 * v + 4);
+                b8[0] = b0.x; b8[1] = b0.y; b8[2] = b0.z; b8[3] = b0.w; b8[4] = b1.x; b8[5] = b1.y; b8[6] = b1.z; b8[7] = b1.w;
+              }
+              uint32_t w4[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                w4[e] = (uint32_t)f32_to_bf16_bits(__uint_as_float(r[8 * v + 2 * e]) + b8[2 * e]) |
+                        ((uint32_t)f32_to_bf16_bits(__uint_as_float(r[8 * v + 2 * e + 1]) + b8[2 * e + 1]) << 16);
+              dst[v] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+          }
+        } else if (ARGMAX) {
           // thread = row: ascending scan of its 32 columns keeps the lowest index on a tie; NaNs never
           // win, except that a NaN in global column 0 pins the row to 0 (the arg-max rule of the ABI)
           if (n0 + c0 + 32 <= N && n0 + c0 > 0 && !epi.bias) {
@@ -293,18 +317,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int e = 0; e < 32; ++e) stage[lane * 33 + e] = __uint_as_float(r[e]);
           __syncwarp();
           const float bias_v = (col_ok && epi.bias) ? epi.bias[col] : 0.0f;
-          if (KVAPPEND && n0 + c0 >= epi.kv_col0) {
-            // this 32-column chunk is K or V (kv_col0 is a multiple of 32, so a chunk never straddles q | k): round into the pages
-            const int kc = col_ok ? col - epi.kv_col0 : 0, kv_dim = epi.kv_heads * epi.kv_hd;
-            u16* cache = kc < kv_dim ? epi.kcache : epi.vcache;
-            const int cc = kc < kv_dim ? kc : kc - kv_dim;
-            const i64 head_off = (i64)(cc / epi.kv_hd) * epi.page_tokens * epi.kv_hd + (cc % epi.kv_hd);
-#pragma unroll 4
-            for (int rr = 0; rr < 32; ++rr) {
-              const i64 dst = __shfl_sync(0xffffffffu, kv_dst, rr);       // every lane takes part in the exchange
-              if (col_ok && dst >= 0) cache[dst + head_off] = f32_to_bf16_bits(stage[rr * 33 + lane] + bias_v);
-            }
-          } else if (col_ok) {
+          if (col_ok) {
             if (full) {
               float vals[32];
 #pragma unroll
@@ -642,16 +655,18 @@ int wkb_gemm_bf16_nt_partial(const void* a, i64 lda, const void* b, i64 ldb, i64
 // The fused QKV projection of a decode step: C[:, :kv_col0] = A.B^T + bias (fp32, the query heads); columns
 // [kv_col0, kv_col0 + 2 * kv_heads * head_dim) -- the new K rows, then the new V rows -- are rounded to bf16 straight
 // into their pages at row_pos through the block table and are not stored to C (the work of wkb_paged_kv_append, without
-// its launch and without the fp32 round trip).  n must be kv_col0 + 2 * kv_heads * head_dim; kv_col0 % 32 == 0.
+// its launch and without the fp32 round trip).  n must be kv_col0 + 2 * kv_heads * head_dim; kv_col0 and head_dim are
+// multiples of 32 (a 32-column piece of the accumulator is then 32 consecutive dims of one head), the caches and the bias
+// 16-byte aligned.
 int wkb_gemm_bf16_nt_qkv_append(const void* a, i64 lda, const void* b, i64 ldb, float* c, i64 ldc, i64 m, i64 n, i64 k, const float* bias,
                                 i64 kv_col0, void* kcache, void* vcache, const uint32_t* block_table, const int* row_slot, const int* row_pos,
                                 i64 kv_heads, i64 head_dim, i64 page_tokens, i64 max_blocks_per_seq, void* stream) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   if (k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return (int)cudaErrorInvalidValue;
-  if (kv_col0 < 0 || kv_col0 % 32 != 0 || kv_heads <= 0 || head_dim <= 0 || page_tokens <= 0 || max_blocks_per_seq <= 0 ||
+  if (kv_col0 < 0 || kv_col0 % 32 != 0 || kv_heads <= 0 || head_dim <= 0 || head_dim % 32 != 0 || page_tokens <= 0 || max_blocks_per_seq <= 0 ||
       n != kv_col0 + 2 * kv_heads * head_dim)
     return (int)cudaErrorInvalidValue;
-  if ((((uintptr_t)a) | ((uintptr_t)b)) & 15) return (int)cudaErrorMisalignedAddress;
+  if ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)kcache) | ((uintptr_t)vcache) | ((uintptr_t)bias)) & 15) return (int)cudaErrorMisalignedAddress;
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, m, k, lda, BM);
   if (rc) return rc;

@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(128) quantize_act_kernel(const float* __restri
 // of the adds (it used to be paid per 4 rows by 4 lanes of every warp).
 constexpr int GQ_RB = 4, GQ_WARPS = 8, GQ_ROWS = GQ_RB * GQ_WARPS;
 
-template <bool Q4>
+template <bool Q4, int U>
 __global__ void __launch_bounds__(GQ_WARPS * 32) gemv_q_contract_kernel(const uint4* __restrict__ qs, const u16* __restrict__ d,
                                                                         const int8_t* __restrict__ xq, const float* __restrict__ dx,
                                                                         const int* __restrict__ sx, float* __restrict__ y, i64 n,
@@ -87,54 +87,74 @@ __global__ void __launch_bounds__(GQ_WARPS * 32) gemv_q_contract_kernel(const ui
   int* sxs = reinterpret_cast<int*>(dxs + nb);
   float* terms = reinterpret_cast<float*>(sxs + nb);      // [32 rows][nb]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int QW = Q4 ? 1 : 2;  // uint4 words per block
+  // U: blocks per lane whose loads are in flight together (a pass covers 32 * U blocks of every row)
+  const i64 nbatches = (n + GQ_ROWS - 1) / GQ_ROWS;
+  uint4 wq[U][GQ_RB][QW];
+  u16 dw[U][GQ_RB];
+  // all the loads of a pass are issued before any of them is used: one trip to HBM per pass instead of one per block
+  auto load_pass = [&](i64 r0, int b0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int b = b0 + 32 * u;
+      if (b < nb) {
+#pragma unroll
+        for (int r = 0; r < GQ_RB; ++r) {
+          const i64 row = r0 + r < n ? r0 + r : n - 1;
+          const uint4* p = qs + (row * nb + b) * QW;
+#pragma unroll
+          for (int h = 0; h < QW; ++h) wq[u][r][h] = p[h];
+          dw[u][r] = d[row * nb + b];
+        }
+      }
+    }
+  };
+  // the first pass of the first batch does not depend on the activations: its loads travel while x is staged
+  const bool preloaded = (i64)blockIdx.x < nbatches && (i64)blockIdx.x * GQ_ROWS + warp * GQ_RB < n;
+  if (preloaded) load_pass((i64)blockIdx.x * GQ_ROWS + warp * GQ_RB, lane);
   for (int i = threadIdx.x; i < nb * 8; i += blockDim.x) {
     int b = i >> 3, w = i & 7;
     xs[w * nb + b] = reinterpret_cast<const int*>(xq)[i];
   }
   for (int i = threadIdx.x; i < nb; i += blockDim.x) { dxs[i] = dx[i]; sxs[i] = sx[i]; }
   __syncthreads();
-  constexpr int QW = Q4 ? 1 : 2;  // uint4 words per block
-  const i64 nbatches = (n + GQ_ROWS - 1) / GQ_ROWS;
   for (i64 batch = blockIdx.x; batch < nbatches; batch += gridDim.x) {
     const i64 rbase = batch * GQ_ROWS;
     const i64 r0 = rbase + warp * GQ_RB;
     if (r0 < n) {
-      for (int b = lane; b < nb; b += 32) {
-        int xw[8];
+      for (int b0 = lane; b0 < nb; b0 += 32 * U) {
+        if (!(preloaded && batch == (i64)blockIdx.x && b0 == lane)) load_pass(r0, b0);
 #pragma unroll
-        for (int w = 0; w < 8; ++w) xw[w] = xs[w * nb + b];
-        float dxb = dxs[b];
-        int sxb = sxs[b];
-        uint4 wq[GQ_RB][QW];
-        u16 dw[GQ_RB];
+        for (int u = 0; u < U; ++u) {
+          const int b = b0 + 32 * u;
+          if (b < nb) {
+            int xw[8];
 #pragma unroll
-        for (int r = 0; r < GQ_RB; ++r) {
-          i64 row = r0 + r < n ? r0 + r : n - 1;
-          const uint4* p = qs + (row * nb + b) * QW;
+            for (int w = 0; w < 8; ++w) xw[w] = xs[w * nb + b];
+            const float dxb = dxs[b];
+            const int sxb = sxs[b];
 #pragma unroll
-          for (int h = 0; h < QW; ++h) wq[r][h] = p[h];
-          dw[r] = d[row * nb + b];
-        }
+            for (int r = 0; r < GQ_RB; ++r) {
+              int isum = 0;
+              if (Q4) {
+                uint32_t ws[4] = {wq[u][r][0].x, wq[u][r][0].y, wq[u][r][0].z, wq[u][r][0].w};
 #pragma unroll
-        for (int r = 0; r < GQ_RB; ++r) {
-          int isum = 0;
-          if (Q4) {
-            uint32_t ws[4] = {wq[r][0].x, wq[r][0].y, wq[r][0].z, wq[r][0].w};
+                for (int w = 0; w < 4; ++w) {
+                  int lo = (int)(ws[w] & 0x0f0f0f0fu), hi = (int)((ws[w] >> 4) & 0x0f0f0f0fu);
+                  isum = __dp4a(lo, xw[w], isum);       // elements 4w..4w+3
+                  isum = __dp4a(hi, xw[w + 4], isum);   // elements 16+4w..16+4w+3
+                }
+                isum -= 8 * sxb;  // sum (nib-8)*x = sum nib*x - 8*sum x, all exact integers
+              } else {
+                uint32_t ws[8] = {wq[u][r][0].x, wq[u][r][0].y, wq[u][r][0].z, wq[u][r][0].w,
+                                  wq[u][r][QW - 1].x, wq[u][r][QW - 1].y, wq[u][r][QW - 1].z, wq[u][r][QW - 1].w};
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              int lo = (int)(ws[w] & 0x0f0f0f0fu), hi = (int)((ws[w] >> 4) & 0x0f0f0f0fu);
-              isum = __dp4a(lo, xw[w], isum);       // elements 4w..4w+3
-              isum = __dp4a(hi, xw[w + 4], isum);   // elements 16+4w..16+4w+3
+                for (int w = 0; w < 8; ++w) isum = __dp4a((int)ws[w], xw[w], isum);
+              }
+              float term = fmul(fmul(f16_bits_to_f32(dw[u][r]), dxb), (float)isum);
+              terms[(warp * GQ_RB + r) * nb + b] = term;
             }
-            isum -= 8 * sxb;  // sum (nib-8)*x = sum nib*x - 8*sum x, all exact integers
-          } else {
-            uint32_t ws[8] = {wq[r][0].x, wq[r][0].y, wq[r][0].z, wq[r][0].w,
-                              wq[r][QW - 1].x, wq[r][QW - 1].y, wq[r][QW - 1].z, wq[r][QW - 1].w};
-#pragma unroll
-            for (int w = 0; w < 8; ++w) isum = __dp4a((int)ws[w], xw[w], isum);
           }
-          float term = fmul(fmul(f16_bits_to_f32(dw[r]), dxb), (float)isum);
-          terms[(warp * GQ_RB + r) * nb + b] = term;
         }
       }
     }
@@ -372,7 +392,10 @@ int wkb_gemv_q_contract(const void* qs, const void* d, const void* xq, const flo
   if (sm > 200 * 1024) return (int)cudaErrorInvalidValue;
   i64 blocks = (n + GQ_ROWS - 1) / GQ_ROWS;
   if (blocks > (i64)WKB_SM_COUNT * 8) blocks = (i64)WKB_SM_COUNT * 8;
-  auto kern = q4 ? gemv_q_contract_kernel<true> : gemv_q_contract_kernel<false>;
+  // a grid that fits the machine once keeps 4 blocks per lane in flight (one trip to HBM for a 4096-wide row); a larger one
+  // runs more CTAs per SM on half the registers
+  const bool deep = q4 && blocks <= (i64)WKB_SM_COUNT;
+  auto kern = q4 ? (deep ? gemv_q_contract_kernel<true, 4> : gemv_q_contract_kernel<true, 2>) : gemv_q_contract_kernel<false, 2>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   if (e != cudaSuccess) return (int)e;
   kern<<<(int)blocks, GQ_WARPS * 32, sm, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const int8_t*)xq, dx, sx, y, n, nb);
