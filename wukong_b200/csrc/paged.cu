@@ -635,10 +635,12 @@ __global__ void __launch_bounds__(PA_WARPS * 32, 2) paged_attn_decode_mma_kernel
     const uint32_t p23 = pack2_bf16(exp2f(s4[2] - mn), exp2f(s4[3] - mn));
     // the normaliser sums the same rounded weights the values are multiplied by
     l = l * corr + ((u2f(p01 << 16) + u2f(p01 & 0xffff0000u)) + (u2f(p23 << 16) + u2f(p23 & 0xffff0000u)));
+    if (__any_sync(0xffffffffu, corr != 1.0f)) {         // most tiles do not move the maximum
 #pragma unroll
-    for (int sl = 0; sl < 2; ++sl)
+      for (int sl = 0; sl < 2; ++sl)
 #pragma unroll
-      for (int jj = 0; jj < 8; ++jj) { acc[sl][jj][0] *= corr; acc[sl][jj][1] *= corr; }
+        for (int jj = 0; jj < 8; ++jj) { acc[sl][jj][0] *= corr; acc[sl][jj][1] *= corr; }
+    }
     // ---- values: 8 dims per slab and register pair, two tokens of one dim per B register
 #pragma unroll
     for (int sl = 0; sl < 2; ++sl) {
@@ -813,10 +815,12 @@ __global__ void __launch_bounds__(32) paged_attn_decode_mma_staged_kernel(
     const uint32_t p01 = pack2_bf16(exp2f(s4[0] - mn), exp2f(s4[1] - mn));
     const uint32_t p23 = pack2_bf16(exp2f(s4[2] - mn), exp2f(s4[3] - mn));
     l = l * corr + ((u2f(p01 << 16) + u2f(p01 & 0xffff0000u)) + (u2f(p23 << 16) + u2f(p23 & 0xffff0000u)));
+    if (__any_sync(0xffffffffu, corr != 1.0f)) {         // most tiles do not move the maximum
 #pragma unroll
-    for (int sl = 0; sl < 2; ++sl)
+      for (int sl = 0; sl < 2; ++sl)
 #pragma unroll
-      for (int jj = 0; jj < 8; ++jj) { acc[sl][jj][0] *= corr; acc[sl][jj][1] *= corr; }
+        for (int jj = 0; jj < 8; ++jj) { acc[sl][jj][0] *= corr; acc[sl][jj][1] *= corr; }
+    }
     // ---- values: k positions 2t, 2t+1, 2t+8, 2t+9 hold tokens tokA, tokB, 8 + tokA, 8 + tokB; dims 64 * sl + 8 * gi .. +8
     uint32_t vrow[4], vsw[4];
 #pragma unroll

@@ -369,8 +369,10 @@ __global__ void __launch_bounds__(32) paged_attn_decode_i8_mma_kernel(
     for (int e = 0; e < 4; ++e) pv[e] = p[e] * (vs4[e] * vinv);
     const uint32_t p01 = pack2_f16(pv[0], pv[1]), p23 = pack2_f16(pv[2], pv[3]);
     const uint32_t r01 = pack2_f16(pv[0] - f16_lo(p01), pv[1] - f16_hi(p01)), r23 = pack2_f16(pv[2] - f16_lo(p23), pv[3] - f16_hi(p23));
+    if (__any_sync(0xffffffffu, corr_all != 1.0f)) {      // most tiles move neither the maximum nor the reference scale
 #pragma unroll
-    for (int e = 0; e < 16; ++e) { acc[e][0] *= corr_all; acc[e][1] *= corr_all; }
+      for (int e = 0; e < 16; ++e) { acc[e][0] *= corr_all; acc[e][1] *= corr_all; }
+    }
     // ---- values: k positions 2t, 2t+1, 2t+8, 2t+9 hold tokens tokA, tokB, 8 + tokA, 8 + tokB; the lane supplies dims
     // 16 gi .. +16 (column gi of output block e is dim 16 gi + e)
     const uint4 v0 = lds128(vslot + (uint32_t)tokA * 128u + ((((uint32_t)gi) ^ (uint32_t)(tokA & 7)) << 4));
