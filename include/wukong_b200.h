@@ -268,6 +268,10 @@ int wkb_add_f32(const float* a, const float* b, float* out, int64_t n, void* str
  * milliseconds and then ends by itself: a way to exercise the deadline. */
 int wkb_stream_sync_within(void* stream, int64_t timeout_ms);
 int wkb_device_sleep_ms(int64_t ms, void* stream);
+/* Upload of the live prefix of a step's row vectors (token, position, slot, visible keys, ... stored `pitch_bytes` apart in a
+ * pinned host block and in the device block alike): `height` vectors, `width_bytes` bytes of each, one asynchronous 2-D copy
+ * (the host side of the reference's per-step upload, crates/wukong_codegen_gpu/src/serving.rs:1536-1575). */
+int wkb_upload_rows(void* dst_dev, const void* src_host, int64_t pitch_bytes, int64_t width_bytes, int64_t height, void* stream);
 /* Decode feedback on the device: row_token = next_tok, row_pos += 1, row_ctx += 1 for active rows.  A row already at
  * max_pos (the last position its block-table row covers; < 0: no limit) is parked instead: pos = -1, ctx = 0. */
 int wkb_decode_advance(int* row_token, int* row_pos, int* row_ctx, const int* next_tok, int64_t n, int64_t max_pos, void* stream);

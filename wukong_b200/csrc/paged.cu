@@ -1032,23 +1032,16 @@ static int launch_decode(const float* q, const void* kc, const void* vc, const u
   // one unit per (row, kv head): it writes the row itself (128-bit stores: a bf16 row pitch must be a multiple of 8)
   const bool direct = g.max_chunks == 1 && (out_dtype == 0 || out_row_stride % 8 == 0);
   cudaError_t e;
-  static const int staged_cfg = [] { const char* s = getenv("WKB_PA_STAGED"); return s ? atoi(s) : 21; }();
+  static const int staged_cfg = [] { const char* s = getenv("WKB_PA_STAGED"); return s ? atoi(s) : 1; }();   // 0: the register-path kernel
   int* status = g.page_tokens == 16 && staged_cfg > 0 ? gemm_status_word() : nullptr;
   if (status) {
     // K / V pages staged in shared memory by bulk copies (16-token pages only)
     void* o = direct ? out : (void*)nullptr;
 #define WKB_PA_STAGED(NST_, WARPS_) launch_staged_cfg<HD, G, NST_, WARPS_>(q, kc, vc, bt, row_slot, row_ctx, scratch, o, out_dtype, out_row_stride, g, scale, st, status)
     if constexpr (HD == 64 && G == 1) {
-      switch (staged_cfg) {
-        case 31: e = WKB_PA_STAGED(3, 1); break;
-        case 41: e = WKB_PA_STAGED(4, 1); break;
-        case 61: e = WKB_PA_STAGED(6, 1); break;
-        case 32: e = WKB_PA_STAGED(3, 2); break;
-        case 42: e = WKB_PA_STAGED(4, 2); break;
-        case 24: e = WKB_PA_STAGED(2, 4); break;
-        case 34: e = WKB_PA_STAGED(3, 4); break;
-        default: e = WKB_PA_STAGED(2, 1); break;
-      }
+      // two ring slots and one warp per CTA were the fastest of the shapes tried (2 - 6 slots, 1 / 2 / 4 warps per CTA) on
+      // 512 rows x 12 heads with contexts up to 640
+      e = WKB_PA_STAGED(2, 1);
     } else if constexpr (HD == 64) {
       e = WKB_PA_STAGED(3, 1);
     } else {

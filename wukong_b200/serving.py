@@ -219,8 +219,7 @@ class Engine:
                 hr[6 * R:6 * R + 2 * n_tiles] = tiles.reshape(-1)
                 vectors = 6
         with torch.cuda.stream(self.stream):
-            for v in range(vectors):
-                self.d_rows[v * R:v * R + U].copy_(self.h_rows[v * R:v * R + U], non_blocking=True)
+            check(lib().wkb_upload_rows(self.d_rows.data_ptr(), self.h_rows.data_ptr(), R * 4, U * 4, vectors, self.stream.cuda_stream), "rows")
             self.h2d_bytes += vectors * U * 4
             if n_tiles:
                 self.d_rows[6 * R:6 * R + 2 * n_tiles].copy_(self.h_rows[6 * R:6 * R + 2 * n_tiles], non_blocking=True)
