@@ -365,6 +365,244 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
+
+// ---- CTA-pair kernel: one 256 x 256 tile per pair of CTAs (tcgen05.mma.cta_group::2) ---------------------------------
+// A single CTA's 128 x 256 tile moves 96 KB through shared memory per 64-K step (48 KB written by TMA, 48 KB read by the
+// MMA) for 4 MMAs of 72 ns: more than the shared memory delivers, which held the kernel above at 0.78 of the cuBLAS burst.
+// Here the two CTAs of a cluster share a tile: each loads its own 128 rows of A and its own 128-column half of B (ordinary
+// per-CTA TMA loads of this GPU's memory, no multicast), and one thread of the even CTA issues M = 256 MMAs that run on
+// both SMs, each SM reading its A rows and both halves of B: 64 KB per CTA per step.
+//   * full barriers live in the even CTA: it arms them for the bytes of both CTAs, and the odd CTA's loads complete on
+//     them through their cluster address;
+//   * a stage is released (and a finished accumulator announced) by two tcgen05.commit, one to each CTA's barrier;
+//   * the odd CTA's epilogue warps hand an accumulator buffer back by a remote arrive on the even CTA's barrier;
+//   * tensor memory is allocated and freed by both CTAs together (cta_group::2); the CTAs meet at a cluster barrier after
+//     the barriers are initialised and before either may exit.
+// Every mbarrier wait is bounded like in the kernel above.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_TILE_BYTES = 128 * BK_BYTES;              // a 128-row operand tile of one stage
+constexpr int PAIR_STAGE_BYTES = 2 * PAIR_TILE_BYTES;        // A tile + this CTA's half of B
+constexpr int SMEM_BYTES_PAIR = PAIR_STAGES * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + 1024 + 256;
+constexpr uint32_t IDESC_PAIR = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+// this CTA's shared-memory address -> the same offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load into this CTA's shared memory whose bytes are counted on a barrier given by its cluster address
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+template <int ACT, bool OUT_BF16>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c, i64 ldc, int M, int N,
+                      int K, GemmEpi epi, int* status) {
+  constexpr int STAGES = PAIR_STAGES, BN2 = 256, BM2 = 256;
+  constexpr int NUM_BARS = 2 * STAGES + 4;
+  constexpr uint32_t TMEM_COLS = 2 * BN2;       // two accumulator buffers of 256 columns (this CTA's 128 rows of the tile)
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  float* stage_all = reinterpret_cast<float*>(gen_base + STAGES * PAIR_STAGE_BYTES);
+  const uint32_t bars = base + STAGES * PAIR_STAGE_BYTES + EPI_STAGE_BYTES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + 8 * NUM_BARS);
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();                 // 0: the CTA that issues the MMAs
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int tiles_m = (M + BM2 - 1) / BM2, tiles_n = (N + BN2 - 1) / BN2;
+  const int num_tiles = tiles_m * tiles_n;
+  constexpr int BK = BK_BYTES / 2;
+  const int kiters = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }   // 4 epilogue warps of each CTA
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
+  pdl_wait();
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                                    // both CTAs' barriers exist before anything arrives on them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs): own A rows, own half of B; bytes counted on the even CTA's barrier ----------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += npairs) {
+        const int m0 = (t % tiles_m) * BM2 + (int)rank * 128, n0 = (t / tiles_m) * BN2 + (int)rank * 128;
+        for (int kk = 0; kk < kiters; ++kk, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1)) { atomicExch(status, 1); ok = false; break; }
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * PAIR_STAGE_BYTES);
+          const uint32_t sa = base + s * PAIR_STAGE_BYTES, sb = sa + PAIR_TILE_BYTES;
+          const uint32_t fb = map_to_cta(full_bar(s), 0);
+          tma_load_2d_pair(sa, &map_a, fb, kk * BK, m0);
+          tma_load_2d_pair(sb, &map_b, fb, kk * BK, n0);
+        }
+      }
+      // (a failed wait leaves this CTA's copies to the other roles' own bounded waits: the pair ends through the cluster
+      // barrier below only after every role of both CTAs has stopped)
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += npairs, ++local) {
+        const int buf = local & 1;
+        if (!mbar_wait(tempty_bar(buf), ((local >> 1) & 1) ^ 1)) { atomicExch(status, 4); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN2);
+        for (int kk = 0; kk < kiters; ++kk, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full_bar(s), (it / STAGES) & 1)) { atomicExch(status, 2); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = base + s * PAIR_STAGE_BYTES, sb = sa + PAIR_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK_BYTES / UMMA_K_BYTES; ++k)
+            umma_bf16_pair(tmem_d, make_sdesc(sa + k * UMMA_K_BYTES), make_sdesc(sb + k * UMMA_K_BYTES), IDESC_PAIR, (kk > 0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(empty_bar(s));                       // frees the stage in this CTA ...
+          umma_commit_pair(map_to_cta(empty_bar(s), 1));        // ... and in the other one
+        }
+        if (ok) {
+          umma_commit_pair(tfull_bar(buf));
+          umma_commit_pair(map_to_cta(tfull_bar(buf), 1));
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 2..5 of both CTAs: this CTA's 128 rows of the tile ----------------
+    const int quarter = warp & 3;
+    float* stage = stage_all + (warp - 2) * (32 * 33);
+    int local = 0;
+    bool ok = true;
+    const uint32_t tempty0[2] = {map_to_cta(tempty_bar(0), 0), map_to_cta(tempty_bar(1), 0)};
+    for (int t = pair; t < num_tiles && ok; t += npairs, ++local) {
+      const int buf = local & 1;
+      const int m0 = (t % tiles_m) * BM2 + (int)rank * 128, n0 = (t / tiles_m) * BN2;
+      int good = 1;
+      if (lane == 0) good = mbar_wait(tfull_bar(buf), (local >> 1) & 1) ? 1 : 0;
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { if (lane == 0) atomicExch(status, 3); ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN2; c0 += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN2 + c0);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 == BN2) {
+          // this CTA's part of the accumulator buffer is in registers: hand it back to the MMA warp of the even CTA
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty0[buf]);
+        }
+        // transpose through shared memory so that a lane owns a column and every global access is one coalesced row segment
+        const int col = n0 + c0 + lane;
+        const bool col_ok = col < N;
+        const int row0 = m0 + quarter * 32;
+        const int nrows = min(32, M - row0);   // rows of this warp inside the matrix (may be <= 0)
+        const bool full = nrows == 32;
+        float res[32];
+        if (epi.residual && full && col_ok) {
+          const float* rp = epi.residual + (i64)row0 * epi.ldr + col;
+#pragma unroll
+          for (int rr = 0; rr < 32; ++rr) res[rr] = rp[(i64)rr * epi.ldr];
+        }
+#pragma unroll
+        for (int e = 0; e < 32; ++e) stage[lane * 33 + e] = __uint_as_float(r[e]);
+        __syncwarp();
+        const float bias_v = (col_ok && epi.bias) ? epi.bias[col] : 0.0f;
+        if (col_ok) {
+          if (full) {
+            float vals[32];
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr) vals[rr] = epi_act<ACT, OUT_BF16>(stage[rr * 33 + lane] + bias_v);
+            if (epi.residual) {
+#pragma unroll
+              for (int rr = 0; rr < 32; ++rr) vals[rr] += res[rr];
+            }
+            if (OUT_BF16) {
+              u16* cp = reinterpret_cast<u16*>(c) + (i64)row0 * ldc + col;
+#pragma unroll
+              for (int rr = 0; rr < 32; ++rr) cp[(i64)rr * ldc] = f32_to_bf16_bits(vals[rr]);
+            } else {
+              float* cp = reinterpret_cast<float*>(c) + (i64)row0 * ldc + col;
+#pragma unroll
+              for (int rr = 0; rr < 32; ++rr) cp[(i64)rr * ldc] = vals[rr];
+            }
+          } else {
+#pragma unroll 1
+            for (int rr = 0; rr < nrows; ++rr) {
+              const i64 grow = row0 + rr;
+              float y = epi_act<ACT, OUT_BF16>(stage[rr * 33 + lane] + bias_v);
+              if (epi.residual) y += epi.residual[grow * epi.ldr + col];
+              if (OUT_BF16) reinterpret_cast<u16*>(c)[grow * ldc + col] = f32_to_bf16_bits(y);
+              else reinterpret_cast<float*>(c)[grow * ldc + col] = y;
+            }
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();          // neither CTA leaves while the other may still read its shared memory or signal its barriers
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // 2-D tensor [rows, k] of bf16 (or 1-byte e4m3) with row pitch ld elements; box = [128 bytes of K,
 // box_rows]; 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* ptr, i64 rows, i64 k, i64 ld, int box_rows, bool f8 = false) {
@@ -535,6 +773,44 @@ static int gemm_bf16_nt_impl(const void* a, i64 lda, const void* b, i64 ldb, voi
       {gemm_bf16_tc_kernel<1, false, false, false, true>, gemm_bf16_tc_kernel<1, true, false, false, true>},
       {gemm_bf16_tc_kernel<2, false, false, false, true>, gemm_bf16_tc_kernel<2, true, false, false, true>},
       {gemm_bf16_tc_kernel<3, false, false, false, true>, gemm_bf16_tc_kernel<3, true, false, false, true>}};
+  // Large products: 256 x 256 tiles on CTA pairs, once every pair has at least two of them.
+  const i64 tiles_pair = ((n + 255) / 256) * ((m + 255) / 256);
+  static const bool pair_on = [] { const char* e = getenv("WKB_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+  if (pair_on && tiles_pair >= sm_count() && sm_count() >= 2) {
+    rc = make_map(&mb, b, n, k, ldb, 128);
+    if (rc) return rc;
+    typedef void (*PairFn)(const CUtensorMap, const CUtensorMap, void*, i64, int, int, int, GemmEpi, int*);
+    static const PairFn ptable[4][2] = {{gemm_bf16_pair_kernel<0, false>, gemm_bf16_pair_kernel<0, true>},
+                                        {gemm_bf16_pair_kernel<1, false>, gemm_bf16_pair_kernel<1, true>},
+                                        {gemm_bf16_pair_kernel<2, false>, gemm_bf16_pair_kernel<2, true>},
+                                        {gemm_bf16_pair_kernel<3, false>, gemm_bf16_pair_kernel<3, true>}};
+    PairFn pk = ptable[act][c_bf16 ? 1 : 0];
+    static bool pattr[64][8] = {{false}};
+    int pdev = 0;
+    cudaGetDevice(&pdev);
+    const int pslot = (int)act * 2 + (c_bf16 ? 1 : 0);
+    if (!pattr[pdev & 63][pslot]) {
+      cudaError_t e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_PAIR);
+      if (e != cudaSuccess) return (int)e;
+      pattr[pdev & 63][pslot] = true;
+    }
+    GemmEpi pepi{bias, residual, ldr, (int)act, c_bf16, nullptr};
+    i64 pairs = sm_count() / 2;
+    if (pairs > tiles_pair) pairs = tiles_pair;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES_PAIR;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, pk, ma, mb, c, ldc, (int)m, (int)n, (int)k, pepi, status);
+  }
   // 128 x 256 tiles halve the operand bytes per flop; they pay off once there are at least two waves of them
   const i64 tiles_wide = ((n + BN_WIDE - 1) / BN_WIDE) * ((m + BM - 1) / BM);
   const bool wide = tiles_wide >= 2 * sm_count();
