@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
                                                            i64 rows, int cols, float eps, int nsl, i64 slice_stride, i64 dld) {
   __shared__ float red[32];
   const int nvec = cols >> 2, nwarps = blockDim.x >> 5;
+  pdl_wait();
+  pdl_trigger();
   for (i64 r = blockIdx.x; r < rows; r += gridDim.x) {
     float4* xr = reinterpret_cast<float4*>(x + r * (i64)cols);
     // delta: nsl planes of pitch dld, added in plane order (the K-slice partials of a split GEMM, or one plain matrix)
@@ -95,6 +97,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(float* qkv, i64 row_st
                                                           int page_tokens, int mbps, int* __restrict__ status) {
   const int heads = hq + 2 * hkv, hd = 2 * half;
   const i64 total = rows * heads * half;
+  pdl_wait();
+  pdl_trigger();
   for (i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
     const int j = (int)(idx % half);
     const i64 rh = idx / half;
@@ -180,7 +184,7 @@ static int launch_add_rmsnorm(float* x, const float* delta, int nsl, i64 slice_s
   const i64 per = (nvec + threads - 1) / threads;
   cudaStream_t st = as_stream(stream);
   u16* o = (u16*)out_bf16;
-#define WKB_ARN(NV_) add_rmsnorm_kernel<NV_><<<grid, threads, 0, st>>>(x, delta, gamma, o, rows, (int)cols, eps, nsl, slice_stride, dld)
+#define WKB_ARN(NV_) launch_pdl(add_rmsnorm_kernel<NV_>, grid, threads, 0, st, x, delta, gamma, o, rows, (int)cols, eps, nsl, slice_stride, dld)
   if (per <= 1) WKB_ARN(1);
   else if (per <= 2) WKB_ARN(2);
   else if (per <= 4) WKB_ARN(4);
@@ -221,10 +225,9 @@ int wkb_rope_qk_paged_append(float* qkv, i64 row_stride, const float* inv_freq, 
   const i64 total = rows * (q_heads + 2 * kv_heads) * half;
   i64 grid = (total + 255) / 256;
   if (grid > (i64)WKB_SM_COUNT * 16) grid = (i64)WKB_SM_COUNT * 16;
-  rope_append_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(qkv, row_stride, nullptr, 0, 0, 0, inv_freq, block_table, row_slot, row_pos,
-                                                               (u16*)kcache, (u16*)vcache, rows, (int)q_heads, (int)kv_heads, (int)half,
-                                                               (int)page_tokens, (int)max_blocks_per_seq, gemm_status_word());
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(rope_append_kernel, (int)grid, 256, 0, as_stream(stream), qkv, row_stride, (const float*)nullptr, 0, (i64)0, (i64)0, inv_freq,
+                         block_table, row_slot, row_pos, (u16*)kcache, (u16*)vcache, rows, (int)q_heads, (int)kv_heads, (int)half,
+                         (int)page_tokens, (int)max_blocks_per_seq, gemm_status_word());
 }
 
 int wkb_rope_qk_paged_append_slices(float* q_out, i64 row_stride, const float* slices, i64 nslices, i64 slice_stride, i64 ld,
@@ -238,10 +241,9 @@ int wkb_rope_qk_paged_append_slices(float* q_out, i64 row_stride, const float* s
   const i64 total = rows * (q_heads + 2 * kv_heads) * half;
   i64 grid = (total + 255) / 256;
   if (grid > (i64)WKB_SM_COUNT * 16) grid = (i64)WKB_SM_COUNT * 16;
-  rope_append_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(q_out, row_stride, slices, (int)nslices, slice_stride, ld, inv_freq, block_table,
-                                                               row_slot, row_pos, (u16*)kcache, (u16*)vcache, rows, (int)q_heads,
-                                                               (int)kv_heads, (int)half, (int)page_tokens, (int)max_blocks_per_seq, gemm_status_word());
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(rope_append_kernel, (int)grid, 256, 0, as_stream(stream), q_out, row_stride, slices, (int)nslices, slice_stride, ld, inv_freq,
+                         block_table, row_slot, row_pos, (u16*)kcache, (u16*)vcache, rows, (int)q_heads, (int)kv_heads, (int)half,
+                         (int)page_tokens, (int)max_blocks_per_seq, gemm_status_word());
 }
 
 int wkb_argmax_pack(const float* logits, i64 ld, const int* idx_local, i64 col_offset, i64 rows, int* pairs, void* stream) {

@@ -53,6 +53,10 @@ __global__ void __launch_bounds__(1024) tp_reduce_add_rmsnorm_kernel(TpPeers pee
                                                                     int cols, float eps, int* status, unsigned long long wait_ns) {
   __shared__ float red[32];
   __shared__ int s_ok;
+  // a programmatic dependent of the GEMM that writes this rank's partial: nothing is read or published before that kernel
+  // has completed
+  pdl_wait();
+  pdl_trigger();
   const uint32_t seq = (*step_ptr) * (uint32_t)phases_per_step + (uint32_t)phase + 1u;
   // slot [rank] of a rank's own flag row is its "gave up" mark
   const bool dead = ld_acquire_sys(peers.flags[rank] + rank) == TP_POISON;
@@ -190,7 +194,7 @@ int wkb_tp_reduce_add_rmsnorm(const void* const* parts, void* const* flags, i64 
   const int threads = (int)(((nvec < 1024 ? nvec : 1024) + 31) / 32 * 32);
   const i64 per = (nvec + threads - 1) / threads;
   cudaStream_t st = as_stream(stream);
-#define WKB_TP_LAUNCH(NV_) tp_reduce_add_rmsnorm_kernel<NV_><<<grid, threads, 0, st>>>(peers, (int)rank, (int)world, (const uint32_t*)step_ptr, \
+#define WKB_TP_LAUNCH(NV_) launch_pdl(tp_reduce_add_rmsnorm_kernel<NV_>, grid, threads, 0, st, peers, (int)rank, (int)world, (const uint32_t*)step_ptr, \
     (int)phase, (int)phases_per_step, x, gamma_or_null, (u16*)out_bf16, (int)rows, (int)cols, eps, status, g_tp_wait_ns)
   if (per <= 1) WKB_TP_LAUNCH(1);
   else if (per <= 2) WKB_TP_LAUNCH(2);
