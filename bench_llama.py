@@ -120,9 +120,12 @@ def _status_over_ranks(D):
 
 def check_fused_reduce_equals_nccl(D, cfg_full, weights, note):
     """Before anything is timed on several ranks: two layers of the stack at full width, three decode steps, once
-    with NCCL all-reduces and once with the fused peer-memory reduce + add + RMSNorm kernel.  Tokens must be equal
-    and the residual streams must agree (bit for bit on two ranks, where each sum has two terms; to fp32
-    re-association otherwise).  Raises on a mismatch."""
+    through NCCL and once with the fused peer-memory reduce + add + RMSNorm kernel.  Tokens and residual streams must be
+    equal bit for bit.  The fused kernel adds the ranks' partials in rank order; NCCL's all-reduce adds in an order of its
+    own, which gives the same bits only for two terms, so on more than two ranks the NCCL side of this check gathers the
+    partials (all_gather) and adds them in rank order too.  (Against the plain all-reduce the streams drift like any two
+    bf16 evaluations of the stack: 2.4e-4 of the largest element after two layers on 8 ranks.)  Returns the largest row difference
+    over row rms (0.0); raises on a mismatch."""
     import torch
     import torch.distributed as dist
     from wukong_b200.llama import LlamaConfig, LlamaDecodeModel, PeerReduce
@@ -134,8 +137,19 @@ def check_fused_reduce_equals_nccl(D, cfg_full, weights, note):
         layers, embed, norm_f, lm_head = weights.layers[:2], weights.embed, weights.norm_f, weights.lm_head
     Bc, mbps = 16, 4
 
+    def sum_in_rank_order(t):
+        if D.world == 2:
+            dist.all_reduce(t)
+            return
+        parts = torch.empty((D.world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(parts, t.contiguous())
+        acc = parts[0].clone()
+        for r in range(1, D.world):
+            acc += parts[r]
+        t.copy_(acc)
+
     def make(peer):
-        m = LlamaDecodeModel(cfg, TwoLayers, D.rank, D.world, Bc, Bc * mbps, mbps, PAGE, device, lambda t: dist.all_reduce(t),
+        m = LlamaDecodeModel(cfg, TwoLayers, D.rank, D.world, Bc, Bc * mbps, mbps, PAGE, device, sum_in_rank_order,
                              lambda a, b: dist.all_gather_into_tensor(b, a), peer)
         g = torch.Generator(device=device)
         g.manual_seed(5 + D.rank)
@@ -149,6 +163,7 @@ def check_fused_reduce_equals_nccl(D, cfg_full, weights, note):
 
     peer = PeerReduce(D.rank, D.world, Bc, cfg.d_model, device)
     ma, mb = make(None), make(peer)
+    worst = 0.0
     _barrier(D)                            # every rank's buffers and mappings exist before the first peer kernel starts
     for _ in range(3):
         ta = ma.forward(Bc).clone()
@@ -160,13 +175,15 @@ def check_fused_reduce_equals_nccl(D, cfg_full, weights, note):
             raise RuntimeError("a kernel reported an expired wait during the fused-reduce check")
         if not torch.equal(ta, tb):
             raise RuntimeError("tokens differ between the NCCL and the fused peer-memory path")
-        scale = ma.x.abs().max().item()
-        diff = (ma.x - mb.x).abs().max().item()
-        if diff > (0.0 if D.world == 2 else 1e-5 * scale):
-            raise RuntimeError("residual streams differ between the NCCL and the fused path: %g (scale %g)" % (diff, scale))
+        xa, xb = ma.x[:Bc].float(), mb.x[:Bc].float()
+        rel = ((xa - xb).pow(2).mean(1).sqrt() / xa.pow(2).mean(1).sqrt().clamp_min(1e-30)).max().item()
+        worst = max(worst, rel)
+        if rel > 0.0 or not torch.equal(ma.x[:Bc], mb.x[:Bc]):
+            raise RuntimeError("residual streams differ between the NCCL and the fused path: %g of a row's rms" % rel)
     _barrier(D)
     peer.close()
     del ma, mb, peer
+    return worst
     torch.cuda.empty_cache()
     note("fused peer-memory reduce == NCCL all-reduce path on %d ranks (2 layers, 3 steps)" % D.world)
 
@@ -341,7 +358,7 @@ def measure_both(args, D, clocks, note):
     res = {"metric": B.METRIC, "unit": B.UNIT, "scaling": "strong", "n_gpus": D.world,
            "config": llama_config_dict(cfg, D.world, BATCH, CTX0)}
     if D.world > 1:
-        check_fused_reduce_equals_nccl(D, cfg, weights, note)
+        res["fused_vs_nccl_row_rms_diff"] = check_fused_reduce_equals_nccl(D, cfg, weights, note)
         res["fused_equals_nccl"] = True
     r = measure(args, D, clocks, note, False, cfg, weights)
     res.update({"value": r["value"], "ms_per_step": r["ms_per_step"], "e2e_value": r["e2e_value"], "roofline": r["roofline"],
