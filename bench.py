@@ -32,7 +32,7 @@ PROMPT_LO, PROMPT_HI = 32, 512
 GEN_NOMINAL = 128
 PAGE = 16
 N_POS = 1024                   # learned positions of the GPT-2 shape: no sequence may grow past this
-CPU_SAMPLE_SEQS = 16           # the one CPU sample definition: a step = one decode step of 16 of the workload's sequences
+CPU_SAMPLE_SEQS = 64           # the one CPU sample definition: a step = one decode step of 64 of the workload's sequences, run as one batch
 METRIC, UNIT = "decode_tokens_per_s", "tok/s"
 
 
@@ -141,10 +141,12 @@ class ClockSampler:
 # CPU port of the reference kernels (the oracle), timed on the host cores
 # ------------------------------------------------------------------------------------------------
 def cpu_decode_tok_s(weights, cfg, steps, warmup, threads):
-    """Decode steps of CPU_SAMPLE_SEQS sequences on the CPU oracle model; contexts drawn from the workload's
-    distribution at mid-generation, KV caches pre-filled with seeded random bf16 values (only the decode step is
-    timed).  Returns (tok/s, seconds, description).  Both the `cpu_baseline` key of this library's line and the
-    reference arm time exactly this sample."""
+    """Decode steps of CPU_SAMPLE_SEQS sequences on the CPU oracle model, batched the way the reference's CPU path runs
+    them: every GEMM over all the sequences' rows at once (weights read once per call), dense fp32 KV caches, one call to
+    the batched KV-cache attention kernel per layer.  Contexts are drawn from the workload's distribution at
+    mid-generation, the caches pre-filled with seeded random bf16 values (only the decode step is timed).  Returns
+    (tok/s, seconds, description).  Both the `cpu_baseline` key of this library's line and the reference arm time exactly
+    this sample."""
     import numpy as np
     from oracle import binding as orc
     from oracle.gpt2_model import OracleGPT2
@@ -153,23 +155,22 @@ def cpu_decode_tok_s(weights, cfg, steps, warmup, threads):
     model = OracleGPT2(cfg, weights, orc)
     rng = np.random.default_rng(1234)
     ctx = rng.integers(PROMPT_LO, PROMPT_HI + 1, seqs) + GEN_NOMINAL // 2
-    caches = [model.new_cache(int(c) + steps + warmup + 2) for c in ctx]
-    for kc, vc in caches:
-        for l in range(cfg.n_layer):
-            kc[l][:] = orc.to_bf16_bits(rng.standard_normal(kc[l].shape, dtype=np.float32))
-            vc[l][:] = orc.to_bf16_bits(rng.standard_normal(vc[l].shape, dtype=np.float32))
+    cap = (int(ctx.max()) + steps + warmup + 2 + 15) // 16 * 16
+    K = [orc.from_bf16_bits(orc.to_bf16_bits(rng.standard_normal((seqs, cap, cfg.d_model), dtype=np.float32))).reshape(seqs, cap, cfg.d_model)
+         for _ in range(cfg.n_layer)]
+    V = [orc.from_bf16_bits(orc.to_bf16_bits(rng.standard_normal((seqs, cap, cfg.d_model), dtype=np.float32))).reshape(seqs, cap, cfg.d_model)
+         for _ in range(cfg.n_layer)]
     toks = rng.integers(0, cfg.vocab, seqs).tolist()
     pos = [int(c) for c in ctx]
-    kcs, vcs = [c[0] for c in caches], [c[1] for c in caches]
     t0 = None
     for it in range(warmup + steps):
         if it == warmup:
             t0 = time.perf_counter()
-        nxt, _ = model.step(toks, pos, kcs, vcs)
+        nxt, _ = model.step_dense_cache(toks, pos, K, V)
         toks = [int(t) for t in nxt]
         pos = [p + 1 for p in pos]
     dt = time.perf_counter() - t0
-    desc = "%d of the workload's sequences x %d decode steps, ctx uniform[%d,%d]+%d, random bf16 KV" % (
+    desc = "%d of the workload's sequences x %d decode steps as one batch, ctx uniform[%d,%d]+%d, random bf16-valued fp32 KV" % (
         seqs, steps, PROMPT_LO, PROMPT_HI, GEN_NOMINAL // 2)
     return seqs * steps / dt, dt, desc
 
@@ -184,7 +185,7 @@ def run_reference(args):
     cfg = GPT2Config()
     weights = synth_weights(cfg, 0)
     threads = os.cpu_count() or 1
-    steps = min(args.steps, 64)             # about 0.2 s per 16-sequence step: the run stays within a few minutes
+    steps = min(args.steps, 64)             # about 0.2 s per 64-sequence step: the run stays within a few minutes
     tok_s, dt, desc = cpu_decode_tok_s(weights, cfg, steps, min(args.warmup, 3), threads)
     n_gpus = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     line = {

@@ -4,6 +4,9 @@
 // :141-180) and gemv_half.rs (`elem_scalar` :73-110, checked entries :440-529).
 #include "oracle_internal.h"
 #include <vector>
+#if defined(__AVX2__) && defined(__FMA__)
+#include <immintrin.h>
+#endif
 #include <cmath>
 
 namespace wko {
@@ -52,10 +55,14 @@ static void gemm_contract(LoadA la, LoadB lb, float* c, size_t m, size_t k, size
   });
 }
 
-// The NT form with B read in its storage type, eight output columns in flight.  Each (i, j) still runs
-// exactly the chain of `gemm_contract` (ascending p per K block, blocks folded in order), so the
-// bits are the same; the eight independent chains only hide the FMA latency, which is what makes
-// the timed CPU baseline a fair port rather than a latency-bound loop.
+// The NT form with B read in its storage type.  Each (i, j) still runs exactly the chain of `gemm_contract` (ascending p
+// per K block from +0.0, blocks folded in order, one fused multiply-add per step), so the bits are the same; what changes
+// is which chains run side by side.  The eight lanes of a vector are eight ROWS of A (A is repacked once per call as
+// [p][row panel][8 rows]); an element of B is widened, broadcast and multiplied into every row of the panel, so each weight
+// is read once per call whatever the number of activation rows -- the traffic pattern of a register-blocked AVX2
+// microkernel, which is what makes the timed CPU baseline a fair port of the reference's CPU path rather than a loop that
+// streams the weight matrix once per activation row.  Four columns x two panels = eight independent chains per thread
+// hide the FMA latency.
 template <typename TB>
 static inline float widen_b(TB v);
 template <> inline float widen_b<float>(float v) { return v; }
@@ -64,34 +71,117 @@ struct F16B { u16 b; };
 template <> inline float widen_b<Bf16B>(Bf16B v) { return bf16_bits_to_f32(v.b); }
 template <> inline float widen_b<F16B>(F16B v) { return f16_bits_to_f32(v.b); }
 
+#if defined(__AVX2__) && defined(__FMA__)
+// eight consecutive elements of B, widened exactly (bf16: the bits moved to the top half; f16: vcvtph2ps)
+template <typename TB>
+static inline __m256 widen8(const TB* p);
+template <> inline __m256 widen8<float>(const float* p) { return _mm256_loadu_ps(p); }
+template <> inline __m256 widen8<Bf16B>(const Bf16B* p) {
+  return _mm256_castsi256_ps(_mm256_slli_epi32(_mm256_cvtepu16_epi32(_mm_loadu_si128(reinterpret_cast<const __m128i*>(p))), 16));
+}
+template <> inline __m256 widen8<F16B>(const F16B* p) { return _mm256_cvtph_ps(_mm_loadu_si128(reinterpret_cast<const __m128i*>(p))); }
+#endif
+
 template <typename TB>
 static void gemm_nt_fast(const float* a, const TB* b, float* c, size_t M, size_t K, size_t N, float beta,
                          const Epi* epi) {
   const size_t kcap = (size_t)select_kc((i64)K);
-  const size_t ngroups = (N + 7) / 8;
-  par_for((i64)(M * ngroups), 8, [&](i64 lo, i64 hi) {
+  constexpr size_t JB = 4, PB = 2;                 // columns and row panels in flight
+  const size_t panels = (M + 7) / 8;
+  // A^T in panels of 8 rows: at[(p * panels + panel) * 8 + lane] = a[panel * 8 + lane][p]; rows past M are zero
+  std::vector<float> at(K * panels * 8, 0.0f);
+  par_for((i64)panels, 1, [&](i64 lo, i64 hi) {
+    for (i64 pn = lo; pn < hi; ++pn)
+      for (size_t lane = 0; lane < 8; ++lane) {
+        const size_t i = (size_t)pn * 8 + lane;
+        if (i >= M) break;
+        const float* ar = a + i * K;
+        for (size_t p = 0; p < K; ++p) at[(p * panels + (size_t)pn) * 8 + lane] = ar[p];
+      }
+  });
+  const size_t jblocks = (N + JB - 1) / JB;
+  par_for((i64)jblocks, 4, [&](i64 lo, i64 hi) {
     for (i64 u = lo; u < hi; ++u) {
-      size_t i = (size_t)u / ngroups, j0 = ((size_t)u % ngroups) * 8;
-      size_t nj = N - j0 < 8 ? N - j0 : 8;
-      const float* ar = a + i * K;
-      const TB* br[8];
-      for (size_t jj = 0; jj < 8; ++jj) br[jj] = b + (j0 + (jj < nj ? jj : 0)) * K;
-      float cv[8];
-      for (size_t jj = 0; jj < 8; ++jj) cv[jj] = jj < nj ? c[i * N + j0 + jj] : 0.0f;
-      for (size_t pc = 0; pc < K; pc += kcap) {
-        size_t kc = K - pc < kcap ? K - pc : kcap;
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (size_t p = pc; p < pc + kc; ++p) {
-          float av = ar[p];
-          for (size_t jj = 0; jj < 8; ++jj) acc[jj] = fmaf(av, widen_b<TB>(br[jj][p]), acc[jj]);
-        }
-        float beta_eff = pc == 0 ? beta : 1.0f;
-        for (size_t jj = 0; jj < 8; ++jj) {
-          float val = beta_eff == 0.0f ? acc[jj] : cv[jj] + acc[jj];
-          cv[jj] = (pc + kc == K && epi) ? epi_apply(*epi, val, j0 + jj < N ? j0 + jj : 0) : val;
+      const size_t j0 = (size_t)u * JB, nj = N - j0 < JB ? N - j0 : JB;
+      const TB* br[JB];
+      for (size_t jj = 0; jj < JB; ++jj) br[jj] = b + (j0 + (jj < nj ? jj : 0)) * K;
+      for (size_t pn0 = 0; pn0 < panels; pn0 += PB) {
+        const size_t np = panels - pn0 < PB ? panels - pn0 : PB;
+        for (size_t pc = 0; pc < K; pc += kcap) {
+          const size_t kc = K - pc < kcap ? K - pc : kcap;
+          float acc[JB][PB][8];
+#if defined(__AVX2__) && defined(__FMA__)
+          __m256 v[JB][PB];
+#pragma GCC unroll 4
+          for (size_t jj = 0; jj < JB; ++jj) {
+            v[jj][0] = _mm256_setzero_ps();
+            v[jj][1] = _mm256_setzero_ps();
+          }
+          // eight consecutive K elements of a column are widened together and broadcast lane by lane from the register
+          // (one shuffle per element instead of a scalar widen + move + broadcast); the chain of every (i, j) still takes
+          // its products in ascending p
+          size_t p = pc;
+          for (; p + 8 <= pc + kc; p += 8) {
+            __m256 bw[JB];
+#pragma GCC unroll 4
+            for (size_t jj = 0; jj < JB; ++jj) bw[jj] = widen8<TB>(br[jj] + p);
+#pragma GCC unroll 8
+            for (size_t e = 0; e < 8; ++e) {
+              const float* ap = at.data() + ((p + e) * panels + pn0) * 8;
+              const __m256 a0 = _mm256_loadu_ps(ap);
+              const __m256 a1 = np > 1 ? _mm256_loadu_ps(ap + 8) : _mm256_setzero_ps();
+              const __m256i idx = _mm256_set1_epi32((int)e);
+#pragma GCC unroll 4
+              for (size_t jj = 0; jj < JB; ++jj) {
+                const __m256 bv = _mm256_permutevar8x32_ps(bw[jj], idx);
+                v[jj][0] = _mm256_fmadd_ps(a0, bv, v[jj][0]);      // one fused multiply-add per lane: fmaf(a, b, acc)
+                v[jj][1] = _mm256_fmadd_ps(a1, bv, v[jj][1]);
+              }
+            }
+          }
+          for (; p < pc + kc; ++p) {
+            const float* ap = at.data() + (p * panels + pn0) * 8;
+            const __m256 a0 = _mm256_loadu_ps(ap);
+            const __m256 a1 = np > 1 ? _mm256_loadu_ps(ap + 8) : _mm256_setzero_ps();
+#pragma GCC unroll 4
+            for (size_t jj = 0; jj < JB; ++jj) {
+              const __m256 bv = _mm256_set1_ps(widen_b<TB>(br[jj][p]));
+              v[jj][0] = _mm256_fmadd_ps(a0, bv, v[jj][0]);
+              v[jj][1] = _mm256_fmadd_ps(a1, bv, v[jj][1]);
+            }
+          }
+#pragma GCC unroll 4
+          for (size_t jj = 0; jj < JB; ++jj) {
+            _mm256_storeu_ps(acc[jj][0], v[jj][0]);
+            _mm256_storeu_ps(acc[jj][1], v[jj][1]);
+          }
+#else
+          for (size_t jj = 0; jj < JB; ++jj)
+            for (size_t q = 0; q < PB; ++q)
+              for (size_t l = 0; l < 8; ++l) acc[jj][q][l] = 0.0f;
+          for (size_t p = pc; p < pc + kc; ++p) {
+            const float* ap = at.data() + (p * panels + pn0) * 8;
+            for (size_t jj = 0; jj < JB; ++jj) {
+              const float bv = widen_b<TB>(br[jj][p]);
+              for (size_t q = 0; q < np; ++q)
+                for (size_t l = 0; l < 8; ++l) acc[jj][q][l] = fmaf(ap[q * 8 + l], bv, acc[jj][q][l]);
+            }
+          }
+#endif
+          const float beta_eff = pc == 0 ? beta : 1.0f;
+          const bool last = pc + kc == K;
+          for (size_t q = 0; q < np; ++q)
+            for (size_t l = 0; l < 8; ++l) {
+              const size_t i = (pn0 + q) * 8 + l;
+              if (i >= M) break;
+              for (size_t jj = 0; jj < nj; ++jj) {
+                float* cij = c + i * N + j0 + jj;
+                const float val = beta_eff == 0.0f ? acc[jj][q][l] : *cij + acc[jj][q][l];
+                *cij = (last && epi) ? epi_apply(*epi, val, j0 + jj) : val;
+              }
+            }
         }
       }
-      for (size_t jj = 0; jj < nj; ++jj) c[i * N + j0 + jj] = cv[jj];
     }
   });
 }

@@ -50,6 +50,37 @@ class OracleGPT2:
         logits = orc.sgemm_half_nt(hf, w["wte"], S, d, cfg.vocab)
         return orc.rowargmax(logits), logits
 
+    def step_dense_cache(self, toks, poss, K, V, want_logits=True):
+        """The same decode step over dense fp32 caches, the way the reference's CPU path keeps them: K[layer] / V[layer] are
+        [S, capacity, d_model] fp32 arrays holding the (bf16-rounded) rows of positions < poss[s]; attention is ONE call
+        per layer to the reference's batched KV-cache kernel (wko_attention_kv_batch_f32: attention_kv.rs entries
+        :1157-1250) instead of one f64 model evaluation per sequence.  This is the form the timed CPU baseline runs."""
+        cfg, w, orc = self.cfg, self.w, self.orc
+        d, H, hd, S = cfg.d_model, cfg.n_head, cfg.head_dim, len(toks)
+        pos = np.asarray(poss, np.int64)
+        rows = np.arange(S)
+        cap = K[0].shape[1]
+        x = (orc.from_bf16_bits(w["wte"][np.asarray(toks)]) + orc.from_bf16_bits(w["wpe"][pos])).astype(np.float32)
+        for li, lw in enumerate(w["layers"]):
+            h = self._round(orc.norm_affine(x, lw["ln1_g"], lw["ln1_b"], 1, cfg.eps))
+            qkv = orc.sgemm_half_nt(h, lw["w_qkv"], S, d, 3 * d, bias=lw["b_qkv"], act=0)
+            K[li][rows, pos] = orc.from_bf16_bits(self._round(qkv[:, d:2 * d]))
+            V[li][rows, pos] = orc.from_bf16_bits(self._round(qkv[:, 2 * d:]))
+            st, att = orc.attention_kv_batch(np.ascontiguousarray(qkv[:, :d]), K[li], V[li], pos + 1, pos, S, 1, cap, H, H, hd,
+                                             1.0 / math.sqrt(hd), True)
+            if st != 0:
+                raise RuntimeError("attention_kv_batch refused its plan: %d" % st)
+            a = self._round(att.reshape(S, d))
+            x = (orc.sgemm_half_nt(a, lw["w_o"], S, d, d, bias=lw["b_o"], act=0) + x).astype(np.float32)
+            h2 = self._round(orc.norm_affine(x, lw["ln2_g"], lw["ln2_b"], 1, cfg.eps))
+            ff = self._round(orc.sgemm_half_nt(h2, lw["w_fc"], S, d, cfg.d_ff, bias=lw["b_fc"], act=2))
+            x = (orc.sgemm_half_nt(ff, lw["w_proj"], S, cfg.d_ff, d, bias=lw["b_proj"], act=0) + x).astype(np.float32)
+        if not want_logits:
+            return None, None
+        hf = self._round(orc.norm_affine(x, w["lnf_g"], w["lnf_b"], 1, cfg.eps))
+        logits = orc.sgemm_half_nt(hf, w["wte"], S, d, cfg.vocab)
+        return orc.rowargmax(logits), logits
+
     def new_cache(self, capacity):
         cap = (capacity + 15) // 16 * 16
         z = lambda: [np.zeros((cap, self.cfg.d_model), np.uint16) for _ in range(self.cfg.n_layer)]

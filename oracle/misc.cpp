@@ -7,6 +7,8 @@
 #include <thread>
 #include <vector>
 #include <atomic>
+#include <condition_variable>
+#include <mutex>
 #include <immintrin.h>
 
 namespace wko {
@@ -17,25 +19,87 @@ float f16_bits_to_f32(u16 b) { return _cvtsh_ss(b); }
 
 static std::atomic<int> g_threads{1};
 
+// Persistent worker pool: the oracle's kernels are called a hundred times per model step, and starting a fresh set of
+// std::threads for each call cost more than the kernels themselves once they were vectorised.  Workers sleep on a
+// condition variable between calls; chunks are handed out through an atomic counter; the caller works too and returns
+// when every worker has checked in.  A call that finds the pool busy (another host thread, or a nested call) runs serially.
+namespace {
+struct Pool {
+  std::mutex m;
+  std::condition_variable cv_start, cv_done;
+  std::vector<std::thread> workers;
+  const std::function<void(i64, i64)>* body = nullptr;
+  std::atomic<i64> next{0};
+  i64 nchunks = 0, chunk = 0, n = 0;
+  unsigned long long gen = 0;
+  int active = 0;
+  bool stop = false;
+  std::atomic_flag busy = ATOMIC_FLAG_INIT;
+
+  void run_chunks() {
+    for (;;) {
+      const i64 c = next.fetch_add(1);
+      if (c >= nchunks) return;
+      const i64 lo = c * chunk, hi = lo + chunk < n ? lo + chunk : n;
+      (*body)(lo, hi);
+    }
+  }
+  void worker_main() {
+    unsigned long long seen = 0;
+    std::unique_lock<std::mutex> lk(m);
+    for (;;) {
+      cv_start.wait(lk, [&] { return stop || gen != seen; });
+      if (stop) return;
+      seen = gen;
+      lk.unlock();
+      run_chunks();
+      lk.lock();
+      if (--active == 0) cv_done.notify_one();
+    }
+  }
+  void resize(int nworkers) {
+    if ((int)workers.size() == nworkers) return;
+    shutdown();
+    stop = false;
+    for (int t = 0; t < nworkers; ++t) workers.emplace_back([this] { worker_main(); });
+  }
+  void shutdown() {
+    {
+      std::lock_guard<std::mutex> lk(m);
+      stop = true;
+    }
+    cv_start.notify_all();
+    for (auto& t : workers) t.join();
+    workers.clear();
+  }
+  ~Pool() { shutdown(); }
+};
+Pool g_pool;
+}  // namespace
+
 void par_for(i64 n, i64 chunk, const std::function<void(i64, i64)>& body) {
   int nt = g_threads.load();
   if (chunk < 1) chunk = 1;
   i64 nchunks = (n + chunk - 1) / chunk;
   if (nt <= 1 || nchunks <= 1) { if (n > 0) body(0, n); return; }
-  if ((i64)nt > nchunks) nt = (int)nchunks;
-  std::atomic<i64> next{0};
-  auto worker = [&]() {
-    for (;;) {
-      i64 c = next.fetch_add(1);
-      if (c >= nchunks) return;
-      i64 lo = c * chunk, hi = lo + chunk < n ? lo + chunk : n;
-      body(lo, hi);
-    }
-  };
-  std::vector<std::thread> th;
-  for (int t = 1; t < nt; ++t) th.emplace_back(worker);
-  worker();
-  for (auto& t : th) t.join();
+  if (g_pool.busy.test_and_set(std::memory_order_acquire)) { body(0, n); return; }
+  g_pool.resize(nt - 1);
+  {
+    std::lock_guard<std::mutex> lk(g_pool.m);
+    g_pool.body = &body;
+    g_pool.n = n; g_pool.chunk = chunk; g_pool.nchunks = nchunks;
+    g_pool.next.store(0);
+    g_pool.active = (int)g_pool.workers.size();
+    ++g_pool.gen;
+  }
+  g_pool.cv_start.notify_all();
+  g_pool.run_chunks();
+  {
+    std::unique_lock<std::mutex> lk(g_pool.m);
+    g_pool.cv_done.wait(lk, [&] { return g_pool.active == 0; });
+    g_pool.body = nullptr;
+  }
+  g_pool.busy.clear(std::memory_order_release);
 }
 
 // fp8.rs:66-164: OCP E4M3FN (bias 7, saturating, NaN S.1111.111) and E5M2 (bias 15, IEEE inf).
