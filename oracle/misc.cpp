@@ -7,6 +7,7 @@
 #include <thread>
 #include <vector>
 #include <atomic>
+#include <unistd.h>
 #include <condition_variable>
 #include <mutex>
 #include <immintrin.h>
@@ -74,7 +75,25 @@ struct Pool {
   }
   ~Pool() { shutdown(); }
 };
-Pool g_pool;
+// The pool of this process.  A forked child inherits the object but none of its threads (and possibly a locked mutex):
+// it is told apart by its pid and starts a pool of its own, leaving the inherited one alone.
+Pool* g_pool_ptr = nullptr;
+pid_t g_pool_pid = 0;
+std::mutex g_pool_guard;
+Pool& pool() {
+  std::lock_guard<std::mutex> lk(g_pool_guard);
+  const pid_t me = getpid();
+  if (!g_pool_ptr || g_pool_pid != me) {
+    g_pool_ptr = new Pool();      // an inherited pool is leaked on purpose: its threads do not exist here
+    g_pool_pid = me;
+  }
+  return *g_pool_ptr;
+}
+struct PoolAtExit {
+  ~PoolAtExit() {
+    if (g_pool_ptr && g_pool_pid == getpid()) g_pool_ptr->shutdown();
+  }
+} g_pool_at_exit;
 }  // namespace
 
 void par_for(i64 n, i64 chunk, const std::function<void(i64, i64)>& body) {
@@ -82,6 +101,7 @@ void par_for(i64 n, i64 chunk, const std::function<void(i64, i64)>& body) {
   if (chunk < 1) chunk = 1;
   i64 nchunks = (n + chunk - 1) / chunk;
   if (nt <= 1 || nchunks <= 1) { if (n > 0) body(0, n); return; }
+  Pool& g_pool = pool();
   if (g_pool.busy.test_and_set(std::memory_order_acquire)) { body(0, n); return; }
   g_pool.resize(nt - 1);
   {
