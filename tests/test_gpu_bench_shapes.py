@@ -254,3 +254,27 @@ def test_dense_gemm_pair_tiles_ragged_edges_and_epilogues(env, orc):
     cs = dev.gemm_bf16_nt(a[:640], b, bias=bias, act=2, out_dtype=torch.bfloat16)
     assert torch.equal(cb[:640].view(torch.int16), cs.view(torch.int16))
     assert dev.gemm_status() == 0
+
+
+def test_paged_attention_int8_microsuite_shape_vs_f64_oracle(env, orc):
+    """The int8-cache case of the micro-suite (batch 64, contexts uniform in [128, 4096], 32 query / 8 KV heads of dim
+    128, int8 values with one f32 scale per token and KV head) on a pool just large enough for its pages: every output
+    within 1e-4 of the f64 attention over the dequantized cache (int8 * scale is exact in f32), the bar of the small
+    int8 test."""
+    torch, dev = env
+    from oracle import kv_int8 as Q
+    from wukong_b200.microbench import build_paged_attn_int8_case
+    c = build_paged_attn_int8_case(seed=0, torch_seed=4321, pool=8704)
+    B, H, HKV, D, page, mbps, kv = c["B"], c["H"], c["HKV"], c["D"], c["page"], c["mbps"], c["kv"]
+    assert c["pages_used"] <= c["pool"]
+    out = torch.empty(B, H * D, dtype=torch.float32, device="cuda")
+    scratch = dev.paged_attn_scratch(B, H, D, c["max_ctx"])
+    dev.paged_attn_decode_int8(c["q"], H * D, kv, 0, c["bt"], c["row_slot"], c["row_ctx"], out, B, H, mbps, c["max_ctx"], c["scale"], scratch)
+    got = out.cpu().numpy()
+    kf = Q.dequantize(kv.k[0].cpu().numpy(), kv.k_scale[0].cpu().numpy())
+    vf = Q.dequantize(kv.v[0].cpu().numpy(), kv.v_scale[0].cpu().numpy())
+    q = c["q"].cpu().numpy()
+    ref = orc.paged_attn_decode(q, kf, vf, 0, c["table"], c["ctx"], B, H, HKV, D, page, mbps, c["scale"], layout=1)
+    mag = orc.paged_attn_decode(q, kf, np.abs(vf), 0, c["table"], c["ctx"], B, H, HKV, D, page, mbps, c["scale"], layout=1)
+    assert np.all(np.abs(got - ref) <= 1e-4 * mag + 1e-6), float((np.abs(got - ref) / (mag + 1e-9)).max())
+    assert dev.gemm_status() == 0

@@ -211,10 +211,12 @@ def case_paged_attn(hbm, tf, src):
             "note": "555 MB of KV per launch exceeds L2", "peak_source": "of " + src}
 
 
-def case_paged_attn_int8(hbm, tf, src):
-    """The paged_attn_decode case over the int8 cache (same batch, heads and context draw)."""
-    rng = np.random.default_rng(0)
-    B, H, HKV, D, page, pool = 64, 32, 8, 128, 16, 65536
+def build_paged_attn_int8_case(seed=0, torch_seed=None, pool=65536):
+    """The paged_attn_decode case over the int8 cache: the same batch, heads and context draw as the bf16 case, int8 values
+    uniform in [-127, 127] with f32 scales uniform in [0.005, 0.03] per (token, KV head), pages a seeded permutation of a
+    `pool`-page pool.  Returns a dict of the device tensors and the host copies of table and contexts."""
+    rng = np.random.default_rng(seed)
+    B, H, HKV, D, page = 64, 32, 8, 128, 16
     ctx = rng.integers(128, 4097, B).astype(np.int32)
     mbps = 256
     perm = rng.permutation(pool).astype(np.uint32)
@@ -224,15 +226,23 @@ def case_paged_attn_int8(hbm, tf, src):
         n = (int(ctx[b]) + page - 1) // page
         table[b, :n] = perm[nxt:nxt + n]
         nxt += n
+    if torch_seed is not None:
+        torch.manual_seed(torch_seed)
     kv = dev.PagedKVInt8(1, pool, HKV, D, page)
     kv.k.copy_(torch.randint(-127, 128, kv.k.shape, dtype=torch.int8, device="cuda"))
     kv.v.copy_(torch.randint(-127, 128, kv.v.shape, dtype=torch.int8, device="cuda"))
     kv.k_scale.uniform_(0.005, 0.03)
     kv.v_scale.uniform_(0.005, 0.03)
     q = torch.randn(B, H * D, device="cuda")
-    bt = torch.from_numpy(table.view(np.int32)).cuda()
-    row_slot = torch.arange(B, dtype=torch.int32, device="cuda")
-    row_ctx = torch.from_numpy(ctx).cuda()
+    return {"B": B, "H": H, "HKV": HKV, "D": D, "page": page, "pool": pool, "mbps": mbps, "ctx": ctx, "table": table, "kv": kv, "q": q,
+            "bt": torch.from_numpy(table.view(np.int32)).cuda(), "row_slot": torch.arange(B, dtype=torch.int32, device="cuda"),
+            "row_ctx": torch.from_numpy(ctx).cuda(), "max_ctx": 4096, "scale": 1.0 / math.sqrt(D), "pages_used": nxt}
+
+
+def case_paged_attn_int8(hbm, tf, src):
+    """The paged_attn_decode case over the int8 cache (same batch, heads and context draw)."""
+    c = build_paged_attn_int8_case()
+    B, H, HKV, D, mbps, kv, q, bt, row_slot, row_ctx, ctx = (c[k] for k in ("B", "H", "HKV", "D", "mbps", "kv", "q", "bt", "row_slot", "row_ctx", "ctx"))
     out = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
     scratch = dev.paged_attn_scratch(B, H, D, 4096)
     fn = lambda i: dev.paged_attn_decode_int8(q, H * D, kv, 0, bt, row_slot, row_ctx, out, B, H, mbps, 4096, 1.0 / math.sqrt(D), scratch)
