@@ -395,6 +395,13 @@ int wkb_gemm_bf16_nt_qkv_append(const void* a, int64_t lda, const void* b, int64
                                 int64_t n, int64_t k, const float* bias, int64_t kv_col0, void* kcache, void* vcache,
                                 const uint32_t* block_table, const int* row_slot, const int* row_pos, int64_t kv_heads,
                                 int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq, void* stream);
+/* Weight-resident hint for the dense tensor-core GEMMs (wkb_gemm_bf16_nt*, per calling thread; returns the previous
+ * setting).  While it is non-zero the caller promises that the B operand of every GEMM it launches is not written by a
+ * kernel still in flight on the launch's stream (resident model weights): the kernel then requests its first B tiles
+ * before it waits for the preceding kernel of the stream, which hides the first weight fetch of a decode-sized GEMM
+ * behind that kernel's tail.  A is always read after the preceding kernel.  wkb_gpt2_step sets it around its launches.
+ * Results do not depend on the setting. */
+int wkb_gemm_b_static(int on);
 /* Reads and clears the library's device status word of the current device (synchronises): 0, or the code of the last
  * event -- 1-4 / 11-17 a bounded pipeline wait of the dense / W4A16 GEMM ran out, 21 the tensor-parallel reduce's flag
  * wait ran out (22: a peer had given up), 31 a KV append met a position past its block-table row (the row was skipped),

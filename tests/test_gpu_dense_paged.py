@@ -233,7 +233,7 @@ def test_qkv_gemm_with_fused_append_equals_gemm_then_append(dev, orc):
     from wukong_b200 import lib
     L, s = lib(), torch.cuda.current_stream().cuda_stream
     rng = np.random.default_rng(5)
-    for (rows, heads, hd, d_in) in [(70, 4, 64, 256), (512, 12, 64, 768), (33, 2, 128, 256)]:
+    for (rows, heads, hd, d_in) in [(70, 4, 64, 256), (512, 12, 64, 768), (33, 2, 128, 256), (600, 12, 64, 768)]:   # the last one is past one wave of 64-column tiles: 128-column tiles
         d = heads * hd
         page, mbps, slots = 16, 6, rows
         nblk = slots * mbps

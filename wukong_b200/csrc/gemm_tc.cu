@@ -67,7 +67,13 @@ struct GemmEpi {
   const int* row_slot;
   const int* row_pos;
   int kv_col0, kv_heads, kv_hd, page_tokens, mbps;
+  // B (the weights) is not written by any kernel still in flight on the stream: the producer may request its first B
+  // tiles before it waits for the preceding kernel (wkb_gemm_b_static)
+  int b_static;
 };
+
+// Set by wkb_gemm_b_static on the calling thread; copied into every launch of gemm_bf16_tc_kernel from that thread.
+static thread_local int g_b_static = 0;
 
 // GELU for bf16 output: x * sigmoid(2u), u = sqrt(2/pi)(x + 0.044715 x^3), with the hardware exp2 and
 // reciprocal.  Relative error ~1e-6, three orders below the bf16 rounding that follows; the exact
@@ -87,12 +93,14 @@ __device__ __forceinline__ float epi_act(float y) {
 // Persistent kernel: CTA b works on tiles b, b + gridDim.x, ...; tile t is (m_tile = t % tiles_m,
 // n_tile = t / tiles_m), so CTAs running side by side share one B (weight) tile through L2.
 // ACT / OUT_BF16 / ARGMAX are compile-time so an identity epilogue carries no transcendental code.
-template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8, bool WIDE, bool KVAPPEND = false>
+template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8, bool WIDE, bool KVAPPEND = false, bool NARROW = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c,
                     i64 ldc, int M, int N, int K, GemmEpi epi, int* status) {
-  // tile shape of this instantiation: 128 x 128 with a 5-stage ring, or 128 x 256 with 4 stages
-  constexpr int BN = WIDE ? 256 : 128;
+  // tile shape of this instantiation: 128 x 128 with a 5-stage ring, 128 x 256 with 4 stages, or 128 x 64 (a problem with
+  // fewer 128-wide tiles than half the SMs then still puts a CTA on most of them)
+  static_assert(!(WIDE && NARROW), "one tile shape per instantiation");
+  constexpr int BN = NARROW ? 64 : WIDE ? 256 : 128;
   constexpr int STAGES = WIDE ? 4 : 5;
   constexpr int TILE_B_BYTES = BN * BK_BYTES, STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
   constexpr int NUM_BARS = 2 * STAGES + 4;
@@ -119,15 +127,28 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int kiters_all = (K + BK - 1) / BK;
   const int kper = (kiters_all + ksplit - 1) / ksplit;   // the host picks ksplit so that no slice is empty
 
+  int pre = 0;   // producer lane: stages whose B tile was requested before the dependency wait
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    if (epi.b_static) {
+      // the first ring of B tiles is on its way while the preceding kernel of the stream is still running: each barrier is
+      // armed for the whole stage, the A tile follows after the wait below
+      for (int w = blockIdx.x; w < num_tiles && pre < STAGES; w += gridDim.x) {
+        const int t = w / ksplit, k0 = (w % ksplit) * kper, kiters = min(kper, kiters_all - k0);
+        const int n0 = (t / tiles_m) * BN;
+        for (int kk = 0; kk < kiters && pre < STAGES; ++kk, ++pre) {
+          mbar_expect_tx(full_bar(pre), STAGE_BYTES);
+          tma_load_2d(base + pre * STAGE_BYTES + TILE_A_BYTES, &map_b, full_bar(pre), (k0 + kk) * BK, n0);
+        }
+      }
+    }
   }
-  // everything above touches only this CTA's shared memory; tensor memory is claimed and operands are read only once
-  // the preceding kernel of the stream has completed
+  // everything above touches only this CTA's shared memory and (b_static) the weights; tensor memory is claimed and A is
+  // read only once the preceding kernel of the stream has completed
   pdl_wait();
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -149,11 +170,13 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
         for (int kk = 0; kk < kiters; ++kk, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1)) { atomicExch(status, 1); ok = false; break; }
-          mbar_expect_tx(full_bar(s), STAGE_BYTES);
           const uint32_t sa = base + s * STAGE_BYTES, sb = sa + TILE_A_BYTES;
+          if (it >= pre) {
+            if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1)) { atomicExch(status, 1); ok = false; break; }
+            mbar_expect_tx(full_bar(s), STAGE_BYTES);
+            tma_load_2d(sb, &map_b, full_bar(s), (k0 + kk) * BK, n0);
+          }
           tma_load_2d(sa, &map_a, full_bar(s), (k0 + kk) * BK, m0);
-          tma_load_2d(sb, &map_b, full_bar(s), (k0 + kk) * BK, n0);
         }
       }
       if (!ok) {
@@ -843,6 +866,7 @@ static int gemm_bf16_nt_impl(const void* a, i64 lda, const void* b, i64 ldb, voi
       attr_set[dev & 63][0] = true;
     }
     GemmEpi part{nullptr, nullptr, 0, 0, 0, nullptr, (int)ks, m * n};
+    part.b_static = g_b_static;
     const i64 items = tiles * ks;
     cudaError_t e = launch_pdl(plain, (unsigned)(items < sm_count() ? items : sm_count()), GEMM_THREADS, SMEM_BYTES, st, ma, mb,
                                (void*)ws, n, (int)m, (int)n, (int)k, part, status);
@@ -854,6 +878,7 @@ static int gemm_bf16_nt_impl(const void* a, i64 lda, const void* b, i64 ldb, voi
                            ldc, c_bf16, bias, (int)act, residual, ldr);
   }
   unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
+  epi.b_static = g_b_static;
   return (int)launch_pdl(kern, grid, GEMM_THREADS, smem, st, ma, mb, c, ldc, (int)m, (int)n, (int)k, epi, status);
 }
 
@@ -923,6 +948,7 @@ int wkb_gemm_bf16_nt_partial(const void* a, i64 lda, const void* b, i64 ldb, i64
   GemmEpi part{};
   part.ksplit = (int)ks;
   part.slice_stride = m * n;
+  part.b_static = g_b_static;
   const i64 items = ((n + BN - 1) / BN) * ((m + BM - 1) / BM) * ks;
   return (int)launch_pdl(kern, (unsigned)(items < sm_count() ? items : sm_count()), GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb, workspace,
                          n, (int)m, (int)n, (int)k, part, status);
@@ -946,18 +972,23 @@ int wkb_gemm_bf16_nt_qkv_append(const void* a, i64 lda, const void* b, i64 ldb, 
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, m, k, lda, BM);
   if (rc) return rc;
-  rc = make_map(&mb, b, n, k, ldb, BN);
+  // 64-column tiles while they still fit one wave: a decode batch of 512 rows x 2304 columns is 72 tiles of 128 columns
+  // (half the SMs idle) but 144 of 64
+  const i64 tiles_narrow = ((n + 63) / 64) * ((m + BM - 1) / BM);
+  const bool narrow = tiles_narrow <= sm_count() && !getenv("WKB_QKV_WIDE");
+  const int bn = narrow ? 64 : BN;
+  rc = make_map(&mb, b, n, k, ldb, bn);
   if (rc) return rc;
   int* status = gemm_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
-  auto kern = gemm_bf16_tc_kernel<0, false, false, false, false, true>;
-  static bool attr_set[64] = {false};
+  auto kern = narrow ? gemm_bf16_tc_kernel<0, false, false, false, false, true, true> : gemm_bf16_tc_kernel<0, false, false, false, false, true, false>;
+  static bool attr_set[64][2] = {{false}};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_set[dev & 63]) {
+  if (!attr_set[dev & 63][narrow ? 1 : 0]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    attr_set[dev & 63] = true;
+    attr_set[dev & 63][narrow ? 1 : 0] = true;
   }
   GemmEpi epi{};
   epi.bias = bias;
@@ -971,7 +1002,8 @@ int wkb_gemm_bf16_nt_qkv_append(const void* a, i64 lda, const void* b, i64 ldb, 
   epi.kv_hd = (int)head_dim;
   epi.page_tokens = (int)page_tokens;
   epi.mbps = (int)max_blocks_per_seq;
-  const i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  epi.b_static = g_b_static;
+  const i64 tiles = ((n + bn - 1) / bn) * ((m + BM - 1) / BM);
   return (int)launch_pdl(kern, (unsigned)(tiles < sm_count() ? tiles : sm_count()), GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb, (void*)c, ldc,
                          (int)m, (int)n, (int)k, epi, status);
 }
@@ -1054,6 +1086,7 @@ int wkb_gemm_bf16_nt_argmax(const void* a, i64 lda, const void* b, i64 ldb, i64 
     attr_set[dev & 63] = true;
   }
   GemmEpi epi{bias, nullptr, 0, 0, 0, part_idx};
+  epi.b_static = g_b_static;
   i64 tiles_n = (n + BN - 1) / BN, tiles = tiles_n * ((m + BM - 1) / BM);
   unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
   cudaError_t e = launch_pdl(kern, grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb, (void*)part_val, (i64)0, (int)m, (int)n, (int)k, epi,
@@ -1061,6 +1094,15 @@ int wkb_gemm_bf16_nt_argmax(const void* a, i64 lda, const void* b, i64 ldb, i64 
   if (e != cudaSuccess) return (int)e;
   return (int)launch_pdl(argmax_tiles_kernel, (unsigned)((m * 32 + 127) / 128), 128, 0, as_stream(stream), (const float*)part_val,
                          (const int*)part_idx, (int)tiles_n, out, (int)m);
+}
+
+// While set (non-zero) on the calling thread, every dense tensor-core GEMM launched from it may read its B operand before
+// the preceding kernel of the stream has completed: the caller promises that B (resident weights) is not written by any
+// kernel still in flight on that stream.  A is always read after that kernel.  Returns the previous setting.
+int wkb_gemm_b_static(int on) {
+  const int was = g_b_static;
+  g_b_static = on ? 1 : 0;
+  return was;
 }
 
 // Reads (and clears) the bounded-wait status of the tensor-core GEMM on the current device:

@@ -40,6 +40,7 @@ int wkb_paged_attn_prefill(const float*, i64, const void*, const void*, const ui
                            i64, i64, i64, i64, i64, float, void*);
 int wkb_decode_advance(int*, int*, int*, const int*, i64, i64, void*);
 int wkb_gemm_init(void);
+int wkb_gemm_b_static(int);
 }
 
 namespace wkb {
@@ -424,6 +425,12 @@ int wkb_gpt2_step(void* h, i64 n_rows, i64 n_sample, i64 n_tiles, int keep_logit
   if (n_rows <= 0) return 0;
   if (n_rows > m->max_rows || n_sample < 0 || n_sample > m->bcap || (keep_logits && !m->logits)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = as_stream(stream);
+  // every B operand of the step is a resident weight: the GEMMs may fetch it ahead of their stream dependency
+  struct WeightsStatic {
+    int was;
+    WeightsStatic() : was(wkb_gemm_b_static(1)) {}
+    ~WeightsStatic() { wkb_gemm_b_static(was); }
+  } weights_static;
   const i64 R = m->max_rows, d = m->d, n = n_rows;
   int* row_token = m->rows;
   int* row_pos = m->rows + R;
