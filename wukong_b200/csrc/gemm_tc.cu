@@ -31,13 +31,13 @@
 
 namespace wkb {
 
-constexpr int BM = 128, BN = 128, STAGES = 5;
+constexpr int BM = 128, BN = 128, STAGES = 6;
 constexpr int BK_BYTES = 128;   // one 128-byte swizzle row of K per stage: 64 bf16 or 128 e4m3 elements
 constexpr int UMMA_K_BYTES = 32;  // K extent of one tcgen05.mma: 16 bf16 or 32 e4m3 elements
 constexpr int TILE_A_BYTES = BM * BK_BYTES, TILE_B_BYTES = BN * BK_BYTES;
 constexpr int STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
-constexpr int GEMM_THREADS = 192;
-constexpr int EPI_STAGE_BYTES = 4 * 32 * 33 * 4;  // one 32 x 33 fp32 transpose pad per epilogue warp
+constexpr int GEMM_THREADS = 320;                 // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quarter)
+constexpr int EPI_STAGE_BYTES = 8 * 32 * 33 * 4;  // one 32 x 33 fp32 transpose pad per epilogue warp
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int BN_WIDE = 256;
 constexpr int SMEM_BYTES_WIDE = 4 * (TILE_A_BYTES + BN_WIDE * BK_BYTES) + EPI_STAGE_BYTES + 1024 + 256;
@@ -97,14 +97,18 @@ template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8, bool WIDE, bool KVAPPEND
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c,
                     i64 ldc, int M, int N, int K, GemmEpi epi, int* status) {
-  // tile shape of this instantiation: 128 x 128 with a 5-stage ring, 128 x 256 with 4 stages, or 128 x 64 (a problem with
+  // tile shape of this instantiation: 128 x 128 with a 6-stage ring, 128 x 256 with 4 stages, or 128 x 64 with 8 (a problem with
   // fewer 128-wide tiles than half the SMs then still puts a CTA on most of them)
   static_assert(!(WIDE && NARROW), "one tile shape per instantiation");
   constexpr int BN = NARROW ? 64 : WIDE ? 256 : 128;
-  constexpr int STAGES = WIDE ? 4 : 5;
+  constexpr int STAGES = NARROW ? 8 : WIDE ? 4 : 6;   // 192 KB of operand ring whatever the tile: the loop of a decode-sized GEMM runs at
+                                                      // one stage per (TMA latency / stages)
   constexpr int TILE_B_BYTES = BN * BK_BYTES, STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
   constexpr int NUM_BARS = 2 * STAGES + 4;
   constexpr uint32_t TMEM_COLS = 2 * BN;       // two accumulator buffers
+  // epilogue warps: two per TMEM lane quarter, taking alternate 32-column chunks (the arg-max epilogue keeps one candidate
+  // per row and tile, so one warp per quarter scans the whole tile there)
+  constexpr int EPI_WARPS = ARGMAX ? 4 : 8, CHUNK_STEP = 32 * (EPI_WARPS / 4);
   constexpr uint32_t IDESC_ = make_idesc(BN, F8);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -130,7 +134,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   int pre = 0;   // producer lane: stages whose B tile was requested before the dependency wait
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), EPI_WARPS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -213,9 +217,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (ok) umma_commit(tfull_bar(buf));
       }
     }
-  } else {
-    // ---------------- epilogue warps 2..5: TMEM lane quarter (warp % 4) ----------------
-    const int quarter = warp & 3;
+  } else if (warp < 2 + EPI_WARPS) {
+    // ---------------- epilogue warps: TMEM lane quarter (warp % 4), column chunks c0 = 32 * half, + CHUNK_STEP, ... ----------------
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     float* stage = stage_all + (warp - 2) * (32 * 33);
     (void)stage;
     int local = 0;
@@ -254,7 +258,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool pinned = false;
       (void)best_v; (void)best_i; (void)pinned;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 32 * half; c0 < BN; c0 += CHUNK_STEP) {
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0);
         asm volatile(
@@ -268,8 +272,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 32 == BN) {
-          // the accumulator buffer is fully in registers: hand it back to the MMA warp
+        if (c0 + CHUNK_STEP >= BN) {
+          // this warp's last chunk of the accumulator buffer is in registers: its share is handed back to the MMA warp
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_bar(buf));
@@ -405,7 +409,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_TILE_BYTES = 128 * BK_BYTES;              // a 128-row operand tile of one stage
 constexpr int PAIR_STAGE_BYTES = 2 * PAIR_TILE_BYTES;        // A tile + this CTA's half of B
-constexpr int SMEM_BYTES_PAIR = PAIR_STAGES * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + 1024 + 256;
+constexpr int PAIR_THREADS = 192;                            // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int PAIR_EPI_STAGE_BYTES = 4 * 32 * 33 * 4;        // one 32 x 33 fp32 transpose pad per epilogue warp
+constexpr int SMEM_BYTES_PAIR = PAIR_STAGES * PAIR_STAGE_BYTES + PAIR_EPI_STAGE_BYTES + 1024 + 256;
 constexpr uint32_t IDESC_PAIR = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 
 __device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
@@ -440,7 +446,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
 }
 
 template <int ACT, bool OUT_BF16>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c, i64 ldc, int M, int N,
                       int K, GemmEpi epi, int* status) {
   constexpr int STAGES = PAIR_STAGES, BN2 = 256, BM2 = 256;
@@ -451,8 +457,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - raw);
   float* stage_all = reinterpret_cast<float*>(gen_base + STAGES * PAIR_STAGE_BYTES);
-  const uint32_t bars = base + STAGES * PAIR_STAGE_BYTES + EPI_STAGE_BYTES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * PAIR_STAGE_BYTES + EPI_STAGE_BYTES + 8 * NUM_BARS);
+  const uint32_t bars = base + STAGES * PAIR_STAGE_BYTES + PAIR_EPI_STAGE_BYTES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen_base + STAGES * PAIR_STAGE_BYTES + PAIR_EPI_STAGE_BYTES + 8 * NUM_BARS);
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
@@ -822,7 +828,7 @@ static int gemm_bf16_nt_impl(const void* a, i64 lda, const void* b, i64 ldb, voi
     if (pairs > tiles_pair) pairs = tiles_pair;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs));
-    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.blockDim = dim3(PAIR_THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES_PAIR;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];

@@ -58,16 +58,18 @@ __device__ __forceinline__ float block_sum_128(float v, float* red) {
 // x[r, :] += bias + sum_s slices[s][r, :] (slice order; either may be absent), then out[r, :] = bf16(LayerNorm(x[r, :])).
 // One CTA of 128 threads per row, a thread keeps VPT 8-element vectors of the row in registers between the update, the
 // two-pass statistics (mean, then centred variance -- the sequence of the bf16 LayerNorm kernel) and the write-back.
+// (The narrow instantiation is held to 85 registers: all 512 one-row CTAs of a decode batch are then resident beside the
+// CTAs of the GEMM that precedes them in the stream and start the moment it completes.)
 template <int VPT>
-__global__ void __launch_bounds__(128) add_slices_bias_layernorm_kernel(float* __restrict__ x, const float* __restrict__ slices, int nsl,
+__global__ void __launch_bounds__(128, VPT == 1 ? 6 : 1) add_slices_bias_layernorm_kernel(float* __restrict__ x, const float* __restrict__ slices, int nsl,
                                                                         i64 slice_stride, i64 ld, const float* __restrict__ bias,
                                                                         const float* __restrict__ gamma, const float* __restrict__ beta,
                                                                         u16* __restrict__ out, i64 rows, int cols, float eps) {
   __shared__ float red[32];
-  pdl_wait();
-  pdl_trigger();
   const int nvec = cols >> 3;
   const bool update = nsl > 0 || bias != nullptr;
+  pdl_wait();
+  pdl_trigger();
   for (i64 r = blockIdx.x; r < rows; r += gridDim.x) {
     float* xr = x + r * (i64)cols;
     float v[VPT][8];
@@ -80,13 +82,30 @@ __global__ void __launch_bounds__(128) add_slices_bias_layernorm_kernel(float* _
         if (update) {
           float d[8];
           if (nsl > 0) {
+            // the loads of four slices are issued together (one trip to L2 per four slices instead of one per slice); the adds
+            // run in slice order
             const float* sp = slices + r * ld + vi * 8;
-            const float4 p = __ldcg(reinterpret_cast<const float4*>(sp)), q = __ldcg(reinterpret_cast<const float4*>(sp + 4));
-            d[0] = p.x; d[1] = p.y; d[2] = p.z; d[3] = p.w; d[4] = q.x; d[5] = q.y; d[6] = q.z; d[7] = q.w;
-            for (int s = 1; s < nsl; ++s) {
-              const float4 p2 = __ldcg(reinterpret_cast<const float4*>(sp + s * slice_stride));
-              const float4 q2 = __ldcg(reinterpret_cast<const float4*>(sp + s * slice_stride + 4));
-              d[0] += p2.x; d[1] += p2.y; d[2] += p2.z; d[3] += p2.w; d[4] += q2.x; d[5] += q2.y; d[6] += q2.z; d[7] += q2.w;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) d[e] = 0.0f;
+            for (int s0 = 0; s0 < nsl; s0 += 4) {
+              float4 p[4], q[4];
+#pragma unroll
+              for (int s = 0; s < 4; ++s) {
+                if (s0 + s < nsl) {
+                  p[s] = __ldcg(reinterpret_cast<const float4*>(sp + (s0 + s) * slice_stride));
+                  q[s] = __ldcg(reinterpret_cast<const float4*>(sp + (s0 + s) * slice_stride + 4));
+                }
+              }
+#pragma unroll
+              for (int s = 0; s < 4; ++s) {
+                if (s0 + s < nsl) {
+                  if (s0 + s == 0) {
+                    d[0] = p[s].x; d[1] = p[s].y; d[2] = p[s].z; d[3] = p[s].w; d[4] = q[s].x; d[5] = q[s].y; d[6] = q[s].z; d[7] = q[s].w;
+                  } else {
+                    d[0] += p[s].x; d[1] += p[s].y; d[2] += p[s].z; d[3] += p[s].w; d[4] += q[s].x; d[5] += q[s].y; d[6] += q[s].z; d[7] += q[s].w;
+                  }
+                }
+              }
             }
           } else {
 #pragma unroll
