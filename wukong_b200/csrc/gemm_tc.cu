@@ -151,9 +151,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   }
-  // everything above touches only this CTA's shared memory and (b_static) the weights; tensor memory is claimed and A is
-  // read only once the preceding kernel of the stream has completed
-  pdl_wait();
+  // Tensor memory is claimed before the wait for the preceding kernel as well: an allocation that meets a still-resident
+  // CTA of that kernel simply blocks until its columns are freed (no kernel waits on its successor), and everything up to
+  // here touches only this CTA's shared memory and (b_static) the weights.  A is read after the wait.
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -162,6 +162,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
   pdl_trigger();
 
   if (warp == 0) {
