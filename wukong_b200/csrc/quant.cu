@@ -277,7 +277,7 @@ static size_t contract_smem(int nb) { return (size_t)nb * (32 + 4 + 4) + (size_t
 // Per block: sum_e (16 + nib_e) * x_e in f32 (the nibble becomes the mantissa of 16 + nib, exact), minus 24 * sum_e x_e,
 // times the f16 scale.
 template <int R, int BPL>
-__global__ void __launch_bounds__(256) gemv_q4_lean_kernel(const uint4* __restrict__ qs, const u16* __restrict__ d,
+__global__ void __launch_bounds__(128, 4) gemv_q4_lean_kernel(const uint4* __restrict__ qs, const u16* __restrict__ d,
                                                            const uint4* __restrict__ xb, float* __restrict__ y, i64 n, int nb, i64 k) {
   const int lane = threadIdx.x & 31;
   const i64 warp = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -409,9 +409,10 @@ int wkb_gemv_q4_0_bf16x(const void* qs, const void* d, const void* x_bf16, float
   // two rows per warp; few rows: one row per warp so that the grid still covers the SMs
   const bool one = n < (i64)WKB_SM_COUNT * 16;
   const i64 warps = one ? n : (n + 1) / 2;
-  const i64 blocks = (warps + 7) / 8;
-  if (one) gemv_q4_lean_kernel<1, 4><<<(int)blocks, 256, 0, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const uint4*)x_bf16, y, n, nb, k);
-  else gemv_q4_lean_kernel<2, 4><<<(int)blocks, 256, 0, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const uint4*)x_bf16, y, n, nb, k);
+  // CTAs of four warps held to 128 registers: four are resident per SM, so that 4096 rows (512 CTAs) are one wave
+  const i64 blocks = (warps + 3) / 4;
+  if (one) gemv_q4_lean_kernel<1, 4><<<(int)blocks, 128, 0, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const uint4*)x_bf16, y, n, nb, k);
+  else gemv_q4_lean_kernel<2, 4><<<(int)blocks, 128, 0, as_stream(stream)>>>((const uint4*)qs, (const u16*)d, (const uint4*)x_bf16, y, n, nb, k);
   return (int)cudaGetLastError();
 }
 
