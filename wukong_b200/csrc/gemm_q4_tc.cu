@@ -9,8 +9,8 @@
 //     256-K stage, so the first MMAs start when a quarter of it has landed) and stays in shared memory; a CTA owns one K slice and walks over weight-row tiles of 128 rows;
 //   * warp 0 streams raw tiles (128 rows x 256 K: 16 KB of nibbles + 2 KB of f16 scales) through a
 //     5-stage TMA ring (128-byte swizzle, no multicast);
-//   * warps 4-19 dequantise, in two teams of eight (one team per tile of the pair, each feeding its own MMA warp,
-//     so a stage is handed over between 8 warps and one lane, not 16): thread = weight row, four 32-value
+//   * warps 4-19 dequantise, in two teams of eight (each feeding its own MMA warp, so a stage is handed over between
+//     8 warps and one lane, not 16; the teams take alternate stages of the stream): thread = weight row, four 32-value
 //     blocks of each stage, written as two half-stage buffers so that the MMAs of one half run while the
 //     other half is converted; nibble -> bf16 with
 //     one byte permute (0x4300 | nib = 128 + nib exactly), subtract 136, multiply by the block scale rounded
@@ -23,12 +23,12 @@
 //   * warps 1 and 2 issue tcgen05.mma with A in tensor memory and B (activations) from shared memory
 //     (M = 128 weight rows, N = 64 activation rows, K = 16) x 16 per stage; tcgen05.commit recycles the
 //     operand stage.  One thread issues such an MMA about every 27-36 ns, the tensor pipe retires one every
-//     19-20 ns (measured with two issuing warps), so the CTA walks over its weight-row tiles two at a time:
-//     the stages of the two tiles alternate in the stream, warp 1 accumulates the even tile and warp 2 the
-//     odd one, each into its own accumulator and in K order (the sum of a tile is the same whichever warp
-//     issues it);
-//   * warps 20-27 read the accumulators (four of them, so a pair of tiles is finished while the next pair
-//     is multiplied; one set of four warps per tile of the pair; thread = weight row, 64 activation rows in
+//     19-20 ns (measured with two issuing warps), so two warps issue: stage s of the CTA's j-th tile belongs to team
+//     (j + s) & 1, each team accumulates its stages of a tile into its own accumulator, and the epilogue adds the two
+//     (team 0's sum + team 1's sum: a fixed order).  Both teams are busy whatever the number of tiles a CTA owns; one
+//     team per tile left a team idle on a single or an odd last tile;
+//   * warps 20-27 read the accumulators (four of them: two per tile, so a tile is finished while the next one
+//     is multiplied; the two sets of four warps take alternate tiles; thread = weight row, 64 activation rows in
 //     registers).
 //     With one K slice they finish the tile directly.  With several, they write the partial tile to
 //     the workspace and count arrivals per (tile, lane quarter); the last arriving warp adds the
@@ -183,6 +183,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 16 consecutive columns of this thread's TMEM lane, added to acc[0..15]
+__device__ __forceinline__ void tmem_ld16_add(uint32_t taddr, float* acc) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int e = 0; e < 16; ++e) acc[e] += __uint_as_float(r[e]);
+}
+
 // Finish 32 activation rows (m0 .. m0+31) of weight row n held one per register.
 // MODE 0: f32 out[m, n]; 1: bf16 out[m, n]; 2: SwiGLU, bf16 out[m, n / 2] from (gate = even n, up = odd n).
 // (MODE 3 never finishes in the kernel: the K-slice partials are the result, left in the workspace for a consumer
@@ -245,18 +260,15 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
   const int ks = blockIdx.x % plan.ksplit, group = blockIdx.x / plan.ksplit;
   const int stage0 = ks * plan.stages_per_slice;
   const int nstages = min(plan.stages_per_slice, plan.kstages - stage0);  // >= 1 by construction
-  // This CTA's tiles are group, group + groups, ...; they are taken two at a time and the stages of a pair alternate in
-  // the stream the producer follows: stream position -> (local tile, stage).  Even local tiles belong to team 0 (dequantiser
-  // warps 4-11, MMA warp 1, epilogue warps 20-23), odd ones to team 1.
+  // This CTA's tiles are group, group + groups, ...; the producer streams them tile by tile, stage by stage.  Stage s of
+  // local tile j belongs to team (j + s) & 1 (dequantiser warps 4-11 + MMA warp 1, or 12-19 + warp 2): the two teams work on
+  // the SAME tile, on alternate stages, each into its own accumulator (2 * (j & 1) + team), and the epilogue adds the two.
+  // Both teams are therefore busy whatever the number of tiles (a CTA with a single tile, or an odd one out, used to
+  // leave one team idle), and they stay in step with the stream.
   const int ntl = group < plan.n_tiles ? (plan.n_tiles - group + plan.groups - 1) / plan.groups : 0;
-  const int pair_its = 2 * nstages, full_pairs = ntl >> 1, total_its = ntl * nstages;
-  auto locate = [&](int it, int& j, int& s) {
-    const int p = it / pair_its;
-    if (p < full_pairs) { const int q = it - p * pair_its; s = q >> 1; j = 2 * p + (q & 1); }
-    else { s = it - full_pairs * pair_its; j = 2 * full_pairs; }
-  };
-  // the inverse for a team: position of stage s of local tile j
-  auto position = [&](int j, int s) { return (j >> 1) < full_pairs ? (j >> 1) * pair_its + 2 * s + (j & 1) : full_pairs * pair_its + s; };
+  const int total_its = ntl * nstages;
+  auto locate = [&](int it, int& j, int& s) { j = it / nstages; s = it - j * nstages; };
+  auto position = [&](int j, int s) { return j * nstages + s; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < X_STAGES; ++s) mbar_init(x_full(s), 1);
@@ -317,12 +329,14 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
       int n = 0;                                    // stages this team has multiplied so far
       const uint64_t bdesc0 = make_sdesc(x_base);   // the start-address field counts 16-byte units: later operands are plain adds
       const uint32_t ta0 = tmem_base + (uint32_t)(A_COL0 + team * A_STAGE_COLS);
-      for (int j = team; j < ntl && ok; j += 2) {
-        const int acc = j & (NUM_ACC - 1);
-        if (!mbar_wait_parked(t_empty(acc), ((j / NUM_ACC) & 1) ^ 1)) { atomicExch(status, 13); ok = false; break; }
+      for (int j = 0; j < ntl && ok; ++j) {
+        const int s_first = (j + team) & 1;        // this team's stages of tile j: s_first, s_first + 2, ...
+        if (s_first >= nstages) continue;          // a one-stage slice: the other team has the tile to itself
+        const int acc = 2 * (j & 1) + team;
+        if (!mbar_wait_parked(t_empty(acc), ((j >> 1) & 1) ^ 1)) { atomicExch(status, 13); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * TM);
-        for (int s = 0; s < nstages && ok; ++s, ++n) {
+        for (int s = s_first; s < nstages && ok; s += 2, ++n) {
           if (!mbar_wait_parked(x_full(s), 0)) { atomicExch(status, 12); ok = false; break; }   // completes once; later tiles pass at once
           const uint64_t bd = bdesc0 + (uint64_t)((s * 4 * X_SUB_BYTES) >> 4);
 #pragma unroll
@@ -332,7 +346,7 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
 #pragma unroll
             for (int k = 8 * half; k < 8 * half + 8; ++k)
               umma_bf16_ts(tmem_d, ta0 + (uint32_t)(k * 8), bd + (uint64_t)(((k >> 2) * X_SUB_BYTES + (k & 3) * 32) >> 4), IDESC,
-                           (s == 0 && k == 0) ? 0u : 1u);   // the first K step of a tile overwrites the accumulator
+                           (s == s_first && k == 0) ? 0u : 1u);   // this team's first K step of a tile overwrites its accumulator
             umma_commit(a_empty(team, half));
           }
         }
@@ -361,8 +375,8 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
         pending = -1;
       }
     };
-    for (int j = team; j < ntl && ok; j += 2) {
-      for (int s = 0; s < nstages && ok; ++s, ++n) {
+    for (int j = 0; j < ntl && ok; ++j) {
+      for (int s = (j + team) & 1; s < nstages && ok; s += 2, ++n) {
         const int it = position(j, s);
         const int slot = it % RAW_STAGES;
         if (!mbar_wait_parked(raw_full(slot), (it / RAW_STAGES) & 1)) { if (lane == 0) atomicExch(status, 15); ok = false; break; }
@@ -401,45 +415,50 @@ gemm_q4_tc_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __re
     const i64 n_pad = (i64)plan.n_tiles * TN;
     bool ok = true;
     pdl_wait();
-    for (int local = (warp - EPI_WARP0) >> 2; local < ntl && ok; local += 2) {   // set 0: even local tiles, set 1: odd ones
+    const int set = (warp - EPI_WARP0) >> 2;                   // set 0: even local tiles, set 1: odd ones
+    for (int local = set; local < ntl && ok; local += 2) {
       const int t = group + local * plan.groups;
-      const int acc = local & (NUM_ACC - 1);
       const int n = t * TN + quarter * 32 + lane;
-      if (!mbar_wait_parked(t_full(acc), (local / NUM_ACC) & 1)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
+      // the tile's two accumulators: team 0's (its stages local & 1, + 2, ...) and team 1's; a one-stage slice has only the
+      // one of team local & 1
+      const int acc0 = 2 * set, acc1 = 2 * set + 1;
+      const bool has0 = (local & 1) < nstages, has1 = ((local + 1) & 1) < nstages;
+      const uint32_t par = (uint32_t)((local >> 1) & 1);
+      if (has0 && !mbar_wait_parked(t_full(acc0), par)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
+      if (has1 && !mbar_wait_parked(t_full(acc1), par)) { if (lane == 0) atomicExch(status, 17); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TM);
-      if (plan.ksplit == 1 && MODE != 3) {
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t taddr = lane_base + (uint32_t)((has0 ? acc0 : acc1) * TM), taddr_b = lane_base + (uint32_t)(acc1 * TM);
+      const bool both = has0 && has1;
+      float* mine = ws + ((i64)ks * TM) * n_pad + n;
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          uint32_t rr[32];
-          tmem_ld32(taddr + h * 32, rr);
-          if (h == 1) {
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(t_empty(acc));
-          }
-          float v[32];
+      for (int h = 0; h < 2; ++h) {
+        uint32_t rr[32];
+        tmem_ld32(taddr + h * 32, rr);
+        float v[32];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(rr[e]);
-          finish32<MODE>(v, h * 32, M, n, N, out, ldo);
+        for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(rr[e]);
+        if (both) {                                             // team 0's sum + team 1's sum, in that order
+          tmem_ld16_add(taddr_b + h * 32, v);
+          tmem_ld16_add(taddr_b + h * 32 + 16, v + 16);
         }
-      } else {
-        // partial sums go to the workspace as [slice][activation row][weight row]; a separate pass adds the
-        // slices in slice order, so the result does not depend on which CTA finished first
-        float* mine = ws + ((i64)ks * TM) * n_pad + n;
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          uint32_t rr[32];
-          tmem_ld32(taddr + h * 32, rr);
-          if (h == 1) {
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(t_empty(acc));
+        if (h == 1) {
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (has0) mbar_arrive(t_empty(acc0));
+            if (has1) mbar_arrive(t_empty(acc1));
           }
+        }
+        if (plan.ksplit == 1 && MODE != 3) {
+          finish32<MODE>(v, h * 32, M, n, N, out, ldo);
+        } else {
+          // partial sums go to the workspace as [slice][activation row][weight row]; a separate pass adds the
+          // slices in slice order, so the result does not depend on which CTA finished first
           const int mcount = min(32, M - h * 32);
 #pragma unroll
           for (int e = 0; e < 32; ++e)
-            if (e < mcount) __stcg(mine + (i64)(h * 32 + e) * n_pad, __uint_as_float(rr[e]));
+            if (e < mcount) __stcg(mine + (i64)(h * 32 + e) * n_pad, v[e]);
         }
       }
     }
