@@ -154,3 +154,37 @@ def test_llama_chunked_prefill_matches_token_by_token_oracle(env, orc):
         torch.cuda.synchronize()
         check_hist([(lg, model.logits.cpu().numpy()[:S], np.asarray(nxt), model.next_tok.cpu().numpy()[:S])], 8e-3)
         toks = [int(t) for t in nxt]
+
+
+def test_fused_rank_sum_with_eight_local_partials_adds_in_rank_order():
+    """The fused tensor-parallel reduce on one GPU: the "ranks" are local buffers whose flags are already published.
+    x must come out as x + (((p0 + p1) + p2) + ...), bit for bit, for 3, 4 and 8 ranks (every rank's piece is loaded
+    before the first add; the adds stay in rank order), and the normed row must match the fp32 formula."""
+    import ctypes
+    import torch
+    from wukong_b200 import _lib, lib, device as dev
+    _lib.require_gpu()
+    L = lib()
+    torch.manual_seed(0)
+    for world, rows, cols in [(8, 16, 4096), (8, 64, 4096), (4, 64, 4096), (3, 5, 1024), (8, 7, 8192)]:
+        parts = [torch.randn(rows, cols, device="cuda") for _ in range(world)]
+        flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(world)]
+        flags[0][:world] = 1                                  # every peer's sequence number for step 0, phase 0
+        step = torch.zeros(1, dtype=torch.int32, device="cuda")
+        x = torch.randn(rows, cols, device="cuda")
+        x0 = x.clone()
+        gamma = torch.rand(cols, device="cuda") + 0.5
+        out = torch.empty(rows, cols, device="cuda", dtype=torch.bfloat16)
+        arr = (ctypes.c_void_p * world)(*[p.data_ptr() for p in parts])
+        farr = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+        rc = L.wkb_tp_reduce_add_rmsnorm(arr, farr, 0, world, step.data_ptr(), 0, 2, x.data_ptr(), gamma.data_ptr(), out.data_ptr(), rows, cols,
+                                         ctypes.c_float(1e-5), torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert rc == 0 and dev.gemm_status() == 0
+        s = parts[0].clone()
+        for p in range(1, world):
+            s += parts[p]
+        ref = x0 + s
+        assert torch.equal(x, ref)
+        normed = ref.double() * torch.rsqrt((ref.double() ** 2).mean(1, keepdim=True) + 1e-5) * gamma.double()
+        assert torch.allclose(out.double(), normed, rtol=2 ** -7, atol=1e-6)

@@ -105,11 +105,16 @@ __global__ void __launch_bounds__(1024) tp_reduce_add_rmsnorm_kernel(TpPeers pee
     for (int k = 0; k < NV; ++k) {
       const int i = threadIdx.x + k * blockDim.x;
       if (i < nvec) {
-        float4 s = __ldcg(reinterpret_cast<const float4*>(peers.part[0] + (i64)r * cols) + i);
-        for (int p = 1; p < world; ++p) {
-          const float4 d = __ldcg(reinterpret_cast<const float4*>(peers.part[p] + (i64)r * cols) + i);
-          s.x += d.x; s.y += d.y; s.z += d.z; s.w += d.w;
-        }
+        // every rank's piece is requested before the first add: one trip over NVLink, not one per rank (a loop over a
+        // run-time rank count issues each load behind the previous add); the adds stay in rank order
+        float4 d[TP_MAX_WORLD];
+#pragma unroll
+        for (int p = 0; p < TP_MAX_WORLD; ++p)
+          if (p < world) d[p] = __ldcg(reinterpret_cast<const float4*>(peers.part[p] + (i64)r * cols) + i);
+        float4 s = d[0];
+#pragma unroll
+        for (int p = 1; p < TP_MAX_WORLD; ++p)
+          if (p < world) { s.x += d[p].x; s.y += d[p].y; s.z += d[p].z; s.w += d[p].w; }
         v[k] = xr[i];
         v[k].x += s.x; v[k].y += s.y; v[k].z += s.z; v[k].w += s.w;
         q = fmaf(v[k].x, v[k].x, q); q = fmaf(v[k].y, v[k].y, q); q = fmaf(v[k].z, v[k].z, q); q = fmaf(v[k].w, v[k].w, q);
@@ -191,7 +196,8 @@ int wkb_tp_reduce_add_rmsnorm(const void* const* parts, void* const* flags, i64 
   }
   const int grid = (int)(rows < (i64)WKB_SM_COUNT ? rows : (i64)WKB_SM_COUNT);
   const i64 nvec = cols / 4;
-  const int threads = (int)(((nvec < 1024 ? nvec : 1024) + 31) / 32 * 32);
+  const int threads = (int)(((nvec < 1024 ? nvec : 1024) + 31) / 32 * 32);   // the thread layout (and with it the order of the row's sum of
+                                                                            // squares) is the one of add_rmsnorm_kernel: the two paths agree bit for bit
   const i64 per = (nvec + threads - 1) / threads;
   cudaStream_t st = as_stream(stream);
 #define WKB_TP_LAUNCH(NV_) launch_pdl(tp_reduce_add_rmsnorm_kernel<NV_>, grid, threads, 0, st, peers, (int)rank, (int)world, (const uint32_t*)step_ptr, \
