@@ -106,9 +106,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr int TILE_B_BYTES = BN * BK_BYTES, STAGE_BYTES = TILE_A_BYTES + TILE_B_BYTES;
   constexpr int NUM_BARS = 2 * STAGES + 4;
   constexpr uint32_t TMEM_COLS = 2 * BN;       // two accumulator buffers
-  // epilogue warps: two per TMEM lane quarter, taking alternate 32-column chunks (the arg-max epilogue keeps one candidate
-  // per row and tile, so one warp per quarter scans the whole tile there)
-  constexpr int EPI_WARPS = ARGMAX ? 4 : 8, CHUNK_STEP = 32 * (EPI_WARPS / 4);
+  // epilogue warps: two per TMEM lane quarter, taking alternate 32-column chunks (the arg-max epilogue leaves one candidate
+  // per row, tile and warp of the pair)
+  constexpr int EPI_WARPS = 8, CHUNK_STEP = 32 * (EPI_WARPS / 4);
   constexpr uint32_t IDESC_ = make_idesc(BN, F8);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -378,8 +378,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
       if (ARGMAX && row < M) {
-        // partial result of this column tile: [row][tile] (value, index); index -1 = no candidate
-        const i64 slot = (i64)row * tiles_n + (t / tiles_m);
+        // partial result of this warp's chunks of the column tile: [row][tile][half] (value, index); index -1 = no candidate
+        const i64 slot = ((i64)row * tiles_n + (t / tiles_m)) * 2 + half;
         reinterpret_cast<float*>(c)[slot] = best_v;
         epi.arg_idx[slot] = best_i;
       }
@@ -662,7 +662,7 @@ __global__ void __launch_bounds__(128) argmax_tiles_kernel(const float* __restri
   for (int t = lane; t < tiles; t += 32) {
     float v = pv[(i64)row * tiles + t];
     int i = pi[(i64)row * tiles + t];
-    if (i >= 0 && (bi < 0 || v > bv)) { bv = v; bi = i; }
+    if (i >= 0 && (bi < 0 || v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
   }
 #pragma unroll
   for (int ofs = 16; ofs > 0; ofs >>= 1) {
@@ -1066,7 +1066,7 @@ int wkb_gemm_e4m3_nt(const void* a, i64 lda, const void* b, i64 ldb, void* c, i6
   return (int)cudaGetLastError();
 }
 
-i64 wkb_gemm_argmax_tiles(i64 n) { return (n + BN - 1) / BN; }
+i64 wkb_gemm_argmax_tiles(i64 n) { return 2 * ((n + BN - 1) / BN); }   // two candidates per 128-column tile
 
 // out[i] = argmax_j (A.B^T + bias)[i, j] without materialising the product: every column tile leaves
 // one (value, column) candidate per row in part_val / part_idx ([m, wkb_gemm_argmax_tiles(n)] each),
@@ -1100,7 +1100,7 @@ int wkb_gemm_bf16_nt_argmax(const void* a, i64 lda, const void* b, i64 ldb, i64 
                              status);
   if (e != cudaSuccess) return (int)e;
   return (int)launch_pdl(argmax_tiles_kernel, (unsigned)((m * 32 + 127) / 128), 128, 0, as_stream(stream), (const float*)part_val,
-                         (const int*)part_idx, (int)tiles_n, out, (int)m);
+                         (const int*)part_idx, (int)(2 * tiles_n), out, (int)m);
 }
 
 // While set (non-zero) on the calling thread, every dense tensor-core GEMM launched from it may read its B operand before
