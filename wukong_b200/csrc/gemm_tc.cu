@@ -1079,24 +1079,30 @@ int wkb_gemm_bf16_nt_argmax(const void* a, i64 lda, const void* b, i64 ldb, i64 
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, m, k, lda, BM);
   if (rc) return rc;
-  rc = make_map(&mb, b, n, k, ldb, BN);
+  // 256-column tiles once they still fill two waves: a tile then moves 48 KB through shared memory per K step for twice the
+  // work of a 128-column one (32 KB); with two epilogue warps per lane quarter the scan of 256 columns keeps up
+  const bool wide = ((n + BN_WIDE - 1) / BN_WIDE) * ((m + BM - 1) / BM) >= 2 * (i64)sm_count();
+  const int bn = wide ? BN_WIDE : BN;
+  rc = make_map(&mb, b, n, k, ldb, bn);
   if (rc) return rc;
   int* status = gemm_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
-  auto kern = gemm_bf16_tc_kernel<0, false, true, false, false>;
-  static bool attr_set[64] = {false};
+  auto kern = wide ? gemm_bf16_tc_kernel<0, false, true, false, true> : gemm_bf16_tc_kernel<0, false, true, false, false>;
+  const int smem = wide ? SMEM_BYTES_WIDE : SMEM_BYTES;
+  static bool attr_set[64][2] = {{false}};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (!attr_set[dev & 63][wide ? 1 : 0]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    attr_set[dev & 63] = true;
+    attr_set[dev & 63][wide ? 1 : 0] = true;
   }
   GemmEpi epi{bias, nullptr, 0, 0, 0, part_idx};
   epi.b_static = g_b_static;
-  i64 tiles_n = (n + BN - 1) / BN, tiles = tiles_n * ((m + BM - 1) / BM);
+  // (the candidate arrays hold wkb_gemm_argmax_tiles(n) entries per row, the count for 128-column tiles: an upper bound)
+  i64 tiles_n = (n + bn - 1) / bn, tiles = tiles_n * ((m + BM - 1) / BM);
   unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
-  cudaError_t e = launch_pdl(kern, grid, GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb, (void*)part_val, (i64)0, (int)m, (int)n, (int)k, epi,
+  cudaError_t e = launch_pdl(kern, grid, GEMM_THREADS, smem, as_stream(stream), ma, mb, (void*)part_val, (i64)0, (int)m, (int)n, (int)k, epi,
                              status);
   if (e != cudaSuccess) return (int)e;
   return (int)launch_pdl(argmax_tiles_kernel, (unsigned)((m * 32 + 127) / 128), 128, 0, as_stream(stream), (const float*)part_val,
