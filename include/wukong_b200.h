@@ -395,6 +395,16 @@ int wkb_gemm_bf16_nt_qkv_append(const void* a, int64_t lda, const void* b, int64
                                 int64_t n, int64_t k, const float* bias, int64_t kv_col0, void* kcache, void* vcache,
                                 const uint32_t* block_table, const int* row_slot, const int* row_pos, int64_t kv_heads,
                                 int64_t head_dim, int64_t page_tokens, int64_t max_blocks_per_seq, void* stream);
+/* x[m, n] += A.B^T + bias (x f32 with row pitch ldx, updated in place) for decode-sized products: K is cut into 2, 4 or 8
+ * slices that run as the CTAs of one thread-block cluster per 128 x 128 tile, and the slices are added -- in slice order,
+ * then the bias, then x -- through distributed shared memory, so that no partial leaves the SMs (the residual update of
+ * the O and down projections, crates/wukong_codegen_gpu/src/serving.rs:684-937).  wkb_gemm_bf16_addto_slices returns the
+ * number of slices for a shape, 0 when the shape is not offered (too many tiles for one wave of clusters, K shorter than
+ * three 64-wide steps per slice, n % 4 != 0): then wkb_gemm_bf16_nt_addto returns cudaErrorNotSupported and the caller
+ * uses wkb_gemm_bf16_nt_partial.  Results equal the partial path's (same slice order) whenever the slice counts agree. */
+int64_t wkb_gemm_bf16_addto_slices(int64_t m, int64_t n, int64_t k);
+int wkb_gemm_bf16_nt_addto(const void* a, int64_t lda, const void* b, int64_t ldb, float* x, int64_t ldx, int64_t m,
+                           int64_t n, int64_t k, const float* bias, void* stream);
 /* Weight-resident hint for the dense tensor-core GEMMs (wkb_gemm_bf16_nt*, per calling thread; returns the previous
  * setting).  While it is non-zero the caller promises that the B operand of every GEMM it launches is not written by a
  * kernel still in flight on the launch's stream (resident model weights): the kernel then requests its first B tiles

@@ -266,6 +266,42 @@ def test_qkv_gemm_with_fused_append_equals_gemm_then_append(dev, orc):
         assert torch.equal(kv.k.view(torch.int16), kv_ref.k.view(torch.int16)) and torch.equal(kv.v.view(torch.int16), kv_ref.v.view(torch.int16))
 
 
+def test_addto_gemm_sums_its_k_slices_inside_a_cluster(dev, orc):
+    """x += A.B^T + bias with the K slices of a tile added through distributed shared memory: exact on small integers
+    whatever the split (2, 4 or 8 slices), ragged rows and columns included; shapes the rule does not offer are refused
+    before anything is launched."""
+    import torch
+    from wukong_b200 import lib
+    L, s = lib(), torch.cuda.current_stream().cuda_stream
+    seen = set()
+    for (m, n, k) in [(512, 768, 768), (512, 768, 3072), (64, 768, 3072), (64, 768, 768), (100, 256, 512), (130, 260, 1024), (16, 128, 4096)]:
+        ks = L.wkb_gemm_bf16_addto_slices(m, n, k)
+        assert ks in (2, 4, 8), (m, n, k, ks)
+        seen.add(ks)
+        a = torch.randint(-3, 4, (m, k), device="cuda").to(torch.bfloat16)
+        b = torch.randint(-3, 4, (n, k), device="cuda").to(torch.bfloat16)
+        bias = torch.randint(-5, 6, (n,), device="cuda").float()
+        x = torch.randint(-9, 10, (m, n), device="cuda").float()
+        want = x + a.float() @ b.float().T + bias
+        assert L.wkb_gemm_bf16_nt_addto(a.data_ptr(), k, b.data_ptr(), k, x.data_ptr(), n, m, n, k, bias.data_ptr(), s) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(x, want), (m, n, k, ks, float((x - want).abs().max()))
+        # without a bias, and on real-valued inputs against the fp32 product (the bar of the dense GEMM)
+        ar = bf16_t(np.random.default_rng(1).standard_normal((m, k)).astype(np.float32), orc)
+        br = bf16_t(np.random.default_rng(2).standard_normal((n, k)).astype(np.float32), orc)
+        x2 = torch.zeros(m, n, device="cuda")
+        assert L.wkb_gemm_bf16_nt_addto(ar.data_ptr(), k, br.data_ptr(), k, x2.data_ptr(), n, m, n, k, None, s) == 0
+        ref = ar.double() @ br.double().T
+        mag = ar.double().abs() @ br.double().abs().T
+        assert bool(((x2.double() - ref).abs() <= 1e-5 * mag + 1e-6).all())
+    assert seen == {2, 4, 8}
+    assert L.wkb_gemm_bf16_addto_slices(2000, 768, 768) == 0          # more tiles than one wave of clusters holds
+    a = torch.zeros(2000, 768, device="cuda", dtype=torch.bfloat16)
+    x = torch.zeros(2000, 768, device="cuda")
+    assert L.wkb_gemm_bf16_nt_addto(a.data_ptr(), 768, a.data_ptr(), 768, x.data_ptr(), 768, 2000, 768, 768, None, s) != 0
+    assert dev.gemm_status() == 0
+
+
 def test_partial_gemm_slices_sum_to_the_product(dev, orc):
     import ctypes
     import torch

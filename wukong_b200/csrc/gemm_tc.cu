@@ -90,10 +90,34 @@ __device__ __forceinline__ float epi_act(float y) {
   return act_apply(ACT, y);
 }
 
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+// this CTA's shared-memory address -> the same offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_shared_f4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 // Persistent kernel: CTA b works on tiles b, b + gridDim.x, ...; tile t is (m_tile = t % tiles_m,
 // n_tile = t / tiles_m), so CTAs running side by side share one B (weight) tile through L2.
 // ACT / OUT_BF16 / ARGMAX are compile-time so an identity epilogue carries no transcendental code.
-template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8, bool WIDE, bool KVAPPEND = false, bool NARROW = false>
+// CLUSTERK instantiation (x += A.B^T + bias for a decode-sized product whose K is cut into slices): the CTAs of a thread-block
+// cluster are the K slices of one tile (cluster rank = slice; the grid is exactly tiles x slices).  Each leaves its fp32
+// partial tile in its own shared memory (the operand ring is free by then), the cluster meets at a barrier, and CTA r adds
+// rows [r * 128 / slices, ...) of all the partials in slice order -- read through distributed shared memory -- plus the bias
+// into x.  The partials never travel through L2, and the row kernel that follows reads x alone.
+template <int ACT, bool OUT_BF16, bool ARGMAX, bool F8, bool WIDE, bool KVAPPEND = false, bool NARROW = false, bool CLUSTERK = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* c,
                     i64 ldc, int M, int N, int K, GemmEpi epi, int* status) {
@@ -279,7 +303,13 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_bar(buf));
         }
-        if (KVAPPEND && n0 + c0 >= epi.kv_col0) {
+        if (CLUSTERK) {
+          // this thread's row of the partial tile, 32 columns: [row][BN + 4] floats at the base of the (idle) operand ring
+          const uint32_t dst = base + (uint32_t)(((quarter * 32 + lane) * (BN + 4) + c0) * 4);
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            st_shared_f4(dst + e * 4, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+        } else if (KVAPPEND && n0 + c0 >= epi.kv_col0) {
           // a K or V chunk (kv_col0 and the head size are multiples of 32, so the 32 columns are consecutive dims of one
           // head): the thread holds them for its own row and writes them as 64 contiguous bytes of that token's cache row --
           // no transpose, no exchange of destinations between lanes
@@ -385,6 +415,40 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   }
+  if (CLUSTERK) {
+    cluster_sync_all();                              // every slice's partial tile is in its CTA's shared memory
+    if (warp >= 2) {
+      const int t = blockIdx.x / ksplit;
+      const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+      const int rows_per = BM / ksplit, row_first = (int)cluster_rank() * rows_per;
+      float* xg = reinterpret_cast<float*>(c);
+      for (int idx = threadIdx.x - 64; idx < rows_per * (BN / 4); idx += GEMM_THREADS - 64) {
+        const int rl = row_first + idx / (BN / 4), c4 = idx % (BN / 4);
+        const int grow = m0 + rl, gcol = n0 + 4 * c4;
+        if (grow < M && gcol < N) {                  // N is a multiple of 4: the four columns are inside together
+          const uint32_t mine = base + (uint32_t)((rl * (BN + 4) + 4 * c4) * 4);
+          // every slice's piece is requested before the first add; the adds run in slice order
+          float4 p[8];
+#pragma unroll
+          for (int sl = 0; sl < 8; ++sl)
+            if (sl < ksplit) p[sl] = ld_cluster_f4(map_to_cta(mine, (uint32_t)sl));
+          float4 d = p[0];
+#pragma unroll
+          for (int sl = 1; sl < 8; ++sl)
+            if (sl < ksplit) { d.x += p[sl].x; d.y += p[sl].y; d.z += p[sl].z; d.w += p[sl].w; }
+          if (epi.bias) {
+            const float4 bb = *reinterpret_cast<const float4*>(epi.bias + gcol);
+            d.x += bb.x; d.y += bb.y; d.z += bb.z; d.w += bb.w;
+          }
+          float4* xp = reinterpret_cast<float4*>(xg + (i64)grow * ldc + gcol);
+          float4 xv = *xp;
+          xv.x += d.x; xv.y += d.y; xv.z += d.z; xv.w += d.w;
+          *xp = xv;
+        }
+      }
+    }
+    cluster_sync_all();                              // nobody leaves while a peer may still read its tile
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
@@ -415,16 +479,6 @@ constexpr int PAIR_EPI_STAGE_BYTES = 4 * 32 * 33 * 4;        // one 32 x 33 fp32
 constexpr int SMEM_BYTES_PAIR = PAIR_STAGES * PAIR_STAGE_BYTES + PAIR_EPI_STAGE_BYTES + 1024 + 256;
 constexpr uint32_t IDESC_PAIR = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 
-__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-// this CTA's shared-memory address -> the same offset in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 // TMA load into this CTA's shared memory whose bytes are counted on a barrier given by its cluster address
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1) {
   asm volatile(
@@ -959,6 +1013,65 @@ int wkb_gemm_bf16_nt_partial(const void* a, i64 lda, const void* b, i64 ldb, i64
   const i64 items = ((n + BN - 1) / BN) * ((m + BM - 1) / BM) * ks;
   return (int)launch_pdl(kern, (unsigned)(items < sm_count() ? items : sm_count()), GEMM_THREADS, SMEM_BYTES, as_stream(stream), ma, mb, workspace,
                          n, (int)m, (int)n, (int)k, part, status);
+}
+
+// x[m, n] += A.B^T + bias with the K slices of a tile summed inside a thread-block cluster (the CLUSTERK instantiation).
+// Slices for a problem: 0 = not offered (the caller uses wkb_gemm_bf16_nt_partial and sums the slices itself).  The rule
+// depends on the shape and the SM count only: 2, 4 or 8 slices, at least three 64-wide K steps each, all CTAs in one wave.
+static i64 cluster_slices(i64 m, i64 n, i64 k) {
+  if (m <= 0 || n <= 0 || k <= 0 || n % 4 != 0 || getenv("WKB_GEMM_NO_CLUSTERK")) return 0;
+  const i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  const i64 kiters = (k + 63) / 64;
+  i64 ks = 8;
+  // (the last slice must not be empty: slices are ceil(kiters / ks) steps long)
+  while (ks >= 2 && (tiles * ks > sm_count() || kiters / ks < 3 || (ks - 1) * ((kiters + ks - 1) / ks) >= kiters)) ks >>= 1;
+  return ks >= 2 ? ks : 0;
+}
+
+i64 wkb_gemm_bf16_addto_slices(i64 m, i64 n, i64 k) { return cluster_slices(m, n, k); }
+
+int wkb_gemm_bf16_nt_addto(const void* a, i64 lda, const void* b, i64 ldb, float* x, i64 ldx, i64 m, i64 n, i64 k, const float* bias,
+                           void* stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if (k % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0 || n % 4 != 0 || ldx % 4 != 0) return (int)cudaErrorInvalidValue;
+  if ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)x) | ((uintptr_t)bias)) & 15) return (int)cudaErrorMisalignedAddress;
+  const i64 ks = cluster_slices(m, n, k);
+  if (ks == 0) return (int)cudaErrorNotSupported;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, m, k, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, b, n, k, ldb, BN);
+  if (rc) return rc;
+  int* status = gemm_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  auto kern = gemm_bf16_tc_kernel<0, false, false, false, false, false, false, true>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63] = true;
+  }
+  GemmEpi epi{};
+  epi.bias = bias;
+  epi.ksplit = (int)ks;
+  epi.slice_stride = 0;
+  epi.b_static = g_b_static;
+  const i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles * ks));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = as_stream(stream);
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)ks; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, ma, mb, (void*)x, ldx, (int)m, (int)n, (int)k, epi, status);
 }
 
 // The fused QKV projection of a decode step: C[:, :kv_col0] = A.B^T + bias (fp32, the query heads); columns

@@ -41,6 +41,8 @@ int wkb_paged_attn_prefill(const float*, i64, const void*, const void*, const ui
 int wkb_decode_advance(int*, int*, int*, const int*, i64, i64, void*);
 int wkb_gemm_init(void);
 int wkb_gemm_b_static(int);
+i64 wkb_gemm_bf16_addto_slices(i64, i64, i64);
+int wkb_gemm_bf16_nt_addto(const void*, i64, const void*, i64, float*, i64, i64, i64, i64, const float*, void*);
 }
 
 namespace wkb {
@@ -314,19 +316,33 @@ static int run_layers(Gpt2Model* m, i64 r0, i64 n, i64 n_tiles, float* gemm_ws, 
       ++m->launches;
     }
     i64 nsl, sst;
-    wkb_gemm_bf16_partial_layout(n, d, d, &nsl, &sst);
-    WKB_TRY(wkb_gemm_bf16_nt_partial(att, d, L.w_o, d, n, d, d, gemm_ws, m->gemm_ws_bytes, stream));
-    ++m->launches;
-    WKB_TRY(add_ln(m, x, n, gemm_ws, nsl, sst, L.b_o, L.ln2_g, L.ln2_b, h, st));
+    // residual update x += att.Wo^T + b_o: K slices summed inside a cluster where the shape allows it (then the row kernel
+    // only normalises), else as partials that the row kernel adds up
+    if (wkb_gemm_bf16_addto_slices(n, d, d) > 0) {
+      WKB_TRY(wkb_gemm_bf16_nt_addto(att, d, L.w_o, d, x, d, n, d, d, L.b_o, stream));
+      ++m->launches;
+      WKB_TRY(add_ln(m, x, n, nullptr, 0, 0, nullptr, L.ln2_g, L.ln2_b, h, st));
+    } else {
+      wkb_gemm_bf16_partial_layout(n, d, d, &nsl, &sst);
+      WKB_TRY(wkb_gemm_bf16_nt_partial(att, d, L.w_o, d, n, d, d, gemm_ws, m->gemm_ws_bytes, stream));
+      ++m->launches;
+      WKB_TRY(add_ln(m, x, n, gemm_ws, nsl, sst, L.b_o, L.ln2_g, L.ln2_b, h, st));
+    }
     WKB_TRY(wkb_gemm_bf16_nt_ws(h, d, L.w_fc, d, ffb, ff, 1, n, ff, d, L.b_fc, 2, nullptr, 0, gemm_ws, m->gemm_ws_bytes, stream));
     m->launches += wkb_gemm_workspace_bytes(n, ff, d) > 0 ? 2 : 1;
-    wkb_gemm_bf16_partial_layout(n, d, ff, &nsl, &sst);
-    WKB_TRY(wkb_gemm_bf16_nt_partial(ffb, ff, L.w_proj, ff, n, d, ff, gemm_ws, m->gemm_ws_bytes, stream));
-    ++m->launches;
     const bool last = li + 1 == m->n_layer;
     const float* g = last ? m->lnf_g : m->layers[(size_t)li + 1].ln1_g;
     const float* b = last ? m->lnf_b : m->layers[(size_t)li + 1].ln1_b;
-    WKB_TRY(add_ln(m, x, n, gemm_ws, nsl, sst, L.b_proj, g, b, h, st));
+    if (wkb_gemm_bf16_addto_slices(n, d, ff) > 0) {
+      WKB_TRY(wkb_gemm_bf16_nt_addto(ffb, ff, L.w_proj, ff, x, d, n, d, ff, L.b_proj, stream));
+      ++m->launches;
+      WKB_TRY(add_ln(m, x, n, nullptr, 0, 0, nullptr, g, b, h, st));
+    } else {
+      wkb_gemm_bf16_partial_layout(n, d, ff, &nsl, &sst);
+      WKB_TRY(wkb_gemm_bf16_nt_partial(ffb, ff, L.w_proj, ff, n, d, ff, gemm_ws, m->gemm_ws_bytes, stream));
+      ++m->launches;
+      WKB_TRY(add_ln(m, x, n, gemm_ws, nsl, sst, L.b_proj, g, b, h, st));
+    }
   }
   return 0;
 }
