@@ -99,6 +99,46 @@ def case_gemm(size, hbm, tf, src):
     return out
 
 
+def case_decode_gemms(hbm, tf, src):
+    """The dense GEMMs of one GPT-2-124M-shape layer at a decode batch of 512 rows, launched the way the serving step
+    launches them: O projection as a residual update with its K slices summed inside a cluster, FC (+bias, GELU, bf16 out),
+    down projection as a residual update.  Weights rotate over 12 layer copies (170 MB), activations stay in L2.  The
+    figure is the time of the three launches; they are bound by their latency chains (dependency wait, first tile,
+    K steps at TMA latency / ring depth, epilogue), not by the 10.6 MB of weights they stream."""
+    L = lib()
+    rows, d, ff, layers = 512, 768, 3072, 12
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    w_o = [(torch.randn(d, d, device="cuda", generator=g) * 0.02).to(torch.bfloat16) for _ in range(layers)]
+    w_fc = [(torch.randn(ff, d, device="cuda", generator=g) * 0.02).to(torch.bfloat16) for _ in range(layers)]
+    w_pr = [(torch.randn(d, ff, device="cuda", generator=g) * 0.02).to(torch.bfloat16) for _ in range(layers)]
+    b_d = torch.zeros(d, device="cuda")
+    b_ff = torch.zeros(ff, device="cuda")
+    att = torch.randn(rows, d, device="cuda", generator=g).to(torch.bfloat16)
+    h = torch.randn(rows, d, device="cuda", generator=g).to(torch.bfloat16)
+    x = torch.zeros(rows, d, device="cuda")
+    ffb = torch.empty(rows, ff, device="cuda", dtype=torch.bfloat16)
+    assert L.wkb_gemm_bf16_addto_slices(rows, d, d) > 0 and L.wkb_gemm_bf16_addto_slices(rows, d, ff) > 0
+    prev = L.wkb_gemm_b_static(1)
+
+    def seq(i):
+        j = i % layers
+        s = _s()
+        check(L.wkb_gemm_bf16_nt_addto(att.data_ptr(), d, w_o[j].data_ptr(), d, x.data_ptr(), d, rows, d, d, b_d.data_ptr(), s), "addto")
+        dev.gemm_bf16_nt(h, w_fc[j], bias=b_ff, act=2, out=ffb)
+        check(L.wkb_gemm_bf16_nt_addto(ffb.data_ptr(), ff, w_pr[j].data_ptr(), ff, x.data_ptr(), d, rows, d, ff, b_d.data_ptr(), s), "addto")
+
+    try:
+        us = time_graph(seq, 24)
+    finally:
+        L.wkb_gemm_b_static(prev)
+    bytes_w = 2.0 * (d * d + 2 * d * ff)
+    gbs = bytes_w / us / 1e3
+    return {"case": "decode_gemms", "shape": {"rows": rows, "d_model": d, "d_ff": ff}, "us": us, "achieved": gbs, "unit": "GB/s", "bound": "hbm",
+            "peak": hbm, "frac": gbs / hbm, "algorithmic_bytes": bytes_w, "launches": 3, "peak_source": "of " + src,
+            "note": "three dependent launches of 4-6 us each; latency-bound"}
+
+
 def q4_weights(n, k, rng):
     nb = k // 32
     raw = rng.integers(0, 256, (n * nb, 18), dtype=np.uint8)
@@ -309,6 +349,7 @@ def run(out=sys.stdout, only=None, reps_scale=1.0):
     plan.append(("paged_attn_decode_int8", lambda: case_paged_attn_int8(hbm, tf, src)))
     for (H, HKV, D, seqs, hist, chunk) in ((12, 12, 64, 64, 0, 512), (32, 8, 128, 16, 0, 512), (32, 8, 128, 16, 2048, 256)):
         plan.append(("paged_attn_prefill", lambda a=(H, HKV, D, seqs, hist, chunk): case_paged_prefill(*a, hbm, tf, src)))
+    plan.append(("decode_gemms", lambda: case_decode_gemms(hbm, tf, src)))
     results = []
     for name, fn in plan:
         if only and only not in name:
