@@ -316,9 +316,12 @@ static int run_layers(Gpt2Model* m, i64 r0, i64 n, i64 n_tiles, float* gemm_ws, 
       ++m->launches;
     }
     i64 nsl, sst;
-    // residual update x += att.Wo^T + b_o: K slices summed inside a cluster where the shape allows it (then the row kernel
-    // only normalises), else as partials that the row kernel adds up
-    if (wkb_gemm_bf16_addto_slices(n, d, d) > 0) {
+    // residual update x += att.Wo^T + b_o: K slices summed inside a cluster (then the row kernel only normalises), or as
+    // partials that the row kernel adds up.  The cluster form pays from about 512 rows on, where the partials are 6-9 MB
+    // of L2 traffic per GEMM (1.653 -> 1.636 ms per step at 512 rows); below that the cluster barrier and the
+    // distributed-shared-memory sum cost more than the small partials (0.680 -> 0.705 ms per step at 64 rows).
+    const bool in_cluster = n >= 512;
+    if (in_cluster && wkb_gemm_bf16_addto_slices(n, d, d) > 0) {
       WKB_TRY(wkb_gemm_bf16_nt_addto(att, d, L.w_o, d, x, d, n, d, d, L.b_o, stream));
       ++m->launches;
       WKB_TRY(add_ln(m, x, n, nullptr, 0, 0, nullptr, L.ln2_g, L.ln2_b, h, st));
@@ -333,7 +336,7 @@ static int run_layers(Gpt2Model* m, i64 r0, i64 n, i64 n_tiles, float* gemm_ws, 
     const bool last = li + 1 == m->n_layer;
     const float* g = last ? m->lnf_g : m->layers[(size_t)li + 1].ln1_g;
     const float* b = last ? m->lnf_b : m->layers[(size_t)li + 1].ln1_b;
-    if (wkb_gemm_bf16_addto_slices(n, d, ff) > 0) {
+    if (in_cluster && wkb_gemm_bf16_addto_slices(n, d, ff) > 0) {
       WKB_TRY(wkb_gemm_bf16_nt_addto(ffb, ff, L.w_proj, ff, x, d, n, d, ff, L.b_proj, stream));
       ++m->launches;
       WKB_TRY(add_ln(m, x, n, nullptr, 0, 0, nullptr, g, b, h, st));
