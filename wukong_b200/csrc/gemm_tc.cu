@@ -1019,7 +1019,8 @@ int wkb_gemm_bf16_nt_partial(const void* a, i64 lda, const void* b, i64 ldb, i64
 // Slices for a problem: 0 = not offered (the caller uses wkb_gemm_bf16_nt_partial and sums the slices itself).  The rule
 // depends on the shape and the SM count only: 2, 4 or 8 slices, at least three 64-wide K steps each, all CTAs in one wave.
 static i64 cluster_slices(i64 m, i64 n, i64 k) {
-  if (m <= 0 || n <= 0 || k <= 0 || n % 4 != 0 || getenv("WKB_GEMM_NO_CLUSTERK")) return 0;
+  static const bool off = getenv("WKB_GEMM_NO_CLUSTERK") != nullptr;   // switch for A/B timing: never offer the cluster form
+  if (m <= 0 || n <= 0 || k <= 0 || n % 4 != 0 || off) return 0;
   const i64 tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
   const i64 kiters = (k + 63) / 64;
   i64 ks = 8;
@@ -1095,7 +1096,8 @@ int wkb_gemm_bf16_nt_qkv_append(const void* a, i64 lda, const void* b, i64 ldb, 
   // 64-column tiles while they still fit one wave: a decode batch of 512 rows x 2304 columns is 72 tiles of 128 columns
   // (half the SMs idle) but 144 of 64
   const i64 tiles_narrow = ((n + 63) / 64) * ((m + BM - 1) / BM);
-  const bool narrow = tiles_narrow <= sm_count() && !getenv("WKB_QKV_WIDE");
+  static const bool keep_wide = getenv("WKB_QKV_WIDE") != nullptr;     // switch for A/B timing: always 128-column tiles
+  const bool narrow = tiles_narrow <= sm_count() && !keep_wide;
   const int bn = narrow ? 64 : BN;
   rc = make_map(&mb, b, n, k, ldb, bn);
   if (rc) return rc;
