@@ -6,19 +6,23 @@
 // convention (both operands K-major, "NT"), fp32 accumulate, same epilogue menu
 // act(alpha-free A.B^T + bias[j]) (+ residual), act codes 0 identity / 1 relu / 2 gelu / 3 silu.
 //
-// Design (persistent CTAs, one per SM, looping over 128 x 128 output tiles; 192 threads):
+// Design (persistent CTAs, one per SM, looping over 128 x 128 output tiles -- 128 x 256 or 128 x 64 in two instantiations;
+// 320 threads):
 //   warp 0   one elected lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, no
-//            multicast) of a 128x64 A tile and a 128x64 B tile per stage into a 5-stage ring,
-//            completion counted on an mbarrier per stage;
-//   warp 1   allocates 256 TMEM columns (two accumulator buffers), and one elected lane issues
+//            multicast) of a 128x64 A tile and a 128x64 B tile per stage into a 192 KB ring (6 stages of 32 KB,
+//            4 of 48 KB, 8 of 24 KB), completion counted on an mbarrier per stage; with the weight-resident hint the
+//            first ring of B tiles is requested before the wait for the preceding kernel of the stream;
+//   warp 1   allocates the TMEM columns of two accumulator buffers (before that wait), and one elected lane issues
 //            tcgen05.mma (cta_group::1, kind::f16, M=128 N=128 K=16) four times per stage straight
 //            from shared memory descriptors; tcgen05.commit releases the stage back to the producer
 //            and, after a tile's last K step, hands the accumulator buffer to the epilogue;
-//   warps 2-5 read the fp32 accumulator out of TMEM with tcgen05.ld (32 lanes x 32 columns per
-//            instruction; warp w owns lanes 32*(w%4)..), release the buffer as soon as it is in
+//   warps 2-9 read the fp32 accumulator out of TMEM with tcgen05.ld (32 lanes x 32 columns per
+//            instruction; warp w owns lanes 32*(w%4).., the two warps of a lane quarter take alternate column chunks),
+//            release the buffer as soon as it is in
 //            registers (so the next tile's MMAs overlap this tile's epilogue), transpose through
 //            shared memory and store coalesced rows with bias / activation / residual applied, or
-//            keep a per-row arg-max candidate instead of storing (greedy LM head).
+//            keep a per-row arg-max candidate instead of storing (greedy LM head), or write K / V rows into their
+//            pages (fused QKV projection), or leave the partial tile in shared memory for the in-cluster K-slice sum.
 // Every mbarrier wait is bounded: on expiry the kernel records a code in `status`, stops issuing,
 // waits (bounded) for the copies it started, frees its TMEM and returns.
 // Ragged M / N / K are handled by TMA zero fill and masked stores; K % 8 == 0 is required (the
