@@ -153,3 +153,92 @@ def test_starved_slots_sit_out_and_resume_when_pages_are_released():
         assert steps < 100
     assert sat_out > 0                                   # the pool did run short at some step
     assert [s.output(i).size for i in ids] == [5, 3, 2] and s.free_blocks() == 5 and s.completed() == 3
+
+
+def test_scheduler_invariants_under_random_load():
+    """Random geometries and request streams, pools that run short: at every step the rows of a slot are consecutive
+    positions that continue its context, causal (ctx = pos + 1), prompt tokens come back in order and each sampled token
+    is fed back exactly once as the next decode row; no page holds tokens of two slots; used + free pages = the pool; every
+    request ends with exactly gen_len tokens, the ones this "model" drew for it."""
+    for seed in range(25):
+        rng = np.random.default_rng(seed)
+        bcap = int(rng.integers(1, 6))
+        bs = int(rng.choice([1, 2, 4, 16]))
+        mbps = int(rng.integers(2, 9))
+        cap_tokens = bs * mbps
+        nblk = int(rng.integers(mbps, bcap * mbps + 1))            # at least one full row of pages, often fewer than bcap rows
+        max_rows = int(rng.integers(bcap, 4 * bcap + 4))
+        chunk = int(rng.integers(1, 8))
+        s = Scheduler(bcap=bcap, num_blocks=nblk, block_size=bs, max_blocks_per_seq=mbps, max_rows=max_rows, prefill_chunk=chunk)
+        reqs = {}
+        for _ in range(int(rng.integers(1, 12))):
+            L = int(rng.integers(1, max(2, cap_tokens)))
+            g = int(rng.integers(1, max(2, cap_tokens - L + 1)))
+            if L + g - 1 > cap_tokens:                             # the last sampled token is never written back
+                continue
+            prompt = rng.integers(0, 1000, L).astype(np.int32)
+            reqs[s.enqueue(prompt, g)] = (prompt, g, [])
+        slot_req = {}                                               # slot -> (request id known to the test) via its prompt
+        fed = {}                                                    # slot -> tokens seen so far for the current occupant
+        pending_feedback = {}                                       # slot -> sampled token that must come back next
+        drawn = {}                                                  # slot -> tokens drawn for the current occupant
+        steps = 0
+        while not s.is_idle():
+            try:
+                n = s.plan_step()
+            except OutOfBlocks:
+                # every resident slot needs a page and none is free: legal only when nothing can move
+                assert s.free_blocks() < s.num_active() or s.free_blocks() == 0
+                break
+            assert 0 < n <= max_rows
+            slots = s.row_slot[:n].tolist()
+            pos = s.row_pos[:n].tolist()
+            ctxs = s.row_ctx[:n].tolist()
+            toks = s.row_token[:n].tolist()
+            ctx_now = s.manager.ctx_lens()
+            for sl in set(slots):
+                idx = [i for i in range(n) if slots[i] == sl]
+                assert idx == list(range(idx[0], idx[-1] + 1))       # a slot's rows are contiguous in the step
+                p = [pos[i] for i in idx]
+                assert p == list(range(p[0], p[0] + len(p)))
+                assert [ctxs[i] for i in idx] == [q + 1 for q in p]
+                assert ctx_now[sl] == p[-1] + 1                      # pages are reserved up to the last row of the step
+                if p[0] == 0:                                        # a new occupant
+                    fed[sl], drawn[sl] = [], []
+                    pending_feedback.pop(sl, None)
+                assert len(fed[sl]) == p[0]
+                if sl in pending_feedback:
+                    assert len(idx) == 1 and toks[idx[0]] == pending_feedback.pop(sl)
+                fed[sl].extend(toks[i] for i in idx)
+            # no page in two slots; accounting adds up
+            table = s.manager.flat_block_table()
+            owned = []
+            for sl in range(bcap):
+                owned.extend(table[sl, :(ctx_now[sl] + bs - 1) // bs].tolist())
+            # (admission reserves a prompt's pages ahead of its rows, so more pages may be in use than the contexts cover)
+            assert len(owned) == len(set(owned)) <= s.manager.used_blocks()
+            assert all(0 <= pg < nblk for pg in owned)
+            assert s.manager.used_blocks() + s.free_blocks() == nblk
+            sampled = np.zeros(bcap, np.int32)
+            for sl in range(bcap):
+                r = int(s.sample_row[sl])
+                if r >= 0:
+                    assert slots[r] == sl and (r == n - 1 or slots[r + 1] != sl)   # the slot's last row of the step
+                    sampled[sl] = int(rng.integers(1000, 2000))
+                    pending_feedback[sl] = int(sampled[sl])
+                    drawn[sl].append(int(sampled[sl]))
+            s.commit_step(sampled)
+            # a slot that retired leaves its prompt + drawn tokens behind: match them to a request
+            for sl in list(drawn):
+                if ctx_now[sl] > 0 and s.manager.ctx_lens()[sl] == 0:
+                    hit = [rid for rid, (pr, g, got) in reqs.items() if not got and len(drawn[sl]) == g and fed[sl][:len(pr)] == pr.tolist()]
+                    assert hit, (seed, sl)
+                    reqs[hit[0]][2].extend(drawn[sl])
+                    pending_feedback.pop(sl, None)
+                    del drawn[sl]
+            steps += 1
+            assert steps < 5000
+        if s.is_idle():
+            assert s.free_blocks() == nblk and s.completed() == len(reqs)
+            for rid, (pr, g, got) in reqs.items():
+                assert s.output(rid).tolist() == got and len(got) == g
